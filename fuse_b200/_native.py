@@ -1,0 +1,147 @@
+"""ctypes binding of libfuse_b200.so (the C ABI declared in include/fuse_b200.h).
+
+Importing this module never falls back to another implementation: if the CUDA library has
+not been built, `lib()` raises with the build command."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libfuse_b200.so")
+
+MAX_WORLD_SIZE = 8
+READY_FLAG_STRIDE = 32
+
+RASTER_HEURISTIC, RASTER_ALONG_M, RASTER_ALONG_N = 0, 1, 2
+DTYPE_BF16, DTYPE_E4M3 = 0, 1
+ROUTE_HEAD_TO_SEQUENCE, ROUTE_QKV_GQA_PACK = 0, 2
+ROUTE_FORWARD, ROUTE_INVERSE = 0, 1
+SKIP_PEER_WAIT = 1
+
+CUDA_SUCCESS = 0
+CUDA_ERROR_INVALID_VALUE = 1
+CUDA_ERROR_NOT_SUPPORTED = 801
+
+
+class MatrixStride(C.Structure):
+    _fields_ = [("row", C.c_int64), ("column", C.c_int64), ("batch", C.c_int64)]
+
+    def __init__(self, row=-1, column=-1, batch=-1):
+        super().__init__(row, column, batch)
+
+
+class GemmProblem(C.Structure):
+    """include/fuse/layout/gemm.h:27-42 of the reference (GemmProblem)."""
+    _fields_ = [("m", C.c_int32), ("n", C.c_int32), ("k", C.c_int32), ("l", C.c_int32),
+                ("stride_a", MatrixStride), ("stride_b", MatrixStride), ("stride_d", MatrixStride),
+                ("input_dtype", C.c_int32), ("weight_dtype", C.c_int32),
+                ("output_dtype", C.c_int32), ("transpose_a", C.c_uint8),
+                ("transpose_b", C.c_uint8), ("raster", C.c_int32), ("max_swizzle_size", C.c_int32)]
+
+    def __init__(self, m=0, n=0, k=0, raster=RASTER_HEURISTIC, max_swizzle_size=1, **kw):
+        super().__init__()
+        self.m, self.n, self.k, self.l = m, n, k, 1
+        self.stride_a, self.stride_b, self.stride_d = MatrixStride(), MatrixStride(), MatrixStride()
+        self.raster, self.max_swizzle_size = raster, max_swizzle_size
+        for key, value in kw.items():
+            setattr(self, key, value)
+
+
+class UlyssesRoute(C.Structure):
+    """include/fuse/layout/ulysses.h:24-63 of the reference (UlyssesRoute)."""
+    _fields_ = [("world_size", C.c_int32), ("rank", C.c_int32), ("batch", C.c_int32),
+                ("global_seq", C.c_int32), ("seq_local", C.c_int32), ("q_heads", C.c_int32),
+                ("kv_heads", C.c_int32), ("local_heads", C.c_int32), ("head_dim", C.c_int32),
+                ("channel_count", C.c_int32), ("qkv_peer_interleaved", C.c_uint8),
+                ("defer_v_a2a", C.c_uint8), ("causal_load_balanced", C.c_uint8),
+                ("cyclic_peer_order", C.c_uint8), ("packed_source_row", C.c_void_p),
+                ("packed_row_granularity", C.c_int32), ("kind", C.c_int32),
+                ("direction", C.c_int32)]
+
+    def __init__(self, **kw):
+        super().__init__()
+        self.world_size, self.batch, self.channel_count = 1, 1, 1
+        self.kind, self.direction = ROUTE_HEAD_TO_SEQUENCE, ROUTE_FORWARD
+        for key, value in kw.items():
+            setattr(self, key, value)
+
+
+class KernelTraits(C.Structure):
+    _fields_ = [("block_m", C.c_int32), ("block_n", C.c_int32), ("block_k", C.c_int32),
+                ("threads", C.c_int32), ("dynamic_smem_bytes", C.c_int32)]
+
+
+class GemmA2AParams(C.Structure):
+    """include/fuse/operators/primitives/gemm_a2a.h:17-30 of the reference."""
+    _fields_ = [("lhs", C.c_void_p), ("rhs_nt", C.c_void_p), ("local_output", C.c_void_p),
+                ("peer_output", C.c_void_p * MAX_WORLD_SIZE),
+                ("peer_route_done_epoch", C.c_void_p * MAX_WORLD_SIZE), ("ready", C.c_void_p),
+                ("completion_epoch", C.c_void_p), ("gemm", GemmProblem), ("route", UlyssesRoute),
+                ("num_comm_ctas", C.c_int32), ("epoch", C.c_uint32), ("alpha", C.c_float)]
+
+    def __init__(self, **kw):
+        super().__init__()
+        self.alpha = 1.0
+        for key, value in kw.items():
+            setattr(self, key, value)
+
+
+class A2AGemmParams(C.Structure):
+    """include/fuse/operators/primitives/a2a_gemm.h:47-61 of the reference."""
+    _fields_ = [("peer_input", C.c_void_p * MAX_WORLD_SIZE), ("input_staging", C.c_void_p),
+                ("peer_input_ready", C.c_void_p * MAX_WORLD_SIZE), ("rhs_nt", C.c_void_p),
+                ("output", C.c_void_p), ("ready", C.c_void_p), ("gemm", GemmProblem),
+                ("route", UlyssesRoute), ("num_comm_ctas", C.c_int32), ("lhs_policy", C.c_int32),
+                ("epoch", C.c_uint32), ("input_epoch", C.c_uint32), ("alpha", C.c_float)]
+
+    def __init__(self, **kw):
+        super().__init__()
+        self.alpha = 1.0
+        for key, value in kw.items():
+            setattr(self, key, value)
+
+
+class Options(C.Structure):
+    _fields_ = [("wait_budget_ns", C.c_uint64), ("flags", C.c_uint32), ("block_n", C.c_int32)]
+
+
+ABI_RECORDS = {0: GemmProblem, 1: UlyssesRoute, 2: GemmA2AParams, 3: A2AGemmParams,
+               4: KernelTraits, 5: Options}
+
+# Every symbol include/fuse_b200.h declares: name -> (restype, argtypes).
+_P = C.c_void_p
+SYMBOLS = {
+    "fuse_launch_gemm_a2a_cutlass": (C.c_int, [C.POINTER(GemmA2AParams), _P]),
+    "fuse_launch_gemm_a2a_cutlass_ex": (C.c_int, [C.POINTER(GemmA2AParams), C.POINTER(Options), _P]),
+    "fuse_launch_a2a_gemm_cutlass": (C.c_int, [C.POINTER(A2AGemmParams), _P]),
+    "fuse_launch_a2a_gemm_cutlass_ex": (C.c_int, [C.POINTER(A2AGemmParams), C.POINTER(Options), _P]),
+    "fuse_launch_batched_cutlass_reference": (C.c_int, [C.POINTER(GemmA2AParams), _P, C.c_int32]),
+    "fuse_launch_a2a_gemm_cutlass_reference": (C.c_int, [C.POINTER(A2AGemmParams), _P, C.c_int32]),
+    "fuse_qkv_cutlass_kernel_traits": (None, [C.POINTER(GemmProblem), C.POINTER(KernelTraits)]),
+    "fuse_cutlass_kernel_traits": (None, [C.POINTER(KernelTraits)]),
+    "fuse_a2a_lhs_gemm_ready_elements": (C.c_int64, [C.POINTER(GemmProblem), C.POINTER(UlyssesRoute)]),
+    "fuse_recommended_gemm_a2a_comm_ctas": (C.c_int32, [C.POINTER(GemmProblem), C.POINTER(UlyssesRoute)]),
+    "fuse_recommended_a2a_lhs_gemm_comm_ctas": (C.c_int32, [C.POINTER(GemmProblem), C.POINTER(UlyssesRoute)]),
+    "fuse_b200_read_status": (C.c_int, [C.POINTER(C.c_uint32 * 16), C.c_int]),
+    "fuse_b200_abi_sizeof": (C.c_int, [C.c_int]),
+    "fuse_b200_launch_count": (C.c_uint64, []),
+}
+
+_LIB = None
+
+
+def lib():
+    """The loaded CUDA library.  Raises when it has not been built: there is no CPU path."""
+    global _LIB
+    if _LIB is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m fuse_b200.build` (nvcc, sm_100a). "
+                "fuse_b200 has no CPU or PyTorch fallback.")
+        handle = C.CDLL(LIB_PATH, mode=C.RTLD_GLOBAL)
+        for name, (restype, argtypes) in SYMBOLS.items():
+            fn = getattr(handle, name)
+            fn.restype, fn.argtypes = restype, argtypes
+        _LIB = handle
+    return _LIB

@@ -1,0 +1,87 @@
+"""Host-side mirror of the reference's operator interface (namespace `fuse`), over the C ABI.
+
+Function names, argument meaning and error behaviour follow the reference's free functions
+(include/fuse/operators/primitives/gemm_a2a.h, a2a_gemm.h): each returns the cudaError_t value
+as an int and never raises for a rejected launch.  Pointers are device addresses (ints);
+`stream` is a cudaStream_t value (int, 0 = legacy default stream)."""
+from __future__ import annotations
+
+import ctypes as C
+
+from . import _native as N
+from ._native import (A2AGemmParams, GemmA2AParams, GemmProblem, KernelTraits, Options,  # noqa: F401
+                      UlyssesRoute)
+
+
+def _opt(options):
+    return C.byref(options) if options is not None else None
+
+
+def launch_gemm_a2a_cutlass(params: GemmA2AParams, stream: int = 0, options: Options | None = None) -> int:
+    """QKV projection + sequence->head all-to-all (fuse::launch_gemm_a2a_cutlass)."""
+    if options is None:
+        return N.lib().fuse_launch_gemm_a2a_cutlass(C.byref(params), stream)
+    return N.lib().fuse_launch_gemm_a2a_cutlass_ex(C.byref(params), _opt(options), stream)
+
+
+def launch_a2a_gemm_cutlass(params: A2AGemmParams, stream: int = 0, options: Options | None = None) -> int:
+    """Head->sequence all-to-all + output projection (fuse::launch_a2a_gemm_cutlass)."""
+    if options is None:
+        return N.lib().fuse_launch_a2a_gemm_cutlass(C.byref(params), stream)
+    return N.lib().fuse_launch_a2a_gemm_cutlass_ex(C.byref(params), _opt(options), stream)
+
+
+def launch_batched_cutlass_reference(params: GemmA2AParams, stream: int = 0,
+                                     reserved_comm_ctas: int = 0) -> int:
+    """Projection GEMM alone on SMs - reserved_comm_ctas CTAs (the pure-GEMM denominator)."""
+    return N.lib().fuse_launch_batched_cutlass_reference(C.byref(params), stream, reserved_comm_ctas)
+
+
+def launch_a2a_gemm_cutlass_reference(params: A2AGemmParams, stream: int = 0,
+                                      reserved_comm_ctas: int = 0) -> int:
+    return N.lib().fuse_launch_a2a_gemm_cutlass_reference(C.byref(params), stream, reserved_comm_ctas)
+
+
+def qkv_cutlass_kernel_traits(problem: GemmProblem) -> KernelTraits:
+    out = KernelTraits()
+    N.lib().fuse_qkv_cutlass_kernel_traits(C.byref(problem), C.byref(out))
+    return out
+
+
+def cutlass_kernel_traits() -> KernelTraits:
+    out = KernelTraits()
+    N.lib().fuse_cutlass_kernel_traits(C.byref(out))
+    return out
+
+
+def a2a_lhs_gemm_ready_elements(problem: GemmProblem, route: UlyssesRoute) -> int:
+    return N.lib().fuse_a2a_lhs_gemm_ready_elements(C.byref(problem), C.byref(route))
+
+
+def recommended_gemm_a2a_comm_ctas(problem: GemmProblem, route: UlyssesRoute) -> int:
+    return N.lib().fuse_recommended_gemm_a2a_comm_ctas(C.byref(problem), C.byref(route))
+
+
+def recommended_a2a_lhs_gemm_comm_ctas(problem: GemmProblem, route: UlyssesRoute) -> int:
+    return N.lib().fuse_recommended_a2a_lhs_gemm_comm_ctas(C.byref(problem), C.byref(route))
+
+
+def read_status(clear: bool = True) -> list[int]:
+    """The device status record of the current device (word 0 != 0: a device wait gave up)."""
+    out = (C.c_uint32 * 16)()
+    rc = N.lib().fuse_b200_read_status(C.byref(out), 1 if clear else 0)
+    if rc != 0:
+        raise RuntimeError(f"fuse_b200_read_status failed with cudaError {rc}")
+    return list(out)
+
+
+def launch_count() -> int:
+    return int(N.lib().fuse_b200_launch_count())
+
+
+def qkv_ready_elements(problem: GemmProblem) -> int:
+    """u32 words the `ready` array of the QKV operator needs (finest publication tile)."""
+    traits = qkv_cutlass_kernel_traits(problem)
+    m_tiles = -(-problem.m // traits.block_m)
+    n_tiles = -(-problem.n // traits.block_n)
+    return m_tiles * n_tiles * N.READY_FLAG_STRIDE

@@ -1,0 +1,342 @@
+// BF16 forward entry points: QKV projection -> sequence-to-head all-to-all, and
+// head-to-sequence all-to-all -> output projection.  Validation follows the reference's
+// launch path (csrc/operators/sm103/detail/launch.cuh:364-591, detail/gemm_a2a.cuh:237-299,
+// detail/gemm.cuh:53-70): the same conditions produce the same error codes.
+#include <cmath>
+#include <cstring>
+
+#include "fuse_b200.h"
+#include "fused_gemm.cuh"
+#include "host.cuh"
+
+namespace fuse_b200 {
+namespace {
+
+using host::DeviceInfo;
+
+int64_t packed_or(int64_t stride, int64_t packed) { return stride < 0 ? packed : stride; }
+
+// detail/gemm.cuh:53-70 (supported_problem): row-major A[M,K], B[N,K], D[M,N], 16-byte rows.
+bool supported_problem(const fuse_gemm_problem& g) {
+  const int64_t lda = packed_or(g.stride_a.row, g.k), ldb = packed_or(g.stride_b.row, g.k),
+                ldd = packed_or(g.stride_d.row, g.n);
+  return g.m > 0 && g.n > 0 && g.k > 0 && g.l == 1 && !g.transpose_a && !g.transpose_b &&
+         g.input_dtype == FUSE_DTYPE_BF16 && g.weight_dtype == FUSE_DTYPE_BF16 &&
+         g.output_dtype == FUSE_DTYPE_BF16 && (g.stride_a.column < 0 || g.stride_a.column == 1) &&
+         (g.stride_b.column < 0 || g.stride_b.column == 1) &&
+         (g.stride_d.column < 0 || g.stride_d.column == 1) && lda >= g.k && lda % 8 == 0 &&
+         ldb >= g.k && ldb % 8 == 0 && ldd >= g.n && ldd % 8 == 0 &&
+         (g.max_swizzle_size == 1 || g.max_swizzle_size == 2 || g.max_swizzle_size == 4 ||
+          g.max_swizzle_size == 8) &&
+         (g.raster == FUSE_RASTER_HEURISTIC || g.raster == FUSE_RASTER_ALONG_M ||
+          g.raster == FUSE_RASTER_ALONG_N);
+}
+
+int choose_block_n(const fuse_gemm_problem& g, const fuse_b200_options* options) {
+  if (options && (options->block_n == 128 || options->block_n == 256)) return options->block_n;
+  return g.n % 256 == 0 || g.n > 1024 ? 256 : 128;
+}
+
+struct Operands {
+  CUtensorMap a, b;
+};
+
+cudaError_t encode_operands(Operands* maps, const void* a, int64_t lda, const void* b, int64_t ldb,
+                            const fuse_gemm_problem& g, int block_n) {
+  cudaError_t status = host::encode_tensor_map_2d(
+      &maps->a, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, uint64_t(g.m), uint64_t(g.k),
+      uint64_t(lda) * 2, kBlockM, kBlockK, CU_TENSOR_MAP_SWIZZLE_128B);
+  if (status != cudaSuccess) return status;
+  return host::encode_tensor_map_2d(&maps->b, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, uint64_t(g.n),
+                                    uint64_t(g.k), uint64_t(ldb) * 2, uint32_t(block_n), kBlockK,
+                                    CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+void fill_core(FusedParams* p, const fuse_gemm_problem& g, int block_n, int num_comm_ctas,
+               float alpha, void* d, int default_raster) {
+  p->m = g.m;
+  p->n = g.n;
+  p->k = g.k;
+  p->order.m_tiles = host::ceil_div(g.m, kBlockM);
+  p->order.n_tiles = host::ceil_div(g.n, block_n);
+  p->order.swizzle = select_swizzle(g.max_swizzle_size, p->order.m_tiles, p->order.n_tiles);
+  const int raster = g.raster == FUSE_RASTER_HEURISTIC ? default_raster : g.raster;
+  p->order.along_n = raster == FUSE_RASTER_ALONG_N ? 1 : 0;
+  p->num_comm_ctas = num_comm_ctas;
+  p->alpha = alpha;
+  p->beta = 0.0f;
+  p->d = static_cast<uint16_t*>(d);
+  p->ldd = packed_or(g.stride_d.row, g.n);
+}
+
+template <int kMode>
+cudaError_t launch_mode(const Operands& maps, const FusedParams& p, int block_n,
+                        const DeviceInfo& info, cudaStream_t stream) {
+  const int64_t tiles = p.order.count();
+  const int compute_capacity = info.sm_count - p.num_comm_ctas;
+  const int compute = int(tiles < compute_capacity ? tiles : compute_capacity);
+  const int grid = p.num_comm_ctas + compute;
+  const bool cooperative = kMode != kModePlain;
+  if (block_n == 256) {
+    using Layout = SmemLayout<256, 4>;
+    return host::launch_kernel(fused_gemm_kernel<256, 4, kMode>, grid, kThreads,
+                               Layout::kDynamicBytes, cooperative, stream, maps.a, maps.b, p);
+  }
+  using Layout = SmemLayout<128, 6>;
+  return host::launch_kernel(fused_gemm_kernel<128, 6, kMode>, grid, kThreads,
+                             Layout::kDynamicBytes, cooperative, stream, maps.a, maps.b, p);
+}
+
+cudaError_t check_device(DeviceInfo* info) {
+  const cudaError_t status = host::device_info(info);
+  if (status != cudaSuccess) return status;
+  // Compiled for sm_100a only: tcgen05 / TMEM kernels exist for no other target.
+  return info->cc_major == 10 ? cudaSuccess : cudaErrorNotSupported;
+}
+
+// detail/gemm_a2a.cuh:237-299 (can_implement) for the plain QKV GQA pack route.
+cudaError_t check_qkv_route(const fuse_gemm_a2a_params& p) {
+  const fuse_ulysses_route& r = p.route;
+  if (r.world_size <= 0 || r.world_size > FUSE_MAX_WORLD_SIZE || r.rank < 0 ||
+      r.rank >= r.world_size || r.batch <= 0 || r.seq_local <= 0 || r.global_seq <= 0 ||
+      r.q_heads <= 0 || r.kv_heads <= 0 || r.head_dim <= 0 || r.kind != FUSE_ROUTE_QKV_GQA_PACK ||
+      r.direction != FUSE_ROUTE_FORWARD || r.channel_count != 1 || r.cyclic_peer_order ||
+      r.packed_source_row != nullptr || r.packed_row_granularity != 0 ||
+      (p.completion_epoch != nullptr && !r.defer_v_a2a) || r.q_heads % r.kv_heads != 0 ||
+      r.q_heads % r.world_size != 0 || r.kv_heads % r.world_size != 0 || r.head_dim % 8 != 0)
+    return cudaErrorNotSupported;
+  // Offline-interleaved weights and the deferred-V variant are not built yet.
+  if (r.qkv_peer_interleaved || r.defer_v_a2a) return cudaErrorNotSupported;
+  if (int64_t(r.seq_local) * r.world_size != r.global_seq ||
+      int64_t(r.batch) * r.seq_local != p.gemm.m ||
+      int64_t(r.batch) * r.global_seq > INT32_MAX ||
+      (int64_t(r.q_heads) + 2 * int64_t(r.kv_heads)) * r.head_dim != p.gemm.n)
+    return cudaErrorNotSupported;
+  if (!host::aligned16(p.lhs) || !host::aligned16(p.rhs_nt) || !host::aligned16(p.local_output) ||
+      !host::aligned4(p.ready))
+    return cudaErrorNotSupported;
+  for (int peer = 0; peer < r.world_size; ++peer)
+    if (!host::aligned16(p.peer_output[peer]) || !host::aligned4(p.peer_route_done_epoch[peer]))
+      return cudaErrorNotSupported;
+  return cudaSuccess;
+}
+
+cudaError_t qkv_forward(const fuse_gemm_a2a_params& p, const fuse_b200_options* options,
+                        cudaStream_t stream) {
+  if (!supported_problem(p.gemm) || !std::isfinite(p.alpha) || p.epoch == 0 || p.num_comm_ctas <= 0)
+    return cudaErrorInvalidValue;
+  DeviceInfo info;
+  cudaError_t status = check_device(&info);
+  if (status != cudaSuccess) return status;
+  if (p.num_comm_ctas >= info.sm_count) return cudaErrorInvalidValue;
+  if ((status = check_qkv_route(p)) != cudaSuccess) return status;
+
+  const int block_n = choose_block_n(p.gemm, options);
+  Operands maps;
+  status = encode_operands(&maps, p.lhs, packed_or(p.gemm.stride_a.row, p.gemm.k), p.rhs_nt,
+                           packed_or(p.gemm.stride_b.row, p.gemm.k), p.gemm, block_n);
+  if (status != cudaSuccess) return status;
+
+  FusedParams k{};
+  fill_core(&k, p.gemm, block_n, p.num_comm_ctas, p.alpha, p.local_output, FUSE_RASTER_ALONG_M);
+  k.ready = p.ready;
+  k.flags = options ? options->flags : 0u;
+  k.wait = host::make_wait(info, p.epoch, options ? options->wait_budget_ns : 0);
+  k.qkv.world = p.route.world_size;
+  k.qkv.rank = p.route.rank;
+  k.qkv.batch = p.route.batch;
+  k.qkv.seq_local = p.route.seq_local;
+  k.qkv.global_seq = p.route.global_seq;
+  k.qkv.q_heads = p.route.q_heads;
+  k.qkv.kv_heads = p.route.kv_heads;
+  k.qkv.head_dim = p.route.head_dim;
+  for (int peer = 0; peer < p.route.world_size; ++peer) {
+    k.qkv.peer_output[peer] = p.peer_output[peer];
+    k.qkv.peer_done[peer] = p.peer_route_done_epoch[peer];
+  }
+  return launch_mode<kModeQkvPush>(maps, k, block_n, info, stream);
+}
+
+// detail/a2a_gemm.cuh (can_implement of the lhs pull) restated for the BF16 row layout.
+cudaError_t check_lhs_route(const fuse_a2a_gemm_params& p) {
+  const fuse_ulysses_route& r = p.route;
+  if (r.world_size <= 0 || r.world_size > FUSE_MAX_WORLD_SIZE || r.rank < 0 ||
+      r.rank >= r.world_size || r.batch <= 0 || r.seq_local <= 0 || r.global_seq <= 0 ||
+      r.kind != FUSE_ROUTE_HEAD_TO_SEQUENCE || r.direction != FUSE_ROUTE_INVERSE ||
+      r.channel_count != 1 || r.packed_source_row != nullptr || r.packed_row_granularity != 0 ||
+      r.qkv_peer_interleaved || r.defer_v_a2a)
+    return cudaErrorNotSupported;
+  if (int64_t(r.seq_local) * r.world_size != r.global_seq ||
+      int64_t(r.batch) * r.seq_local != p.gemm.m || p.gemm.k % r.world_size != 0 ||
+      (p.gemm.k / r.world_size) % 8 != 0 || (r.causal_load_balanced && r.seq_local % 2 != 0))
+    return cudaErrorNotSupported;
+  if (r.q_heads > 0 && r.head_dim > 0 && int64_t(r.q_heads) * r.head_dim != p.gemm.k)
+    return cudaErrorNotSupported;
+  if (!host::aligned16(p.input_staging) || !host::aligned16(p.rhs_nt) || !host::aligned16(p.output) ||
+      !host::aligned4(p.ready))
+    return cudaErrorNotSupported;
+  for (int peer = 0; peer < r.world_size; ++peer) {
+    if (!host::aligned16(p.peer_input[peer])) return cudaErrorNotSupported;
+    if (p.peer_input_ready[peer] != nullptr && !host::aligned4(p.peer_input_ready[peer]))
+      return cudaErrorNotSupported;
+  }
+  return cudaSuccess;
+}
+
+cudaError_t oproj_forward(const fuse_a2a_gemm_params& p, const fuse_b200_options* options,
+                          cudaStream_t stream) {
+  if (!supported_problem(p.gemm) || !std::isfinite(p.alpha) || p.epoch == 0 || p.lhs_policy != 0)
+    return cudaErrorInvalidValue;
+  int num_comm_ctas = p.num_comm_ctas;
+  if (num_comm_ctas == 0)
+    num_comm_ctas = fuse_recommended_a2a_lhs_gemm_comm_ctas(&p.gemm, &p.route);
+  if (num_comm_ctas < 0) return cudaErrorInvalidValue;
+  if (num_comm_ctas == 0) return cudaErrorNotSupported;
+  DeviceInfo info;
+  cudaError_t status = check_device(&info);
+  if (status != cudaSuccess) return status;
+  if (num_comm_ctas >= info.sm_count) return cudaErrorInvalidValue;
+  if ((status = check_lhs_route(p)) != cudaSuccess) return status;
+
+  const int block_n = choose_block_n(p.gemm, options);
+  const int64_t lda = packed_or(p.gemm.stride_a.row, p.gemm.k);
+  Operands maps;
+  status = encode_operands(&maps, p.input_staging, lda, p.rhs_nt,
+                           packed_or(p.gemm.stride_b.row, p.gemm.k), p.gemm, block_n);
+  if (status != cudaSuccess) return status;
+
+  FusedParams k{};
+  fill_core(&k, p.gemm, block_n, num_comm_ctas, p.alpha, p.output, FUSE_RASTER_ALONG_N);
+  k.ready = p.ready;
+  k.flags = options ? options->flags : 0u;
+  k.wait = host::make_wait(info, p.epoch, options ? options->wait_budget_ns : 0);
+  k.lhs.world = p.route.world_size;
+  k.lhs.rank = p.route.rank;
+  k.lhs.seq_local = p.route.seq_local;
+  k.lhs.global_seq = p.route.global_seq;
+  k.lhs.shard_width = p.gemm.k / p.route.world_size;
+  k.lhs.causal = p.route.causal_load_balanced ? 1 : 0;
+  k.lhs.cyclic = p.route.cyclic_peer_order ? 1 : 0;
+  k.lhs.input_epoch = p.input_epoch;
+  k.lhs.staging = p.input_staging;
+  k.lhs.lda = lda;
+  for (int peer = 0; peer < p.route.world_size; ++peer) {
+    k.lhs.peer_input[peer] = p.peer_input[peer];
+    k.lhs.peer_input_ready[peer] = p.peer_input_ready[peer];
+  }
+  return launch_mode<kModeLhsPull>(maps, k, block_n, info, stream);
+}
+
+cudaError_t plain_gemm(const fuse_gemm_problem& g, const void* a, const void* b, void* d, float alpha,
+                       int reserved_comm_ctas, cudaStream_t stream) {
+  if (!supported_problem(g) || !std::isfinite(alpha) || reserved_comm_ctas < 0)
+    return cudaErrorInvalidValue;
+  DeviceInfo info;
+  cudaError_t status = check_device(&info);
+  if (status != cudaSuccess) return status;
+  if (reserved_comm_ctas >= info.sm_count || !host::aligned16(a) || !host::aligned16(b) ||
+      !host::aligned16(d))
+    return cudaErrorInvalidValue;
+  const int block_n = choose_block_n(g, nullptr);
+  Operands maps;
+  status = encode_operands(&maps, a, packed_or(g.stride_a.row, g.k), b,
+                           packed_or(g.stride_b.row, g.k), g, block_n);
+  if (status != cudaSuccess) return status;
+  FusedParams k{};
+  fill_core(&k, g, block_n, 0, alpha, d, FUSE_RASTER_ALONG_M);
+  k.wait = host::make_wait(info, 1, 0);
+  // The reserved CTAs are simply not launched: the GEMM runs on SMs - reserved.
+  DeviceInfo reduced = info;
+  reduced.sm_count = info.sm_count - reserved_comm_ctas;
+  return launch_mode<kModePlain>(maps, k, block_n, reduced, stream);
+}
+
+}  // namespace
+}  // namespace fuse_b200
+
+extern "C" {
+
+int fuse_launch_gemm_a2a_cutlass_ex(const fuse_gemm_a2a_params* params,
+                                    const fuse_b200_options* options, fuse_stream stream) {
+  if (params == nullptr) return int(cudaErrorInvalidValue);
+  return int(fuse_b200::qkv_forward(*params, options, reinterpret_cast<cudaStream_t>(stream)));
+}
+
+int fuse_launch_gemm_a2a_cutlass(const fuse_gemm_a2a_params* params, fuse_stream stream) {
+  return fuse_launch_gemm_a2a_cutlass_ex(params, nullptr, stream);
+}
+
+int fuse_launch_a2a_gemm_cutlass_ex(const fuse_a2a_gemm_params* params,
+                                    const fuse_b200_options* options, fuse_stream stream) {
+  if (params == nullptr) return int(cudaErrorInvalidValue);
+  return int(fuse_b200::oproj_forward(*params, options, reinterpret_cast<cudaStream_t>(stream)));
+}
+
+int fuse_launch_a2a_gemm_cutlass(const fuse_a2a_gemm_params* params, fuse_stream stream) {
+  return fuse_launch_a2a_gemm_cutlass_ex(params, nullptr, stream);
+}
+
+int fuse_launch_batched_cutlass_reference(const fuse_gemm_a2a_params* params, fuse_stream stream,
+                                          int32_t reserved_comm_ctas) {
+  if (params == nullptr) return int(cudaErrorInvalidValue);
+  return int(fuse_b200::plain_gemm(params->gemm, params->lhs, params->rhs_nt, params->local_output,
+                                   params->alpha, reserved_comm_ctas,
+                                   reinterpret_cast<cudaStream_t>(stream)));
+}
+
+int fuse_launch_a2a_gemm_cutlass_reference(const fuse_a2a_gemm_params* params, fuse_stream stream,
+                                           int32_t reserved_comm_ctas) {
+  if (params == nullptr) return int(cudaErrorInvalidValue);
+  return int(fuse_b200::plain_gemm(params->gemm, params->input_staging, params->rhs_nt,
+                                   params->output, params->alpha, reserved_comm_ctas,
+                                   reinterpret_cast<cudaStream_t>(stream)));
+}
+
+void fuse_qkv_cutlass_kernel_traits(const fuse_gemm_problem* problem, fuse_kernel_traits* out) {
+  (void)problem;
+  // Finest publication tile this library launches; `ready` sized for it fits every choice.
+  using Layout = fuse_b200::SmemLayout<128, 6>;
+  *out = {fuse_b200::kBlockM, 128, fuse_b200::kBlockK, fuse_b200::kThreads,
+          int32_t(Layout::kDynamicBytes)};
+}
+
+void fuse_cutlass_kernel_traits(fuse_kernel_traits* out) {
+  using Layout = fuse_b200::SmemLayout<256, 4>;
+  *out = {fuse_b200::kBlockM, 256, fuse_b200::kBlockK, fuse_b200::kThreads,
+          int32_t(Layout::kDynamicBytes)};
+}
+
+int64_t fuse_a2a_lhs_gemm_ready_elements(const fuse_gemm_problem* problem,
+                                         const fuse_ulysses_route* route) {
+  if (problem == nullptr || route == nullptr || problem->m <= 0 || route->world_size <= 0) return 0;
+  return int64_t(fuse_b200::host::ceil_div(problem->m, fuse_b200::kBlockM)) * route->world_size *
+         FUSE_READY_FLAG_STRIDE;
+}
+
+int32_t fuse_recommended_gemm_a2a_comm_ctas(const fuse_gemm_problem* problem,
+                                            const fuse_ulysses_route* route) {
+  (void)problem;
+  (void)route;
+  return 0;  // no calibrated plan yet: the caller passes an explicit budget
+}
+
+int32_t fuse_recommended_a2a_lhs_gemm_comm_ctas(const fuse_gemm_problem* problem,
+                                                const fuse_ulysses_route* route) {
+  (void)problem;
+  (void)route;
+  return 0;
+}
+
+int fuse_b200_abi_sizeof(int record) {
+  switch (record) {
+    case 0: return int(sizeof(fuse_gemm_problem));
+    case 1: return int(sizeof(fuse_ulysses_route));
+    case 2: return int(sizeof(fuse_gemm_a2a_params));
+    case 3: return int(sizeof(fuse_a2a_gemm_params));
+    case 4: return int(sizeof(fuse_kernel_traits));
+    case 5: return int(sizeof(fuse_b200_options));
+    default: return -1;
+  }
+}
+
+}  // extern "C"

@@ -1,0 +1,530 @@
+// One persistent kernel per fused operator.
+//
+// CTAs [0, num_comm_ctas) are communication CTAs; the rest are compute CTAs that walk the
+// static tile order round-robin.  A compute CTA is warp-specialised:
+//
+//   warp 0  TMA producer   global -> 128B-swizzled shared tiles, `kStages` deep ring of
+//                          full/empty mbarriers
+//   warp 1  UMMA issuer    one thread issues tcgen05.mma (cta_group::1, 128 x kBlockN x 16)
+//                          into one of two TMEM accumulator stages and commits to mbarriers
+//   warp 2  TMEM allocator
+//   warps 4-7 epilogue     tcgen05.ld -> alpha/beta -> BF16 -> 16-byte global stores, then
+//                          (when the operator routes its output) publishes the tile's epoch
+//
+// The operator-specific parts are three hooks selected at compile time by `kMode`:
+//   * a load gate      (wait until the rows of A this K block reads have arrived),
+//   * a tile publisher (release flag after the tile's stores),
+//   * the communication role run by the communication CTAs.
+//
+// Replaces the role-dispatch kernel and CUTLASS collectives of the reference
+// (csrc/operators/sm103/detail/persistent_gemm.cuh:186-263, detail/gemm.cuh:112-188,
+// detail/cutlass_pipeline.cuh:335-814) with hand-written tcgen05/TMEM code.
+#pragma once
+
+#include <cooperative_groups.h>
+#include <cuda_bf16.h>
+
+#include "ptx.cuh"
+#include "sync.cuh"
+#include "tile_order.cuh"
+
+namespace fuse_b200 {
+
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 64;        // 64 BF16 = one 128-byte swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kThreads = 256;
+constexpr int kEpilogueThreads = 128;
+constexpr int kAccumStages = 2;
+
+enum FusedMode : int {
+  kModePlain = 0,     // GEMM only
+  kModeQkvPush = 1,   // GEMM -> publish tiles -> comm CTAs push to peers' planar Q|K|V
+  kModeLhsPull = 2,   // comm CTAs pull the lhs shards from peers -> gated GEMM
+};
+
+enum LaunchFlags : uint32_t {
+  // Skip the wait for the peers' completion epochs (single-GPU emulation of several ranks,
+  // where the "peers" are later launches on the same stream).
+  kFlagSkipPeerWait = 1u,
+};
+
+struct QkvRoute {
+  int32_t world, rank, batch, seq_local, global_seq;
+  int32_t q_heads, kv_heads, head_dim;
+  uint16_t* peer_output[kMaxWorldSize];
+  uint32_t* peer_done[kMaxWorldSize];
+};
+
+struct LhsRoute {
+  int32_t world, rank, seq_local, global_seq;
+  int32_t shard_width;        // K / world, elements
+  int32_t causal, cyclic;
+  const uint16_t* peer_input[kMaxWorldSize];
+  const uint32_t* peer_input_ready[kMaxWorldSize];
+  uint32_t input_epoch;
+  uint16_t* staging;          // [M, lda]
+  int64_t lda;
+};
+
+struct FusedParams {
+  int32_t m, n, k;
+  TileOrder order;
+  int32_t num_comm_ctas;
+  float alpha, beta;
+  uint16_t* d;
+  int64_t ldd;
+  uint32_t* ready;            // tile flags (QkvPush) or (m-tile, k-shard) flags (LhsPull)
+  uint32_t flags;
+  WaitContext wait;
+  QkvRoute qkv;
+  LhsRoute lhs;
+};
+
+template <int kBlockN, int kStages>
+struct SmemLayout {
+  static constexpr uint32_t kABytes = kBlockM * kBlockK * 2;
+  static constexpr uint32_t kBBytes = kBlockN * kBlockK * 2;
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr uint32_t kBarrierOffset = kStages * kStageBytes;
+  static constexpr uint32_t kNumBarriers = 2 * kStages + 2 * kAccumStages;
+  static constexpr uint32_t kTmemSlotOffset = kBarrierOffset + kNumBarriers * 8;
+  static constexpr uint32_t kBytes = kTmemSlotOffset + 16;
+  // + 1024 so the kernel can align the base itself; total is above half of the SM's shared
+  // memory, which pins residency at exactly one CTA per SM.
+  static constexpr uint32_t kDynamicBytes = kBytes + 1024;
+  static_assert(kDynamicBytes <= 227 * 1024, "shared memory budget");
+  static_assert(kDynamicBytes > 114 * 1024, "must force one CTA per SM");
+};
+
+// ------------------------------------------------------------------------------------------
+// Row mapping shared by the routes: rank-local row -> row of the global [batch, S] axis.
+// Contiguous shards (csrc/operators/sm103/detail/gemm_a2a.cuh:115-132) or the causal
+// two-chunk assignment (csrc/operators/sm103/detail/a2a_gemm.cuh:410-420).
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ int64_t global_row(int32_t world, int32_t rank, int32_t seq_local,
+                                              int32_t global_seq, bool causal, int32_t local_row) {
+  const int32_t batch = local_row / seq_local;
+  const int32_t seq = local_row - batch * seq_local;
+  if (causal) {
+    const int32_t half = seq_local / 2;
+    const int32_t chunk = seq < half ? rank : 2 * world - rank - 1;
+    return int64_t(batch) * global_seq + int64_t(chunk) * half + seq % half;
+  }
+  return int64_t(batch) * global_seq + int64_t(rank) * seq_local + seq;
+}
+
+// ------------------------------------------------------------------------------------------
+// Communication role: forward QKV push.
+//
+// For each published output tile (same linear order as the producers), copy every 16-byte
+// chunk of the tile from the local GEMM output (L2-resident, just written) to its place in
+// the owning rank's planar Q | K | V tensor.  Column chunks and rows are mapped once per tile
+// into shared-memory tables; the copy itself is 8 independent 16-byte loads followed by 8
+// stores per thread.  Address map: include/fuse/layout/ulysses.h:77-107 (feature -> owner,
+// local feature) and csrc/operators/sm103/detail/gemm_a2a.cuh:190-215 (planar bases).
+// ------------------------------------------------------------------------------------------
+template <int kBlockN>
+__device__ __forceinline__ void qkv_push_role(const FusedParams& p, uint8_t* smem) {
+  constexpr int kChunks = kBlockN / 8;
+  uint16_t** col_base = reinterpret_cast<uint16_t**>(smem);                 // [kChunks]
+  int64_t* col_stride = reinterpret_cast<int64_t*>(smem + 8 * kChunks);     // [kChunks]
+  int64_t* row_dest = reinterpret_cast<int64_t*>(smem + 16 * kChunks);      // [kBlockM]
+  uint32_t* ok_slot = reinterpret_cast<uint32_t*>(smem + 16 * kChunks + 8 * kBlockM);
+  const QkvRoute& r = p.qkv;
+  const int tid = threadIdx.x;
+  const int64_t tiles = p.order.count();
+  const int64_t rows_total = int64_t(r.batch) * r.global_seq;
+  const int32_t q_width = r.q_heads * r.head_dim, kv_width = r.kv_heads * r.head_dim;
+  const int32_t q_local = q_width / r.world, kv_local = kv_width / r.world;
+
+  for (int64_t t = blockIdx.x; t < tiles; t += p.num_comm_ctas) {
+    int32_t mt, nt;
+    p.order.decode(t, mt, nt);
+    const int32_t m0 = mt * kBlockM, n0 = nt * kBlockN;
+    __syncthreads();  // the previous tile's table readers are done
+    if (tid < kChunks) {
+      const int32_t feature = n0 + tid * 8;
+      uint16_t* base = nullptr;
+      int64_t stride = 0;
+      if (feature < p.n) {
+        const int32_t segment = feature < q_width ? 0 : (feature < q_width + kv_width ? 1 : 2);
+        const int32_t within = feature - (segment == 0 ? 0 : q_width + (segment == 2 ? kv_width : 0));
+        const int32_t local_width = segment == 0 ? q_local : kv_local;
+        const int32_t owner = within / local_width;
+        const int32_t local_col = within - owner * local_width;
+        const int64_t segment_base =
+            segment == 0 ? 0 : rows_total * q_local + (segment == 2 ? rows_total * kv_local : 0);
+        base = r.peer_output[owner] + segment_base + local_col;
+        stride = local_width;
+      }
+      col_base[tid] = base;
+      col_stride[tid] = stride;
+    } else if (tid >= 128) {
+      const int32_t row = m0 + (tid - 128);
+      row_dest[tid - 128] =
+          row < p.m ? global_row(r.world, r.rank, r.seq_local, r.global_seq, false, row) : -1;
+    }
+    if (tid == 0) {
+      const int64_t flag = (int64_t(mt) * p.order.n_tiles + nt) * kReadyFlagStride;
+      *ok_slot = flag_wait<false>(p.ready + flag, p.wait.epoch, p.wait, kSiteTileReady,
+                                  uint32_t(flag / kReadyFlagStride))
+                     ? 1u : 0u;
+    }
+    __syncthreads();
+    if (*ok_slot == 0u) break;
+
+    constexpr int kPerThread = kBlockM * kChunks / kThreads;
+    constexpr int kUnroll = 8;
+    static_assert(kPerThread % kUnroll == 0, "copy unroll");
+    for (int j0 = 0; j0 < kPerThread; j0 += kUnroll) {
+      uint4 value[kUnroll];
+      uint16_t* dst[kUnroll];
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int i = tid + (j0 + u) * kThreads;
+        const int row = i / kChunks, chunk = i % kChunks;
+        uint16_t* base = col_base[chunk];
+        const int64_t dest_row = row_dest[row];
+        dst[u] = (base != nullptr && dest_row >= 0) ? base + dest_row * col_stride[chunk] : nullptr;
+        if (dst[u] != nullptr)
+          value[u] = ptx::ld_cg_v4(p.d + int64_t(m0 + row) * p.ldd + n0 + chunk * 8);
+      }
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u)
+        if (dst[u] != nullptr) ptx::st_v4(dst[u], value[u]);
+    }
+  }
+  __threadfence_system();  // this thread's peer stores are performed before the CTA joins
+}
+
+// Cross-rank completion after the grid has joined: tell every destination that this rank's
+// pushes into it are complete, then wait until every source has said the same to this rank
+// (protocol of csrc/operators/sm103/detail/gemm_a2a.cuh:760-786, with a bounded wait).
+__device__ __forceinline__ void qkv_finalize(const FusedParams& p) {
+  if (blockIdx.x != 0 || threadIdx.x >= 32) return;
+  const QkvRoute& r = p.qkv;
+  const int lane = threadIdx.x;
+  if (lane == 0) ptx::fence_sc_sys();
+  __syncwarp();
+  if (lane < r.world)
+    ptx::st_release_sys(r.peer_done[lane] + r.rank * kReadyFlagStride, p.wait.epoch);
+  __syncwarp();
+  if (lane < r.world && !(p.flags & kFlagSkipPeerWait))
+    flag_wait<true>(r.peer_done[r.rank] + lane * kReadyFlagStride, p.wait.epoch, p.wait,
+                    kSitePeerDone, uint32_t(lane));
+  __syncwarp();
+}
+
+// ------------------------------------------------------------------------------------------
+// Communication role: inverse (head -> sequence) pull feeding the output projection.
+//
+// Unit of work = (M tile, K shard): 128 rows x (K / world) columns read from the owning
+// peer's head-sharded tensor [B*S_global, K/world] and written into the local row-major lhs
+// staging [M, K] at column shard*K/world.  One warp moves one row at a time with 16-byte
+// accesses, four rows in flight per warp.  When the unit is in place the CTA publishes
+// ready[(m_tile*world + shard)*32] = epoch.  Address map: benchmarks/sm103/fused_inputs.cuh:79-104;
+// unit/flag layout: csrc/operators/sm103/api/policy.cuh:312-329.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void lhs_pull_role(const FusedParams& p, uint8_t* smem) {
+  uint32_t* ok_slot = reinterpret_cast<uint32_t*>(smem);
+  const LhsRoute& r = p.lhs;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int64_t units = int64_t(p.order.m_tiles) * r.world;
+  const int32_t chunks_per_row = r.shard_width / 8;  // 16-byte chunks
+  uint32_t upstream_seen = 0;                        // bit per peer (thread 0 only)
+
+  for (int64_t u = blockIdx.x; u < units; u += p.num_comm_ctas) {
+    const int32_t mt = int32_t(u / r.world), shard = int32_t(u % r.world);
+    const int32_t peer = r.cyclic ? (r.rank + shard) % r.world : shard;
+    const int32_t m0 = mt * kBlockM;
+    bool ok = true;
+    if (r.peer_input_ready[peer] != nullptr) {
+      // Upstream producer (attention on the peer) publishes one epoch per tensor.
+      __syncthreads();
+      if (tid == 0) {
+        uint32_t good = 1u;
+        if (!((upstream_seen >> peer) & 1u)) {
+          good = flag_wait<true>(r.peer_input_ready[peer], r.input_epoch, p.wait,
+                                 kSiteUpstreamReady, uint32_t(peer))
+                     ? 1u : 0u;
+          upstream_seen |= good << peer;
+        }
+        *ok_slot = good;
+      }
+      __syncthreads();
+      ok = *ok_slot != 0u;
+    }
+    if (!ok) break;
+
+    const uint16_t* src_base = r.peer_input[peer];
+    uint16_t* dst_base = r.staging + int64_t(shard) * r.shard_width;
+    const int32_t rows = p.m - m0 < kBlockM ? p.m - m0 : kBlockM;
+    constexpr int kRowsInFlight = 4;
+    for (int32_t row0 = warp * kRowsInFlight; row0 < rows; row0 += (kThreads / 32) * kRowsInFlight) {
+      for (int32_t c0 = lane; c0 < chunks_per_row; c0 += 32 * 2) {
+        uint4 value[kRowsInFlight][2];
+        bool valid[kRowsInFlight][2];
+#pragma unroll
+        for (int i = 0; i < kRowsInFlight; ++i) {
+          const int32_t row = m0 + row0 + i;
+          const int64_t src_row =
+              row0 + i < rows
+                  ? global_row(r.world, r.rank, r.seq_local, r.global_seq, r.causal != 0, row)
+                  : -1;
+#pragma unroll
+          for (int j = 0; j < 2; ++j) {
+            const int32_t c = c0 + j * 32;
+            valid[i][j] = src_row >= 0 && c < chunks_per_row;
+            if (valid[i][j]) value[i][j] = ptx::ld_cg_v4(src_base + src_row * r.shard_width + c * 8);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < kRowsInFlight; ++i)
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+            if (valid[i][j])
+              ptx::st_v4(dst_base + int64_t(m0 + row0 + i) * r.lda + (c0 + j * 32) * 8, value[i][j]);
+      }
+    }
+    __syncthreads();  // every thread's stores of this unit are issued ...
+    if (tid == 0) {
+      __threadfence();                    // ... and ordered before the flag at GPU scope,
+      ptx::fence_proxy_async_global();    // also for the TMA (async proxy) reads that follow
+      ptx::st_release_gpu(p.ready + (int64_t(mt) * r.world + shard) * kReadyFlagStride,
+                          p.wait.epoch);
+    }
+  }
+}
+
+// 32 FP32 accumulators of one output row -> alpha (and beta * old D) -> BF16 -> four 16-byte
+// stores.  `col` is the global column of acc[0]; vectors past N are skipped (N % 8 == 0).
+__device__ __forceinline__ void store_accumulators(const uint32_t (&acc)[32], uint16_t* dst,
+                                                   int32_t col, bool row_ok, const FusedParams& p) {
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    if (row_ok && col + v * 8 < p.n) {
+      float f[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = p.alpha * __uint_as_float(acc[v * 8 + e]);
+      if (p.beta != 0.0f) {
+        const uint4 old = *reinterpret_cast<const uint4*>(dst + v * 8);
+        f[0] += p.beta * __uint_as_float(old.x << 16);
+        f[1] += p.beta * __uint_as_float(old.x & 0xffff0000u);
+        f[2] += p.beta * __uint_as_float(old.y << 16);
+        f[3] += p.beta * __uint_as_float(old.y & 0xffff0000u);
+        f[4] += p.beta * __uint_as_float(old.z << 16);
+        f[5] += p.beta * __uint_as_float(old.z & 0xffff0000u);
+        f[6] += p.beta * __uint_as_float(old.w << 16);
+        f[7] += p.beta * __uint_as_float(old.w & 0xffff0000u);
+      }
+      uint4 out;
+      __nv_bfloat162 pair = __floats2bfloat162_rn(f[0], f[1]);
+      out.x = *reinterpret_cast<const uint32_t*>(&pair);
+      pair = __floats2bfloat162_rn(f[2], f[3]);
+      out.y = *reinterpret_cast<const uint32_t*>(&pair);
+      pair = __floats2bfloat162_rn(f[4], f[5]);
+      out.z = *reinterpret_cast<const uint32_t*>(&pair);
+      pair = __floats2bfloat162_rn(f[6], f[7]);
+      out.w = *reinterpret_cast<const uint32_t*>(&pair);
+      ptx::st_v4(dst + v * 8, out);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// The kernel.
+// ------------------------------------------------------------------------------------------
+template <int kBlockN, int kStages, int kMode>
+__global__ void __launch_bounds__(kThreads, 1)
+fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                  const __grid_constant__ CUtensorMap tmap_b, const FusedParams p) {
+  using Layout = SmemLayout<kBlockN, kStages>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool is_comm = int(blockIdx.x) < p.num_comm_ctas;
+
+  if (is_comm) {
+    if constexpr (kMode == kModeQkvPush) qkv_push_role<kBlockN>(p, smem);
+    if constexpr (kMode == kModeLhsPull) lhs_pull_role(p, smem);
+  } else {
+    const uint32_t bar_base = base + Layout::kBarrierOffset;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+    auto tmem_full_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };
+    auto tmem_empty_bar = [&](int s) { return bar_base + 8u * (2 * kStages + kAccumStages + s); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + Layout::kTmemSlotOffset);
+    constexpr uint32_t kTmemColumns = kAccumStages * kBlockN;
+    static_assert(kTmemColumns == 256 || kTmemColumns == 512, "TMEM allocation is a power of two");
+
+    if (threadIdx.x == 0) {
+      ptx::prefetch_tensormap(&tmap_a);
+      ptx::prefetch_tensormap(&tmap_b);
+      for (int s = 0; s < kStages; ++s) {
+        ptx::mbar_init(full_bar(s), 1);
+        ptx::mbar_init(empty_bar(s), 1);
+      }
+      for (int s = 0; s < kAccumStages; ++s) {
+        ptx::mbar_init(tmem_full_bar(s), 1);
+        ptx::mbar_init(tmem_empty_bar(s), kEpilogueThreads);
+      }
+      ptx::fence_mbar_init();
+    }
+    if (warp == 2) {
+      ptx::tmem_alloc(base + Layout::kTmemSlotOffset, kTmemColumns);
+      ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int32_t compute_ctas = int32_t(gridDim.x) - p.num_comm_ctas;
+    const int32_t compute_id = int32_t(blockIdx.x) - p.num_comm_ctas;
+    const int64_t tiles = p.order.count();
+    const int32_t k_blocks = (p.k + kBlockK - 1) / kBlockK;
+
+    if (warp == 0) {
+      // ------------------------------------------------------------------ TMA producer
+      if (lane == 0) {
+        uint32_t stage = 0, phase = 0;
+        uint32_t issued_mask = 0, issued_parity = 0;  // last armed phase per stage (for the drain)
+        bool ok = true;
+        for (int64_t t = compute_id; ok && t < tiles; t += compute_ctas) {
+          int32_t mt, nt;
+          p.order.decode(t, mt, nt);
+          int32_t gated_upto = -1;  // highest K shard already acquired for this tile
+          for (int32_t kb = 0; kb < k_blocks; ++kb) {
+            if constexpr (kMode == kModeLhsPull) {
+              int32_t last = (kb * kBlockK + kBlockK - 1) / p.lhs.shard_width;
+              if (last >= p.lhs.world) last = p.lhs.world - 1;
+              while (ok && gated_upto < last) {
+                ++gated_upto;
+                const int64_t flag = (int64_t(mt) * p.lhs.world + gated_upto) * kReadyFlagStride;
+                ok = flag_wait<false>(p.ready + flag, p.wait.epoch, p.wait, kSiteLhsReady,
+                                      uint32_t(flag / kReadyFlagStride));
+                ptx::fence_proxy_async_global();
+              }
+              if (!ok) break;
+            }
+            ok = mbar_wait(empty_bar(stage), phase ^ 1u, p.wait, kSiteSmemEmpty);
+            if (!ok) break;
+            ptx::mbar_expect_tx(full_bar(stage), Layout::kStageBytes);
+            const uint32_t a_dst = base + stage * Layout::kStageBytes;
+            ptx::tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * kBlockK, mt * kBlockM);
+            ptx::tma_load_2d(a_dst + Layout::kABytes, &tmap_b, full_bar(stage), kb * kBlockK,
+                             nt * kBlockN);
+            issued_mask |= 1u << stage;
+            issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
+            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          }
+          (void)gated_upto;
+        }
+        if (!ok) {
+          // Unwinding: let every copy this thread started land before shared memory goes away.
+          for (int s = 0; s < kStages; ++s)
+            if ((issued_mask >> s) & 1u)
+              mbar_wait(full_bar(s), (issued_parity >> s) & 1u, p.wait, kSiteDrain, false);
+        }
+      }
+    } else if (warp == 1) {
+      // ------------------------------------------------------------------ UMMA issuer
+      if (lane == 0) {
+        constexpr uint32_t kIdesc = ptx::idesc_bf16_f32(kBlockM, kBlockN, 0, 0);
+        uint32_t stage = 0, phase = 0, accum = 0, accum_phase = 0;
+        bool ok = true;
+        for (int64_t t = compute_id; ok && t < tiles; t += compute_ctas) {
+          ok = mbar_wait(tmem_empty_bar(accum), accum_phase ^ 1u, p.wait, kSiteTmemEmpty);
+          if (!ok) break;
+          ptx::tc_fence_after();
+          const uint32_t d_tmem = tmem_base + accum * kBlockN;
+          for (int32_t kb = 0; kb < k_blocks; ++kb) {
+            ok = mbar_wait(full_bar(stage), phase, p.wait, kSiteSmemFull);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            const uint32_t a_addr = base + stage * Layout::kStageBytes;
+            const uint64_t a_desc = ptx::smem_desc_k_sw128(a_addr);
+            const uint64_t b_desc = ptx::smem_desc_k_sw128(a_addr + Layout::kABytes);
+#pragma unroll
+            for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+              // +32 bytes along K inside the swizzle row = +2 in the descriptor's address field
+              ptx::umma_f16(d_tmem, a_desc + uint64_t(2 * k), b_desc + uint64_t(2 * k), kIdesc,
+                            (kb | k) != 0 ? 1u : 0u);
+            }
+            ptx::umma_commit(empty_bar(stage));  // frees the stage when these UMMAs retire
+            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          }
+          if (!ok) break;
+          ptx::umma_commit(tmem_full_bar(accum));
+          if (++accum == kAccumStages) { accum = 0; accum_phase ^= 1u; }
+        }
+        if (!ok) {
+          // Unwinding: UMMAs already issued must retire before TMEM is released.
+          ptx::umma_commit(tmem_full_bar(accum));
+          mbar_wait(tmem_full_bar(accum), accum_phase, p.wait, kSiteDrain, false);
+        }
+      }
+    } else if (warp >= 4) {
+      // ------------------------------------------------------------------ epilogue
+      const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+      const int epi_tid = threadIdx.x - 128;
+      uint32_t accum = 0, accum_phase = 0;
+      bool ok = true;
+      for (int64_t t = compute_id; ok && t < tiles; t += compute_ctas) {
+        int32_t mt, nt;
+        p.order.decode(t, mt, nt);
+        ok = mbar_wait(tmem_full_bar(accum), accum_phase, p.wait, kSiteTmemFull);
+        // The four epilogue warps leave together or not at all (they share a named barrier).
+        ok = ptx::named_bar_all(2, kEpilogueThreads, ok);
+        if (!ok) break;
+        ptx::tc_fence_after();
+        const int32_t row = mt * kBlockM + quarter * 32 + lane;
+        const bool row_ok = row < p.m;
+        uint16_t* d_row = p.d + int64_t(row) * p.ldd + nt * kBlockN;
+        const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + accum * kBlockN;
+#pragma unroll 1
+        for (int c = 0; c < kBlockN; c += 64) {
+          uint32_t acc0[32], acc1[32];
+          ptx::tmem_ld_32x32b_x32(taddr + c, acc0);
+          ptx::tmem_ld_32x32b_x32(taddr + c + 32, acc1);
+          ptx::tmem_wait_ld();
+          if (c + 64 >= kBlockN) {
+            // Accumulator fully read: hand the TMEM stage back to the UMMA issuer.
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(tmem_empty_bar(accum));
+          }
+          store_accumulators(acc0, d_row + c, nt * kBlockN + c, row_ok, p);
+          store_accumulators(acc1, d_row + c + 32, nt * kBlockN + c + 32, row_ok, p);
+        }
+        if constexpr (kMode == kModeQkvPush) {
+          // Publish the tile: all 128 epilogue threads' stores, then one release at GPU scope
+          // (flag index m*n_tiles+n, csrc/operators/sm103/detail/producer_consumer.cuh:42-48).
+          ptx::named_bar_sync(1, kEpilogueThreads);
+          if (epi_tid == 0) {
+            __threadfence();
+            ptx::st_release_gpu(
+                p.ready + (int64_t(mt) * p.order.n_tiles + nt) * kReadyFlagStride, p.wait.epoch);
+          }
+        }
+        if (++accum == kAccumStages) { accum = 0; accum_phase ^= 1u; }
+      }
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+      ptx::tc_fence_after();
+      ptx::tmem_dealloc(tmem_base, kTmemColumns);
+    }
+  }
+
+  if constexpr (kMode == kModeQkvPush) {
+    cooperative_groups::this_grid().sync();
+    qkv_finalize(p);
+  }
+}
+
+}  // namespace fuse_b200

@@ -1,0 +1,179 @@
+/*
+ * fuse_b200 -- C ABI of the B200 (sm_100a) implementation of the fused Ulysses projection
+ * operators.
+ *
+ * Every entry point takes plain pointers and sizes.  The parameter records are
+ * layout-identical to the C++ records of the interface they replace (same members, same
+ * order, enums as int32_t, bool as uint8_t), so a C++ caller of that interface can pass its
+ * own struct through a reinterpret_cast; fuse_b200_abi_sizeof() lets a binding check this at
+ * load time.  All functions return a cudaError_t value as int (0 = success, 1 = invalid
+ * value, 801 = not supported, ...); nothing throws.
+ *
+ * Ownership is the caller's throughout: inputs, outputs, staging, ready/done flag arrays
+ * (zeroed once; epochs start at 1 and must grow with every launch), peer mappings.  The
+ * library allocates no device memory on the launch path.
+ *
+ * Each declaration cites the interface it replaces as file:line inside the reference
+ * project (CyberSecurityErial/fuse).
+ */
+#ifndef FUSE_B200_H_
+#define FUSE_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define FUSE_API __attribute__((visibility("default")))
+#else
+#define FUSE_API
+#endif
+
+#define FUSE_MAX_WORLD_SIZE 8      /* include/fuse/types.h:16 */
+#define FUSE_READY_FLAG_STRIDE 32  /* include/fuse/types.h:18 : u32 words per flag */
+
+typedef uint16_t fuse_bf16;            /* BF16 bit pattern */
+typedef struct CUstream_st* fuse_stream; /* cudaStream_t */
+
+/* include/fuse/layout/gemm.h:8-12 */
+enum { FUSE_RASTER_HEURISTIC = 0, FUSE_RASTER_ALONG_M = 1, FUSE_RASTER_ALONG_N = 2 };
+/* include/fuse/layout/gemm.h:14-17 */
+enum { FUSE_DTYPE_BF16 = 0, FUSE_DTYPE_E4M3 = 1 };
+/* include/fuse/layout/ulysses.h:14-22 */
+enum { FUSE_ROUTE_HEAD_TO_SEQUENCE = 0, FUSE_ROUTE_QKV_GQA_PACK = 2 };
+enum { FUSE_ROUTE_FORWARD = 0, FUSE_ROUTE_INVERSE = 1 };
+
+/* include/fuse/layout/gemm.h:21-25.  Strides in elements; negative = packed. */
+typedef struct fuse_matrix_stride {
+  int64_t row, column, batch;
+} fuse_matrix_stride;
+
+/* include/fuse/layout/gemm.h:27-42 (GemmProblem / GemmShape4D). */
+typedef struct fuse_gemm_problem {
+  int32_t m, n, k, l;
+  fuse_matrix_stride stride_a, stride_b, stride_d;
+  int32_t input_dtype, weight_dtype, output_dtype;
+  uint8_t transpose_a, transpose_b;
+  int32_t raster;
+  int32_t max_swizzle_size;
+} fuse_gemm_problem;
+
+/* include/fuse/layout/ulysses.h:24-63 (UlyssesRoute). */
+typedef struct fuse_ulysses_route {
+  int32_t world_size, rank, batch, global_seq, seq_local;
+  int32_t q_heads, kv_heads, local_heads, head_dim, channel_count;
+  uint8_t qkv_peer_interleaved, defer_v_a2a, causal_load_balanced, cyclic_peer_order;
+  const int32_t* packed_source_row;
+  int32_t packed_row_granularity;
+  int32_t kind;
+  int32_t direction;
+} fuse_ulysses_route;
+
+/* include/fuse/types.h:37-43 (KernelTraits). */
+typedef struct fuse_kernel_traits {
+  int32_t block_m, block_n, block_k, threads, dynamic_smem_bytes;
+} fuse_kernel_traits;
+
+/* include/fuse/operators/primitives/gemm_a2a.h:17-30 (GemmA2AParams): dense projection
+ * Y[M,N] = alpha * X[M,K] W[N,K]^T followed by the sequence->head all-to-all.  peer_output[r]
+ * is rank r's contiguous planar Q | K | V tensor ([B*S_global, q_local], [.., kv_local] x 2);
+ * peer_route_done_epoch[r] is rank r's array of world_size completion flags (one
+ * FUSE_READY_FLAG_STRIDE apart); ready has (M/block_m)*(N/block_n) flags of the same
+ * stride. */
+typedef struct fuse_gemm_a2a_params {
+  const fuse_bf16* lhs;
+  const fuse_bf16* rhs_nt;
+  fuse_bf16* local_output;
+  fuse_bf16* peer_output[FUSE_MAX_WORLD_SIZE];
+  uint32_t* peer_route_done_epoch[FUSE_MAX_WORLD_SIZE];
+  uint32_t* ready;
+  uint32_t* completion_epoch;
+  fuse_gemm_problem gemm;
+  fuse_ulysses_route route;
+  int32_t num_comm_ctas;
+  uint32_t epoch;
+  float alpha;
+} fuse_gemm_a2a_params;
+
+/* include/fuse/operators/primitives/a2a_gemm.h:47-61 (A2AGemmParams): head->sequence
+ * all-to-all producing the row-major lhs [M,K] in input_staging, then
+ * Y[M,N] = alpha * lhs W[N,K]^T.  peer_input[p] is rank p's head-sharded tensor
+ * [B*S_global, K/world]; peer_input_ready[p] (optional) is the upstream epoch word of that
+ * tensor; ready has fuse_a2a_lhs_gemm_ready_elements() words. */
+typedef struct fuse_a2a_gemm_params {
+  const fuse_bf16* peer_input[FUSE_MAX_WORLD_SIZE];
+  fuse_bf16* input_staging;
+  const uint32_t* peer_input_ready[FUSE_MAX_WORLD_SIZE];
+  fuse_bf16* rhs_nt;
+  fuse_bf16* output;
+  uint32_t* ready;
+  fuse_gemm_problem gemm;
+  fuse_ulysses_route route;
+  int32_t num_comm_ctas;
+  int32_t lhs_policy;
+  uint32_t epoch;
+  uint32_t input_epoch;
+  float alpha;
+} fuse_a2a_gemm_params;
+
+/* Additions of this implementation, all optional (pass NULL for defaults).  They have no
+ * counterpart in the reference, whose device waits are unbounded. */
+enum {
+  /* Do not wait for the peers' completion epochs (used when several ranks are emulated by
+   * consecutive launches on one GPU). */
+  FUSE_B200_SKIP_PEER_WAIT = 1u
+};
+typedef struct fuse_b200_options {
+  uint64_t wait_budget_ns; /* per-wait limit; 0 = FUSE_B200_WAIT_MS env (default 2000 ms) */
+  uint32_t flags;
+  int32_t block_n;         /* 0 = choose; 128 or 256 */
+} fuse_b200_options;
+
+/* csrc/operators/sm103/api/forward.cuh:12-14 -> detail/launch.cuh:497-625. */
+FUSE_API int fuse_launch_gemm_a2a_cutlass(const fuse_gemm_a2a_params* params, fuse_stream stream);
+FUSE_API int fuse_launch_gemm_a2a_cutlass_ex(const fuse_gemm_a2a_params* params,
+                                    const fuse_b200_options* options, fuse_stream stream);
+/* csrc/operators/sm103/api/forward.cuh:6-10 -> detail/launch.cuh:364-485. */
+FUSE_API int fuse_launch_a2a_gemm_cutlass(const fuse_a2a_gemm_params* params, fuse_stream stream);
+FUSE_API int fuse_launch_a2a_gemm_cutlass_ex(const fuse_a2a_gemm_params* params,
+                                    const fuse_b200_options* options, fuse_stream stream);
+/* include/fuse/operators/primitives/gemm_a2a.h:107-110 (launch_batched_cutlass_reference):
+ * the projection GEMM alone on (SMs - reserved_comm_ctas) CTAs; the full-SM denominator. */
+FUSE_API int fuse_launch_batched_cutlass_reference(const fuse_gemm_a2a_params* params, fuse_stream stream,
+                                          int32_t reserved_comm_ctas);
+/* include/fuse/operators/primitives/a2a_gemm.h:126-129 (launch_a2a_gemm_cutlass_reference):
+ * GEMM alone reading input_staging. */
+FUSE_API int fuse_launch_a2a_gemm_cutlass_reference(const fuse_a2a_gemm_params* params, fuse_stream stream,
+                                           int32_t reserved_comm_ctas);
+
+/* include/fuse/operators/primitives/gemm_a2a.h:59-66 (qkv_cutlass_kernel_traits): the finest
+ * publication geometry, for sizing `ready`. */
+FUSE_API void fuse_qkv_cutlass_kernel_traits(const fuse_gemm_problem* problem, fuse_kernel_traits* out);
+/* include/fuse/operators/primitives/a2a_gemm.h:86 (cutlass_kernel_traits). */
+FUSE_API void fuse_cutlass_kernel_traits(fuse_kernel_traits* out);
+/* include/fuse/operators/primitives/a2a_gemm.h:88-90. */
+FUSE_API int64_t fuse_a2a_lhs_gemm_ready_elements(const fuse_gemm_problem* problem,
+                                         const fuse_ulysses_route* route);
+/* include/fuse/operators/primitives/gemm_a2a.h:76-78 and a2a_gemm.h:92-94: communication-CTA
+ * budget chosen by the host plan (0 where no plan exists for the geometry). */
+FUSE_API int32_t fuse_recommended_gemm_a2a_comm_ctas(const fuse_gemm_problem* problem,
+                                            const fuse_ulysses_route* route);
+FUSE_API int32_t fuse_recommended_a2a_lhs_gemm_comm_ctas(const fuse_gemm_problem* problem,
+                                                const fuse_ulysses_route* route);
+
+/* Device status record of the current device (16 words; see csrc/sync.cuh).  word 0 != 0
+ * means a device-side wait gave up; `clear` resets the record.  No reference counterpart. */
+FUSE_API int fuse_b200_read_status(uint32_t out[16], int clear);
+/* sizeof of the ABI records as compiled: 0 gemm_problem, 1 ulysses_route, 2 gemm_a2a_params,
+ * 3 a2a_gemm_params, 4 kernel_traits, 5 options.  -1 for unknown ids. */
+FUSE_API int fuse_b200_abi_sizeof(int record);
+/* Number of kernels this library has launched in this process (all entry points). */
+FUSE_API uint64_t fuse_b200_launch_count(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FUSE_B200_H_ */

@@ -123,6 +123,13 @@ SYMBOLS = {
     "fuse_a2a_lhs_gemm_ready_elements": (C.c_int64, [C.POINTER(GemmProblem), C.POINTER(UlyssesRoute)]),
     "fuse_recommended_gemm_a2a_comm_ctas": (C.c_int32, [C.POINTER(GemmProblem), C.POINTER(UlyssesRoute)]),
     "fuse_recommended_a2a_lhs_gemm_comm_ctas": (C.c_int32, [C.POINTER(GemmProblem), C.POINTER(UlyssesRoute)]),
+    "fuse_b200_generate_bf16": (C.c_int, [_P, C.c_uint64, C.c_uint64, C.c_float, C.c_int, _P]),
+    "fuse_b200_tile_order_decode": (C.c_int, [C.c_int32] * 4 + [C.c_int64, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
+    "fuse_b200_select_swizzle": (C.c_int32, [C.c_int32] * 3),
+    "fuse_b200_symmetric_alloc": (C.c_int, [C.c_size_t, C.POINTER(C.c_void_p), C.c_char_p]),
+    "fuse_b200_symmetric_open": (C.c_int, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "fuse_b200_symmetric_close": (C.c_int, [C.c_void_p]),
+    "fuse_b200_symmetric_free": (C.c_int, [C.c_void_p]),
     "fuse_b200_read_status": (C.c_int, [C.POINTER(C.c_uint32 * 16), C.c_int]),
     "fuse_b200_abi_sizeof": (C.c_int, [C.c_int]),
     "fuse_b200_launch_count": (C.c_uint64, []),

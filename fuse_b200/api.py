@@ -85,3 +85,8 @@ def qkv_ready_elements(problem: GemmProblem) -> int:
     m_tiles = -(-problem.m // traits.block_m)
     n_tiles = -(-problem.n // traits.block_n)
     return m_tiles * n_tiles * N.READY_FLAG_STRIDE
+
+
+def generate_bf16(ptr: int, count: int, seed: int, scale: float, normal: bool = False, stream: int = 0) -> int:
+    """Seeded device-side fill (uniform, or N(0, scale^2) when `normal`)."""
+    return N.lib().fuse_b200_generate_bf16(ptr, count, seed, scale, 1 if normal else 0, stream)

@@ -4,6 +4,7 @@
 #include <mutex>
 
 #include "fuse_b200.h"
+#include "tile_order.cuh"
 
 namespace fuse_b200 {
 
@@ -118,6 +119,24 @@ int fuse_b200_read_status(uint32_t out[16], int clear) {
   if (status != cudaSuccess) return int(status);
   if (clear) status = cudaMemset(info.status, 0, sizeof(uint32_t) * fuse_b200::kStatusWords);
   return int(status);
+}
+
+int fuse_b200_tile_order_decode(int32_t m_tiles, int32_t n_tiles, int32_t swizzle, int32_t along_n,
+                                int64_t linear, int32_t* m, int32_t* n) {
+  if (m_tiles <= 0 || n_tiles <= 0 || (swizzle != 1 && swizzle != 2 && swizzle != 4 && swizzle != 8) ||
+      linear < 0 || linear >= int64_t(m_tiles) * n_tiles || m == nullptr || n == nullptr)
+    return 1;
+  fuse_b200::TileOrder order;
+  order.m_tiles = m_tiles;
+  order.n_tiles = n_tiles;
+  order.swizzle = swizzle;
+  order.along_n = along_n ? 1 : 0;
+  order.decode(linear, *m, *n);
+  return order.linear(*m, *n) == linear ? 0 : 1;
+}
+
+int32_t fuse_b200_select_swizzle(int32_t max_swizzle, int32_t m_tiles, int32_t n_tiles) {
+  return fuse_b200::select_swizzle(max_swizzle, m_tiles, n_tiles);
 }
 
 uint64_t fuse_b200_launch_count(void) { return fuse_b200::host::g_launch_count.load(); }

@@ -164,6 +164,30 @@ FUSE_API int32_t fuse_recommended_gemm_a2a_comm_ctas(const fuse_gemm_problem* pr
 FUSE_API int32_t fuse_recommended_a2a_lhs_gemm_comm_ctas(const fuse_gemm_problem* problem,
                                                 const fuse_ulysses_route* route);
 
+/* The static tile order shared by compute and communication CTAs: linear index -> (m, n) tile
+ * for a grid of m_tiles x n_tiles, swizzle in {1,2,4,8}, along_n = 0 (index runs down M inside
+ * bands of `swizzle` N tiles) or 1 (transpose).  Same knobs as the reference scheduler
+ * (csrc/operators/sm103/detail/persistent_gemm.cuh:27-182); returns 0, or 1 for bad input. */
+FUSE_API int fuse_b200_tile_order_decode(int32_t m_tiles, int32_t n_tiles, int32_t swizzle, int32_t along_n,
+                                int64_t linear, int32_t* m, int32_t* n);
+/* benchmarks/sm103/fused_bf16.cu:196-206: swizzle actually used for a cap and a tile grid. */
+FUSE_API int32_t fuse_b200_select_swizzle(int32_t max_swizzle, int32_t m_tiles, int32_t n_tiles);
+
+/* Fills `count` BF16 values on the device from a seed: uniform in [-scale, scale) with the
+ * reference harness's Philox4x32-10 element mapping and word->value map
+ * (benchmarks/sm103/fused_inputs.cuh:22-29,117-141), or N(0, scale^2) when `normal` != 0. */
+FUSE_API int fuse_b200_generate_bf16(fuse_bf16* out, uint64_t count, uint64_t seed, float scale, int normal,
+                            fuse_stream stream);
+
+/* Symmetric buffers for one-process-per-GPU ranks (harness helpers, not on the launch path;
+ * the reference's harness does the same with cudaIpc*: benchmarks/sm103/fused_bf16.cu:1080-1139).
+ * alloc: zero-filled cudaMalloc + 64-byte IPC handle; open: map a peer's handle (peer access is
+ * enabled lazily); close / free undo them. */
+FUSE_API int fuse_b200_symmetric_alloc(size_t bytes, void** ptr, unsigned char handle[64]);
+FUSE_API int fuse_b200_symmetric_open(const unsigned char handle[64], void** ptr);
+FUSE_API int fuse_b200_symmetric_close(void* ptr);
+FUSE_API int fuse_b200_symmetric_free(void* ptr);
+
 /* Device status record of the current device (16 words; see csrc/sync.cuh).  word 0 != 0
  * means a device-side wait gave up; `clear` resets the record.  No reference counterpart. */
 FUSE_API int fuse_b200_read_status(uint32_t out[16], int clear);

@@ -1,0 +1,100 @@
+"""GPU-side helpers for the parity tests: move BF16 bit patterns to the device, drive the
+operators through the C ABI (fuse_b200.api), bring results back as numpy bit patterns.
+
+Several ranks are emulated on ONE GPU by launching each rank's kernel in turn on one stream
+with all `peer_*` pointers aimed at buffers of the same device; the cross-rank completion wait
+is skipped (FUSE_B200_SKIP_PEER_WAIT) because later launches play the peers."""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from fuse_b200 import _native as N
+from fuse_b200 import api
+
+DEV = "cuda:0"
+POISON = 0xFFFF  # BF16 NaN pattern: outputs are poisoned before every run
+
+
+def to_device(bits: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(np.ascontiguousarray(bits).view(np.int16)).to(DEV).view(torch.bfloat16)
+
+
+def to_bits(t: torch.Tensor) -> np.ndarray:
+    return t.detach().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def poisoned(*shape) -> torch.Tensor:
+    return torch.full(shape, -1, dtype=torch.int16, device=DEV).view(torch.bfloat16)
+
+
+def options(wait_ms: float = 500.0, flags: int = 0, block_n: int = 0) -> N.Options:
+    o = N.Options()
+    o.wait_budget_ns = int(wait_ms * 1e6)
+    o.flags = flags
+    o.block_n = block_n
+    return o
+
+
+def check_status():
+    torch.cuda.synchronize()
+    status = api.read_status(clear=True)
+    assert status[0] == 0, f"device wait gave up: {status[:8]}"
+
+
+def qkv_forward(world, batch, seq_local, q_heads, kv_heads, head_dim, lhs_bits, w_bits, comm=4,
+                alpha=1.0, raster=N.RASTER_HEURISTIC, swizzle=4, block_n=0, epochs=1):
+    """Runs every rank of the QKV operator.  Returns (local_outputs, peer_outputs) as bits."""
+    m = batch * seq_local
+    n = (q_heads + 2 * kv_heads) * head_dim
+    k = w_bits.shape[1]
+    rows = batch * seq_local * world
+    w = to_device(w_bits)
+    xs = [to_device(x) for x in lhs_bits]
+    problem = N.GemmProblem(m, n, k, raster=raster, max_swizzle_size=swizzle)
+    local = [poisoned(m, n) for _ in range(world)]
+    peer = [poisoned(rows * n // world) for _ in range(world)]
+    done = [torch.zeros(world * N.READY_FLAG_STRIDE, dtype=torch.int32, device=DEV) for _ in range(world)]
+    ready = [torch.zeros(api.qkv_ready_elements(problem), dtype=torch.int32, device=DEV) for _ in range(world)]
+    opts = options(flags=N.SKIP_PEER_WAIT if world > 1 else 0, block_n=block_n)
+    for epoch in range(1, epochs + 1):
+        for r in range(world):
+            route = N.UlyssesRoute(world_size=world, rank=r, batch=batch, global_seq=seq_local * world,
+                                   seq_local=seq_local, q_heads=q_heads, kv_heads=kv_heads,
+                                   head_dim=head_dim, kind=N.ROUTE_QKV_GQA_PACK)
+            p = N.GemmA2AParams(lhs=xs[r].data_ptr(), rhs_nt=w.data_ptr(), local_output=local[r].data_ptr(),
+                                ready=ready[r].data_ptr(), gemm=problem, route=route, num_comm_ctas=comm,
+                                epoch=epoch, alpha=alpha)
+            for peer_rank in range(world):
+                p.peer_output[peer_rank] = peer[peer_rank].data_ptr()
+                p.peer_route_done_epoch[peer_rank] = done[peer_rank].data_ptr()
+            rc = api.launch_gemm_a2a_cutlass(p, 0, opts)
+            assert rc == 0, f"launch_gemm_a2a_cutlass -> cudaError {rc}"
+    check_status()
+    for d in done:  # every source told every destination
+        assert (d[::N.READY_FLAG_STRIDE][:world] == epochs).all()
+    return [to_bits(t) for t in local], [to_bits(t) for t in peer]
+
+
+def oproj_forward(world, rank, batch, seq_local, peer_bits, w_bits, comm=4, causal=False, cyclic=False,
+                  alpha=1.0, raster=N.RASTER_HEURISTIC, swizzle=8, block_n=0):
+    """Runs one rank of the output-projection operator.  Returns (staging, output) bits."""
+    n, k = w_bits.shape
+    m = batch * seq_local
+    w = to_device(w_bits)
+    peers = [to_device(x) for x in peer_bits]
+    staging, out = poisoned(m, k), poisoned(m, n)
+    problem = N.GemmProblem(m, n, k, raster=raster, max_swizzle_size=swizzle)
+    route = N.UlyssesRoute(world_size=world, rank=rank, batch=batch, global_seq=seq_local * world,
+                           seq_local=seq_local, kind=N.ROUTE_HEAD_TO_SEQUENCE, direction=N.ROUTE_INVERSE,
+                           causal_load_balanced=int(causal), cyclic_peer_order=int(cyclic))
+    ready = torch.zeros(api.a2a_lhs_gemm_ready_elements(problem, route), dtype=torch.int32, device=DEV)
+    p = N.A2AGemmParams(input_staging=staging.data_ptr(), rhs_nt=w.data_ptr(), output=out.data_ptr(),
+                        ready=ready.data_ptr(), gemm=problem, route=route, num_comm_ctas=comm, epoch=1,
+                        alpha=alpha)
+    for q in range(world):
+        p.peer_input[q] = peers[q].data_ptr()
+    rc = api.launch_a2a_gemm_cutlass(p, 0, options(block_n=block_n))
+    assert rc == 0, f"launch_a2a_gemm_cutlass -> cudaError {rc}"
+    check_status()
+    return to_bits(staging), to_bits(out)

@@ -1,0 +1,120 @@
+"""CPU-side checks of the drop-in boundary: the library loads, exports every symbol that
+include/fuse_b200.h declares, its records have the layout the binding assumes, the launch
+entry points reject bad parameters with the reference's error codes before touching a device,
+and the host-side tile order is a bijection."""
+import ctypes as C
+import os
+import re
+
+import numpy as np
+
+from fuse_b200 import _native as N
+from fuse_b200 import api, synthetic
+from oracle import oracle as O
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "fuse_b200.h")).read()
+    return sorted(set(re.findall(r"FUSE_API\s+[\w\s\*]+?\b(fuse_\w+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    names = declared_symbols()
+    assert len(names) >= 14
+    handle = C.CDLL(N.LIB_PATH)
+    for name in names:
+        assert hasattr(handle, name), name
+    assert set(names) == set(N.SYMBOLS), set(names) ^ set(N.SYMBOLS)
+
+
+def test_record_layouts_match_the_compiled_library():
+    lib = N.lib()
+    for record, cls in N.ABI_RECORDS.items():
+        assert lib.fuse_b200_abi_sizeof(record) == C.sizeof(cls), cls.__name__
+    assert lib.fuse_b200_abi_sizeof(99) == -1
+    # Offsets the reference's C++ records have (include/fuse/layout/gemm.h:27-42,
+    # include/fuse/layout/ulysses.h:24-63 under the Itanium ABI).
+    assert N.GemmProblem.raster.offset == 104 and N.GemmProblem.transpose_a.offset == 100
+    assert N.UlyssesRoute.packed_source_row.offset == 48 and N.UlyssesRoute.kind.offset == 60
+    assert N.GemmA2AParams.gemm.offset == 168 and N.GemmA2AParams.num_comm_ctas.offset == 352
+    assert N.A2AGemmParams.gemm.offset == 160 and N.A2AGemmParams.alpha.offset == 360
+
+
+def test_parameter_validation_without_a_device():
+    # csrc/operators/sm103/detail/launch.cuh:508-511: epoch 0, no communication CTAs, a
+    # non-finite alpha or an unsupported problem are cudaErrorInvalidValue.
+    good = N.GemmProblem(256, 384, 64)
+    p = N.GemmA2AParams(gemm=good, num_comm_ctas=4, epoch=0)
+    assert api.launch_gemm_a2a_cutlass(p) == N.CUDA_ERROR_INVALID_VALUE
+    p = N.GemmA2AParams(gemm=good, num_comm_ctas=0, epoch=1)
+    assert api.launch_gemm_a2a_cutlass(p) == N.CUDA_ERROR_INVALID_VALUE
+    p = N.GemmA2AParams(gemm=good, num_comm_ctas=4, epoch=1, alpha=float("inf"))
+    assert api.launch_gemm_a2a_cutlass(p) == N.CUDA_ERROR_INVALID_VALUE
+    for bad in (N.GemmProblem(0, 384, 64), N.GemmProblem(256, 384, 60), N.GemmProblem(256, 384, 64, max_swizzle_size=3),
+                N.GemmProblem(256, 384, 64, transpose_b=1), N.GemmProblem(256, 384, 64, input_dtype=N.DTYPE_E4M3)):
+        p = N.GemmA2AParams(gemm=bad, num_comm_ctas=4, epoch=1)
+        assert api.launch_gemm_a2a_cutlass(p) == N.CUDA_ERROR_INVALID_VALUE
+        q = N.A2AGemmParams(gemm=bad, num_comm_ctas=4, epoch=1)
+        assert api.launch_a2a_gemm_cutlass(q) == N.CUDA_ERROR_INVALID_VALUE
+    q = N.A2AGemmParams(gemm=good, num_comm_ctas=4, epoch=1, lhs_policy=2)
+    assert api.launch_a2a_gemm_cutlass(q) == N.CUDA_ERROR_INVALID_VALUE
+    assert N.lib().fuse_launch_gemm_a2a_cutlass(None, None) == N.CUDA_ERROR_INVALID_VALUE
+
+
+def test_ready_sizes():
+    prob = N.GemmProblem(16384, 6144, 4096)
+    traits = api.qkv_cutlass_kernel_traits(prob)
+    assert (traits.block_m, traits.threads) == (128, 256) and traits.block_n in (64, 128)
+    assert api.qkv_ready_elements(prob) == 128 * (6144 // traits.block_n) * 32
+    route = N.UlyssesRoute(world_size=8)
+    assert api.a2a_lhs_gemm_ready_elements(N.GemmProblem(16384, 4096, 4096), route) == 128 * 8 * 32
+    assert api.a2a_lhs_gemm_ready_elements(N.GemmProblem(130, 4096, 4096), route) == 2 * 8 * 32
+
+
+def test_tile_order_is_a_bijection_and_bands_are_compact():
+    lib = N.lib()
+    for (mt, nt) in [(1, 1), (7, 5), (128, 24), (16, 3), (3, 16), (9, 9)]:
+        for swizzle in (1, 2, 4, 8):
+            for along_n in (0, 1):
+                seen = set()
+                prev = None
+                for linear in range(mt * nt):
+                    m, n = C.c_int32(), C.c_int32()
+                    assert lib.fuse_b200_tile_order_decode(mt, nt, swizzle, along_n, linear, C.byref(m), C.byref(n)) == 0
+                    assert 0 <= m.value < mt and 0 <= n.value < nt
+                    seen.add((m.value, n.value))
+                    minor = m.value if along_n else n.value
+                    if prev is not None:  # the banded axis never moves backwards by more than a band
+                        assert minor // swizzle >= prev // swizzle
+                    prev = minor
+                assert len(seen) == mt * nt
+    m, n = C.c_int32(), C.c_int32()
+    assert lib.fuse_b200_tile_order_decode(4, 4, 3, 0, 0, C.byref(m), C.byref(n)) == 1
+    assert lib.fuse_b200_tile_order_decode(4, 4, 2, 0, 16, C.byref(m), C.byref(n)) == 1
+
+
+def test_swizzle_selection_matches_oracle():
+    for cap in (1, 2, 4, 8):
+        for mt in (1, 2, 3, 5, 6, 40):
+            for nt in (1, 2, 3, 5, 6, 40):
+                assert N.lib().fuse_b200_select_swizzle(cap, mt, nt) == O.lib().fo_swizzle_size(cap, mt, nt)
+
+
+def test_philox_known_answers_and_value_map():
+    kat = [((0, 0, 0, 0), (0, 0), (0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8)),
+           ((0xffffffff,) * 4, (0xffffffff,) * 2, (0x408f276d, 0x41c83b0e, 0xa20bc7c6, 0x6d5451fd)),
+           ((0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344), (0xa4093822, 0x299f31d0),
+            (0xd16cfe09, 0x94fdcceb, 0x5001e420, 0x24126ea1))]
+    for counter, key, want in kat:
+        got = synthetic.philox4x32_10(np.array([counter], dtype=np.uint32), np.array(key, dtype=np.uint32))[0]
+        assert tuple(int(x) for x in got) == want
+    words = synthetic.random_words(70000, 1234)
+    assert np.array_equal(words[:100], synthetic.random_words(100, 1234))  # prefix stable
+    vals = synthetic.uniform_bf16((70000,), 1234, 0.125)
+    expect = np.array([O.lib().fo_f32_to_bf16(O.lib().fo_uniform_value(int(w), 0.125)) for w in words[:2000]],
+                      dtype=np.uint16)
+    assert np.array_equal(vals[:2000], expect)
+    z = synthetic.bf16_bits_to_f32(synthetic.normal_bf16((1 << 16,), 5, 0.02))
+    assert abs(z.mean()) < 5e-4 and abs(z.std() - 0.02) < 5e-4

@@ -248,9 +248,12 @@ def run_gpu_arm(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    qkv_options = N.Options()
+    qkv_options.flags = N.QKV_ROUTE_DIRECT if args.qkv_route == "direct" else N.QKV_ROUTE_COMM_CTAS
+
     def launch_qkv():
         qkv.epoch = epoch[0]
-        rc = api.launch_gemm_a2a_cutlass(qkv, stream.cuda_stream)
+        rc = api.launch_gemm_a2a_cutlass(qkv, stream.cuda_stream, qkv_options)
         if rc:
             raise RuntimeError(f"launch_gemm_a2a_cutlass -> cudaError {rc}")
 
@@ -371,14 +374,15 @@ def run_gpu_arm(args):
             "per_gpu": FLOPS_PER_RANK / (ms_per_step * 1e-3) / 1e15,
             "kernels": {
                 "qkv_gemm_a2a": {"ms": qkv_ms, "pflops_per_gpu": QKV_FLOPS / (qkv_ms * 1e-3) / 1e15,
-                                 "comm_ctas": args.qkv_comm},
+                                 "route": args.qkv_route,
+                                 "comm_ctas": args.qkv_comm if args.qkv_route == "comm" else 0},
                 "a2a_oproj_gemm": {"ms": oproj_ms,
                                    "pflops_per_gpu": (FLOPS_PER_RANK - QKV_FLOPS) / (oproj_ms * 1e-3) / 1e15,
                                    "comm_ctas": args.oproj_comm},
             },
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak, "traffic": QKV_DRAM_TRAFFIC_BYTES,
-                         "kernel": "fused_gemm_kernel<256,4,QkvPush> (QKVProj GEMM -> A2A)",
+                         "kernel": "fused_gemm_kernel<256,4,%s> (QKVProj GEMM -> A2A)" % ("QkvDirect" if args.qkv_route == "direct" else "QkvPush"),
                          "peak_source": peak_source},
             "e2e": {"value": FLOPS_PER_RANK * world_size / (e2e_ms * 1e-3) / 1e15, "unit": "PFLOPS",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
@@ -417,6 +421,8 @@ def main():
     parser.add_argument("--qkv-comm", type=int, default=16)
     parser.add_argument("--oproj-comm", type=int, default=16)
     parser.add_argument("--swizzle", type=int, default=8)
+    parser.add_argument("--qkv-route", default="direct", choices=["comm", "direct"],
+                        help="QKV routing from communication CTAs or from the GEMM epilogue")
     parser.add_argument("--e2e-steps", type=int, default=5)
     parser.add_argument("--cpu-rows", type=int, default=1024)
     parser.add_argument("--skip-cpu", action="store_true")

@@ -18,6 +18,8 @@ DTYPE_BF16, DTYPE_E4M3 = 0, 1
 ROUTE_HEAD_TO_SEQUENCE, ROUTE_QKV_GQA_PACK = 0, 2
 ROUTE_FORWARD, ROUTE_INVERSE = 0, 1
 SKIP_PEER_WAIT = 1
+QKV_ROUTE_COMM_CTAS = 2
+QKV_ROUTE_DIRECT = 4
 
 CUDA_SUCCESS = 0
 CUDA_ERROR_INVALID_VALUE = 1

@@ -94,6 +94,20 @@ cudaError_t check_device(DeviceInfo* info) {
   return info->cc_major == 10 ? cudaSuccess : cudaErrorNotSupported;
 }
 
+// How the routed output leaves the SM: from communication CTAs that copy published tiles
+// (the reference's structure, `num_comm_ctas` of them), or straight from the GEMM epilogue of
+// every compute CTA ("direct", all SMs compute).  Option flag first, then the environment
+// variable FUSE_B200_QKV_ROUTE = comm | direct (read on every launch, like the reference's
+// FUSE_QKV_GEMM_POLICY: csrc/operators/sm103/detail/launch.cuh:165-195).
+bool qkv_direct_push(const fuse_b200_options* options) {
+  if (options != nullptr && (options->flags & FUSE_B200_QKV_ROUTE_COMM_CTAS)) return false;
+  if (options != nullptr && (options->flags & FUSE_B200_QKV_ROUTE_DIRECT)) return true;
+  const char* text = std::getenv("FUSE_B200_QKV_ROUTE");
+  if (text != nullptr && std::strcmp(text, "comm") == 0) return false;
+  if (text != nullptr && std::strcmp(text, "direct") == 0) return true;
+  return false;
+}
+
 // detail/gemm_a2a.cuh:237-299 (can_implement) for the plain QKV GQA pack route.
 cudaError_t check_qkv_route(const fuse_gemm_a2a_params& p) {
   const fuse_ulysses_route& r = p.route;
@@ -130,6 +144,7 @@ cudaError_t qkv_forward(const fuse_gemm_a2a_params& p, const fuse_b200_options* 
   if (status != cudaSuccess) return status;
   if (p.num_comm_ctas >= info.sm_count) return cudaErrorInvalidValue;
   if ((status = check_qkv_route(p)) != cudaSuccess) return status;
+  const bool direct = qkv_direct_push(options);
 
   const int block_n = choose_block_n(p.gemm, options);
   Operands maps;
@@ -138,7 +153,8 @@ cudaError_t qkv_forward(const fuse_gemm_a2a_params& p, const fuse_b200_options* 
   if (status != cudaSuccess) return status;
 
   FusedParams k{};
-  fill_core(&k, p.gemm, block_n, p.num_comm_ctas, p.alpha, p.local_output, FUSE_RASTER_ALONG_M);
+  fill_core(&k, p.gemm, block_n, direct ? 0 : p.num_comm_ctas, p.alpha, p.local_output,
+            FUSE_RASTER_ALONG_M);
   k.ready = p.ready;
   k.flags = options ? options->flags : 0u;
   k.wait = host::make_wait(info, p.epoch, options ? options->wait_budget_ns : 0);
@@ -154,6 +170,7 @@ cudaError_t qkv_forward(const fuse_gemm_a2a_params& p, const fuse_b200_options* 
     k.qkv.peer_output[peer] = p.peer_output[peer];
     k.qkv.peer_done[peer] = p.peer_route_done_epoch[peer];
   }
+  if (direct) return launch_mode<kModeQkvDirect>(maps, k, block_n, info, stream);
   return launch_mode<kModeQkvPush>(maps, k, block_n, info, stream);
 }
 

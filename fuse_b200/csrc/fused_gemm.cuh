@@ -41,6 +41,8 @@ enum FusedMode : int {
   kModePlain = 0,     // GEMM only
   kModeQkvPush = 1,   // GEMM -> publish tiles -> comm CTAs push to peers' planar Q|K|V
   kModeLhsPull = 2,   // comm CTAs pull the lhs shards from peers -> gated GEMM
+  kModeQkvDirect = 3, // GEMM whose epilogue stores each vector to local_output AND to its place
+                      // in the owning peer's planar Q|K|V; no communication CTAs, no tile flags
 };
 
 enum LaunchFlags : uint32_t {
@@ -89,7 +91,11 @@ struct SmemLayout {
   static constexpr uint32_t kBarrierOffset = kStages * kStageBytes;
   static constexpr uint32_t kNumBarriers = 2 * kStages + 2 * kAccumStages;
   static constexpr uint32_t kTmemSlotOffset = kBarrierOffset + kNumBarriers * 8;
-  static constexpr uint32_t kBytes = kTmemSlotOffset + 16;
+  // Two per-tile route tables (column chunk -> destination base pointer, row pitch) used by
+  // the direct-push epilogue, double-buffered by tile parity.
+  static constexpr uint32_t kRouteTableOffset = kTmemSlotOffset + 16;
+  static constexpr uint32_t kRouteTableBytes = 2 * (kBlockN / 8) * 16;
+  static constexpr uint32_t kBytes = kRouteTableOffset + kRouteTableBytes;
   // + 1024 so the kernel can align the base itself; total is above half of the SM's shared
   // memory, which pins residency at exactly one CTA per SM.
   static constexpr uint32_t kDynamicBytes = kBytes + 1024;
@@ -114,6 +120,25 @@ __device__ __forceinline__ int64_t global_row(int32_t world, int32_t rank, int32
   return int64_t(batch) * global_seq + int64_t(rank) * seq_local + seq;
 }
 
+// Destination of one 8-column chunk of the packed QKV feature axis: base pointer of row 0 in
+// the owning rank's planar Q | K | V tensor and that tensor's row pitch
+// (include/fuse/layout/ulysses.h:77-107; csrc/operators/sm103/detail/gemm_a2a.cuh:190-215).
+__device__ __forceinline__ void qkv_chunk_destination(const QkvRoute& r, int32_t feature,
+                                                      uint16_t*& base, int64_t& stride) {
+  const int64_t rows_total = int64_t(r.batch) * r.global_seq;
+  const int32_t q_width = r.q_heads * r.head_dim, kv_width = r.kv_heads * r.head_dim;
+  const int32_t q_local = q_width / r.world, kv_local = kv_width / r.world;
+  const int32_t segment = feature < q_width ? 0 : (feature < q_width + kv_width ? 1 : 2);
+  const int32_t within = feature - (segment == 0 ? 0 : q_width + (segment == 2 ? kv_width : 0));
+  const int32_t local_width = segment == 0 ? q_local : kv_local;
+  const int32_t owner = within / local_width;
+  const int32_t local_col = within - owner * local_width;
+  const int64_t segment_base =
+      segment == 0 ? 0 : rows_total * q_local + (segment == 2 ? rows_total * kv_local : 0);
+  base = r.peer_output[owner] + segment_base + local_col;
+  stride = local_width;
+}
+
 // ------------------------------------------------------------------------------------------
 // Communication role: forward QKV push.
 //
@@ -134,9 +159,6 @@ __device__ __forceinline__ void qkv_push_role(const FusedParams& p, uint8_t* sme
   const QkvRoute& r = p.qkv;
   const int tid = threadIdx.x;
   const int64_t tiles = p.order.count();
-  const int64_t rows_total = int64_t(r.batch) * r.global_seq;
-  const int32_t q_width = r.q_heads * r.head_dim, kv_width = r.kv_heads * r.head_dim;
-  const int32_t q_local = q_width / r.world, kv_local = kv_width / r.world;
 
   for (int64_t t = blockIdx.x; t < tiles; t += p.num_comm_ctas) {
     int32_t mt, nt;
@@ -147,17 +169,7 @@ __device__ __forceinline__ void qkv_push_role(const FusedParams& p, uint8_t* sme
       const int32_t feature = n0 + tid * 8;
       uint16_t* base = nullptr;
       int64_t stride = 0;
-      if (feature < p.n) {
-        const int32_t segment = feature < q_width ? 0 : (feature < q_width + kv_width ? 1 : 2);
-        const int32_t within = feature - (segment == 0 ? 0 : q_width + (segment == 2 ? kv_width : 0));
-        const int32_t local_width = segment == 0 ? q_local : kv_local;
-        const int32_t owner = within / local_width;
-        const int32_t local_col = within - owner * local_width;
-        const int64_t segment_base =
-            segment == 0 ? 0 : rows_total * q_local + (segment == 2 ? rows_total * kv_local : 0);
-        base = r.peer_output[owner] + segment_base + local_col;
-        stride = local_width;
-      }
+      if (feature < p.n) qkv_chunk_destination(r, feature, base, stride);
       col_base[tid] = base;
       col_stride[tid] = stride;
     } else if (tid >= 128) {
@@ -299,8 +311,17 @@ __device__ __forceinline__ void lhs_pull_role(const FusedParams& p, uint8_t* sme
 
 // 32 FP32 accumulators of one output row -> alpha (and beta * old D) -> BF16 -> four 16-byte
 // stores.  `col` is the global column of acc[0]; vectors past N are skipped (N % 8 == 0).
+struct PeerRow {
+  uint16_t* const* col_base;   // per 8-column chunk of the tile: destination base (row 0)
+  const int64_t* col_stride;   // per chunk: destination row pitch in elements
+  int64_t dest_row;            // destination row of this thread's output row
+  int32_t chunk0;              // chunk index of acc[0] inside the tile
+};
+
+template <bool kPushToPeer>
 __device__ __forceinline__ void store_accumulators(const uint32_t (&acc)[32], uint16_t* dst,
-                                                   int32_t col, bool row_ok, const FusedParams& p) {
+                                                   int32_t col, bool row_ok, const FusedParams& p,
+                                                   const PeerRow& peer) {
 #pragma unroll
   for (int v = 0; v < 4; ++v) {
     if (row_ok && col + v * 8 < p.n) {
@@ -328,6 +349,10 @@ __device__ __forceinline__ void store_accumulators(const uint32_t (&acc)[32], ui
       pair = __floats2bfloat162_rn(f[6], f[7]);
       out.w = *reinterpret_cast<const uint32_t*>(&pair);
       ptx::st_v4(dst + v * 8, out);
+      if constexpr (kPushToPeer) {
+        uint16_t* base = peer.col_base[peer.chunk0 + v];
+        ptx::st_v4(base + peer.dest_row * peer.col_stride[peer.chunk0 + v], out);
+      }
     }
   }
 }
@@ -473,9 +498,33 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       const int epi_tid = threadIdx.x - 128;
       uint32_t accum = 0, accum_phase = 0;
       bool ok = true;
+      constexpr bool kDirect = kMode == kModeQkvDirect;
+      constexpr int kChunks = kBlockN / 8;
+      uint32_t table = 0;  // which of the two route tables this tile uses
       for (int64_t t = compute_id; ok && t < tiles; t += compute_ctas) {
         int32_t mt, nt;
         p.order.decode(t, mt, nt);
+        PeerRow peer{};
+        if constexpr (kDirect) {
+          uint16_t** col_base =
+              reinterpret_cast<uint16_t**>(smem + Layout::kRouteTableOffset + table * kChunks * 16);
+          int64_t* col_stride = reinterpret_cast<int64_t*>(col_base + kChunks);
+          if (epi_tid < kChunks) {
+            const int32_t feature = nt * kBlockN + epi_tid * 8;
+            uint16_t* base = nullptr;
+            int64_t stride = 0;
+            if (feature < p.n) qkv_chunk_destination(p.qkv, feature, base, stride);
+            col_base[epi_tid] = base;
+            col_stride[epi_tid] = stride;
+          }
+          peer.col_base = col_base;
+          peer.col_stride = col_stride;
+          const int32_t local_row = mt * kBlockM + quarter * 32 + lane;
+          peer.dest_row = local_row < p.m ? global_row(p.qkv.world, p.qkv.rank, p.qkv.seq_local,
+                                                       p.qkv.global_seq, false, local_row)
+                                          : 0;
+          table ^= 1u;
+        }
         ok = mbar_wait(tmem_full_bar(accum), accum_phase, p.wait, kSiteTmemFull);
         // The four epilogue warps leave together or not at all (they share a named barrier).
         ok = ptx::named_bar_all(2, kEpilogueThreads, ok);
@@ -496,8 +545,10 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ptx::tc_fence_before();
             ptx::mbar_arrive(tmem_empty_bar(accum));
           }
-          store_accumulators(acc0, d_row + c, nt * kBlockN + c, row_ok, p);
-          store_accumulators(acc1, d_row + c + 32, nt * kBlockN + c + 32, row_ok, p);
+          peer.chunk0 = c / 8;
+          store_accumulators<kDirect>(acc0, d_row + c, nt * kBlockN + c, row_ok, p, peer);
+          peer.chunk0 = c / 8 + 4;
+          store_accumulators<kDirect>(acc1, d_row + c + 32, nt * kBlockN + c + 32, row_ok, p, peer);
         }
         if constexpr (kMode == kModeQkvPush) {
           // Publish the tile: all 128 epilogue threads' stores, then one release at GPU scope
@@ -513,6 +564,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       }
     }
 
+    if constexpr (kMode == kModeQkvDirect) __threadfence_system();  // peer stores performed
     ptx::tc_fence_before();
     __syncthreads();
     if (warp == 2) {
@@ -521,7 +573,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   }
 
-  if constexpr (kMode == kModeQkvPush) {
+  if constexpr (kMode == kModeQkvPush || kMode == kModeQkvDirect) {
     cooperative_groups::this_grid().sync();
     qkv_finalize(p);
   }

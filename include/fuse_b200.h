@@ -124,7 +124,12 @@ typedef struct fuse_a2a_gemm_params {
 enum {
   /* Do not wait for the peers' completion epochs (used when several ranks are emulated by
    * consecutive launches on one GPU). */
-  FUSE_B200_SKIP_PEER_WAIT = 1u
+  FUSE_B200_SKIP_PEER_WAIT = 1u,
+  /* QKV operator: route the output from communication CTAs (the reference's structure) or
+   * straight from every compute CTA's epilogue (num_comm_ctas then only has to be valid).
+   * Neither flag: environment variable FUSE_B200_QKV_ROUTE = comm | direct, else comm. */
+  FUSE_B200_QKV_ROUTE_COMM_CTAS = 2u,
+  FUSE_B200_QKV_ROUTE_DIRECT = 4u
 };
 typedef struct fuse_b200_options {
   uint64_t wait_budget_ns; /* per-wait limit; 0 = FUSE_B200_WAIT_MS env (default 2000 ms) */

@@ -43,8 +43,8 @@ def check_status():
 
 
 def qkv_forward(world, batch, seq_local, q_heads, kv_heads, head_dim, lhs_bits, w_bits, comm=4,
-                alpha=1.0, raster=N.RASTER_HEURISTIC, swizzle=4, block_n=0, epochs=1):
-    """Runs every rank of the QKV operator.  Returns (local_outputs, peer_outputs) as bits."""
+                alpha=1.0, raster=N.RASTER_HEURISTIC, swizzle=4, block_n=0, epochs=1, route="comm"):
+    """Runs every rank of the QKV operator (route: "comm" CTAs or "direct" epilogue push).  Returns (local_outputs, peer_outputs) as bits."""
     m = batch * seq_local
     n = (q_heads + 2 * kv_heads) * head_dim
     k = w_bits.shape[1]
@@ -56,7 +56,8 @@ def qkv_forward(world, batch, seq_local, q_heads, kv_heads, head_dim, lhs_bits, 
     peer = [poisoned(rows * n // world) for _ in range(world)]
     done = [torch.zeros(world * N.READY_FLAG_STRIDE, dtype=torch.int32, device=DEV) for _ in range(world)]
     ready = [torch.zeros(api.qkv_ready_elements(problem), dtype=torch.int32, device=DEV) for _ in range(world)]
-    opts = options(flags=N.SKIP_PEER_WAIT if world > 1 else 0, block_n=block_n)
+    route_flag = N.QKV_ROUTE_DIRECT if route == "direct" else N.QKV_ROUTE_COMM_CTAS
+    opts = options(flags=(N.SKIP_PEER_WAIT if world > 1 else 0) | route_flag, block_n=block_n)
     for epoch in range(1, epochs + 1):
         for r in range(world):
             route = N.UlyssesRoute(world_size=world, rank=r, batch=batch, global_seq=seq_local * world,

@@ -38,13 +38,14 @@ QKV_CASES = [
 ]
 
 
+@pytest.mark.parametrize("route", ["comm", "direct"])
 @pytest.mark.parametrize("case", QKV_CASES)
-def test_qkv_forward_matches_oracle(case):
+def test_qkv_forward_matches_oracle(case, route):
     from tests import harness as H
     world, batch, s, q, kv, d, k, comm = case
     m, n = batch * s, (q + 2 * kv) * d
     lhs, w = _inputs(world, m, k, n)
-    local, peers = H.qkv_forward(world, batch, s, q, kv, d, lhs, w, comm=comm)
+    local, peers = H.qkv_forward(world, batch, s, q, kv, d, lhs, w, comm=comm, route=route)
     want_local, want_peers = O.qkv_forward(world, batch, s, q, kv, d, lhs, w)
     for r in range(world):
         _assert_close(local[r], want_local[r], f"local_output[{r}]")
@@ -83,10 +84,11 @@ def test_qkv_forward_knobs_do_not_change_results(raster, swizzle, block_n):
     m, n = batch * s, (q + 2 * kv) * d
     lhs, w = _inputs(world, m, k, n)
     base_local, base_peers = H.qkv_forward(world, batch, s, q, kv, d, lhs, w, comm=4)
-    local, peers = H.qkv_forward(world, batch, s, q, kv, d, lhs, w, comm=7, raster=raster, swizzle=swizzle,
-                                 block_n=block_n)
-    for r in range(world):  # same K order per element => identical bits whatever the schedule
-        assert np.array_equal(local[r], base_local[r]) and np.array_equal(peers[r], base_peers[r])
+    for route in ("comm", "direct"):
+        local, peers = H.qkv_forward(world, batch, s, q, kv, d, lhs, w, comm=7, raster=raster, swizzle=swizzle,
+                                     block_n=block_n, route=route)
+        for r in range(world):  # same K order per element => identical bits whatever the schedule
+            assert np.array_equal(local[r], base_local[r]) and np.array_equal(peers[r], base_peers[r])
 
 
 # (world, batch, seq_local, heads, head_dim, n, comm, causal, cyclic)

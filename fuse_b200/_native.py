@@ -20,6 +20,8 @@ ROUTE_FORWARD, ROUTE_INVERSE = 0, 1
 SKIP_PEER_WAIT = 1
 QKV_ROUTE_COMM_CTAS = 2
 QKV_ROUTE_DIRECT = 4
+VECTOR_PULL = 8
+VECTOR_EPILOGUE = 16
 
 CUDA_SUCCESS = 0
 CUDA_ERROR_INVALID_VALUE = 1

@@ -69,9 +69,17 @@ void fill_core(FusedParams* p, const fuse_gemm_problem& g, int block_n, int num_
   p->ldd = packed_or(g.stride_d.row, g.n);
 }
 
-template <int kMode>
-cudaError_t launch_mode(const Operands& maps, const FusedParams& p, int block_n,
-                        const DeviceInfo& info, cudaStream_t stream) {
+// Tensor map of a row-major BF16 [rows, cols] destination for the TMA-store epilogue.
+cudaError_t encode_store_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                             int64_t pitch_elements) {
+  return host::encode_tensor_map_2d(map, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, cols,
+                                    uint64_t(pitch_elements) * 2, kBlockM, 64,
+                                    CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+template <int kMode, bool kTmaEpilogue>
+cudaError_t launch_variant(const Operands& maps, const StoreMaps& stores, const FusedParams& p,
+                           int block_n, const DeviceInfo& info, cudaStream_t stream) {
   const int64_t tiles = p.order.count();
   const int compute_capacity = info.sm_count - p.num_comm_ctas;
   const int compute = int(tiles < compute_capacity ? tiles : compute_capacity);
@@ -79,12 +87,32 @@ cudaError_t launch_mode(const Operands& maps, const FusedParams& p, int block_n,
   const bool cooperative = kMode != kModePlain;
   if (block_n == 256) {
     using Layout = SmemLayout<256, 4>;
-    return host::launch_kernel(fused_gemm_kernel<256, 4, kMode>, grid, kThreads,
-                               Layout::kDynamicBytes, cooperative, stream, maps.a, maps.b, p);
+    return host::launch_kernel(fused_gemm_kernel<256, 4, kMode, kTmaEpilogue>, grid, kThreads,
+                               Layout::kDynamicBytes, cooperative, stream, maps.a, maps.b, stores, p);
   }
   using Layout = SmemLayout<128, 6>;
-  return host::launch_kernel(fused_gemm_kernel<128, 6, kMode>, grid, kThreads,
-                             Layout::kDynamicBytes, cooperative, stream, maps.a, maps.b, p);
+  return host::launch_kernel(fused_gemm_kernel<128, 6, kMode, kTmaEpilogue>, grid, kThreads,
+                             Layout::kDynamicBytes, cooperative, stream, maps.a, maps.b, stores, p);
+}
+
+// The epilogue writes the local output through the copy engine unless the caller asked for the
+// 16-byte vector epilogue (FUSE_B200_VECTOR_EPILOGUE) or the mode needs it (beta != 0, tile
+// publication to communication CTAs).
+template <int kMode>
+cudaError_t launch_mode(const Operands& maps, StoreMaps& stores, const FusedParams& p, int block_n,
+                        const DeviceInfo& info, cudaStream_t stream, bool tma_epilogue) {
+  if constexpr (kMode != kModeQkvPush) {
+    if (tma_epilogue) {
+      const cudaError_t status = encode_store_map(&stores.local, p.d, uint64_t(p.m), uint64_t(p.n), p.ldd);
+      if (status != cudaSuccess) return status;
+      return launch_variant<kMode, true>(maps, stores, p, block_n, info, stream);
+    }
+  }
+  return launch_variant<kMode, false>(maps, stores, p, block_n, info, stream);
+}
+
+bool vector_epilogue_requested(const fuse_b200_options* options) {
+  return options != nullptr && (options->flags & FUSE_B200_VECTOR_EPILOGUE) != 0;
 }
 
 cudaError_t check_device(DeviceInfo* info) {
@@ -170,8 +198,28 @@ cudaError_t qkv_forward(const fuse_gemm_a2a_params& p, const fuse_b200_options* 
     k.qkv.peer_output[peer] = p.peer_output[peer];
     k.qkv.peer_done[peer] = p.peer_route_done_epoch[peer];
   }
-  if (direct) return launch_mode<kModeQkvDirect>(maps, k, block_n, info, stream);
-  return launch_mode<kModeQkvPush>(maps, k, block_n, info, stream);
+  StoreMaps stores{};
+  if (!direct) return launch_mode<kModeQkvPush>(maps, stores, k, block_n, info, stream, false);
+  // The tensor-store push needs every 64-column block inside one head and every 128-row tile
+  // on consecutive destination rows; other shapes push with 16-byte stores from registers.
+  const fuse_ulysses_route& r = p.route;
+  bool tma = !vector_epilogue_requested(options) && r.head_dim % 64 == 0 && r.seq_local % kBlockM == 0;
+  if (tma) {
+    const uint64_t rows_total = uint64_t(r.batch) * uint64_t(r.global_seq);
+    const int64_t q_local = int64_t(r.q_heads) / r.world_size * r.head_dim;
+    const int64_t kv_local = int64_t(r.kv_heads) / r.world_size * r.head_dim;
+    for (int peer = 0; peer < r.world_size && tma; ++peer) {
+      for (int segment = 0; segment < 3; ++segment) {
+        const int64_t width = segment == 0 ? q_local : kv_local;
+        const int64_t offset = segment == 0 ? 0 : int64_t(rows_total) * q_local +
+                                                      (segment == 2 ? int64_t(rows_total) * kv_local : 0);
+        if (encode_store_map(&stores.peer[peer][segment], p.peer_output[peer] + offset, rows_total,
+                             uint64_t(width), width) != cudaSuccess)
+          tma = false;
+      }
+    }
+  }
+  return launch_mode<kModeQkvDirect>(maps, stores, k, block_n, info, stream, tma);
 }
 
 // detail/a2a_gemm.cuh (can_implement of the lhs pull) restated for the BF16 row layout.
@@ -226,6 +274,7 @@ cudaError_t oproj_forward(const fuse_a2a_gemm_params& p, const fuse_b200_options
   fill_core(&k, p.gemm, block_n, num_comm_ctas, p.alpha, p.output, FUSE_RASTER_ALONG_N);
   k.ready = p.ready;
   k.flags = options ? options->flags : 0u;
+  if (options && (options->flags & FUSE_B200_VECTOR_PULL)) k.flags |= kFlagVectorPull;
   k.wait = host::make_wait(info, p.epoch, options ? options->wait_budget_ns : 0);
   k.lhs.world = p.route.world_size;
   k.lhs.rank = p.route.rank;
@@ -241,7 +290,9 @@ cudaError_t oproj_forward(const fuse_a2a_gemm_params& p, const fuse_b200_options
     k.lhs.peer_input[peer] = p.peer_input[peer];
     k.lhs.peer_input_ready[peer] = p.peer_input_ready[peer];
   }
-  return launch_mode<kModeLhsPull>(maps, k, block_n, info, stream);
+  StoreMaps stores{};
+  return launch_mode<kModeLhsPull>(maps, stores, k, block_n, info, stream,
+                                   !vector_epilogue_requested(options));
 }
 
 cudaError_t plain_gemm(const fuse_gemm_problem& g, const void* a, const void* b, void* d, float alpha,
@@ -265,7 +316,8 @@ cudaError_t plain_gemm(const fuse_gemm_problem& g, const void* a, const void* b,
   // The reserved CTAs are simply not launched: the GEMM runs on SMs - reserved.
   DeviceInfo reduced = info;
   reduced.sm_count = info.sm_count - reserved_comm_ctas;
-  return launch_mode<kModePlain>(maps, k, block_n, reduced, stream);
+  StoreMaps stores{};
+  return launch_mode<kModePlain>(maps, stores, k, block_n, reduced, stream, true);
 }
 
 }  // namespace

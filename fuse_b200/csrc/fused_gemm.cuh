@@ -49,6 +49,16 @@ enum LaunchFlags : uint32_t {
   // Skip the wait for the peers' completion epochs (single-GPU emulation of several ranks,
   // where the "peers" are later launches on the same stream).
   kFlagSkipPeerWait = 1u,
+  // Communication CTAs of the lhs pull move data with 16-byte loads/stores instead of the
+  // bulk-copy pipeline (kept for comparison and as the fallback).
+  kFlagVectorPull = 8u,
+};
+
+// Tensor maps of the TMA-store epilogue: the local output and, for the direct QKV push, every
+// (peer, segment) planar tensor.  Boxes are 64 columns x 128 rows, 128-byte swizzle.
+struct alignas(64) StoreMaps {
+  CUtensorMap local;
+  CUtensorMap peer[kMaxWorldSize][3];
 };
 
 struct QkvRoute {
@@ -88,7 +98,10 @@ struct SmemLayout {
   static constexpr uint32_t kABytes = kBlockM * kBlockK * 2;
   static constexpr uint32_t kBBytes = kBlockN * kBlockK * 2;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
-  static constexpr uint32_t kBarrierOffset = kStages * kStageBytes;
+  // Epilogue staging for TMA stores: two 128-row x 64-column BF16 blocks (16 KiB each).
+  static constexpr uint32_t kStagingOffset = kStages * kStageBytes;
+  static constexpr uint32_t kStagingBlockBytes = kBlockM * 64 * 2;
+  static constexpr uint32_t kBarrierOffset = kStagingOffset + 2 * kStagingBlockBytes;
   static constexpr uint32_t kNumBarriers = 2 * kStages + 2 * kAccumStages;
   static constexpr uint32_t kTmemSlotOffset = kBarrierOffset + kNumBarriers * 8;
   // Two per-tile route tables (column chunk -> destination base pointer, row pitch) used by
@@ -309,6 +322,202 @@ __device__ __forceinline__ void lhs_pull_role(const FusedParams& p, uint8_t* sme
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Communication role: the same pull with the copy engine.
+//
+// The (M tile, K shard) units are cut into chunks of at most kPullStageBytes (whole rows, or
+// pieces of a row when one row is wider than a stage).  Chunks are dealt round-robin, in unit
+// order, to the kPullWarps x num_comm_ctas pull warps, so the rows the first GEMM wave needs
+// arrive first and through every warp at once.  Each warp runs its own pipeline: one thread
+// starts bulk copies peer -> shared memory (kPullStages chunks in flight per warp, so NVLink
+// latency is covered by ~190 KiB in flight per CTA instead of by registers); as a chunk lands
+// the lanes start one bulk copy per row shared -> local staging.  When a chunk's stores have
+// completed the warp counts an arrival in word 1 of the unit's flag line; the arrival that
+// completes the unit publishes word 0 = epoch (arrival counting as in
+// csrc/operators/sm103/detail/a2a_gemm.cuh:466-642, but the epoch need not advance by one).
+// ------------------------------------------------------------------------------------------
+constexpr int kPullWarps = 4;
+constexpr int kPullStages = 3;
+constexpr uint32_t kPullStageBytes = 16384;
+
+__device__ __forceinline__ void lhs_pull_bulk_role(const FusedParams& p, uint32_t smem_base) {
+  const LhsRoute& r = p.lhs;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp >= kPullWarps) return;
+  const uint32_t ring = smem_base + uint32_t(warp) * kPullStages * kPullStageBytes;
+  const uint32_t bars = smem_base + kPullWarps * kPullStages * kPullStageBytes +
+                        uint32_t(warp) * kPullStages * 8u;
+  if (lane == 0) {
+    for (int s = 0; s < kPullStages; ++s) ptx::mbar_init(bars + 8u * s, 1);
+    ptx::fence_mbar_init();
+  }
+  __syncwarp();
+
+  // All chunk arithmetic is 32-bit (a single warp pays for every dependent division).
+  const int32_t workers = p.num_comm_ctas * kPullWarps;
+  const int32_t worker = warp * p.num_comm_ctas + int32_t(blockIdx.x);  // neighbours on different SMs
+  const uint32_t shard_bytes = uint32_t(r.shard_width) * 2u;
+  const int32_t pieces = int32_t((shard_bytes + kPullStageBytes - 1) / kPullStageBytes);
+  const uint32_t piece_bytes = pieces == 1 ? shard_bytes : kPullStageBytes;
+  const int32_t rows_per_chunk = pieces == 1 ? int32_t(kPullStageBytes / shard_bytes) : 1;
+  const int32_t chunks_per_unit = ((kBlockM + rows_per_chunk - 1) / rows_per_chunk) * pieces;
+  const int32_t chunks_total = p.order.m_tiles * r.world * chunks_per_unit;
+  const int32_t row_block = r.causal ? r.seq_local / 2 : r.seq_local;  // rows contiguous at the source
+
+  struct Chunk {
+    const uint8_t* src;   // first source row (peer memory), already offset to the piece
+    uint8_t* dst;         // first destination row (local staging), already offset to the piece
+    int32_t rows, peer, flag, needed, row;
+    uint32_t bytes_per_row, piece_offset;
+    bool contiguous, valid;
+  };
+  auto describe = [&](int32_t g) {
+    Chunk k;
+    const int32_t u = g / chunks_per_unit, c = g - u * chunks_per_unit;
+    const int32_t mt = u / r.world, shard = u - mt * r.world;
+    const int32_t rows_in_unit = p.m - mt * kBlockM < kBlockM ? p.m - mt * kBlockM : kBlockM;
+    const int32_t row0 = pieces == 1 ? c * rows_per_chunk : c / pieces;
+    const int32_t piece = pieces == 1 ? 0 : c - row0 * pieces;
+    k.valid = row0 < rows_in_unit;
+    k.peer = r.cyclic ? (r.rank + shard) % r.world : shard;
+    k.flag = u;
+    k.needed = ((rows_in_unit + rows_per_chunk - 1) / rows_per_chunk) * pieces;
+    k.rows = rows_in_unit - row0 < rows_per_chunk ? rows_in_unit - row0 : rows_per_chunk;
+    k.piece_offset = uint32_t(piece) * kPullStageBytes;
+    k.bytes_per_row = shard_bytes - k.piece_offset < piece_bytes ? shard_bytes - k.piece_offset : piece_bytes;
+    k.row = mt * kBlockM + row0;
+    const int64_t first = global_row(r.world, r.rank, r.seq_local, r.global_seq, r.causal != 0, k.row);
+    k.contiguous = pieces == 1 && (k.row % row_block) + k.rows <= row_block;
+    k.src = reinterpret_cast<const uint8_t*>(r.peer_input[k.peer]) + first * shard_bytes + k.piece_offset;
+    k.dst = reinterpret_cast<uint8_t*>(r.staging) +
+            (int64_t(k.row) * r.lda + int64_t(shard) * r.shard_width) * 2 + k.piece_offset;
+    return k;
+  };
+  // Only chunks past the ragged end of the last M tile are invalid.
+  auto next_valid = [&](int32_t g) {
+    while (g < chunks_total) {
+      const int32_t u = g / chunks_per_unit, c = g - u * chunks_per_unit;
+      const int32_t mt = u / r.world;
+      const int32_t row0 = pieces == 1 ? c * rows_per_chunk : c / pieces;
+      if (mt * kBlockM + row0 < p.m) break;
+      g += workers;
+    }
+    return g;
+  };
+
+  uint32_t upstream_seen = 0;
+  bool ok = true;
+  auto start_load = [&](int32_t g, int stage) {  // whole warp
+    const Chunk k = describe(g);
+    if (r.peer_input_ready[k.peer] != nullptr && !((upstream_seen >> k.peer) & 1u)) {
+      uint32_t good = 1u;
+      if (lane == 0)
+        good = flag_wait<true>(r.peer_input_ready[k.peer], r.input_epoch, p.wait, kSiteUpstreamReady,
+                               uint32_t(k.peer)) ? 1u : 0u;
+      good = __shfl_sync(0xffffffffu, good, 0);
+      if (!good) { ok = false; return; }
+      upstream_seen |= 1u << k.peer;
+    }
+    const uint32_t dst = ring + uint32_t(stage) * kPullStageBytes;
+    const uint32_t bar = bars + 8u * stage;
+    if (lane == 0) ptx::mbar_expect_tx(bar, uint32_t(k.rows) * k.bytes_per_row);
+    __syncwarp();
+    if (k.contiguous) {
+      if (lane == 0) ptx::bulk_load(dst, k.src, uint32_t(k.rows) * k.bytes_per_row, bar);
+    } else {
+      for (int32_t row = lane; row < k.rows; row += 32) {
+        const int64_t src_row =
+            global_row(r.world, r.rank, r.seq_local, r.global_seq, r.causal != 0, k.row + row);
+        ptx::bulk_load(dst + uint32_t(row) * k.bytes_per_row,
+                       reinterpret_cast<const uint8_t*>(r.peer_input[k.peer]) + src_row * shard_bytes +
+                           k.piece_offset,
+                       k.bytes_per_row, bar);
+      }
+    }
+  };
+  // Arrival counting, split in two so that the atomic's round trip overlaps the next chunk:
+  // `count` adds one finished chunk to word 1 of the unit's flag line, `publish` (one step
+  // later) writes word 0 = epoch if that arrival completed the unit.
+  uint32_t counted_before = 0;
+  int32_t counted_flag = -1, counted_needed = 1;
+  auto publish = [&]() {
+    if (lane == 0 && counted_flag >= 0 && (counted_before + 1u) % uint32_t(counted_needed) == 0u)
+      ptx::st_release_gpu(p.ready + int64_t(counted_flag) * kReadyFlagStride, p.wait.epoch);
+    counted_flag = -1;
+  };
+  auto count = [&](int32_t flag, int32_t needed) {
+    publish();
+    if (lane == 0) {
+      // The rows were written by completed bulk copies and are only ever read by TMA (the
+      // consumer fences the proxies after its acquire), so no proxy fence here: it would wait
+      // for the stores still in flight and serialise the pipeline.
+      __threadfence();
+      counted_before = ptx::atom_acq_rel_gpu_add(p.ready + int64_t(flag) * kReadyFlagStride + 1, 1u);
+    }
+    counted_flag = flag;
+    counted_needed = needed;
+  };
+
+  int32_t load_g = next_valid(worker), store_g = load_g;
+  int32_t issued = 0, consumed = 0;
+  while (issued < kPullStages && load_g < chunks_total) {
+    start_load(load_g, int(issued % kPullStages));
+    if (!ok) break;
+    load_g = next_valid(load_g + workers);
+    ++issued;
+  }
+  // Chunks whose stores are in flight: [0] issued in the previous step, [1] the one before.
+  int32_t lag_flag[2] = {-1, -1}, lag_needed[2] = {1, 1};
+  while (ok && store_g < chunks_total) {
+    const int stage = int(consumed % kPullStages);
+    uint32_t landed = 1u;
+    if (lane == 0)
+      landed = mbar_wait(bars + 8u * stage, uint32_t(consumed / kPullStages) & 1u, p.wait,
+                         kSiteCommStage) ? 1u : 0u;
+    landed = __shfl_sync(0xffffffffu, landed, 0);
+    if (!landed) { ok = false; break; }
+    const Chunk k = describe(store_g);
+    const uint32_t src = ring + uint32_t(stage) * kPullStageBytes;
+    for (int32_t row = lane; row < k.rows; row += 32)
+      ptx::bulk_store(k.dst + int64_t(row) * r.lda * 2, src + uint32_t(row) * k.bytes_per_row,
+                      k.bytes_per_row);
+    ptx::bulk_commit();
+    ++consumed;
+    // The previous chunk's stores have finished READING shared memory: its stage takes the next
+    // load.  (Their writes may still be in flight; completion is checked two steps behind.)
+    ptx::bulk_wait_read<1>();
+    __syncwarp();
+    if (consumed >= 2 && load_g < chunks_total && issued < consumed - 1 + kPullStages) {
+      start_load(load_g, int(issued % kPullStages));
+      if (ok) {
+        load_g = next_valid(load_g + workers);
+        ++issued;
+      }
+    }
+    ptx::bulk_wait<2>();  // all but the two newest store groups are complete
+    __syncwarp();
+    if (lag_flag[1] >= 0) count(lag_flag[1], lag_needed[1]);
+    lag_flag[1] = lag_flag[0];
+    lag_needed[1] = lag_needed[0];
+    lag_flag[0] = k.flag;
+    lag_needed[0] = k.needed;
+    store_g = next_valid(store_g + workers);
+  }
+  ptx::bulk_wait<0>();
+  __syncwarp();
+  if (ok) {
+    if (lag_flag[1] >= 0) count(lag_flag[1], lag_needed[1]);
+    if (lag_flag[0] >= 0) count(lag_flag[0], lag_needed[0]);
+    publish();
+  }
+  if (!ok && lane == 0) {
+    // Unwinding: loads started but not consumed must land before shared memory goes away.
+    for (int32_t i = consumed; i < issued; ++i)
+      mbar_wait(bars + 8u * uint32_t(i % kPullStages), uint32_t(i / kPullStages) & 1u, p.wait,
+                kSiteDrain, false);
+  }
+}
+
 // 32 FP32 accumulators of one output row -> alpha (and beta * old D) -> BF16 -> four 16-byte
 // stores.  `col` is the global column of acc[0]; vectors past N are skipped (N % 8 == 0).
 struct PeerRow {
@@ -357,13 +566,34 @@ __device__ __forceinline__ void store_accumulators(const uint32_t (&acc)[32], ui
   }
 }
 
+// 32 FP32 accumulators of one row -> alpha -> BF16 -> four 16-byte chunks of that row inside a
+// 128B-swizzled staging block (chunk index XOR row%8, the layout TMA's SWIZZLE_128B expects).
+__device__ __forceinline__ void stage_accumulators(const uint32_t (&acc)[32], uint32_t row_addr,
+                                                   int32_t first_chunk, int32_t row, float alpha) {
+#pragma unroll
+  for (int v = 0; v < 4; ++v) {
+    uint4 out;
+    __nv_bfloat162 pair = __floats2bfloat162_rn(alpha * __uint_as_float(acc[v * 8 + 0]),
+                                                alpha * __uint_as_float(acc[v * 8 + 1]));
+    out.x = *reinterpret_cast<const uint32_t*>(&pair);
+    pair = __floats2bfloat162_rn(alpha * __uint_as_float(acc[v * 8 + 2]), alpha * __uint_as_float(acc[v * 8 + 3]));
+    out.y = *reinterpret_cast<const uint32_t*>(&pair);
+    pair = __floats2bfloat162_rn(alpha * __uint_as_float(acc[v * 8 + 4]), alpha * __uint_as_float(acc[v * 8 + 5]));
+    out.z = *reinterpret_cast<const uint32_t*>(&pair);
+    pair = __floats2bfloat162_rn(alpha * __uint_as_float(acc[v * 8 + 6]), alpha * __uint_as_float(acc[v * 8 + 7]));
+    out.w = *reinterpret_cast<const uint32_t*>(&pair);
+    ptx::st_shared_v4(row_addr + uint32_t(((first_chunk + v) ^ (row & 7)) * 16), out);
+  }
+}
+
 // ------------------------------------------------------------------------------------------
 // The kernel.
 // ------------------------------------------------------------------------------------------
-template <int kBlockN, int kStages, int kMode>
+template <int kBlockN, int kStages, int kMode, bool kTmaEpilogue>
 __global__ void __launch_bounds__(kThreads, 1)
 fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                  const __grid_constant__ CUtensorMap tmap_b, const FusedParams p) {
+                  const __grid_constant__ CUtensorMap tmap_b,
+                  const __grid_constant__ StoreMaps store_maps, const FusedParams p) {
   using Layout = SmemLayout<kBlockN, kStages>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
@@ -374,7 +604,10 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
 
   if (is_comm) {
     if constexpr (kMode == kModeQkvPush) qkv_push_role<kBlockN>(p, smem);
-    if constexpr (kMode == kModeLhsPull) lhs_pull_role(p, smem);
+    if constexpr (kMode == kModeLhsPull) {
+      if (p.flags & kFlagVectorPull) lhs_pull_role(p, smem);
+      else lhs_pull_bulk_role(p, base);
+    }
   } else {
     const uint32_t bar_base = base + Layout::kBarrierOffset;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -499,13 +732,15 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       uint32_t accum = 0, accum_phase = 0;
       bool ok = true;
       constexpr bool kDirect = kMode == kModeQkvDirect;
+      constexpr bool kVectorPush = kDirect && !kTmaEpilogue;
       constexpr int kChunks = kBlockN / 8;
       uint32_t table = 0;  // which of the two route tables this tile uses
+      uint32_t staged_blocks = 0;  // 64-column blocks staged so far (selects the staging buffer)
       for (int64_t t = compute_id; ok && t < tiles; t += compute_ctas) {
         int32_t mt, nt;
         p.order.decode(t, mt, nt);
         PeerRow peer{};
-        if constexpr (kDirect) {
+        if constexpr (kDirect && !kTmaEpilogue) {
           uint16_t** col_base =
               reinterpret_cast<uint16_t**>(smem + Layout::kRouteTableOffset + table * kChunks * 16);
           int64_t* col_stride = reinterpret_cast<int64_t*>(col_base + kChunks);
@@ -534,21 +769,67 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const bool row_ok = row < p.m;
         uint16_t* d_row = p.d + int64_t(row) * p.ldd + nt * kBlockN;
         const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + accum * kBlockN;
+        if constexpr (kTmaEpilogue) {
+          // Stage 64-column blocks in 128B-swizzled shared memory and let the copy engine write
+          // them: one tensor store into the local output and, for the direct QKV push, one into
+          // the owning peer's planar tensor (full-line writes over NVLink).
+          const int32_t row_in_tile = quarter * 32 + lane;
 #pragma unroll 1
-        for (int c = 0; c < kBlockN; c += 64) {
-          uint32_t acc0[32], acc1[32];
-          ptx::tmem_ld_32x32b_x32(taddr + c, acc0);
-          ptx::tmem_ld_32x32b_x32(taddr + c + 32, acc1);
-          ptx::tmem_wait_ld();
-          if (c + 64 >= kBlockN) {
-            // Accumulator fully read: hand the TMEM stage back to the UMMA issuer.
-            ptx::tc_fence_before();
-            ptx::mbar_arrive(tmem_empty_bar(accum));
+          for (int c = 0; c < kBlockN; c += 64) {
+            const uint32_t staging =
+                base + Layout::kStagingOffset + (staged_blocks & 1u) * Layout::kStagingBlockBytes;
+            ++staged_blocks;
+            if (epi_tid == 0) ptx::bulk_wait_read<1>();  // the block stored two steps ago is drained
+            ptx::named_bar_sync(1, kEpilogueThreads);
+            uint32_t acc0[32], acc1[32];
+            ptx::tmem_ld_32x32b_x32(taddr + c, acc0);
+            ptx::tmem_ld_32x32b_x32(taddr + c + 32, acc1);
+            ptx::tmem_wait_ld();
+            if (c + 64 >= kBlockN) {
+              ptx::tc_fence_before();
+              ptx::mbar_arrive(tmem_empty_bar(accum));
+            }
+            const uint32_t row_addr = staging + uint32_t(row_in_tile) * 128u;
+            stage_accumulators(acc0, row_addr, 0, row_in_tile, p.alpha);
+            stage_accumulators(acc1, row_addr, 4, row_in_tile, p.alpha);
+            ptx::fence_proxy_async_shared();
+            ptx::named_bar_sync(1, kEpilogueThreads);
+            if (epi_tid == 0) {
+              const int32_t col = nt * kBlockN + c;
+              if (col < p.n) {
+                ptx::tma_store_2d(&store_maps.local, staging, col, mt * kBlockM);
+                if constexpr (kMode == kModeQkvDirect) {
+                  const QkvRoute& r = p.qkv;
+                  const int32_t q_width = r.q_heads * r.head_dim, kv_width = r.kv_heads * r.head_dim;
+                  const int32_t segment = col < q_width ? 0 : (col < q_width + kv_width ? 1 : 2);
+                  const int32_t within = col - (segment == 0 ? 0 : q_width + (segment == 2 ? kv_width : 0));
+                  const int32_t local_width = (segment == 0 ? q_width : kv_width) / r.world;
+                  const int32_t owner = within / local_width;
+                  ptx::tma_store_2d(&store_maps.peer[owner][segment], staging, within - owner * local_width,
+                                    int32_t(global_row(r.world, r.rank, r.seq_local, r.global_seq, false,
+                                                       mt * kBlockM)));
+                }
+              }
+              ptx::bulk_commit();
+            }
           }
-          peer.chunk0 = c / 8;
-          store_accumulators<kDirect>(acc0, d_row + c, nt * kBlockN + c, row_ok, p, peer);
-          peer.chunk0 = c / 8 + 4;
-          store_accumulators<kDirect>(acc1, d_row + c + 32, nt * kBlockN + c + 32, row_ok, p, peer);
+        } else {
+#pragma unroll 1
+          for (int c = 0; c < kBlockN; c += 64) {
+            uint32_t acc0[32], acc1[32];
+            ptx::tmem_ld_32x32b_x32(taddr + c, acc0);
+            ptx::tmem_ld_32x32b_x32(taddr + c + 32, acc1);
+            ptx::tmem_wait_ld();
+            if (c + 64 >= kBlockN) {
+              // Accumulator fully read: hand the TMEM stage back to the UMMA issuer.
+              ptx::tc_fence_before();
+              ptx::mbar_arrive(tmem_empty_bar(accum));
+            }
+            peer.chunk0 = c / 8;
+            store_accumulators<kVectorPush>(acc0, d_row + c, nt * kBlockN + c, row_ok, p, peer);
+            peer.chunk0 = c / 8 + 4;
+            store_accumulators<kVectorPush>(acc1, d_row + c + 32, nt * kBlockN + c + 32, row_ok, p, peer);
+          }
         }
         if constexpr (kMode == kModeQkvPush) {
           // Publish the tile: all 128 epilogue threads' stores, then one release at GPU scope
@@ -561,6 +842,9 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
         }
         if (++accum == kAccumStages) { accum = 0; accum_phase ^= 1u; }
+      }
+      if constexpr (kTmaEpilogue) {
+        if (epi_tid == 0) ptx::bulk_wait<0>();  // every tensor store of this CTA is performed
       }
     }
 

@@ -109,7 +109,7 @@ __device__ __forceinline__ void st_v4(void* p, const uint4& v) {
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
-// 2-D tiled load global -> shared, completion counted in bytes on an mbarrier.  No multicast.
+// 2-D tiled load global -> shared, completion counted in bytes on an mbarrier.  Each CTA loads only for itself.
 __device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const CUtensorMap* map, uint32_t bar,
                                             int32_t c0, int32_t c1) {
   asm volatile(
@@ -138,6 +138,29 @@ __device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gmem_sr
 __device__ __forceinline__ void bulk_store(void* gmem_dst, uint32_t smem_src, uint32_t bytes) {
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gmem_dst),
                "r"(smem_src), "r"(bytes)
+               : "memory");
+}
+// 2-D tiled store shared -> global (local or peer memory), tracked by the issuing thread's
+// bulk async-group; elements outside the tensor's bounds are not written.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t smem_src, int32_t c0,
+                                             int32_t c1) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(map),
+               "r"(smem_src), "r"(c0), "r"(c1)
+               : "memory");
+}
+// Waits until at most kPending of the issuing thread's most recent bulk groups are still
+// READING shared memory / are still incomplete (writes not yet performed).
+template <int kPending>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(kPending) : "memory");
+}
+template <int kPending>
+__device__ __forceinline__ void bulk_wait() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(kPending) : "memory");
+}
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4& v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
                : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }

@@ -129,7 +129,13 @@ enum {
    * straight from every compute CTA's epilogue (num_comm_ctas then only has to be valid).
    * Neither flag: environment variable FUSE_B200_QKV_ROUTE = comm | direct, else comm. */
   FUSE_B200_QKV_ROUTE_COMM_CTAS = 2u,
-  FUSE_B200_QKV_ROUTE_DIRECT = 4u
+  FUSE_B200_QKV_ROUTE_DIRECT = 4u,
+  /* Output-projection operator: communication CTAs pull with 16-byte loads/stores instead of
+   * the bulk-copy pipeline. */
+  FUSE_B200_VECTOR_PULL = 8u,
+  /* Write outputs with 16-byte stores from registers instead of tensor stores staged in
+   * shared memory. */
+  FUSE_B200_VECTOR_EPILOGUE = 16u
 };
 typedef struct fuse_b200_options {
   uint64_t wait_budget_ns; /* per-wait limit; 0 = FUSE_B200_WAIT_MS env (default 2000 ms) */

@@ -43,7 +43,8 @@ def check_status():
 
 
 def qkv_forward(world, batch, seq_local, q_heads, kv_heads, head_dim, lhs_bits, w_bits, comm=4,
-                alpha=1.0, raster=N.RASTER_HEURISTIC, swizzle=4, block_n=0, epochs=1, route="comm"):
+                alpha=1.0, raster=N.RASTER_HEURISTIC, swizzle=4, block_n=0, epochs=1, route="comm",
+                vector_epilogue=False):
     """Runs every rank of the QKV operator (route: "comm" CTAs or "direct" epilogue push).  Returns (local_outputs, peer_outputs) as bits."""
     m = batch * seq_local
     n = (q_heads + 2 * kv_heads) * head_dim
@@ -57,7 +58,8 @@ def qkv_forward(world, batch, seq_local, q_heads, kv_heads, head_dim, lhs_bits, 
     done = [torch.zeros(world * N.READY_FLAG_STRIDE, dtype=torch.int32, device=DEV) for _ in range(world)]
     ready = [torch.zeros(api.qkv_ready_elements(problem), dtype=torch.int32, device=DEV) for _ in range(world)]
     route_flag = N.QKV_ROUTE_DIRECT if route == "direct" else N.QKV_ROUTE_COMM_CTAS
-    opts = options(flags=(N.SKIP_PEER_WAIT if world > 1 else 0) | route_flag, block_n=block_n)
+    opts = options(flags=(N.SKIP_PEER_WAIT if world > 1 else 0) | route_flag |
+                   (N.VECTOR_EPILOGUE if vector_epilogue else 0), block_n=block_n)
     for epoch in range(1, epochs + 1):
         for r in range(world):
             route = N.UlyssesRoute(world_size=world, rank=r, batch=batch, global_seq=seq_local * world,
@@ -78,8 +80,10 @@ def qkv_forward(world, batch, seq_local, q_heads, kv_heads, head_dim, lhs_bits, 
 
 
 def oproj_forward(world, rank, batch, seq_local, peer_bits, w_bits, comm=4, causal=False, cyclic=False,
-                  alpha=1.0, raster=N.RASTER_HEURISTIC, swizzle=8, block_n=0):
-    """Runs one rank of the output-projection operator.  Returns (staging, output) bits."""
+                  alpha=1.0, raster=N.RASTER_HEURISTIC, swizzle=8, block_n=0, pull="bulk",
+                  vector_epilogue=False):
+    """Runs one rank of the output-projection operator (pull: "bulk" copy pipeline or "vector"
+    loads/stores).  Returns (staging, output) bits."""
     n, k = w_bits.shape
     m = batch * seq_local
     w = to_device(w_bits)
@@ -95,7 +99,8 @@ def oproj_forward(world, rank, batch, seq_local, peer_bits, w_bits, comm=4, caus
                         alpha=alpha)
     for q in range(world):
         p.peer_input[q] = peers[q].data_ptr()
-    rc = api.launch_a2a_gemm_cutlass(p, 0, options(block_n=block_n))
+    flags = (N.VECTOR_PULL if pull == "vector" else 0) | (N.VECTOR_EPILOGUE if vector_epilogue else 0)
+    rc = api.launch_a2a_gemm_cutlass(p, 0, options(block_n=block_n, flags=flags))
     assert rc == 0, f"launch_a2a_gemm_cutlass -> cudaError {rc}"
     check_status()
     return to_bits(staging), to_bits(out)

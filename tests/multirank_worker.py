@@ -1,0 +1,105 @@
+"""One rank of a real multi-GPU parity run (launched by tests/test_gpu_multirank.py through
+torch.distributed.run, one process per GPU).  Every rank runs the QKV operator and the output
+projection operator against its peers' symmetric buffers and checks its own results against
+the CPU oracle, which simulates all ranks from the same seeds."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+from fuse_b200 import _native as N  # noqa: E402
+from fuse_b200 import api, synthetic  # noqa: E402
+from fuse_b200.world import World  # noqa: E402
+from oracle import oracle as O  # noqa: E402
+
+
+def bits(t):
+    return t.detach().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local_rank = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    dist.init_process_group("nccl", device_id=dev)
+    route_mode = sys.argv[1] if len(sys.argv) > 1 else "direct"
+    batch, s, q, kv, d, k = 1, 512, 8 * world // 2, 8, 128, 512
+    if kv % world:
+        kv = world
+    m, n = batch * s, (q + 2 * kv) * d
+    rows = batch * s * world
+    ko = q * d
+    w = World(rank, world, local_rank)
+    sym = w.allocate({"planar": rows * (n // world) * 2, "done": world * N.READY_FLAG_STRIDE * 4,
+                      "attn": rows * (ko // world) * 2})
+    lhs = [synthetic.normal_bf16((m, k), synthetic.rank_seed(r) + 1000, 1.0) for r in range(world)]
+    wq = synthetic.normal_bf16((n, k), synthetic.BASE_SEED + 11, 0.02)
+    attn_all = [synthetic.normal_bf16((rows, ko // world), synthetic.rank_seed(r) + 2000, 1.0) for r in range(world)]
+    wo = synthetic.normal_bf16((384, ko), synthetic.BASE_SEED + 17, 0.02)
+    to_dev = lambda a: torch.from_numpy(a.view(np.int16)).to(dev).view(torch.bfloat16)
+    x, wq_d, wo_d = to_dev(lhs[rank]), to_dev(wq), to_dev(wo)
+    sym["attn"].view(torch.bfloat16).copy_(to_dev(attn_all[rank]).reshape(-1))
+    sym["planar"].view(torch.int16).fill_(-1)
+    local = torch.full((m, n), -1, dtype=torch.int16, device=dev).view(torch.bfloat16)
+    staging = torch.full((m, ko), -1, dtype=torch.int16, device=dev).view(torch.bfloat16)
+    out = torch.full((m, 384), -1, dtype=torch.int16, device=dev).view(torch.bfloat16)
+    torch.cuda.synchronize()
+    dist.barrier()
+
+    problem = N.GemmProblem(m, n, k, max_swizzle_size=4)
+    route = N.UlyssesRoute(world_size=world, rank=rank, batch=batch, global_seq=s * world, seq_local=s,
+                           q_heads=q, kv_heads=kv, head_dim=d, kind=N.ROUTE_QKV_GQA_PACK)
+    ready = torch.zeros(api.qkv_ready_elements(problem), dtype=torch.int32, device=dev)
+    p = N.GemmA2AParams(lhs=x.data_ptr(), rhs_nt=wq_d.data_ptr(), local_output=local.data_ptr(),
+                        ready=ready.data_ptr(), gemm=problem, route=route, num_comm_ctas=8, epoch=1)
+    for r in range(world):
+        p.peer_output[r] = sym["planar"].peer_ptrs[r]
+        p.peer_route_done_epoch[r] = sym["done"].peer_ptrs[r]
+    opts = N.Options()
+    opts.wait_budget_ns = 2_000_000_000
+    opts.flags = N.QKV_ROUTE_DIRECT if route_mode == "direct" else N.QKV_ROUTE_COMM_CTAS
+    for epoch in (1, 2):  # second launch re-uses flags with the next epoch
+        p.epoch = epoch
+        assert api.launch_gemm_a2a_cutlass(p, 0, opts) == 0
+    torch.cuda.synchronize()
+    status = api.read_status()
+    assert status[0] == 0, status[:8]
+    # When this rank's kernel has finished, every peer's pushes into it are complete
+    # (cross-rank completion handshake): no host barrier before reading.
+    want_local, want_peers = O.qkv_forward(world, batch, s, q, kv, d, lhs, wq)
+    ok, worst, bad = O.within_tolerance(bits(local), want_local[rank])
+    assert ok, ("local", worst, bad)
+    ok, worst, bad = O.within_tolerance(bits(sym["planar"].view(torch.bfloat16)), want_peers[rank])
+    assert ok, ("planar", worst, bad)
+
+    dist.barrier()
+    o_problem = N.GemmProblem(m, 384, ko, max_swizzle_size=8)
+    o_route = N.UlyssesRoute(world_size=world, rank=rank, batch=batch, global_seq=s * world, seq_local=s,
+                             kind=N.ROUTE_HEAD_TO_SEQUENCE, direction=N.ROUTE_INVERSE)
+    o_ready = torch.zeros(api.a2a_lhs_gemm_ready_elements(o_problem, o_route), dtype=torch.int32, device=dev)
+    po = N.A2AGemmParams(input_staging=staging.data_ptr(), rhs_nt=wo_d.data_ptr(), output=out.data_ptr(),
+                         ready=o_ready.data_ptr(), gemm=o_problem, route=o_route, num_comm_ctas=8, epoch=1)
+    for r in range(world):
+        po.peer_input[r] = sym["attn"].peer_ptrs[r]
+    assert api.launch_a2a_gemm_cutlass(po, 0, opts) == 0
+    torch.cuda.synchronize()
+    status = api.read_status()
+    assert status[0] == 0, status[:8]
+    want_staging, want_out = O.oproj_forward(world, rank, batch, s, attn_all, wo)
+    assert np.array_equal(bits(staging), want_staging), "gathered lhs differs"
+    ok, worst, bad = O.within_tolerance(bits(out), want_out)
+    assert ok, ("oproj", worst, bad)
+    dist.barrier()  # peers' inputs stay immutable until every rank is done
+    w.close()
+    dist.destroy_process_group()
+    print(f"MULTIRANK PASS rank {rank}/{world} route={route_mode}", flush=True)
+
+
+if __name__ == "__main__":
+    main()

@@ -84,9 +84,9 @@ def test_qkv_forward_knobs_do_not_change_results(raster, swizzle, block_n):
     m, n = batch * s, (q + 2 * kv) * d
     lhs, w = _inputs(world, m, k, n)
     base_local, base_peers = H.qkv_forward(world, batch, s, q, kv, d, lhs, w, comm=4)
-    for route in ("comm", "direct"):
+    for route, vector in (("comm", False), ("direct", False), ("direct", True)):
         local, peers = H.qkv_forward(world, batch, s, q, kv, d, lhs, w, comm=7, raster=raster, swizzle=swizzle,
-                                     block_n=block_n, route=route)
+                                     block_n=block_n, route=route, vector_epilogue=vector)
         for r in range(world):  # same K order per element => identical bits whatever the schedule
             assert np.array_equal(local[r], base_local[r]) and np.array_equal(peers[r], base_peers[r])
 
@@ -98,11 +98,13 @@ OPROJ_CASES = [
     (4, 2, 200, 16, 64, 520, 5, True, False),     # causal two-chunk rows, ragged M and N
     (8, 1, 128, 32, 128, 4096, 16, False, True),  # cyclic K-shard order
     (4, 1, 96, 8, 40, 256, 3, True, True),        # K shard (80) not a multiple of the K block
+    (1, 1, 130, 80, 128, 128, 2, False, False),   # one 20 KiB row per shard: rows cut into pieces
 ]
 
 
+@pytest.mark.parametrize("pull", ["bulk", "vector"])
 @pytest.mark.parametrize("case", OPROJ_CASES)
-def test_oproj_forward_matches_oracle(case):
+def test_oproj_forward_matches_oracle(case, pull):
     from tests import harness as H
     world, batch, s, heads, d, n, comm, causal, cyclic = case
     k = heads * d
@@ -110,7 +112,8 @@ def test_oproj_forward_matches_oracle(case):
                for r in range(world)]
     w = synthetic.normal_bf16((n, k), synthetic.BASE_SEED + 17, 0.02)
     for rank in sorted({0, world - 1, world // 2}):
-        staging, out = H.oproj_forward(world, rank, batch, s, peer_in, w, comm=comm, causal=causal, cyclic=cyclic)
+        staging, out = H.oproj_forward(world, rank, batch, s, peer_in, w, comm=comm, causal=causal,
+                                       cyclic=cyclic, pull=pull, vector_epilogue=(pull == "vector"))
         want_staging, want_out = O.oproj_forward(world, rank, batch, s, peer_in, w, causal=causal, cyclic=cyclic)
         assert np.array_equal(staging, want_staging), f"gathered lhs differs on rank {rank}"
         _assert_close(out, want_out, f"output[{rank}]")

@@ -107,7 +107,8 @@ class A2AGemmParams(C.Structure):
 
 
 class Options(C.Structure):
-    _fields_ = [("wait_budget_ns", C.c_uint64), ("flags", C.c_uint32), ("block_n", C.c_int32)]
+    _fields_ = [("wait_budget_ns", C.c_uint64), ("flags", C.c_uint32), ("block_n", C.c_int32),
+                ("trace", C.c_void_p), ("trace_capacity", C.c_uint32), ("trace_cta", C.c_int32)]
 
 
 ABI_RECORDS = {0: GemmProblem, 1: UlyssesRoute, 2: GemmA2AParams, 3: A2AGemmParams,

@@ -276,6 +276,11 @@ cudaError_t oproj_forward(const fuse_a2a_gemm_params& p, const fuse_b200_options
   k.flags = options ? options->flags : 0u;
   if (options && (options->flags & FUSE_B200_VECTOR_PULL)) k.flags |= kFlagVectorPull;
   k.wait = host::make_wait(info, p.epoch, options ? options->wait_budget_ns : 0);
+  if (options != nullptr) {
+    k.trace = options->trace;
+    k.trace_capacity = options->trace_capacity;
+    k.trace_cta = options->trace_cta;
+  }
   k.lhs.world = p.route.world_size;
   k.lhs.rank = p.route.rank;
   k.lhs.seq_local = p.route.seq_local;

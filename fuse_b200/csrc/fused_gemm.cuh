@@ -88,6 +88,11 @@ struct FusedParams {
   int64_t ldd;
   uint32_t* ready;            // tile flags (QkvPush) or (m-tile, k-shard) flags (LhsPull)
   uint32_t flags;
+  // Optional %globaltimer trace: CTA `trace_cta` appends (site, timestamp) pairs until the
+  // buffer holds trace_capacity records; word 0 of the buffer is the record count.
+  unsigned long long* trace;
+  uint32_t trace_capacity;
+  int32_t trace_cta;
   WaitContext wait;
   QkvRoute qkv;
   LhsRoute lhs;
@@ -115,6 +120,15 @@ struct SmemLayout {
   static_assert(kDynamicBytes <= 227 * 1024, "shared memory budget");
   static_assert(kDynamicBytes > 114 * 1024, "must force one CTA per SM");
 };
+
+__device__ __forceinline__ void trace_event(const FusedParams& p, uint32_t site) {
+  if (p.trace == nullptr || int32_t(blockIdx.x) != p.trace_cta) return;
+  const unsigned long long slot = atomicAdd(p.trace, 1ull);
+  if (slot < p.trace_capacity) {
+    p.trace[1 + 2 * slot] = (static_cast<unsigned long long>(threadIdx.x) << 32) | site;
+    p.trace[2 + 2 * slot] = ptx::globaltimer();
+  }
+}
 
 // ------------------------------------------------------------------------------------------
 // Row mapping shared by the routes: rank-local row -> row of the global [batch, S] axis.
@@ -325,20 +339,37 @@ __device__ __forceinline__ void lhs_pull_role(const FusedParams& p, uint8_t* sme
 // ------------------------------------------------------------------------------------------
 // Communication role: the same pull with the copy engine.
 //
-// The (M tile, K shard) units are cut into chunks of at most kPullStageBytes (whole rows, or
-// pieces of a row when one row is wider than a stage).  Chunks are dealt round-robin, in unit
-// order, to the kPullWarps x num_comm_ctas pull warps, so the rows the first GEMM wave needs
-// arrive first and through every warp at once.  Each warp runs its own pipeline: one thread
-// starts bulk copies peer -> shared memory (kPullStages chunks in flight per warp, so NVLink
-// latency is covered by ~190 KiB in flight per CTA instead of by registers); as a chunk lands
-// the lanes start one bulk copy per row shared -> local staging.  When a chunk's stores have
-// completed the warp counts an arrival in word 1 of the unit's flag line; the arrival that
-// completes the unit publishes word 0 = epoch (arrival counting as in
+// A (M tile, K shard) unit is cut into sub-units of kPullSubRows rows, dealt round-robin in unit
+// order to the kPullWarps x num_comm_ctas pull warps, so the rows the first GEMM wave needs
+// arrive first and through every warp at once.  A warp walks its sub-units in chunks of at most
+// kPullStageBytes (whole rows, or pieces of a row wider than a stage) through its own pipeline:
+// one thread starts bulk copies peer -> shared memory (kPullStages chunks in flight per warp, so
+// NVLink latency is covered by shared memory rather than registers); as a chunk lands the lanes
+// start one bulk copy per row shared -> local staging.  Addresses are derived once per sub-unit;
+// the per-chunk work of the single issuing warp is a few adds.  When the stores of a sub-unit's
+// last chunk have completed (checked kPullLag chunks late, a bulk store's completion takes
+// microseconds) the warp counts an arrival in word 1 of the unit's flag line, and the arrival
+// that completes the unit publishes word 0 = epoch (arrival counting as in
 // csrc/operators/sm103/detail/a2a_gemm.cuh:466-642, but the epoch need not advance by one).
 // ------------------------------------------------------------------------------------------
-constexpr int kPullWarps = 4;
-constexpr int kPullStages = 3;
+constexpr int kPullWarps = 7;
+constexpr int kPullStages = 2;
 constexpr uint32_t kPullStageBytes = 16384;
+constexpr int kPullLag = 4;
+constexpr int kPullSubRows = 32;
+constexpr int kPullSubsPerTile = kBlockM / kPullSubRows;
+
+struct PullCursor {
+  int32_t sub;        // global sub-unit index; advances by the number of pull warps
+  int32_t chunk;      // chunk inside the sub-unit
+  int32_t chunks;     // chunks of this sub-unit
+  int32_t rows;       // rows of this sub-unit
+  int32_t row;        // rank-local row of its first row
+  int32_t flag, needed, peer;
+  bool contiguous;    // its source rows are consecutive in the peer's tensor
+  const uint8_t* src; // source of its first row (valid when contiguous)
+  uint8_t* dst;       // destination of its first row
+};
 
 __device__ __forceinline__ void lhs_pull_bulk_role(const FusedParams& p, uint32_t smem_base) {
   const LhsRoute& r = p.lhs;
@@ -353,91 +384,106 @@ __device__ __forceinline__ void lhs_pull_bulk_role(const FusedParams& p, uint32_
   }
   __syncwarp();
 
-  // All chunk arithmetic is 32-bit (a single warp pays for every dependent division).
   const int32_t workers = p.num_comm_ctas * kPullWarps;
   const int32_t worker = warp * p.num_comm_ctas + int32_t(blockIdx.x);  // neighbours on different SMs
   const uint32_t shard_bytes = uint32_t(r.shard_width) * 2u;
   const int32_t pieces = int32_t((shard_bytes + kPullStageBytes - 1) / kPullStageBytes);
-  const uint32_t piece_bytes = pieces == 1 ? shard_bytes : kPullStageBytes;
-  const int32_t rows_per_chunk = pieces == 1 ? int32_t(kPullStageBytes / shard_bytes) : 1;
-  const int32_t chunks_per_unit = ((kBlockM + rows_per_chunk - 1) / rows_per_chunk) * pieces;
-  const int32_t chunks_total = p.order.m_tiles * r.world * chunks_per_unit;
-  const int32_t row_block = r.causal ? r.seq_local / 2 : r.seq_local;  // rows contiguous at the source
+  const int32_t rows_per_chunk =
+      pieces == 1 ? (int32_t(kPullStageBytes / shard_bytes) < kPullSubRows ? int32_t(kPullStageBytes / shard_bytes)
+                                                                          : kPullSubRows)
+                  : 1;
+  const int32_t subs_total = p.order.m_tiles * r.world * kPullSubsPerTile;
+  const int32_t row_block = r.causal ? r.seq_local / 2 : r.seq_local;  // rows consecutive at the source
+  const int64_t dst_pitch = r.lda * 2;
 
-  struct Chunk {
-    const uint8_t* src;   // first source row (peer memory), already offset to the piece
-    uint8_t* dst;         // first destination row (local staging), already offset to the piece
-    int32_t rows, peer, flag, needed, row;
-    uint32_t bytes_per_row, piece_offset;
-    bool contiguous, valid;
-  };
-  auto describe = [&](int32_t g) {
-    Chunk k;
-    const int32_t u = g / chunks_per_unit, c = g - u * chunks_per_unit;
-    const int32_t mt = u / r.world, shard = u - mt * r.world;
-    const int32_t rows_in_unit = p.m - mt * kBlockM < kBlockM ? p.m - mt * kBlockM : kBlockM;
-    const int32_t row0 = pieces == 1 ? c * rows_per_chunk : c / pieces;
-    const int32_t piece = pieces == 1 ? 0 : c - row0 * pieces;
-    k.valid = row0 < rows_in_unit;
-    k.peer = r.cyclic ? (r.rank + shard) % r.world : shard;
-    k.flag = u;
-    k.needed = ((rows_in_unit + rows_per_chunk - 1) / rows_per_chunk) * pieces;
-    k.rows = rows_in_unit - row0 < rows_per_chunk ? rows_in_unit - row0 : rows_per_chunk;
-    k.piece_offset = uint32_t(piece) * kPullStageBytes;
-    k.bytes_per_row = shard_bytes - k.piece_offset < piece_bytes ? shard_bytes - k.piece_offset : piece_bytes;
-    k.row = mt * kBlockM + row0;
-    const int64_t first = global_row(r.world, r.rank, r.seq_local, r.global_seq, r.causal != 0, k.row);
-    k.contiguous = pieces == 1 && (k.row % row_block) + k.rows <= row_block;
-    k.src = reinterpret_cast<const uint8_t*>(r.peer_input[k.peer]) + first * shard_bytes + k.piece_offset;
-    k.dst = reinterpret_cast<uint8_t*>(r.staging) +
-            (int64_t(k.row) * r.lda + int64_t(shard) * r.shard_width) * 2 + k.piece_offset;
-    return k;
-  };
-  // Only chunks past the ragged end of the last M tile are invalid.
-  auto next_valid = [&](int32_t g) {
-    while (g < chunks_total) {
-      const int32_t u = g / chunks_per_unit, c = g - u * chunks_per_unit;
-      const int32_t mt = u / r.world;
-      const int32_t row0 = pieces == 1 ? c * rows_per_chunk : c / pieces;
-      if (mt * kBlockM + row0 < p.m) break;
-      g += workers;
+  // Positions `c` on the first sub-unit at or after c.sub that has rows; false past the end.
+  auto seek = [&](PullCursor& c) {
+    for (; c.sub < subs_total; c.sub += workers) {
+      const int32_t unit = c.sub / kPullSubsPerTile, quarter = c.sub - unit * kPullSubsPerTile;
+      const int32_t mt = unit / r.world, shard = unit - mt * r.world;
+      const int32_t rows_in_unit = p.m - mt * kBlockM < kBlockM ? p.m - mt * kBlockM : kBlockM;
+      const int32_t row0 = quarter * kPullSubRows;
+      if (row0 >= rows_in_unit) continue;
+      c.rows = rows_in_unit - row0 < kPullSubRows ? rows_in_unit - row0 : kPullSubRows;
+      c.row = mt * kBlockM + row0;
+      c.chunk = 0;
+      c.chunks = ((c.rows + rows_per_chunk - 1) / rows_per_chunk) * pieces;
+      c.flag = unit;
+      c.needed = (rows_in_unit + kPullSubRows - 1) / kPullSubRows;
+      c.peer = r.cyclic ? (r.rank + shard) % r.world : shard;
+      c.contiguous = (c.row % row_block) + c.rows <= row_block;
+      c.src = reinterpret_cast<const uint8_t*>(r.peer_input[c.peer]) +
+              global_row(r.world, r.rank, r.seq_local, r.global_seq, r.causal != 0, c.row) * shard_bytes;
+      c.dst = reinterpret_cast<uint8_t*>(r.staging) + int64_t(c.row) * dst_pitch +
+              int64_t(shard) * shard_bytes;
+      return true;
     }
-    return g;
+    return false;
+  };
+  auto advance = [&](PullCursor& c) {
+    if (++c.chunk < c.chunks) return true;
+    c.sub += workers;
+    return seek(c);
+  };
+  // Geometry of the chunk under a cursor: first row inside the sub-unit, rows, byte range.
+  struct Chunk { int32_t row_off, rows; uint32_t col_off, bytes_per_row; };
+  auto chunk_of = [&](const PullCursor& c) {
+    Chunk k;
+    if (pieces == 1) {
+      k.row_off = c.chunk * rows_per_chunk;
+      k.rows = c.rows - k.row_off < rows_per_chunk ? c.rows - k.row_off : rows_per_chunk;
+      k.col_off = 0;
+      k.bytes_per_row = shard_bytes;
+    } else {
+      k.row_off = c.chunk / pieces;
+      k.rows = 1;
+      k.col_off = uint32_t(c.chunk - k.row_off * pieces) * kPullStageBytes;
+      k.bytes_per_row = shard_bytes - k.col_off < kPullStageBytes ? shard_bytes - k.col_off : kPullStageBytes;
+    }
+    return k;
   };
 
   uint32_t upstream_seen = 0;
   bool ok = true;
-  auto start_load = [&](int32_t g, int stage) {  // whole warp
-    const Chunk k = describe(g);
-    if (r.peer_input_ready[k.peer] != nullptr && !((upstream_seen >> k.peer) & 1u)) {
+  auto start_load = [&](const PullCursor& c, int stage) {  // whole warp
+    if (r.peer_input_ready[c.peer] != nullptr && !((upstream_seen >> c.peer) & 1u)) {
       uint32_t good = 1u;
       if (lane == 0)
-        good = flag_wait<true>(r.peer_input_ready[k.peer], r.input_epoch, p.wait, kSiteUpstreamReady,
-                               uint32_t(k.peer)) ? 1u : 0u;
+        good = flag_wait<true>(r.peer_input_ready[c.peer], r.input_epoch, p.wait, kSiteUpstreamReady,
+                               uint32_t(c.peer)) ? 1u : 0u;
       good = __shfl_sync(0xffffffffu, good, 0);
       if (!good) { ok = false; return; }
-      upstream_seen |= 1u << k.peer;
+      upstream_seen |= 1u << c.peer;
     }
+    const Chunk k = chunk_of(c);
     const uint32_t dst = ring + uint32_t(stage) * kPullStageBytes;
     const uint32_t bar = bars + 8u * stage;
     if (lane == 0) ptx::mbar_expect_tx(bar, uint32_t(k.rows) * k.bytes_per_row);
     __syncwarp();
-    if (k.contiguous) {
-      if (lane == 0) ptx::bulk_load(dst, k.src, uint32_t(k.rows) * k.bytes_per_row, bar);
+    if (c.contiguous) {
+      // consecutive source rows: one copy for the whole chunk (rows are shard_bytes apart)
+      if (pieces == 1) {
+        if (lane == 0)
+          ptx::bulk_load(dst, c.src + int64_t(k.row_off) * shard_bytes, uint32_t(k.rows) * shard_bytes, bar);
+      } else if (lane == 0) {
+        ptx::bulk_load(dst, c.src + int64_t(k.row_off) * shard_bytes + k.col_off, k.bytes_per_row, bar);
+      }
     } else {
       for (int32_t row = lane; row < k.rows; row += 32) {
-        const int64_t src_row =
-            global_row(r.world, r.rank, r.seq_local, r.global_seq, r.causal != 0, k.row + row);
+        const int64_t src_row = global_row(r.world, r.rank, r.seq_local, r.global_seq, r.causal != 0,
+                                           c.row + k.row_off + row);
         ptx::bulk_load(dst + uint32_t(row) * k.bytes_per_row,
-                       reinterpret_cast<const uint8_t*>(r.peer_input[k.peer]) + src_row * shard_bytes +
-                           k.piece_offset,
+                       reinterpret_cast<const uint8_t*>(r.peer_input[c.peer]) + src_row * shard_bytes + k.col_off,
                        k.bytes_per_row, bar);
       }
     }
   };
-  // Arrival counting, split in two so that the atomic's round trip overlaps the next chunk:
-  // `count` adds one finished chunk to word 1 of the unit's flag line, `publish` (one step
-  // later) writes word 0 = epoch if that arrival completed the unit.
+
+  // Arrival counting, split in two so that the atomic's round trip overlaps later chunks:
+  // `count` adds one finished sub-unit to word 1 of the unit's flag line, `publish` (at the
+  // next count) writes word 0 = epoch if that arrival completed the unit.  The rows were
+  // written by completed bulk copies and are only read by TMA (the consumer fences the proxies
+  // after its acquire); the acq_rel RMW orders them before the count.
   uint32_t counted_before = 0;
   int32_t counted_flag = -1, counted_needed = 1;
   auto publish = [&]() {
@@ -447,67 +493,74 @@ __device__ __forceinline__ void lhs_pull_bulk_role(const FusedParams& p, uint32_
   };
   auto count = [&](int32_t flag, int32_t needed) {
     publish();
-    if (lane == 0) {
-      // The rows were written by completed bulk copies and are only ever read by TMA (the
-      // consumer fences the proxies after its acquire), so no proxy fence here: it would wait
-      // for the stores still in flight and serialise the pipeline.
-      __threadfence();
+    if (lane == 0)
       counted_before = ptx::atom_acq_rel_gpu_add(p.ready + int64_t(flag) * kReadyFlagStride + 1, 1u);
-    }
     counted_flag = flag;
     counted_needed = needed;
   };
 
-  int32_t load_g = next_valid(worker), store_g = load_g;
+  PullCursor load_cursor{};
+  load_cursor.sub = worker;
+  bool more_loads = seek(load_cursor);
+  if (!more_loads) return;
+  PullCursor store_cursor = load_cursor;
   int32_t issued = 0, consumed = 0;
-  while (issued < kPullStages && load_g < chunks_total) {
-    start_load(load_g, int(issued % kPullStages));
+  while (issued < kPullStages && more_loads) {
+    start_load(load_cursor, issued % kPullStages);
     if (!ok) break;
-    load_g = next_valid(load_g + workers);
+    more_loads = advance(load_cursor);
     ++issued;
   }
-  // Chunks whose stores are in flight: [0] issued in the previous step, [1] the one before.
-  int32_t lag_flag[2] = {-1, -1}, lag_needed[2] = {1, 1};
-  while (ok && store_g < chunks_total) {
-    const int stage = int(consumed % kPullStages);
+  // Sub-units closed by the newest store groups (newest first; -1 = that chunk closed nothing).
+  int32_t lag_flag[kPullLag], lag_needed[kPullLag];
+#pragma unroll
+  for (int i = 0; i < kPullLag; ++i) { lag_flag[i] = -1; lag_needed[i] = 1; }
+  bool more_stores = true;
+  while (ok && more_stores) {
+    const int stage = consumed % kPullStages;
     uint32_t landed = 1u;
     if (lane == 0)
       landed = mbar_wait(bars + 8u * stage, uint32_t(consumed / kPullStages) & 1u, p.wait,
                          kSiteCommStage) ? 1u : 0u;
     landed = __shfl_sync(0xffffffffu, landed, 0);
     if (!landed) { ok = false; break; }
-    const Chunk k = describe(store_g);
+    if (lane == 0) trace_event(p, 1);  // chunk landed
+    const Chunk k = chunk_of(store_cursor);
     const uint32_t src = ring + uint32_t(stage) * kPullStageBytes;
+    uint8_t* dst = store_cursor.dst + int64_t(k.row_off) * dst_pitch + k.col_off;
     for (int32_t row = lane; row < k.rows; row += 32)
-      ptx::bulk_store(k.dst + int64_t(row) * r.lda * 2, src + uint32_t(row) * k.bytes_per_row,
-                      k.bytes_per_row);
+      ptx::bulk_store(dst + int64_t(row) * dst_pitch, src + uint32_t(row) * k.bytes_per_row, k.bytes_per_row);
     ptx::bulk_commit();
     ++consumed;
-    // The previous chunk's stores have finished READING shared memory: its stage takes the next
-    // load.  (Their writes may still be in flight; completion is checked two steps behind.)
-    ptx::bulk_wait_read<1>();
+    if (lane == 0) trace_event(p, 2);  // stores issued
+    // Once these stores have finished READING shared memory the stage takes the next load.
+    ptx::bulk_wait_read<0>();
     __syncwarp();
-    if (consumed >= 2 && load_g < chunks_total && issued < consumed - 1 + kPullStages) {
-      start_load(load_g, int(issued % kPullStages));
+    if (more_loads && issued < consumed + kPullStages) {
+      start_load(load_cursor, issued % kPullStages);
       if (ok) {
-        load_g = next_valid(load_g + workers);
+        more_loads = advance(load_cursor);
         ++issued;
       }
     }
-    ptx::bulk_wait<2>();  // all but the two newest store groups are complete
-    __syncwarp();
-    if (lag_flag[1] >= 0) count(lag_flag[1], lag_needed[1]);
-    lag_flag[1] = lag_flag[0];
-    lag_needed[1] = lag_needed[0];
-    lag_flag[0] = k.flag;
-    lag_needed[0] = k.needed;
-    store_g = next_valid(store_g + workers);
+    if (lane == 0) trace_event(p, 3);  // next load issued
+    ptx::bulk_wait<kPullLag>();  // all but the kPullLag newest store groups are complete ...
+    __syncwarp();                // ... for every lane's rows, before lane 0 counts the arrival
+    if (lag_flag[kPullLag - 1] >= 0) count(lag_flag[kPullLag - 1], lag_needed[kPullLag - 1]);
+#pragma unroll
+    for (int i = kPullLag - 1; i > 0; --i) { lag_flag[i] = lag_flag[i - 1]; lag_needed[i] = lag_needed[i - 1]; }
+    const bool closes = store_cursor.chunk + 1 == store_cursor.chunks;
+    lag_flag[0] = closes ? store_cursor.flag : -1;
+    lag_needed[0] = store_cursor.needed;
+    more_stores = advance(store_cursor);
+    if (lane == 0) trace_event(p, 4);  // bookkeeping done
   }
   ptx::bulk_wait<0>();
   __syncwarp();
   if (ok) {
-    if (lag_flag[1] >= 0) count(lag_flag[1], lag_needed[1]);
-    if (lag_flag[0] >= 0) count(lag_flag[0], lag_needed[0]);
+#pragma unroll
+    for (int i = kPullLag - 1; i >= 0; --i)
+      if (lag_flag[i] >= 0) count(lag_flag[i], lag_needed[i]);
     publish();
   }
   if (!ok && lane == 0) {

@@ -141,6 +141,11 @@ typedef struct fuse_b200_options {
   uint64_t wait_budget_ns; /* per-wait limit; 0 = FUSE_B200_WAIT_MS env (default 2000 ms) */
   uint32_t flags;
   int32_t block_n;         /* 0 = choose; 128 or 256 */
+  /* Optional %globaltimer trace of one CTA (device buffer of 1 + 2*trace_capacity uint64:
+   * word 0 = record count, then (thread<<32 | site, nanoseconds) pairs).  NULL = off. */
+  unsigned long long* trace;
+  uint32_t trace_capacity;
+  int32_t trace_cta;
 } fuse_b200_options;
 
 /* csrc/operators/sm103/api/forward.cuh:12-14 -> detail/launch.cuh:497-625. */

@@ -22,6 +22,8 @@ QKV_ROUTE_COMM_CTAS = 2
 QKV_ROUTE_DIRECT = 4
 VECTOR_PULL = 8
 VECTOR_EPILOGUE = 16
+COMM_ONLY = 32
+COMPUTE_ONLY = 64
 
 CUDA_SUCCESS = 0
 CUDA_ERROR_INVALID_VALUE = 1
@@ -111,8 +113,75 @@ class Options(C.Structure):
                 ("trace", C.c_void_p), ("trace_capacity", C.c_uint32), ("trace_cta", C.c_int32)]
 
 
+class _Record(C.Structure):
+    def __init__(self, **kw):
+        super().__init__()
+        for key, value in getattr(self, "_defaults_", {}).items():
+            setattr(self, key, value)
+        for key, value in kw.items():
+            setattr(self, key, value)
+
+
+class BackwardGemmTuning(C.Structure):
+    _fields_ = [("epilogue_n", C.c_int32), ("max_swizzle_size", C.c_int32), ("along_m", C.c_uint8)]
+
+
+class QkvBackwardDataParams(_Record):
+    """include/fuse/operators/ulysses/qkv_backward.h:24-49 of the reference."""
+    _fields_ = [("grad_q", C.c_void_p), ("grad_k", C.c_void_p), ("grad_v", C.c_void_p),
+                ("peer_dqkv_staging", C.c_void_p * MAX_WORLD_SIZE), ("peer_ready", C.c_void_p * MAX_WORLD_SIZE),
+                ("peer_done_epoch", C.c_void_p * MAX_WORLD_SIZE), ("weight", C.c_void_p),
+                ("grad_input", C.c_void_p), ("local_tokens", C.c_int32), ("hidden", C.c_int32),
+                ("batch", C.c_int32), ("q_heads", C.c_int32), ("kv_heads", C.c_int32), ("head_dim", C.c_int32),
+                ("world_size", C.c_int32), ("rank", C.c_int32), ("num_comm_ctas", C.c_int32),
+                ("gemm_policy", C.c_int32), ("gemm_tuning", BackwardGemmTuning), ("epoch", C.c_uint32),
+                ("causal_load_balanced", C.c_uint8), ("alpha", C.c_float)]
+    _defaults_ = {"batch": 1, "world_size": 1, "alpha": 1.0}
+
+
+class QkvBackwardWeightParams(_Record):
+    """include/fuse/operators/ulysses/qkv_backward.h:62-73 of the reference."""
+    _fields_ = [("dqkv_staging", C.c_void_p), ("saved_input", C.c_void_p), ("grad_weight", C.c_void_p),
+                ("local_tokens", C.c_int32), ("hidden", C.c_int32), ("q_heads", C.c_int32),
+                ("kv_heads", C.c_int32), ("head_dim", C.c_int32), ("alpha", C.c_float), ("beta", C.c_float)]
+    _defaults_ = {"alpha": 1.0}
+
+
+class QkvBackwardParams(_Record):
+    _fields_ = [("data", QkvBackwardDataParams), ("weight", QkvBackwardWeightParams),
+                ("weight_mode", C.c_int32)]
+
+
+class OprojBackwardDataParams(_Record):
+    """include/fuse/operators/ulysses/oproj_backward.h:21-43 of the reference."""
+    _fields_ = [("grad_output", C.c_void_p), ("weight", C.c_void_p), ("local_grad_attention", C.c_void_p),
+                ("peer_grad_attention", C.c_void_p * MAX_WORLD_SIZE),
+                ("peer_done_epoch", C.c_void_p * MAX_WORLD_SIZE), ("ready", C.c_void_p),
+                ("local_tokens", C.c_int32), ("hidden", C.c_int32), ("batch", C.c_int32),
+                ("q_heads", C.c_int32), ("head_dim", C.c_int32), ("world_size", C.c_int32),
+                ("rank", C.c_int32), ("num_comm_ctas", C.c_int32), ("gemm_policy", C.c_int32),
+                ("gemm_tuning", BackwardGemmTuning), ("epoch", C.c_uint32),
+                ("causal_load_balanced", C.c_uint8), ("alpha", C.c_float)]
+    _defaults_ = {"batch": 1, "world_size": 1, "alpha": 1.0}
+
+
+class OprojBackwardWeightParams(_Record):
+    """include/fuse/operators/ulysses/oproj_backward.h:54-64 of the reference."""
+    _fields_ = [("grad_output", C.c_void_p), ("saved_attention", C.c_void_p), ("grad_weight", C.c_void_p),
+                ("local_tokens", C.c_int32), ("hidden", C.c_int32), ("q_heads", C.c_int32),
+                ("head_dim", C.c_int32), ("alpha", C.c_float), ("beta", C.c_float)]
+    _defaults_ = {"alpha": 1.0}
+
+
+class OprojBackwardParams(_Record):
+    _fields_ = [("data", OprojBackwardDataParams), ("weight", OprojBackwardWeightParams),
+                ("weight_mode", C.c_int32)]
+
+
 ABI_RECORDS = {0: GemmProblem, 1: UlyssesRoute, 2: GemmA2AParams, 3: A2AGemmParams,
-               4: KernelTraits, 5: Options}
+               4: KernelTraits, 5: Options, 6: QkvBackwardDataParams, 7: QkvBackwardWeightParams,
+               8: QkvBackwardParams, 9: OprojBackwardDataParams, 10: OprojBackwardWeightParams,
+               11: OprojBackwardParams}
 
 # Every symbol include/fuse_b200.h declares: name -> (restype, argtypes).
 _P = C.c_void_p
@@ -123,6 +192,18 @@ SYMBOLS = {
     "fuse_launch_a2a_gemm_cutlass_ex": (C.c_int, [C.POINTER(A2AGemmParams), C.POINTER(Options), _P]),
     "fuse_launch_batched_cutlass_reference": (C.c_int, [C.POINTER(GemmA2AParams), _P, C.c_int32]),
     "fuse_launch_a2a_gemm_cutlass_reference": (C.c_int, [C.POINTER(A2AGemmParams), _P, C.c_int32]),
+    "fuse_launch_qkv_backward_data": (C.c_int, [C.POINTER(QkvBackwardDataParams), _P]),
+    "fuse_launch_qkv_backward_data_ex": (C.c_int, [C.POINTER(QkvBackwardDataParams), C.POINTER(Options), _P]),
+    "fuse_launch_qkv_backward_weight": (C.c_int, [C.POINTER(QkvBackwardWeightParams), _P]),
+    "fuse_launch_qkv_backward": (C.c_int, [C.POINTER(QkvBackwardParams), _P]),
+    "fuse_launch_oproj_backward_data": (C.c_int, [C.POINTER(OprojBackwardDataParams), _P]),
+    "fuse_launch_oproj_backward_data_ex": (C.c_int, [C.POINTER(OprojBackwardDataParams), C.POINTER(Options), _P]),
+    "fuse_launch_oproj_backward_weight": (C.c_int, [C.POINTER(OprojBackwardWeightParams), _P]),
+    "fuse_launch_oproj_backward": (C.c_int, [C.POINTER(OprojBackwardParams), _P]),
+    "fuse_qkv_backward_ready_elements": (C.c_int64, [C.POINTER(QkvBackwardDataParams)]),
+    "fuse_oproj_backward_ready_elements": (C.c_int64, [C.POINTER(OprojBackwardDataParams)]),
+    "fuse_recommended_qkv_backward_comm_ctas": (C.c_int32, [C.POINTER(QkvBackwardDataParams)]),
+    "fuse_recommended_oproj_backward_comm_ctas": (C.c_int32, [C.POINTER(OprojBackwardDataParams)]),
     "fuse_qkv_cutlass_kernel_traits": (None, [C.POINTER(GemmProblem), C.POINTER(KernelTraits)]),
     "fuse_cutlass_kernel_traits": (None, [C.POINTER(KernelTraits)]),
     "fuse_a2a_lhs_gemm_ready_elements": (C.c_int64, [C.POINTER(GemmProblem), C.POINTER(UlyssesRoute)]),

@@ -10,7 +10,8 @@ import ctypes as C
 
 from . import _native as N
 from ._native import (A2AGemmParams, GemmA2AParams, GemmProblem, KernelTraits, Options,  # noqa: F401
-                      UlyssesRoute)
+                      OprojBackwardDataParams, OprojBackwardParams, OprojBackwardWeightParams,
+                      QkvBackwardDataParams, QkvBackwardParams, QkvBackwardWeightParams, UlyssesRoute)
 
 
 def _opt(options):
@@ -90,3 +91,45 @@ def qkv_ready_elements(problem: GemmProblem) -> int:
 def generate_bf16(ptr: int, count: int, seed: int, scale: float, normal: bool = False, stream: int = 0) -> int:
     """Seeded device-side fill (uniform, or N(0, scale^2) when `normal`)."""
     return N.lib().fuse_b200_generate_bf16(ptr, count, seed, scale, 1 if normal else 0, stream)
+
+
+# ---- backward (include/fuse/operators/ulysses/{qkv,oproj}_backward.h of the reference) ----------
+
+def launch_qkv_backward_data(params: QkvBackwardDataParams, stream: int = 0, options: Options | None = None) -> int:
+    """Reverse all-to-all of planar dQ/dK/dV + dX = dQKV W (fuse::launch_qkv_backward_data)."""
+    if options is None:
+        return N.lib().fuse_launch_qkv_backward_data(C.byref(params), stream)
+    return N.lib().fuse_launch_qkv_backward_data_ex(C.byref(params), _opt(options), stream)
+
+
+def launch_qkv_backward_weight(params: QkvBackwardWeightParams, stream: int = 0) -> int:
+    """dW = alpha dQKV^T X + beta dW (fuse::launch_qkv_backward_weight)."""
+    return N.lib().fuse_launch_qkv_backward_weight(C.byref(params), stream)
+
+
+def launch_qkv_backward(params: QkvBackwardParams, stream: int = 0) -> int:
+    return N.lib().fuse_launch_qkv_backward(C.byref(params), stream)
+
+
+def launch_oproj_backward_data(params: OprojBackwardDataParams, stream: int = 0,
+                               options: Options | None = None) -> int:
+    """dA = dY Wo + sequence->head all-to-all (fuse::launch_oproj_backward_data)."""
+    if options is None:
+        return N.lib().fuse_launch_oproj_backward_data(C.byref(params), stream)
+    return N.lib().fuse_launch_oproj_backward_data_ex(C.byref(params), _opt(options), stream)
+
+
+def launch_oproj_backward_weight(params: OprojBackwardWeightParams, stream: int = 0) -> int:
+    return N.lib().fuse_launch_oproj_backward_weight(C.byref(params), stream)
+
+
+def launch_oproj_backward(params: OprojBackwardParams, stream: int = 0) -> int:
+    return N.lib().fuse_launch_oproj_backward(C.byref(params), stream)
+
+
+def qkv_backward_ready_elements(params: QkvBackwardDataParams) -> int:
+    return N.lib().fuse_qkv_backward_ready_elements(C.byref(params))
+
+
+def oproj_backward_ready_elements(params: OprojBackwardDataParams) -> int:
+    return N.lib().fuse_oproj_backward_ready_elements(C.byref(params))

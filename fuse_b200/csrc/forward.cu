@@ -5,16 +5,12 @@
 #include <cmath>
 #include <cstring>
 
-#include "fuse_b200.h"
-#include "fused_gemm.cuh"
-#include "host.cuh"
+#include "launch.cuh"
 
 namespace fuse_b200 {
 namespace {
 
-using host::DeviceInfo;
-
-int64_t packed_or(int64_t stride, int64_t packed) { return stride < 0 ? packed : stride; }
+using namespace launch;
 
 // detail/gemm.cuh:53-70 (supported_problem): row-major A[M,K], B[N,K], D[M,N], 16-byte rows.
 bool supported_problem(const fuse_gemm_problem& g) {
@@ -32,94 +28,21 @@ bool supported_problem(const fuse_gemm_problem& g) {
           g.raster == FUSE_RASTER_ALONG_N);
 }
 
-int choose_block_n(const fuse_gemm_problem& g, const fuse_b200_options* options) {
-  if (options && (options->block_n == 128 || options->block_n == 256)) return options->block_n;
-  return g.n % 256 == 0 || g.n > 1024 ? 256 : 128;
-}
-
-struct Operands {
-  CUtensorMap a, b;
-};
-
 cudaError_t encode_operands(Operands* maps, const void* a, int64_t lda, const void* b, int64_t ldb,
                             const fuse_gemm_problem& g, int block_n) {
-  cudaError_t status = host::encode_tensor_map_2d(
-      &maps->a, a, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, uint64_t(g.m), uint64_t(g.k),
-      uint64_t(lda) * 2, kBlockM, kBlockK, CU_TENSOR_MAP_SWIZZLE_128B);
+  cudaError_t status = encode_operand(&maps->a, a, g.m, g.k, lda, false, kBlockM);
   if (status != cudaSuccess) return status;
-  return host::encode_tensor_map_2d(&maps->b, b, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, uint64_t(g.n),
-                                    uint64_t(g.k), uint64_t(ldb) * 2, uint32_t(block_n), kBlockK,
-                                    CU_TENSOR_MAP_SWIZZLE_128B);
+  return encode_operand(&maps->b, b, g.n, g.k, ldb, false, block_n);
 }
 
 void fill_core(FusedParams* p, const fuse_gemm_problem& g, int block_n, int num_comm_ctas,
                float alpha, void* d, int default_raster) {
-  p->m = g.m;
-  p->n = g.n;
-  p->k = g.k;
-  p->order.m_tiles = host::ceil_div(g.m, kBlockM);
-  p->order.n_tiles = host::ceil_div(g.n, block_n);
-  p->order.swizzle = select_swizzle(g.max_swizzle_size, p->order.m_tiles, p->order.n_tiles);
-  const int raster = g.raster == FUSE_RASTER_HEURISTIC ? default_raster : g.raster;
-  p->order.along_n = raster == FUSE_RASTER_ALONG_N ? 1 : 0;
-  p->num_comm_ctas = num_comm_ctas;
-  p->alpha = alpha;
-  p->beta = 0.0f;
-  p->d = static_cast<uint16_t*>(d);
-  p->ldd = packed_or(g.stride_d.row, g.n);
+  launch::fill_core(p, g.m, g.n, g.k, block_n, num_comm_ctas, alpha, 0.0f, d, packed_or(g.stride_d.row, g.n),
+                    g.raster == FUSE_RASTER_HEURISTIC ? default_raster : g.raster, g.max_swizzle_size);
 }
 
-// Tensor map of a row-major BF16 [rows, cols] destination for the TMA-store epilogue.
-cudaError_t encode_store_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
-                             int64_t pitch_elements) {
-  return host::encode_tensor_map_2d(map, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, cols,
-                                    uint64_t(pitch_elements) * 2, kBlockM, 64,
-                                    CU_TENSOR_MAP_SWIZZLE_128B);
-}
-
-template <int kMode, bool kTmaEpilogue>
-cudaError_t launch_variant(const Operands& maps, const StoreMaps& stores, const FusedParams& p,
-                           int block_n, const DeviceInfo& info, cudaStream_t stream) {
-  const int64_t tiles = p.order.count();
-  const int compute_capacity = info.sm_count - p.num_comm_ctas;
-  const int compute = int(tiles < compute_capacity ? tiles : compute_capacity);
-  const int grid = p.num_comm_ctas + compute;
-  const bool cooperative = kMode != kModePlain;
-  if (block_n == 256) {
-    using Layout = SmemLayout<256, 4>;
-    return host::launch_kernel(fused_gemm_kernel<256, 4, kMode, kTmaEpilogue>, grid, kThreads,
-                               Layout::kDynamicBytes, cooperative, stream, maps.a, maps.b, stores, p);
-  }
-  using Layout = SmemLayout<128, 6>;
-  return host::launch_kernel(fused_gemm_kernel<128, 6, kMode, kTmaEpilogue>, grid, kThreads,
-                             Layout::kDynamicBytes, cooperative, stream, maps.a, maps.b, stores, p);
-}
-
-// The epilogue writes the local output through the copy engine unless the caller asked for the
-// 16-byte vector epilogue (FUSE_B200_VECTOR_EPILOGUE) or the mode needs it (beta != 0, tile
-// publication to communication CTAs).
-template <int kMode>
-cudaError_t launch_mode(const Operands& maps, StoreMaps& stores, const FusedParams& p, int block_n,
-                        const DeviceInfo& info, cudaStream_t stream, bool tma_epilogue) {
-  if constexpr (kMode != kModeQkvPush) {
-    if (tma_epilogue) {
-      const cudaError_t status = encode_store_map(&stores.local, p.d, uint64_t(p.m), uint64_t(p.n), p.ldd);
-      if (status != cudaSuccess) return status;
-      return launch_variant<kMode, true>(maps, stores, p, block_n, info, stream);
-    }
-  }
-  return launch_variant<kMode, false>(maps, stores, p, block_n, info, stream);
-}
-
-bool vector_epilogue_requested(const fuse_b200_options* options) {
-  return options != nullptr && (options->flags & FUSE_B200_VECTOR_EPILOGUE) != 0;
-}
-
-cudaError_t check_device(DeviceInfo* info) {
-  const cudaError_t status = host::device_info(info);
-  if (status != cudaSuccess) return status;
-  // Compiled for sm_100a only: tcgen05 / TMEM kernels exist for no other target.
-  return info->cc_major == 10 ? cudaSuccess : cudaErrorNotSupported;
+int choose_block_n(const fuse_gemm_problem& g, const fuse_b200_options* options) {
+  return launch::choose_block_n(g.n, options);
 }
 
 // How the routed output leaves the SM: from communication CTAs that copy published tiles
@@ -205,19 +128,10 @@ cudaError_t qkv_forward(const fuse_gemm_a2a_params& p, const fuse_b200_options* 
   const fuse_ulysses_route& r = p.route;
   bool tma = !vector_epilogue_requested(options) && r.head_dim % 64 == 0 && r.seq_local % kBlockM == 0;
   if (tma) {
-    const uint64_t rows_total = uint64_t(r.batch) * uint64_t(r.global_seq);
-    const int64_t q_local = int64_t(r.q_heads) / r.world_size * r.head_dim;
-    const int64_t kv_local = int64_t(r.kv_heads) / r.world_size * r.head_dim;
-    for (int peer = 0; peer < r.world_size && tma; ++peer) {
-      for (int segment = 0; segment < 3; ++segment) {
-        const int64_t width = segment == 0 ? q_local : kv_local;
-        const int64_t offset = segment == 0 ? 0 : int64_t(rows_total) * q_local +
-                                                      (segment == 2 ? int64_t(rows_total) * kv_local : 0);
-        if (encode_store_map(&stores.peer[peer][segment], p.peer_output[peer] + offset, rows_total,
-                             uint64_t(width), width) != cudaSuccess)
-          tma = false;
-      }
-    }
+    tma = encode_peer_store_maps(&stores, p.peer_output, r.world_size,
+                                 uint64_t(r.batch) * uint64_t(r.global_seq),
+                                 int64_t(r.q_heads) / r.world_size * r.head_dim,
+                                 int64_t(r.kv_heads) / r.world_size * r.head_dim);
   }
   return launch_mode<kModeQkvDirect>(maps, stores, k, block_n, info, stream, tma);
 }
@@ -276,11 +190,7 @@ cudaError_t oproj_forward(const fuse_a2a_gemm_params& p, const fuse_b200_options
   k.flags = options ? options->flags : 0u;
   if (options && (options->flags & FUSE_B200_VECTOR_PULL)) k.flags |= kFlagVectorPull;
   k.wait = host::make_wait(info, p.epoch, options ? options->wait_budget_ns : 0);
-  if (options != nullptr) {
-    k.trace = options->trace;
-    k.trace_capacity = options->trace_capacity;
-    k.trace_cta = options->trace_cta;
-  }
+  copy_trace(&k, options);
   k.lhs.world = p.route.world_size;
   k.lhs.rank = p.route.rank;
   k.lhs.seq_local = p.route.seq_local;
@@ -409,6 +319,12 @@ int fuse_b200_abi_sizeof(int record) {
     case 3: return int(sizeof(fuse_a2a_gemm_params));
     case 4: return int(sizeof(fuse_kernel_traits));
     case 5: return int(sizeof(fuse_b200_options));
+    case 6: return int(sizeof(fuse_qkv_backward_data_params));
+    case 7: return int(sizeof(fuse_qkv_backward_weight_params));
+    case 8: return int(sizeof(fuse_qkv_backward_params));
+    case 9: return int(sizeof(fuse_oproj_backward_data_params));
+    case 10: return int(sizeof(fuse_oproj_backward_weight_params));
+    case 11: return int(sizeof(fuse_oproj_backward_params));
     default: return -1;
   }
 }

@@ -36,6 +36,7 @@ constexpr int kUmmaK = 16;
 constexpr int kThreads = 256;
 constexpr int kEpilogueThreads = 128;
 constexpr int kAccumStages = 2;
+constexpr uint32_t kMnGroupBytes = 64 * kBlockK * 2;  // one [64 K rows x 64 MN] box of an MN-major tile
 
 enum FusedMode : int {
   kModePlain = 0,     // GEMM only
@@ -43,6 +44,8 @@ enum FusedMode : int {
   kModeLhsPull = 2,   // comm CTAs pull the lhs shards from peers -> gated GEMM
   kModeQkvDirect = 3, // GEMM whose epilogue stores each vector to local_output AND to its place
                       // in the owning peer's planar Q|K|V; no communication CTAs, no tile flags
+  kModeHeadGate = 4,  // QKV backward data: comm CTAs push this rank's planar dQ/dK/dV into every
+                      // destination's packed staging; the GEMM's K loop is gated per (M tile, head)
 };
 
 enum LaunchFlags : uint32_t {
@@ -52,6 +55,10 @@ enum LaunchFlags : uint32_t {
   // Communication CTAs of the lhs pull move data with 16-byte loads/stores instead of the
   // bulk-copy pipeline (kept for comparison and as the fallback).
   kFlagVectorPull = 8u,
+  // Run only one of the two roles of a fused kernel (single-GPU emulation of operators whose
+  // GEMM waits for data pushed by other ranks: all ranks push first, then all ranks compute).
+  kFlagCommOnly = 32u,
+  kFlagComputeOnly = 64u,
 };
 
 // Tensor maps of the TMA-store epilogue: the local output and, for the direct QKV push, every
@@ -64,6 +71,7 @@ struct alignas(64) StoreMaps {
 struct QkvRoute {
   int32_t world, rank, batch, seq_local, global_seq;
   int32_t q_heads, kv_heads, head_dim;
+  int32_t causal;  // head-only (output-projection backward) routes may use the causal row map
   uint16_t* peer_output[kMaxWorldSize];
   uint32_t* peer_done[kMaxWorldSize];
 };
@@ -77,6 +85,17 @@ struct LhsRoute {
   uint32_t input_epoch;
   uint16_t* staging;          // [M, lda]
   int64_t lda;
+};
+
+// QKV backward reverse route (head -> sequence), sender side: this rank holds planar
+// dQ, dK, dV for its local heads and all global rows, and writes each destination's rows into
+// that destination's packed staging [M, (q + 2 kv) * head_dim].
+struct GradRoute {
+  int32_t world, rank, seq_local, global_seq, m;   // m = rows per rank (same on every rank)
+  int32_t q_heads, kv_heads, head_dim, causal;
+  const uint16_t* grad[3];                          // dQ, dK, dV planes of this rank
+  uint16_t* peer_staging[kMaxWorldSize];
+  uint32_t* peer_ready[kMaxWorldSize];              // [m_tiles * (q + 2 kv)] flags on each peer
 };
 
 struct FusedParams {
@@ -96,6 +115,7 @@ struct FusedParams {
   WaitContext wait;
   QkvRoute qkv;
   LhsRoute lhs;
+  GradRoute grad;
 };
 
 template <int kBlockN, int kStages>
@@ -202,7 +222,7 @@ __device__ __forceinline__ void qkv_push_role(const FusedParams& p, uint8_t* sme
     } else if (tid >= 128) {
       const int32_t row = m0 + (tid - 128);
       row_dest[tid - 128] =
-          row < p.m ? global_row(r.world, r.rank, r.seq_local, r.global_seq, false, row) : -1;
+          row < p.m ? global_row(r.world, r.rank, r.seq_local, r.global_seq, r.causal != 0, row) : -1;
     }
     if (tid == 0) {
       const int64_t flag = (int64_t(mt) * p.order.n_tiles + nt) * kReadyFlagStride;
@@ -571,6 +591,74 @@ __device__ __forceinline__ void lhs_pull_bulk_role(const FusedParams& p, uint32_
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Communication role: QKV backward reverse route, sender push.
+//
+// Unit of work = (destination rank, destination M tile, one of this rank's local heads of
+// dQ / dK / dV): 128 rows x head_dim columns copied with 16-byte accesses from the local plane
+// [B*S_global, local_heads*head_dim] into the destination's packed staging at the head's place
+// in [all Q, all K, all V] order, then ready[m_tile * heads + head] = epoch is released at
+// system scope on the destination (csrc/operators/sm103/detail/backward.cuh:208-279).
+// Destinations are visited starting from the next rank so that ranks do not all write to the
+// same peer at once.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void grad_push_role(const FusedParams& p) {
+  const GradRoute& g = p.grad;
+  const int tid = threadIdx.x;
+  const int32_t m_tiles = (g.m + kBlockM - 1) / kBlockM;
+  const int32_t q_local = g.q_heads / g.world, kv_local = g.kv_heads / g.world;
+  const int32_t local_heads = q_local + 2 * kv_local;
+  const int32_t heads_total = g.q_heads + 2 * g.kv_heads;
+  const int32_t width = heads_total * g.head_dim;
+  const int32_t chunks_per_row = g.head_dim / 8;
+  const int64_t units = int64_t(m_tiles) * g.world * local_heads;
+  for (int64_t u = blockIdx.x; u < units; u += p.num_comm_ctas) {
+    const int32_t head_slot = int32_t(u % local_heads);
+    const int32_t rest = int32_t(u / local_heads);
+    const int32_t dest = (g.rank + 1 + rest % g.world) % g.world;
+    const int32_t mt = rest / g.world;
+    const int32_t segment = head_slot < q_local ? 0 : (head_slot < q_local + kv_local ? 1 : 2);
+    const int32_t local_head = head_slot - (segment == 0 ? 0 : q_local + (segment == 2 ? kv_local : 0));
+    const int32_t seg_local_heads = segment == 0 ? q_local : kv_local;
+    const int32_t seg_heads = segment == 0 ? g.q_heads : g.kv_heads;
+    const int32_t head = (segment == 0 ? 0 : g.q_heads + (segment == 2 ? g.kv_heads : 0)) +
+                         g.rank * seg_local_heads + local_head;
+    (void)seg_heads;
+    const int64_t plane_width = int64_t(seg_local_heads) * g.head_dim;
+    const uint16_t* src = g.grad[segment] + int64_t(local_head) * g.head_dim;
+    uint16_t* dst = g.peer_staging[dest] + int64_t(head) * g.head_dim;
+    const int32_t m0 = mt * kBlockM;
+    const int32_t rows = g.m - m0 < kBlockM ? g.m - m0 : kBlockM;
+    const int32_t total = rows * chunks_per_row;
+    for (int32_t i0 = tid; i0 < total; i0 += kThreads * 4) {
+      uint4 value[4];
+      uint16_t* out[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int32_t i = i0 + j * kThreads;
+        out[j] = nullptr;
+        if (i < total) {
+          const int32_t row = i / chunks_per_row, chunk = i - row * chunks_per_row;
+          const int64_t src_row = global_row(g.world, dest, g.seq_local, g.global_seq, g.causal != 0, m0 + row);
+          value[j] = *reinterpret_cast<const uint4*>(src + src_row * plane_width + chunk * 8);
+          out[j] = dst + int64_t(m0 + row) * width + chunk * 8;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (out[j] != nullptr) ptx::st_v4(out[j], value[j]);
+    }
+    __syncthreads();  // every thread's stores of this unit are issued ...
+    if (tid == 0) {
+      __threadfence_system();  // ... and performed before the destination sees the flag
+      ptx::fence_proxy_async_global();
+      ptx::st_release_sys(g.peer_ready[dest] + (int64_t(mt) * heads_total + head) * kReadyFlagStride,
+                          p.wait.epoch);
+    }
+  }
+  __threadfence_system();
+}
+
 // 32 FP32 accumulators of one output row -> alpha (and beta * old D) -> BF16 -> four 16-byte
 // stores.  `col` is the global column of acc[0]; vectors past N are skipped (N % 8 == 0).
 struct PeerRow {
@@ -642,7 +730,11 @@ __device__ __forceinline__ void stage_accumulators(const uint32_t (&acc)[32], ui
 // ------------------------------------------------------------------------------------------
 // The kernel.
 // ------------------------------------------------------------------------------------------
-template <int kBlockN, int kStages, int kMode, bool kTmaEpilogue>
+// kAMn / kBMn: the operand is stored with its M (resp. N) axis contiguous -- [K, M] / [K, N]
+// row-major -- and is fed to the tensor core as an MN-major tile: 64-element groups along MN,
+// each a [64 K rows x 128 bytes] swizzled box (the data-gradient GEMMs read the forward weight
+// as stored, the weight-gradient GEMMs read both operands along the token axis).
+template <int kBlockN, int kStages, int kMode, bool kTmaEpilogue, bool kAMn = false, bool kBMn = false>
 __global__ void __launch_bounds__(kThreads, 1)
 fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b,
@@ -654,13 +746,17 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   uint8_t* smem = smem_raw + (base - raw_addr);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool is_comm = int(blockIdx.x) < p.num_comm_ctas;
+  const bool skip_role = (p.flags & (is_comm ? kFlagComputeOnly : kFlagCommOnly)) != 0u;
 
-  if (is_comm) {
+  if (skip_role) {
+    // nothing: this launch runs the other role only
+  } else if (is_comm) {
     if constexpr (kMode == kModeQkvPush) qkv_push_role<kBlockN>(p, smem);
     if constexpr (kMode == kModeLhsPull) {
       if (p.flags & kFlagVectorPull) lhs_pull_role(p, smem);
       else lhs_pull_bulk_role(p, base);
     }
+    if constexpr (kMode == kModeHeadGate) grad_push_role(p);
   } else {
     const uint32_t bar_base = base + Layout::kBarrierOffset;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -709,14 +805,20 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           p.order.decode(t, mt, nt);
           int32_t gated_upto = -1;  // highest K shard already acquired for this tile
           for (int32_t kb = 0; kb < k_blocks; ++kb) {
-            if constexpr (kMode == kModeLhsPull) {
-              int32_t last = (kb * kBlockK + kBlockK - 1) / p.lhs.shard_width;
-              if (last >= p.lhs.world) last = p.lhs.world - 1;
+            if constexpr (kMode == kModeLhsPull || kMode == kModeHeadGate) {
+              // K groups whose rows arrive separately: peers' shards (forward pull, flags set by
+              // this GPU's communication CTAs) or Q/K/V heads (backward, flags set by the
+              // sending GPUs at system scope).
+              constexpr bool kRemoteWriter = kMode == kModeHeadGate;
+              const int32_t group_width = kRemoteWriter ? p.grad.head_dim : p.lhs.shard_width;
+              const int32_t groups = kRemoteWriter ? p.grad.q_heads + 2 * p.grad.kv_heads : p.lhs.world;
+              int32_t last = (kb * kBlockK + kBlockK - 1) / group_width;
+              if (last >= groups) last = groups - 1;
               while (ok && gated_upto < last) {
                 ++gated_upto;
-                const int64_t flag = (int64_t(mt) * p.lhs.world + gated_upto) * kReadyFlagStride;
-                ok = flag_wait<false>(p.ready + flag, p.wait.epoch, p.wait, kSiteLhsReady,
-                                      uint32_t(flag / kReadyFlagStride));
+                const int64_t flag = (int64_t(mt) * groups + gated_upto) * kReadyFlagStride;
+                ok = flag_wait<kRemoteWriter>(p.ready + flag, p.wait.epoch, p.wait, kSiteLhsReady,
+                                              uint32_t(flag / kReadyFlagStride));
                 ptx::fence_proxy_async_global();
               }
               if (!ok) break;
@@ -725,9 +827,23 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             if (!ok) break;
             ptx::mbar_expect_tx(full_bar(stage), Layout::kStageBytes);
             const uint32_t a_dst = base + stage * Layout::kStageBytes;
-            ptx::tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * kBlockK, mt * kBlockM);
-            ptx::tma_load_2d(a_dst + Layout::kABytes, &tmap_b, full_bar(stage), kb * kBlockK,
-                             nt * kBlockN);
+            if constexpr (!kAMn) {
+              ptx::tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * kBlockK, mt * kBlockM);
+            } else {
+#pragma unroll
+              for (int g = 0; g < kBlockM / 64; ++g)
+                ptx::tma_load_2d(a_dst + g * kMnGroupBytes, &tmap_a, full_bar(stage),
+                                 mt * kBlockM + g * 64, kb * kBlockK);
+            }
+            if constexpr (!kBMn) {
+              ptx::tma_load_2d(a_dst + Layout::kABytes, &tmap_b, full_bar(stage), kb * kBlockK,
+                               nt * kBlockN);
+            } else {
+#pragma unroll
+              for (int g = 0; g < kBlockN / 64; ++g)
+                ptx::tma_load_2d(a_dst + Layout::kABytes + g * kMnGroupBytes, &tmap_b, full_bar(stage),
+                                 nt * kBlockN + g * 64, kb * kBlockK);
+            }
             issued_mask |= 1u << stage;
             issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
             if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -744,7 +860,11 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     } else if (warp == 1) {
       // ------------------------------------------------------------------ UMMA issuer
       if (lane == 0) {
-        constexpr uint32_t kIdesc = ptx::idesc_bf16_f32(kBlockM, kBlockN, 0, 0);
+        constexpr uint32_t kIdesc = ptx::idesc_bf16_f32(kBlockM, kBlockN, kAMn ? 1 : 0, kBMn ? 1 : 0);
+        // Descriptor address step per UMMA (16 K values): 32 bytes inside the swizzle row of a
+        // K-major tile, 16 rows of 128 bytes in an MN-major tile.
+        constexpr uint64_t kAStep = kAMn ? (kUmmaK * 128) >> 4 : (kUmmaK * 2) >> 4;
+        constexpr uint64_t kBStep = kBMn ? (kUmmaK * 128) >> 4 : (kUmmaK * 2) >> 4;
         uint32_t stage = 0, phase = 0, accum = 0, accum_phase = 0;
         bool ok = true;
         for (int64_t t = compute_id; ok && t < tiles; t += compute_ctas) {
@@ -757,12 +877,13 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             if (!ok) break;
             ptx::tc_fence_after();
             const uint32_t a_addr = base + stage * Layout::kStageBytes;
-            const uint64_t a_desc = ptx::smem_desc_k_sw128(a_addr);
-            const uint64_t b_desc = ptx::smem_desc_k_sw128(a_addr + Layout::kABytes);
+            const uint64_t a_desc = kAMn ? ptx::smem_desc_mn_sw128(a_addr, kMnGroupBytes)
+                                         : ptx::smem_desc_k_sw128(a_addr);
+            const uint64_t b_desc = kBMn ? ptx::smem_desc_mn_sw128(a_addr + Layout::kABytes, kMnGroupBytes)
+                                         : ptx::smem_desc_k_sw128(a_addr + Layout::kABytes);
 #pragma unroll
             for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-              // +32 bytes along K inside the swizzle row = +2 in the descriptor's address field
-              ptx::umma_f16(d_tmem, a_desc + uint64_t(2 * k), b_desc + uint64_t(2 * k), kIdesc,
+              ptx::umma_f16(d_tmem, a_desc + kAStep * k, b_desc + kBStep * k, kIdesc,
                             (kb | k) != 0 ? 1u : 0u);
             }
             ptx::umma_commit(empty_bar(stage));  // frees the stage when these UMMAs retire
@@ -809,7 +930,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           peer.col_stride = col_stride;
           const int32_t local_row = mt * kBlockM + quarter * 32 + lane;
           peer.dest_row = local_row < p.m ? global_row(p.qkv.world, p.qkv.rank, p.qkv.seq_local,
-                                                       p.qkv.global_seq, false, local_row)
+                                                       p.qkv.global_seq, p.qkv.causal != 0, local_row)
                                           : 0;
           table ^= 1u;
         }
@@ -857,10 +978,10 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const int32_t segment = col < q_width ? 0 : (col < q_width + kv_width ? 1 : 2);
                   const int32_t within = col - (segment == 0 ? 0 : q_width + (segment == 2 ? kv_width : 0));
                   const int32_t local_width = (segment == 0 ? q_width : kv_width) / r.world;
-                  const int32_t owner = within / local_width;
+                  const int32_t owner = within / local_width;  // segment > 0 only when kv_heads > 0
                   ptx::tma_store_2d(&store_maps.peer[owner][segment], staging, within - owner * local_width,
-                                    int32_t(global_row(r.world, r.rank, r.seq_local, r.global_seq, false,
-                                                       mt * kBlockM)));
+                                    int32_t(global_row(r.world, r.rank, r.seq_local, r.global_seq,
+                                                       r.causal != 0, mt * kBlockM)));
                 }
               }
               ptx::bulk_commit();
@@ -910,7 +1031,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   }
 
-  if constexpr (kMode == kModeQkvPush || kMode == kModeQkvDirect) {
+  if constexpr (kMode == kModeQkvPush || kMode == kModeQkvDirect || kMode == kModeHeadGate) {
     cooperative_groups::this_grid().sync();
     qkv_finalize(p);
   }

@@ -1,0 +1,135 @@
+// Host-side launch helpers shared by the operator entry points: operand tensor maps for K-major
+// and MN-major operands, the epilogue's store maps, grid sizing and the kernel launch itself.
+#pragma once
+
+#include <cmath>
+#include <cstring>
+
+#include "fuse_b200.h"
+#include "fused_gemm.cuh"
+#include "host.cuh"
+
+namespace fuse_b200 {
+namespace launch {
+
+using host::DeviceInfo;
+
+inline int64_t packed_or(int64_t stride, int64_t packed) { return stride < 0 ? packed : stride; }
+
+struct Operands {
+  CUtensorMap a, b;
+};
+
+// K-major operand: stored [rows, k] row-major (rows = M for A, N for B), boxed
+// [block_rows x 64].  MN-major operand: stored [k, rows] row-major, boxed [64 x 64].
+inline cudaError_t encode_operand(CUtensorMap* map, const void* base, int64_t rows, int64_t k,
+                                  int64_t pitch_elements, bool mn_major, int block_rows) {
+  if (!mn_major)
+    return host::encode_tensor_map_2d(map, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, uint64_t(rows),
+                                      uint64_t(k), uint64_t(pitch_elements) * 2, uint32_t(block_rows),
+                                      kBlockK, CU_TENSOR_MAP_SWIZZLE_128B);
+  return host::encode_tensor_map_2d(map, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, uint64_t(k),
+                                    uint64_t(rows), uint64_t(pitch_elements) * 2, kBlockK, 64,
+                                    CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+// Tensor map of a row-major BF16 [rows, cols] destination for the TMA-store epilogue.
+inline cudaError_t encode_store_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t cols,
+                                    int64_t pitch_elements) {
+  return host::encode_tensor_map_2d(map, base, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, cols,
+                                    uint64_t(pitch_elements) * 2, kBlockM, 64,
+                                    CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+inline void fill_core(FusedParams* p, int m, int n, int k, int block_n, int num_comm_ctas, float alpha,
+                      float beta, void* d, int64_t ldd, int raster, int max_swizzle) {
+  p->m = m;
+  p->n = n;
+  p->k = k;
+  p->order.m_tiles = host::ceil_div(m, kBlockM);
+  p->order.n_tiles = host::ceil_div(n, block_n);
+  p->order.swizzle = select_swizzle(max_swizzle, p->order.m_tiles, p->order.n_tiles);
+  p->order.along_n = raster == FUSE_RASTER_ALONG_N ? 1 : 0;
+  p->num_comm_ctas = num_comm_ctas;
+  p->alpha = alpha;
+  p->beta = beta;
+  p->d = static_cast<uint16_t*>(d);
+  p->ldd = ldd;
+}
+
+template <int kMode, bool kTmaEpilogue, bool kAMn, bool kBMn>
+cudaError_t launch_variant(const Operands& maps, const StoreMaps& stores, const FusedParams& p,
+                           int block_n, const DeviceInfo& info, cudaStream_t stream) {
+  const int64_t tiles = p.order.count();
+  const int compute_capacity = info.sm_count - p.num_comm_ctas;
+  const int compute = int(tiles < compute_capacity ? tiles : compute_capacity);
+  const int grid = p.num_comm_ctas + compute;
+  const bool cooperative = kMode != kModePlain;
+  if (block_n == 256) {
+    using Layout = SmemLayout<256, 4>;
+    return host::launch_kernel(fused_gemm_kernel<256, 4, kMode, kTmaEpilogue, kAMn, kBMn>, grid, kThreads,
+                               Layout::kDynamicBytes, cooperative, stream, maps.a, maps.b, stores, p);
+  }
+  using Layout = SmemLayout<128, 6>;
+  return host::launch_kernel(fused_gemm_kernel<128, 6, kMode, kTmaEpilogue, kAMn, kBMn>, grid, kThreads,
+                             Layout::kDynamicBytes, cooperative, stream, maps.a, maps.b, stores, p);
+}
+
+// The epilogue writes the local output through the copy engine unless the caller asked for the
+// 16-byte vector epilogue or the mode needs it (beta != 0, tile publication to communication
+// CTAs).
+template <int kMode, bool kAMn = false, bool kBMn = false>
+cudaError_t launch_mode(const Operands& maps, StoreMaps& stores, const FusedParams& p, int block_n,
+                        const DeviceInfo& info, cudaStream_t stream, bool tma_epilogue) {
+  if constexpr (kMode != kModeQkvPush) {
+    if (tma_epilogue) {
+      const cudaError_t status = encode_store_map(&stores.local, p.d, uint64_t(p.m), uint64_t(p.n), p.ldd);
+      if (status != cudaSuccess) return status;
+      return launch_variant<kMode, true, kAMn, kBMn>(maps, stores, p, block_n, info, stream);
+    }
+  }
+  return launch_variant<kMode, false, kAMn, kBMn>(maps, stores, p, block_n, info, stream);
+}
+
+inline bool vector_epilogue_requested(const fuse_b200_options* options) {
+  return options != nullptr && (options->flags & FUSE_B200_VECTOR_EPILOGUE) != 0;
+}
+
+inline cudaError_t check_device(DeviceInfo* info) {
+  const cudaError_t status = host::device_info(info);
+  if (status != cudaSuccess) return status;
+  // Compiled for sm_100a only: tcgen05 / TMEM kernels exist for no other target.
+  return info->cc_major == 10 ? cudaSuccess : cudaErrorNotSupported;
+}
+
+inline int choose_block_n(int n, const fuse_b200_options* options) {
+  if (options && (options->block_n == 128 || options->block_n == 256)) return options->block_n;
+  return n % 256 == 0 || n > 1024 ? 256 : 128;
+}
+
+// Fills the (peer, segment) store maps of a head-sharded planar destination; false when a map
+// cannot be encoded.
+inline bool encode_peer_store_maps(StoreMaps* stores, fuse_bf16* const* peer_output, int world,
+                                   uint64_t rows_total, int64_t q_local, int64_t kv_local) {
+  for (int peer = 0; peer < world; ++peer)
+    for (int segment = 0; segment < (kv_local > 0 ? 3 : 1); ++segment) {
+      const int64_t width = segment == 0 ? q_local : kv_local;
+      const int64_t offset =
+          segment == 0 ? 0 : int64_t(rows_total) * q_local + (segment == 2 ? int64_t(rows_total) * kv_local : 0);
+      if (encode_store_map(&stores->peer[peer][segment], peer_output[peer] + offset, rows_total,
+                           uint64_t(width), width) != cudaSuccess)
+        return false;
+    }
+  return true;
+}
+
+inline void copy_trace(FusedParams* k, const fuse_b200_options* options) {
+  if (options != nullptr) {
+    k->trace = options->trace;
+    k->trace_capacity = options->trace_capacity;
+    k->trace_cta = options->trace_cta;
+  }
+}
+
+}  // namespace launch
+}  // namespace fuse_b200

@@ -135,7 +135,12 @@ enum {
   FUSE_B200_VECTOR_PULL = 8u,
   /* Write outputs with 16-byte stores from registers instead of tensor stores staged in
    * shared memory. */
-  FUSE_B200_VECTOR_EPILOGUE = 16u
+  FUSE_B200_VECTOR_EPILOGUE = 16u,
+  /* Run only the communication CTAs / only the compute CTAs of a fused kernel.  For emulating
+   * several ranks on one GPU when the GEMM waits for data that other ranks push (QKV backward):
+   * every rank pushes first, then every rank computes. */
+  FUSE_B200_COMM_ONLY = 32u,
+  FUSE_B200_COMPUTE_ONLY = 64u
 };
 typedef struct fuse_b200_options {
   uint64_t wait_budget_ns; /* per-wait limit; 0 = FUSE_B200_WAIT_MS env (default 2000 ms) */
@@ -180,6 +185,108 @@ FUSE_API int32_t fuse_recommended_gemm_a2a_comm_ctas(const fuse_gemm_problem* pr
 FUSE_API int32_t fuse_recommended_a2a_lhs_gemm_comm_ctas(const fuse_gemm_problem* problem,
                                                 const fuse_ulysses_route* route);
 
+/* ---------------------------------------------------------------------------------------------
+ * Backward (BF16).  include/fuse/operators/ulysses/{backward_common,qkv_backward,oproj_backward}.h
+ * ------------------------------------------------------------------------------------------- */
+/* backward_common.h:12-15 */
+enum { FUSE_WEIGHT_GRADIENT_IMMEDIATE = 0, FUSE_WEIGHT_GRADIENT_DEFERRED = 1 };
+/* backward_common.h:20-28 (BackwardGemmPolicy): 0 auto, 1..5 M128 x N{64,128,160,192,256}, 6 N64 cluster. */
+/* backward_common.h:33-37 (BackwardGemmTuning). */
+typedef struct fuse_backward_gemm_tuning {
+  int32_t epilogue_n;
+  int32_t max_swizzle_size;
+  uint8_t along_m;
+} fuse_backward_gemm_tuning;
+
+/* qkv_backward.h:24-49 (QkvBackwardDataParams): grad_q/k/v are this rank's planar gradients
+ * [B*S_global, local_heads*head_dim]; peer_dqkv_staging[r] is rank r's packed [M, (q+2kv)*d]
+ * staging, peer_ready[r] its fuse_qkv_backward_ready_elements() flags, weight the stored
+ * forward weight [QKV, H], grad_input dX [M, H]. */
+typedef struct fuse_qkv_backward_data_params {
+  const fuse_bf16* grad_q;
+  const fuse_bf16* grad_k;
+  const fuse_bf16* grad_v;
+  fuse_bf16* peer_dqkv_staging[FUSE_MAX_WORLD_SIZE];
+  uint32_t* peer_ready[FUSE_MAX_WORLD_SIZE];
+  uint32_t* peer_done_epoch[FUSE_MAX_WORLD_SIZE];
+  const fuse_bf16* weight;
+  fuse_bf16* grad_input;
+  int32_t local_tokens, hidden, batch, q_heads, kv_heads, head_dim, world_size, rank, num_comm_ctas;
+  int32_t gemm_policy;
+  fuse_backward_gemm_tuning gemm_tuning;
+  uint32_t epoch;
+  uint8_t causal_load_balanced;
+  float alpha;
+} fuse_qkv_backward_data_params;
+
+/* qkv_backward.h:62-73 (QkvBackwardWeightParams): dW[QKV,H] = alpha dQKV^T X + beta dW. */
+typedef struct fuse_qkv_backward_weight_params {
+  const fuse_bf16* dqkv_staging;
+  const fuse_bf16* saved_input;
+  fuse_bf16* grad_weight;
+  int32_t local_tokens, hidden, q_heads, kv_heads, head_dim;
+  float alpha, beta;
+} fuse_qkv_backward_weight_params;
+
+/* qkv_backward.h:75-79 (QkvBackwardParams). */
+typedef struct fuse_qkv_backward_params {
+  fuse_qkv_backward_data_params data;
+  fuse_qkv_backward_weight_params weight;
+  int32_t weight_mode;
+} fuse_qkv_backward_params;
+
+/* oproj_backward.h:21-43 (OprojBackwardDataParams): dA[M,A] = alpha dY[M,H] Wo[H,A] into
+ * local_grad_attention, routed to peer_grad_attention[r] = rank r's [B*S_global, local_heads*d]. */
+typedef struct fuse_oproj_backward_data_params {
+  const fuse_bf16* grad_output;
+  const fuse_bf16* weight;
+  fuse_bf16* local_grad_attention;
+  fuse_bf16* peer_grad_attention[FUSE_MAX_WORLD_SIZE];
+  uint32_t* peer_done_epoch[FUSE_MAX_WORLD_SIZE];
+  uint32_t* ready;
+  int32_t local_tokens, hidden, batch, q_heads, head_dim, world_size, rank, num_comm_ctas;
+  int32_t gemm_policy;
+  fuse_backward_gemm_tuning gemm_tuning;
+  uint32_t epoch;
+  uint8_t causal_load_balanced;
+  float alpha;
+} fuse_oproj_backward_data_params;
+
+/* oproj_backward.h:54-64 (OprojBackwardWeightParams): dWo[H,A] = alpha dY^T A + beta dWo. */
+typedef struct fuse_oproj_backward_weight_params {
+  const fuse_bf16* grad_output;
+  const fuse_bf16* saved_attention;
+  fuse_bf16* grad_weight;
+  int32_t local_tokens, hidden, q_heads, head_dim;
+  float alpha, beta;
+} fuse_oproj_backward_weight_params;
+
+/* oproj_backward.h:66-70 (OprojBackwardParams). */
+typedef struct fuse_oproj_backward_params {
+  fuse_oproj_backward_data_params data;
+  fuse_oproj_backward_weight_params weight;
+  int32_t weight_mode;
+} fuse_oproj_backward_params;
+
+/* qkv_backward.h:145-167 / csrc/operators/sm103/api/backward.cuh:304-329. */
+FUSE_API int fuse_launch_qkv_backward_data(const fuse_qkv_backward_data_params* params, fuse_stream stream);
+FUSE_API int fuse_launch_qkv_backward_data_ex(const fuse_qkv_backward_data_params* params,
+                                     const fuse_b200_options* options, fuse_stream stream);
+FUSE_API int fuse_launch_qkv_backward_weight(const fuse_qkv_backward_weight_params* params, fuse_stream stream);
+FUSE_API int fuse_launch_qkv_backward(const fuse_qkv_backward_params* params, fuse_stream stream);
+/* oproj_backward.h:131-149. */
+FUSE_API int fuse_launch_oproj_backward_data(const fuse_oproj_backward_data_params* params, fuse_stream stream);
+FUSE_API int fuse_launch_oproj_backward_data_ex(const fuse_oproj_backward_data_params* params,
+                                       const fuse_b200_options* options, fuse_stream stream);
+FUSE_API int fuse_launch_oproj_backward_weight(const fuse_oproj_backward_weight_params* params, fuse_stream stream);
+FUSE_API int fuse_launch_oproj_backward(const fuse_oproj_backward_params* params, fuse_stream stream);
+/* api/backward.cuh:294-303. */
+FUSE_API int64_t fuse_qkv_backward_ready_elements(const fuse_qkv_backward_data_params* params);
+FUSE_API int64_t fuse_oproj_backward_ready_elements(const fuse_oproj_backward_data_params* params);
+/* api/backward.cuh:270-271. */
+FUSE_API int32_t fuse_recommended_qkv_backward_comm_ctas(const fuse_qkv_backward_data_params* params);
+FUSE_API int32_t fuse_recommended_oproj_backward_comm_ctas(const fuse_oproj_backward_data_params* params);
+
 /* The static tile order shared by compute and communication CTAs: linear index -> (m, n) tile
  * for a grid of m_tiles x n_tiles, swizzle in {1,2,4,8}, along_n = 0 (index runs down M inside
  * bands of `swizzle` N tiles) or 1 (transpose).  Same knobs as the reference scheduler
@@ -208,7 +315,9 @@ FUSE_API int fuse_b200_symmetric_free(void* ptr);
  * means a device-side wait gave up; `clear` resets the record.  No reference counterpart. */
 FUSE_API int fuse_b200_read_status(uint32_t out[16], int clear);
 /* sizeof of the ABI records as compiled: 0 gemm_problem, 1 ulysses_route, 2 gemm_a2a_params,
- * 3 a2a_gemm_params, 4 kernel_traits, 5 options.  -1 for unknown ids. */
+ * 3 a2a_gemm_params, 4 kernel_traits, 5 options, 6 qkv_backward_data_params,
+ * 7 qkv_backward_weight_params, 8 qkv_backward_params, 9 oproj_backward_data_params,
+ * 10 oproj_backward_weight_params, 11 oproj_backward_params.  -1 for unknown ids. */
 FUSE_API int fuse_b200_abi_sizeof(int record);
 /* Number of kernels this library has launched in this process (all entry points). */
 FUSE_API uint64_t fuse_b200_launch_count(void);

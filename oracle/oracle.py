@@ -226,3 +226,56 @@ def within_tolerance(actual_bits, expected_bits, absolute=0.01, relative=0.01):
     err = np.abs(a - b)
     bad = ~(err <= absolute + relative * np.abs(b))
     return (not bad.any()), float(err.max() if err.size else 0.0), int(bad.sum())
+
+
+def qkv_backward(world, rank, batch, seq_local, q_heads, kv_heads, head_dim, planes, weight, saved_input,
+                 causal=False, alpha=1.0, beta=0.0, grad_weight=None):
+    """One rank of the QKV projection backward.  planes[r] = (dQ, dK, dV) of rank r, each
+    [B*S_global, local_heads*head_dim]; weight [QKV, H]; saved_input [M, H].
+    Returns (staging [M, QKV], dX [M, H], dW [QKV, H])."""
+    m = batch * seq_local
+    width = (q_heads + 2 * kv_heads) * head_dim
+    hidden = weight.shape[1]
+    flat = [np.ascontiguousarray(pl) for r in range(world) for pl in planes[r]]
+    staging = np.empty((m, width), dtype=np.uint16)
+    lib().fo_qkv_backward_gather(world, rank, batch, seq_local, q_heads, kv_heads, head_dim, int(causal),
+                                 ptr_array(flat), ptr(staging))
+    dx = gemm_bf16(1, staging, weight, m, hidden, width, alpha)
+    dw = gemm_bf16(2, staging, saved_input, width, hidden, m, alpha, beta,
+                   None if grad_weight is None else grad_weight.copy())
+    return staging, dx, dw
+
+
+def oproj_backward(world, batch, seq_local, q_heads, head_dim, grad_outputs, weight, saved_attention,
+                   causal=False, alpha=1.0):
+    """Every rank of the output projection backward.  grad_outputs[r] = dY of rank r [M, H];
+    weight Wo [H, A]; saved_attention[r] = forward lhs of rank r [M, A].
+    Returns (dA per rank [M, A], routed per rank [B*S_global, A/world] flat, dWo per rank [H, A])."""
+    m = batch * seq_local
+    hidden, a = weight.shape
+    da = [gemm_bf16(1, grad_outputs[r], weight, m, a, hidden, alpha) for r in range(world)]
+    shard = a // world
+    rows = batch * seq_local * world
+    routed = []
+    rank_out, offset_out = C.c_int32(), C.c_uint64()
+    for dest in range(world):
+        idx = np.arange(rows * shard, dtype=np.uint64)
+        # vectorised restatement of fo_oproj_backward_source (checked against it below)
+        row, col = idx // shard, idx % shard
+        b, seq = row // (seq_local * world), row % (seq_local * world)
+        if causal:
+            half = seq_local // 2
+            chunk = seq // half
+            src = np.where(chunk < world, chunk, 2 * world - chunk - 1)
+            local_row = np.where(chunk < world, 0, half) + seq % half
+        else:
+            src, local_row = seq // seq_local, seq % seq_local
+        off = (b * seq_local + local_row) * a + dest * shard + col
+        for probe in (0, int(idx[-1]) // 2, int(idx[-1])):
+            lib().fo_oproj_backward_source(world, dest, batch, seq_local, a, int(causal), probe,
+                                           C.byref(rank_out), C.byref(offset_out))
+            assert (rank_out.value, offset_out.value) == (int(src[probe]), int(off[probe]))
+        stacked = np.stack([x.reshape(-1) for x in da])
+        routed.append(stacked[src.astype(np.int64), off.astype(np.int64)])
+    dwo = [gemm_bf16(2, grad_outputs[r], saved_attention[r], hidden, a, m, alpha) for r in range(world)]
+    return da, routed, dwo

@@ -104,3 +104,92 @@ def oproj_forward(world, rank, batch, seq_local, peer_bits, w_bits, comm=4, caus
     assert rc == 0, f"launch_a2a_gemm_cutlass -> cudaError {rc}"
     check_status()
     return to_bits(staging), to_bits(out)
+
+
+def qkv_backward(world, batch, seq_local, q_heads, kv_heads, head_dim, planes_bits, w_bits, x_bits, comm=4,
+                 causal=False, alpha=1.0, beta=0.0, dw_init_bits=None, block_n=0, tuning=(1, False)):
+    """Runs every rank of the QKV backward (data + weight).  planes_bits[r] = (dQ, dK, dV) of rank r.
+    Several ranks on one GPU: every rank's communication CTAs push first (COMM_ONLY), then every
+    rank's GEMM runs (COMPUTE_ONLY).  Returns per rank (staging, dX, dW) bits."""
+    m = batch * seq_local
+    width = (q_heads + 2 * kv_heads) * head_dim
+    hidden = w_bits.shape[1]
+    w = to_device(w_bits)
+    planes = [[to_device(pl) for pl in planes_bits[r]] for r in range(world)]
+    xs = [to_device(x) for x in x_bits]
+    staging = [poisoned(m, width) for _ in range(world)]
+    dx = [poisoned(m, hidden) for _ in range(world)]
+    dw = [to_device(dw_init_bits[r]) if dw_init_bits is not None else poisoned(width, hidden) for r in range(world)]
+    done = [torch.zeros(world * N.READY_FLAG_STRIDE, dtype=torch.int32, device=DEV) for _ in range(world)]
+    params = []
+    for r in range(world):
+        p = N.QkvBackwardDataParams(grad_q=planes[r][0].data_ptr(), grad_k=planes[r][1].data_ptr(),
+                                    grad_v=planes[r][2].data_ptr(), weight=w.data_ptr(),
+                                    grad_input=dx[r].data_ptr(), local_tokens=m, hidden=hidden, batch=batch,
+                                    q_heads=q_heads, kv_heads=kv_heads, head_dim=head_dim, world_size=world,
+                                    rank=r, num_comm_ctas=comm, epoch=1, causal_load_balanced=int(causal),
+                                    alpha=alpha)
+        p.gemm_tuning.max_swizzle_size = tuning[0]
+        p.gemm_tuning.along_m = int(tuning[1])
+        params.append(p)
+    ready = [torch.zeros(api.qkv_backward_ready_elements(params[0]), dtype=torch.int32, device=DEV)
+             for _ in range(world)]
+    for p in params:
+        for peer in range(world):
+            p.peer_dqkv_staging[peer] = staging[peer].data_ptr()
+            p.peer_ready[peer] = ready[peer].data_ptr()
+            p.peer_done_epoch[peer] = done[peer].data_ptr()
+    phases = [0] if world == 1 else [N.COMM_ONLY, N.COMPUTE_ONLY]
+    for phase in phases:
+        for p in params:
+            opts = options(flags=phase | (N.SKIP_PEER_WAIT if world > 1 else 0), block_n=block_n)
+            rc = api.launch_qkv_backward_data(p, 0, opts)
+            assert rc == 0, f"launch_qkv_backward_data -> cudaError {rc}"
+    check_status()
+    for r in range(world):
+        wp = N.QkvBackwardWeightParams(dqkv_staging=staging[r].data_ptr(), saved_input=xs[r].data_ptr(),
+                                       grad_weight=dw[r].data_ptr(), local_tokens=m, hidden=hidden,
+                                       q_heads=q_heads, kv_heads=kv_heads, head_dim=head_dim, alpha=alpha,
+                                       beta=beta)
+        rc = api.launch_qkv_backward_weight(wp, 0)
+        assert rc == 0, f"launch_qkv_backward_weight -> cudaError {rc}"
+    check_status()
+    return [(to_bits(staging[r]), to_bits(dx[r]), to_bits(dw[r])) for r in range(world)]
+
+
+def oproj_backward(world, batch, seq_local, q_heads, head_dim, dy_bits, wo_bits, attn_bits, comm=4,
+                   causal=False, alpha=1.0, route="direct", vector_epilogue=False, block_n=0):
+    """Runs every rank of the output-projection backward.  Returns (dA list, routed list, dWo list)."""
+    m = batch * seq_local
+    hidden, a = wo_bits.shape
+    rows = batch * seq_local * world
+    wo = to_device(wo_bits)
+    dys = [to_device(x) for x in dy_bits]
+    attn = [to_device(x) for x in attn_bits]
+    da = [poisoned(m, a) for _ in range(world)]
+    routed = [poisoned(rows * (a // world)) for _ in range(world)]
+    dwo = [poisoned(hidden, a) for _ in range(world)]
+    done = [torch.zeros(world * N.READY_FLAG_STRIDE, dtype=torch.int32, device=DEV) for _ in range(world)]
+    for r in range(world):
+        p = N.OprojBackwardDataParams(grad_output=dys[r].data_ptr(), weight=wo.data_ptr(),
+                                      local_grad_attention=da[r].data_ptr(), local_tokens=m, hidden=hidden,
+                                      batch=batch, q_heads=q_heads, head_dim=head_dim, world_size=world, rank=r,
+                                      num_comm_ctas=comm, epoch=1, causal_load_balanced=int(causal), alpha=alpha)
+        p.gemm_tuning.max_swizzle_size = 4
+        ready = torch.zeros(api.oproj_backward_ready_elements(p), dtype=torch.int32, device=DEV)
+        p.ready = ready.data_ptr()
+        for peer in range(world):
+            p.peer_grad_attention[peer] = routed[peer].data_ptr()
+            p.peer_done_epoch[peer] = done[peer].data_ptr()
+        flags = (N.SKIP_PEER_WAIT if world > 1 else 0) | (N.VECTOR_EPILOGUE if vector_epilogue else 0) | \
+            (N.QKV_ROUTE_COMM_CTAS if route == "comm" else N.QKV_ROUTE_DIRECT)
+        rc = api.launch_oproj_backward_data(p, 0, options(flags=flags, block_n=block_n))
+        assert rc == 0, f"launch_oproj_backward_data -> cudaError {rc}"
+        wp = N.OprojBackwardWeightParams(grad_output=dys[r].data_ptr(), saved_attention=attn[r].data_ptr(),
+                                         grad_weight=dwo[r].data_ptr(), local_tokens=m, hidden=hidden,
+                                         q_heads=q_heads, head_dim=head_dim, alpha=alpha)
+        rc = api.launch_oproj_backward_weight(wp, 0)
+        assert rc == 0, f"launch_oproj_backward_weight -> cudaError {rc}"
+        torch.cuda.synchronize()
+    check_status()
+    return [to_bits(t) for t in da], [to_bits(t) for t in routed], [to_bits(t) for t in dwo]

@@ -178,8 +178,43 @@ class OprojBackwardParams(_Record):
                 ("weight_mode", C.c_int32)]
 
 
+class Mxfp8Activation(_Record):
+    """include/fuse/types.h:31-35 of the reference."""
+    _fields_ = [("data", C.c_void_p), ("scales", C.c_void_p), ("data_bytes", C.c_size_t),
+                ("scale_bytes", C.c_size_t)]
+
+
+class QkvPostprocess(_Record):
+    _fields_ = [("q_gamma", C.c_void_p), ("k_gamma", C.c_void_p), ("cos", C.c_void_p), ("sin", C.c_void_p),
+                ("epsilon", C.c_float)]
+    _defaults_ = {"epsilon": 1e-6}
+
+
+class Mxfp8GemmA2AParams(_Record):
+    """include/fuse/operators/primitives/gemm_a2a_mxfp8.h:23-39 of the reference."""
+    _fields_ = [("projection", GemmA2AParams), ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t),
+                ("activation", Mxfp8Activation), ("weight_preparation", C.c_int32), ("epilogue_n", C.c_int32),
+                ("postprocess", QkvPostprocess)]
+    _defaults_ = {"epilogue_n": 64}
+
+
+class ResidualRmsNorm(_Record):
+    _fields_ = [("residual", C.c_void_p), ("gamma", C.c_void_p), ("residual_output", C.c_void_p),
+                ("epsilon", C.c_float)]
+    _defaults_ = {"epsilon": 1e-6}
+
+
+class Mxfp8A2AGemmParams(_Record):
+    """include/fuse/operators/primitives/a2a_gemm_mxfp8.h:25-46 of the reference."""
+    _fields_ = [("projection", A2AGemmParams), ("activation", Mxfp8Activation * MAX_WORLD_SIZE),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t), ("epilogue_n", C.c_int32),
+                ("m_window_tiles", C.c_int32), ("n_group_tiles", C.c_int32), ("postprocess", ResidualRmsNorm),
+                ("overlap_postnorm", C.c_uint8), ("weight_preparation", C.c_int32)]
+    _defaults_ = {"epilogue_n": 32}
+
+
 ABI_RECORDS = {0: GemmProblem, 1: UlyssesRoute, 2: GemmA2AParams, 3: A2AGemmParams,
-               4: KernelTraits, 5: Options, 6: QkvBackwardDataParams, 7: QkvBackwardWeightParams,
+               4: KernelTraits, 5: Options, 14: Mxfp8A2AGemmParams, 12: Mxfp8Activation, 13: Mxfp8GemmA2AParams, 6: QkvBackwardDataParams, 7: QkvBackwardWeightParams,
                8: QkvBackwardParams, 9: OprojBackwardDataParams, 10: OprojBackwardWeightParams,
                11: OprojBackwardParams}
 
@@ -204,6 +239,23 @@ SYMBOLS = {
     "fuse_oproj_backward_ready_elements": (C.c_int64, [C.POINTER(OprojBackwardDataParams)]),
     "fuse_recommended_qkv_backward_comm_ctas": (C.c_int32, [C.POINTER(QkvBackwardDataParams)]),
     "fuse_recommended_oproj_backward_comm_ctas": (C.c_int32, [C.POINTER(OprojBackwardDataParams)]),
+    "fuse_gemm_a2a_mxfp8_activation_size": (C.c_int, [C.POINTER(GemmProblem), C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
+    "fuse_quantize_gemm_a2a_mxfp8_activation": (C.c_int, [C.POINTER(GemmProblem), _P, C.POINTER(Mxfp8Activation), _P]),
+    "fuse_gemm_a2a_mxfp8_workspace_size": (C.c_int, [C.POINTER(GemmProblem), C.POINTER(C.c_size_t)]),
+    "fuse_launch_gemm_a2a_mxfp8_cutlass": (C.c_int, [C.POINTER(Mxfp8GemmA2AParams), _P]),
+    "fuse_launch_gemm_a2a_mxfp8_cutlass_ex": (C.c_int, [C.POINTER(Mxfp8GemmA2AParams), C.POINTER(Options), _P]),
+    "fuse_prepare_gemm_a2a_mxfp8": (C.c_int, [C.POINTER(Mxfp8GemmA2AParams), _P]),
+    "fuse_launch_gemm_a2a_mxfp8_prequantized": (C.c_int, [C.POINTER(Mxfp8GemmA2AParams), _P]),
+    "fuse_launch_gemm_a2a_mxfp8_prequantized_ex": (C.c_int, [C.POINTER(Mxfp8GemmA2AParams), C.POINTER(Options), _P]),
+    "fuse_launch_gemm_a2a_mxfp8_compute_reference": (C.c_int, [C.POINTER(Mxfp8GemmA2AParams), _P]),
+    "fuse_b200_quantize_mxfp8": (C.c_int, [_P, C.c_int64, C.c_int32, C.c_int32, _P, _P, _P]),
+    "fuse_b200_quantize_mxfp8_transposed": (C.c_int, [_P, C.c_int64, C.c_int32, C.c_int32, _P, _P, _P]),
+    "fuse_b200_mxfp8_scale_bytes": (C.c_size_t, [C.c_int64, C.c_int64]),
+    "fuse_a2a_gemm_mxfp8_activation_size": (C.c_int, [C.POINTER(GemmProblem), C.POINTER(UlyssesRoute), C.POINTER(C.c_size_t), C.POINTER(C.c_size_t)]),
+    "fuse_a2a_gemm_mxfp8_workspace_size": (C.c_int, [C.POINTER(GemmProblem), C.POINTER(C.c_size_t)]),
+    "fuse_a2a_gemm_mxfp8_staging_view": (C.c_int, [C.POINTER(Mxfp8A2AGemmParams), C.POINTER(Mxfp8Activation)]),
+    "fuse_launch_a2a_gemm_mxfp8_cutlass": (C.c_int, [C.POINTER(Mxfp8A2AGemmParams), _P]),
+    "fuse_launch_a2a_gemm_mxfp8_cutlass_ex": (C.c_int, [C.POINTER(Mxfp8A2AGemmParams), C.POINTER(Options), _P]),
     "fuse_qkv_cutlass_kernel_traits": (None, [C.POINTER(GemmProblem), C.POINTER(KernelTraits)]),
     "fuse_cutlass_kernel_traits": (None, [C.POINTER(KernelTraits)]),
     "fuse_a2a_lhs_gemm_ready_elements": (C.c_int64, [C.POINTER(GemmProblem), C.POINTER(UlyssesRoute)]),

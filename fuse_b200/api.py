@@ -133,3 +133,87 @@ def qkv_backward_ready_elements(params: QkvBackwardDataParams) -> int:
 
 def oproj_backward_ready_elements(params: OprojBackwardDataParams) -> int:
     return N.lib().fuse_oproj_backward_ready_elements(C.byref(params))
+
+
+# ---- MXFP8 (include/fuse/operators/primitives/gemm_a2a_mxfp8.h of the reference) ----------------
+from ._native import Mxfp8Activation, Mxfp8GemmA2AParams  # noqa: E402,F401
+
+
+def gemm_a2a_mxfp8_activation_size(problem: GemmProblem):
+    data, scales = C.c_size_t(), C.c_size_t()
+    rc = N.lib().fuse_gemm_a2a_mxfp8_activation_size(C.byref(problem), C.byref(data), C.byref(scales))
+    return rc, data.value, scales.value
+
+
+def gemm_a2a_mxfp8_workspace_size(problem: GemmProblem):
+    size = C.c_size_t()
+    rc = N.lib().fuse_gemm_a2a_mxfp8_workspace_size(C.byref(problem), C.byref(size))
+    return rc, size.value
+
+
+def quantize_gemm_a2a_mxfp8_activation(problem: GemmProblem, source: int, output: Mxfp8Activation, stream: int = 0) -> int:
+    return N.lib().fuse_quantize_gemm_a2a_mxfp8_activation(C.byref(problem), source, C.byref(output), stream)
+
+
+def launch_gemm_a2a_mxfp8_cutlass(params: Mxfp8GemmA2AParams, stream: int = 0, options: Options | None = None) -> int:
+    """MXFP8 QKV projection (weight quantised in-kernel) + all-to-all, BF16 out."""
+    if options is None:
+        return N.lib().fuse_launch_gemm_a2a_mxfp8_cutlass(C.byref(params), stream)
+    return N.lib().fuse_launch_gemm_a2a_mxfp8_cutlass_ex(C.byref(params), _opt(options), stream)
+
+
+def prepare_gemm_a2a_mxfp8(params: Mxfp8GemmA2AParams, stream: int = 0) -> int:
+    return N.lib().fuse_prepare_gemm_a2a_mxfp8(C.byref(params), stream)
+
+
+def launch_gemm_a2a_mxfp8_prequantized(params: Mxfp8GemmA2AParams, stream: int = 0, options: Options | None = None) -> int:
+    if options is None:
+        return N.lib().fuse_launch_gemm_a2a_mxfp8_prequantized(C.byref(params), stream)
+    return N.lib().fuse_launch_gemm_a2a_mxfp8_prequantized_ex(C.byref(params), _opt(options), stream)
+
+
+def launch_gemm_a2a_mxfp8_compute_reference(params: Mxfp8GemmA2AParams, stream: int = 0) -> int:
+    return N.lib().fuse_launch_gemm_a2a_mxfp8_compute_reference(C.byref(params), stream)
+
+
+def quantize_mxfp8(source: int, row_stride: int, rows: int, k: int, data: int, scales: int, stream: int = 0) -> int:
+    return N.lib().fuse_b200_quantize_mxfp8(source, row_stride, rows, k, data, scales, stream)
+
+
+def quantize_mxfp8_transposed(source: int, row_stride: int, rows: int, cols: int, data: int, scales: int,
+                              stream: int = 0) -> int:
+    return N.lib().fuse_b200_quantize_mxfp8_transposed(source, row_stride, rows, cols, data, scales, stream)
+
+
+def mxfp8_scale_bytes(rows: int, k: int) -> int:
+    return int(N.lib().fuse_b200_mxfp8_scale_bytes(rows, k))
+
+
+from ._native import Mxfp8A2AGemmParams  # noqa: E402,F401
+
+
+def a2a_gemm_mxfp8_activation_size(problem: GemmProblem, route: UlyssesRoute):
+    data, scales = C.c_size_t(), C.c_size_t()
+    rc = N.lib().fuse_a2a_gemm_mxfp8_activation_size(C.byref(problem), C.byref(route), C.byref(data), C.byref(scales))
+    return rc, data.value, scales.value
+
+
+def a2a_gemm_mxfp8_workspace_size(problem: GemmProblem):
+    size = C.c_size_t()
+    rc = N.lib().fuse_a2a_gemm_mxfp8_workspace_size(C.byref(problem), C.byref(size))
+    return rc, size.value
+
+
+def a2a_gemm_mxfp8_staging_view(params: Mxfp8A2AGemmParams) -> Mxfp8Activation:
+    out = Mxfp8Activation()
+    rc = N.lib().fuse_a2a_gemm_mxfp8_staging_view(C.byref(params), C.byref(out))
+    if rc != 0:
+        raise RuntimeError(f"a2a_gemm_mxfp8_staging_view -> cudaError {rc}")
+    return out
+
+
+def launch_a2a_gemm_mxfp8_cutlass(params: Mxfp8A2AGemmParams, stream: int = 0, options: Options | None = None) -> int:
+    """MXFP8 head->sequence all-to-all (bytes + scale atoms) + output projection, BF16 out."""
+    if options is None:
+        return N.lib().fuse_launch_a2a_gemm_mxfp8_cutlass(C.byref(params), stream)
+    return N.lib().fuse_launch_a2a_gemm_mxfp8_cutlass_ex(C.byref(params), _opt(options), stream)

@@ -201,6 +201,7 @@ cudaError_t oproj_forward(const fuse_a2a_gemm_params& p, const fuse_b200_options
   k.lhs.input_epoch = p.input_epoch;
   k.lhs.staging = p.input_staging;
   k.lhs.lda = lda;
+  k.lhs.element_bytes = 2;
   for (int peer = 0; peer < p.route.world_size; ++peer) {
     k.lhs.peer_input[peer] = p.peer_input[peer];
     k.lhs.peer_input_ready[peer] = p.peer_input_ready[peer];
@@ -325,6 +326,9 @@ int fuse_b200_abi_sizeof(int record) {
     case 9: return int(sizeof(fuse_oproj_backward_data_params));
     case 10: return int(sizeof(fuse_oproj_backward_weight_params));
     case 11: return int(sizeof(fuse_oproj_backward_params));
+    case 12: return int(sizeof(fuse_mxfp8_activation));
+    case 13: return int(sizeof(fuse_mxfp8_gemm_a2a_params));
+    case 14: return int(sizeof(fuse_mxfp8_a2a_gemm_params));
     default: return -1;
   }
 }

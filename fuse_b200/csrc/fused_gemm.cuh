@@ -23,6 +23,7 @@
 
 #include <cooperative_groups.h>
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 
 #include "ptx.cuh"
 #include "sync.cuh"
@@ -35,7 +36,6 @@ constexpr int kBlockK = 64;        // 64 BF16 = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
 constexpr int kThreads = 256;
 constexpr int kEpilogueThreads = 128;
-constexpr int kAccumStages = 2;
 constexpr uint32_t kMnGroupBytes = 64 * kBlockK * 2;  // one [64 K rows x 64 MN] box of an MN-major tile
 
 enum FusedMode : int {
@@ -85,6 +85,12 @@ struct LhsRoute {
   uint32_t input_epoch;
   uint16_t* staging;          // [M, lda]
   int64_t lda;
+  // Block-scaled lhs: one-byte elements plus the native scale atoms of every peer's shard
+  // ([B*S_global, K/world]) which are re-homed into the local [M, K] scale storage.
+  int32_t element_bytes;      // 2 (BF16) or 1 (E4M3)
+  const uint8_t* peer_scales[kMaxWorldSize];
+  uint8_t* local_scales;
+  int32_t k_atoms, shard_atoms;  // K/128 and (K/world)/128
 };
 
 // QKV backward reverse route (head -> sequence), sender side: this rank holds planar
@@ -105,6 +111,21 @@ struct FusedParams {
   float alpha, beta;
   uint16_t* d;
   int64_t ldd;
+  // Block-scaled operands: native K32 scale storage of A ([M,K]) and B ([N,K]) -- 512-byte
+  // atoms of 128 rows x 4 K-blocks, K atoms before row atoms -- and K/128.
+  const uint8_t* sfa;
+  const uint8_t* sfb;
+  int32_t k_atoms;
+  // In-kernel preparation run by every CTA before the roles start (block-scaled kernels):
+  // quantise the BF16 master weight [wq_rows, wq_k] into B's E4M3 bytes + scales, and clear
+  // invocation-private flag words that live in caller scratch.
+  const uint16_t* wq_source;
+  uint8_t* wq_data;
+  uint8_t* wq_scales;
+  int32_t wq_rows, wq_k;
+  int64_t wq_stride;
+  uint32_t* clear_words;
+  int64_t clear_count;
   uint32_t* ready;            // tile flags (QkvPush) or (m-tile, k-shard) flags (LhsPull)
   uint32_t flags;
   // Optional %globaltimer trace: CTA `trace_cta` appends (site, timestamp) pairs until the
@@ -118,27 +139,56 @@ struct FusedParams {
   GradRoute grad;
 };
 
-template <int kBlockN, int kStages>
+// Geometry of the bulk-copy pull pipeline run by communication CTAs (lhs_pull_bulk_role).
+constexpr int kPullWarps = 7;
+constexpr int kPullStages = 2;
+constexpr uint32_t kPullStageBytes = 16384;
+constexpr int kPullLag = 4;
+constexpr int kPullSubRows = 32;
+constexpr int kPullSubsPerTile = kBlockM / kPullSubRows;
+// Shared memory a communication CTA needs for it: the warps' rings plus their mbarriers.
+constexpr uint32_t kPullSmemBytes = kPullWarps * kPullStages * (kPullStageBytes + 8u);
+
+// kMx: block-scaled E4M3 operands (one UE8M0 scale per 32 K values).  A K block is then 128
+// one-byte elements (the same 128-byte swizzle rows), each stage also carries the 512-byte scale
+// atoms of its A rows and B rows, the accumulator is single-buffered (TMEM also holds the
+// scales) and the epilogue stages through one buffer.
+template <int kBlockN, int kStages, bool kMx = false>
 struct SmemLayout {
   static constexpr uint32_t kABytes = kBlockM * kBlockK * 2;
   static constexpr uint32_t kBBytes = kBlockN * kBlockK * 2;
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
-  // Epilogue staging for TMA stores: two 128-row x 64-column BF16 blocks (16 KiB each).
-  static constexpr uint32_t kStagingOffset = kStages * kStageBytes;
+  // Scale atoms per stage: one for the 128 A rows, one per 128 B rows.
+  static constexpr uint32_t kSfaBytes = kMx ? 512u : 0u;
+  static constexpr uint32_t kSfbBytes = kMx ? 512u * ((kBlockN + 127) / 128) : 0u;
+  static constexpr uint32_t kSfOffset = kStages * kStageBytes;
+  static constexpr uint32_t kSfStageBytes = kSfaBytes + kSfbBytes;
+  // Epilogue staging for TMA stores: 128-row x 64-column BF16 blocks (16 KiB each).
+  static constexpr uint32_t kStagingBuffers = kMx ? 1u : 2u;
+  static constexpr uint32_t kStagingOffset = kSfOffset + ((kStages * kSfStageBytes + 1023u) & ~1023u);
   static constexpr uint32_t kStagingBlockBytes = kBlockM * 64 * 2;
-  static constexpr uint32_t kBarrierOffset = kStagingOffset + 2 * kStagingBlockBytes;
+  static constexpr uint32_t kBarrierOffset = kStagingOffset + kStagingBuffers * kStagingBlockBytes;
+  static constexpr uint32_t kAccumStages = (kMx && kBlockN > 240) ? 1u : 2u;
   static constexpr uint32_t kNumBarriers = 2 * kStages + 2 * kAccumStages;
   static constexpr uint32_t kTmemSlotOffset = kBarrierOffset + kNumBarriers * 8;
   // Two per-tile route tables (column chunk -> destination base pointer, row pitch) used by
   // the direct-push epilogue, double-buffered by tile parity.
   static constexpr uint32_t kRouteTableOffset = kTmemSlotOffset + 16;
   static constexpr uint32_t kRouteTableBytes = 2 * (kBlockN / 8) * 16;
-  static constexpr uint32_t kBytes = kRouteTableOffset + kRouteTableBytes;
+  static constexpr uint32_t kComputeBytes = kRouteTableOffset + kRouteTableBytes;
+  // Communication CTAs of the same launch lay their own pipeline over the same allocation.
+  static constexpr uint32_t kBytes = kComputeBytes > kPullSmemBytes ? kComputeBytes : kPullSmemBytes;
   // + 1024 so the kernel can align the base itself; total is above half of the SM's shared
   // memory, which pins residency at exactly one CTA per SM.
   static constexpr uint32_t kDynamicBytes = kBytes + 1024;
   static_assert(kDynamicBytes <= 227 * 1024, "shared memory budget");
   static_assert(kDynamicBytes > 114 * 1024, "must force one CTA per SM");
+  // TMEM: accumulators, then (kMx) two sets of scale columns: 4 for A, 4 per 128 B rows.
+  static constexpr uint32_t kSfColumns = kMx ? 4u + 4u * ((kBlockN + 127) / 128) : 0u;
+  static constexpr uint32_t kTmemSfOffset = kAccumStages * kBlockN;
+  static constexpr uint32_t kTmemUsed = kTmemSfOffset + 2 * kSfColumns;
+  static constexpr uint32_t kTmemColumns = kTmemUsed <= 256 ? 256u : 512u;
+  static_assert(kTmemUsed <= 512, "TMEM budget");
 };
 
 __device__ __forceinline__ void trace_event(const FusedParams& p, uint32_t site) {
@@ -372,12 +422,6 @@ __device__ __forceinline__ void lhs_pull_role(const FusedParams& p, uint8_t* sme
 // that completes the unit publishes word 0 = epoch (arrival counting as in
 // csrc/operators/sm103/detail/a2a_gemm.cuh:466-642, but the epoch need not advance by one).
 // ------------------------------------------------------------------------------------------
-constexpr int kPullWarps = 7;
-constexpr int kPullStages = 2;
-constexpr uint32_t kPullStageBytes = 16384;
-constexpr int kPullLag = 4;
-constexpr int kPullSubRows = 32;
-constexpr int kPullSubsPerTile = kBlockM / kPullSubRows;
 
 struct PullCursor {
   int32_t sub;        // global sub-unit index; advances by the number of pull warps
@@ -389,6 +433,9 @@ struct PullCursor {
   bool contiguous;    // its source rows are consecutive in the peer's tensor
   const uint8_t* src; // source of its first row (valid when contiguous)
   uint8_t* dst;       // destination of its first row
+  int32_t data_chunks;       // chunks [data_chunks, chunks) carry the unit's scale atoms
+  const uint8_t* scale_src;  // first scale atom of the unit at the source / in local storage
+  uint8_t* scale_dst;
 };
 
 __device__ __forceinline__ void lhs_pull_bulk_role(const FusedParams& p, uint32_t smem_base) {
@@ -406,15 +453,20 @@ __device__ __forceinline__ void lhs_pull_bulk_role(const FusedParams& p, uint32_
 
   const int32_t workers = p.num_comm_ctas * kPullWarps;
   const int32_t worker = warp * p.num_comm_ctas + int32_t(blockIdx.x);  // neighbours on different SMs
-  const uint32_t shard_bytes = uint32_t(r.shard_width) * 2u;
+  const uint32_t shard_bytes = uint32_t(r.shard_width) * uint32_t(r.element_bytes);
   const int32_t pieces = int32_t((shard_bytes + kPullStageBytes - 1) / kPullStageBytes);
+  // Scale atoms of one unit travel as extra chunks of its first sub-unit: the K atoms of one
+  // 128-row group are contiguous at the source and at the destination.
+  const bool with_scales = r.local_scales != nullptr;
+  constexpr int32_t kAtomsPerChunk = int32_t(kPullStageBytes / 512);
+  const int32_t scale_chunks = with_scales ? (r.shard_atoms + kAtomsPerChunk - 1) / kAtomsPerChunk : 0;
   const int32_t rows_per_chunk =
       pieces == 1 ? (int32_t(kPullStageBytes / shard_bytes) < kPullSubRows ? int32_t(kPullStageBytes / shard_bytes)
                                                                           : kPullSubRows)
                   : 1;
   const int32_t subs_total = p.order.m_tiles * r.world * kPullSubsPerTile;
   const int32_t row_block = r.causal ? r.seq_local / 2 : r.seq_local;  // rows consecutive at the source
-  const int64_t dst_pitch = r.lda * 2;
+  const int64_t dst_pitch = r.lda * r.element_bytes;
 
   // Positions `c` on the first sub-unit at or after c.sub that has rows; false past the end.
   auto seek = [&](PullCursor& c) {
@@ -427,7 +479,8 @@ __device__ __forceinline__ void lhs_pull_bulk_role(const FusedParams& p, uint32_
       c.rows = rows_in_unit - row0 < kPullSubRows ? rows_in_unit - row0 : kPullSubRows;
       c.row = mt * kBlockM + row0;
       c.chunk = 0;
-      c.chunks = ((c.rows + rows_per_chunk - 1) / rows_per_chunk) * pieces;
+      c.data_chunks = ((c.rows + rows_per_chunk - 1) / rows_per_chunk) * pieces;
+      c.chunks = c.data_chunks + (quarter == 0 ? scale_chunks : 0);
       c.flag = unit;
       c.needed = (rows_in_unit + kPullSubRows - 1) / kPullSubRows;
       c.peer = r.cyclic ? (r.rank + shard) % r.world : shard;
@@ -436,6 +489,11 @@ __device__ __forceinline__ void lhs_pull_bulk_role(const FusedParams& p, uint32_
               global_row(r.world, r.rank, r.seq_local, r.global_seq, r.causal != 0, c.row) * shard_bytes;
       c.dst = reinterpret_cast<uint8_t*>(r.staging) + int64_t(c.row) * dst_pitch +
               int64_t(shard) * shard_bytes;
+      if (with_scales) {
+        const int64_t src_row = global_row(r.world, r.rank, r.seq_local, r.global_seq, r.causal != 0, mt * kBlockM);
+        c.scale_src = r.peer_scales[c.peer] + (src_row >> 7) * int64_t(r.shard_atoms) * 512;
+        c.scale_dst = r.local_scales + (int64_t(mt) * r.k_atoms + int64_t(shard) * r.shard_atoms) * 512;
+      }
       return true;
     }
     return false;
@@ -449,6 +507,15 @@ __device__ __forceinline__ void lhs_pull_bulk_role(const FusedParams& p, uint32_
   struct Chunk { int32_t row_off, rows; uint32_t col_off, bytes_per_row; };
   auto chunk_of = [&](const PullCursor& c) {
     Chunk k;
+    if (c.chunk >= c.data_chunks) {  // scale atoms: one contiguous run, described as a single row
+      const int32_t first_atom = (c.chunk - c.data_chunks) * kAtomsPerChunk;
+      const int32_t atoms = r.shard_atoms - first_atom < kAtomsPerChunk ? r.shard_atoms - first_atom : kAtomsPerChunk;
+      k.row_off = 0;
+      k.rows = 1;
+      k.col_off = uint32_t(first_atom) * 512u;
+      k.bytes_per_row = uint32_t(atoms) * 512u;
+      return k;
+    }
     if (pieces == 1) {
       k.row_off = c.chunk * rows_per_chunk;
       k.rows = c.rows - k.row_off < rows_per_chunk ? c.rows - k.row_off : rows_per_chunk;
@@ -480,7 +547,9 @@ __device__ __forceinline__ void lhs_pull_bulk_role(const FusedParams& p, uint32_
     const uint32_t bar = bars + 8u * stage;
     if (lane == 0) ptx::mbar_expect_tx(bar, uint32_t(k.rows) * k.bytes_per_row);
     __syncwarp();
-    if (c.contiguous) {
+    if (c.chunk >= c.data_chunks) {
+      if (lane == 0) ptx::bulk_load(dst, c.scale_src + k.col_off, k.bytes_per_row, bar);
+    } else if (c.contiguous) {
       // consecutive source rows: one copy for the whole chunk (rows are shard_bytes apart)
       if (pieces == 1) {
         if (lane == 0)
@@ -547,7 +616,9 @@ __device__ __forceinline__ void lhs_pull_bulk_role(const FusedParams& p, uint32_
     if (lane == 0) trace_event(p, 1);  // chunk landed
     const Chunk k = chunk_of(store_cursor);
     const uint32_t src = ring + uint32_t(stage) * kPullStageBytes;
-    uint8_t* dst = store_cursor.dst + int64_t(k.row_off) * dst_pitch + k.col_off;
+    uint8_t* dst = store_cursor.chunk >= store_cursor.data_chunks
+                       ? store_cursor.scale_dst + k.col_off
+                       : store_cursor.dst + int64_t(k.row_off) * dst_pitch + k.col_off;
     for (int32_t row = lane; row < k.rows; row += 32)
       ptx::bulk_store(dst + int64_t(row) * dst_pitch, src + uint32_t(row) * k.bytes_per_row, k.bytes_per_row);
     ptx::bulk_commit();
@@ -730,16 +801,87 @@ __device__ __forceinline__ void stage_accumulators(const uint32_t (&acc)[32], ui
 // ------------------------------------------------------------------------------------------
 // The kernel.
 // ------------------------------------------------------------------------------------------
+// ------------------------------------------------------------------------------------------
+// MXFP8 K32 quantisation of one group of 32 consecutive K values (device side).
+// exponent: csrc/operators/sm103/detail/quantization.cuh:91-105 (integer form, 448 = 1.75*2^8);
+// scaling by an exact power of two: :107-118; E4M3 conversion round-to-nearest-even,
+// saturating; scale byte exponent+127 at the native offset
+// (benchmarks/sm103/fused_mxfp8.cuh:13-16).
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ int mxfp8_scale_exponent(float amax) {
+  if (!(amax > 0.0f)) return 0;
+  const int exponent = int((__float_as_uint(amax) + 0x001fffffu) >> 23) - 127 - 8;
+  return exponent < -127 ? -127 : exponent > 127 ? 127 : exponent;
+}
+__device__ __forceinline__ float mxfp8_inverse_scale(int exponent) {
+  return __uint_as_float(exponent == 127 ? 0x00400000u : uint32_t(127 - exponent) << 23);
+}
+__device__ __forceinline__ int64_t mxfp8_scale_offset(int64_t row, int64_t k, int64_t k_atoms) {
+  return ((row >> 7) * k_atoms + (k >> 7)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 + ((k & 127) >> 5);
+}
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+  const uint32_t lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  const uint32_t hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+// One thread quantises one K32 group read as four 16-byte vectors.
+__device__ __forceinline__ void mxfp8_quantize_group(const uint16_t* in, uint8_t* out, uint8_t* scale_byte) {
+  uint4 v[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) v[i] = reinterpret_cast<const uint4*>(in)[i];
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(v);
+  float f[32];
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    f[2 * i] = __uint_as_float(w[i] << 16);
+    f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    amax = fmaxf(amax, fmaxf(fabsf(f[2 * i]), fabsf(f[2 * i + 1])));
+  }
+  const int exponent = mxfp8_scale_exponent(amax);
+  const float inverse = mxfp8_inverse_scale(exponent);
+  uint4 o[2];
+  uint32_t* ow = reinterpret_cast<uint32_t*>(o);
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    ow[i] = pack_e4m3x4(f[4 * i] * inverse, f[4 * i + 1] * inverse, f[4 * i + 2] * inverse, f[4 * i + 3] * inverse);
+  reinterpret_cast<uint4*>(out)[0] = o[0];
+  reinterpret_cast<uint4*>(out)[1] = o[1];
+  *scale_byte = uint8_t(exponent + 127);
+}
+// Grid-stride quantisation of a row-major BF16 [rows, k] operand; rows up to the next multiple
+// of 128 get the neutral scale (2^0), as the reference's quantiser writes them.
+__device__ __forceinline__ void mxfp8_quantize_rows(const uint16_t* source, int64_t stride, int32_t rows,
+                                                    int32_t k, uint8_t* data, uint8_t* scales,
+                                                    int64_t first, int64_t step) {
+  const int32_t groups_per_row = k >> 5;
+  const int64_t k_atoms = (k + 127) >> 7;
+  const int64_t padded_rows = (int64_t(rows) + 127) & ~int64_t(127);
+  const int64_t total = padded_rows * groups_per_row;
+  for (int64_t g = first; g < total; g += step) {
+    const int64_t row = g / groups_per_row;
+    const int32_t group = int32_t(g - row * groups_per_row);
+    uint8_t* scale = scales + mxfp8_scale_offset(row, int64_t(group) << 5, k_atoms);
+    if (row < rows)
+      mxfp8_quantize_group(source + row * stride + (group << 5), data + row * k + (group << 5), scale);
+    else
+      *scale = 127;
+  }
+}
+
 // kAMn / kBMn: the operand is stored with its M (resp. N) axis contiguous -- [K, M] / [K, N]
 // row-major -- and is fed to the tensor core as an MN-major tile: 64-element groups along MN,
 // each a [64 K rows x 128 bytes] swizzled box (the data-gradient GEMMs read the forward weight
 // as stored, the weight-gradient GEMMs read both operands along the token axis).
-template <int kBlockN, int kStages, int kMode, bool kTmaEpilogue, bool kAMn = false, bool kBMn = false>
+template <int kBlockN, int kStages, int kMode, bool kTmaEpilogue, bool kAMn = false, bool kBMn = false,
+          bool kMx = false>
 __global__ void __launch_bounds__(kThreads, 1)
 fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b,
                   const __grid_constant__ StoreMaps store_maps, const FusedParams p) {
-  using Layout = SmemLayout<kBlockN, kStages>;
+  using Layout = SmemLayout<kBlockN, kStages, kMx>;
+  constexpr uint32_t kAccumStages = Layout::kAccumStages;
+  static_assert(!kMx || (!kAMn && !kBMn), "block-scaled operands are K-major");
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = ptx::smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -747,6 +889,20 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const bool is_comm = int(blockIdx.x) < p.num_comm_ctas;
   const bool skip_role = (p.flags & (is_comm ? kFlagComputeOnly : kFlagCommOnly)) != 0u;
+
+  if constexpr (kMx) {
+    // Preparation by every CTA of the (cooperative) grid, then one grid-wide join.
+    if (p.wq_source != nullptr || p.clear_words != nullptr) {
+      const int64_t first = int64_t(blockIdx.x) * kThreads + threadIdx.x;
+      const int64_t step = int64_t(gridDim.x) * kThreads;
+      if (p.wq_source != nullptr)
+        mxfp8_quantize_rows(p.wq_source, p.wq_stride, p.wq_rows, p.wq_k, p.wq_data, p.wq_scales, first, step);
+      for (int64_t i = first; i < p.clear_count; i += step) p.clear_words[i] = 0u;
+      __threadfence();
+      ptx::fence_proxy_async_global();  // the quantised bytes are read by TMA after the join
+      cooperative_groups::this_grid().sync();
+    }
+  }
 
   if (skip_role) {
     // nothing: this launch runs the other role only
@@ -764,8 +920,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     auto tmem_full_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };
     auto tmem_empty_bar = [&](int s) { return bar_base + 8u * (2 * kStages + kAccumStages + s); };
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + Layout::kTmemSlotOffset);
-    constexpr uint32_t kTmemColumns = kAccumStages * kBlockN;
-    static_assert(kTmemColumns == 256 || kTmemColumns == 512, "TMEM allocation is a power of two");
+    constexpr uint32_t kTmemColumns = Layout::kTmemColumns;
 
     if (threadIdx.x == 0) {
       ptx::prefetch_tensormap(&tmap_a);
@@ -792,7 +947,8 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const int32_t compute_ctas = int32_t(gridDim.x) - p.num_comm_ctas;
     const int32_t compute_id = int32_t(blockIdx.x) - p.num_comm_ctas;
     const int64_t tiles = p.order.count();
-    const int32_t k_blocks = (p.k + kBlockK - 1) / kBlockK;
+    constexpr int32_t kBlockElems = kMx ? 2 * kBlockK : kBlockK;  // K elements per 128-byte row
+    const int32_t k_blocks = (p.k + kBlockElems - 1) / kBlockElems;
 
     if (warp == 0) {
       // ------------------------------------------------------------------ TMA producer
@@ -812,7 +968,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
               constexpr bool kRemoteWriter = kMode == kModeHeadGate;
               const int32_t group_width = kRemoteWriter ? p.grad.head_dim : p.lhs.shard_width;
               const int32_t groups = kRemoteWriter ? p.grad.q_heads + 2 * p.grad.kv_heads : p.lhs.world;
-              int32_t last = (kb * kBlockK + kBlockK - 1) / group_width;
+              int32_t last = (kb * kBlockElems + kBlockElems - 1) / group_width;
               if (last >= groups) last = groups - 1;
               while (ok && gated_upto < last) {
                 ++gated_upto;
@@ -825,10 +981,24 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             }
             ok = mbar_wait(empty_bar(stage), phase ^ 1u, p.wait, kSiteSmemEmpty);
             if (!ok) break;
-            ptx::mbar_expect_tx(full_bar(stage), Layout::kStageBytes);
             const uint32_t a_dst = base + stage * Layout::kStageBytes;
+            if constexpr (kMx) {
+              // scale atoms of this K block: one for the A rows, one per 128 B rows that exist
+              constexpr int kBAtoms = (kBlockN + 127) / 128;
+              const int32_t n_atoms_total = (p.n + 127) / 128;
+              const int32_t first_b_atom = nt * kBAtoms;
+              const int32_t b_atoms = n_atoms_total - first_b_atom < kBAtoms ? n_atoms_total - first_b_atom : kBAtoms;
+              ptx::mbar_expect_tx(full_bar(stage), Layout::kStageBytes + 512u * uint32_t(1 + b_atoms));
+              const uint32_t sf_dst = base + Layout::kSfOffset + stage * Layout::kSfStageBytes;
+              ptx::bulk_load(sf_dst, p.sfa + (int64_t(mt) * p.k_atoms + kb) * 512, 512u, full_bar(stage));
+              for (int32_t j = 0; j < b_atoms; ++j)
+                ptx::bulk_load(sf_dst + 512u * uint32_t(1 + j),
+                               p.sfb + (int64_t(first_b_atom + j) * p.k_atoms + kb) * 512, 512u, full_bar(stage));
+            } else {
+              ptx::mbar_expect_tx(full_bar(stage), Layout::kStageBytes);
+            }
             if constexpr (!kAMn) {
-              ptx::tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * kBlockK, mt * kBlockM);
+              ptx::tma_load_2d(a_dst, &tmap_a, full_bar(stage), kb * kBlockElems, mt * kBlockM);
             } else {
 #pragma unroll
               for (int g = 0; g < kBlockM / 64; ++g)
@@ -836,7 +1006,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                  mt * kBlockM + g * 64, kb * kBlockK);
             }
             if constexpr (!kBMn) {
-              ptx::tma_load_2d(a_dst + Layout::kABytes, &tmap_b, full_bar(stage), kb * kBlockK,
+              ptx::tma_load_2d(a_dst + Layout::kABytes, &tmap_b, full_bar(stage), kb * kBlockElems,
                                nt * kBlockN);
             } else {
 #pragma unroll
@@ -866,6 +1036,8 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         constexpr uint64_t kAStep = kAMn ? (kUmmaK * 128) >> 4 : (kUmmaK * 2) >> 4;
         constexpr uint64_t kBStep = kBMn ? (kUmmaK * 128) >> 4 : (kUmmaK * 2) >> 4;
         uint32_t stage = 0, phase = 0, accum = 0, accum_phase = 0;
+        uint32_t sf_parity = 0;
+        (void)sf_parity;
         bool ok = true;
         for (int64_t t = compute_id; ok && t < tiles; t += compute_ctas) {
           ok = mbar_wait(tmem_empty_bar(accum), accum_phase ^ 1u, p.wait, kSiteTmemEmpty);
@@ -881,10 +1053,30 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                          : ptx::smem_desc_k_sw128(a_addr);
             const uint64_t b_desc = kBMn ? ptx::smem_desc_mn_sw128(a_addr + Layout::kABytes, kMnGroupBytes)
                                          : ptx::smem_desc_k_sw128(a_addr + Layout::kABytes);
+            if constexpr (kMx) {
+              // Copy this K block's scale atoms shared -> TMEM (32 lanes x 16 bytes each, broadcast
+              // to the four lane quarters), then four K=32 UMMAs; UMMA k reads byte k of every
+              // 32-bit scale column.  tcgen05.cp and tcgen05.mma of one thread execute in order;
+              // two sets of scale columns alternate anyway.
+              constexpr int kBAtoms = (kBlockN + 127) / 128;
+              const uint32_t sf_smem = base + Layout::kSfOffset + stage * Layout::kSfStageBytes;
+              const uint32_t sf_tmem = tmem_base + Layout::kTmemSfOffset + (sf_parity ? Layout::kSfColumns : 0u);
+              sf_parity ^= 1u;
+              ptx::tmem_cp_32x128b_warpx4(sf_tmem, ptx::smem_desc_scale_atom(sf_smem));
 #pragma unroll
-            for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-              ptx::umma_f16(d_tmem, a_desc + kAStep * k, b_desc + kBStep * k, kIdesc,
-                            (kb | k) != 0 ? 1u : 0u);
+              for (int j = 0; j < kBAtoms; ++j)
+                ptx::tmem_cp_32x128b_warpx4(sf_tmem + 4u + 4u * j, ptx::smem_desc_scale_atom(sf_smem + 512u * (1 + j)));
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                ptx::umma_mxf8(d_tmem, a_desc + 2u * k, b_desc + 2u * k,
+                               ptx::idesc_mxf8_e4m3(kBlockM, kBlockN, k, k), sf_tmem, sf_tmem + 4u,
+                               (kb | k) != 0 ? 1u : 0u);
+            } else {
+#pragma unroll
+              for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+                ptx::umma_f16(d_tmem, a_desc + kAStep * k, b_desc + kBStep * k, kIdesc,
+                              (kb | k) != 0 ? 1u : 0u);
+              }
             }
             ptx::umma_commit(empty_bar(stage));  // frees the stage when these UMMAs retire
             if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -951,9 +1143,10 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
 #pragma unroll 1
           for (int c = 0; c < kBlockN; c += 64) {
             const uint32_t staging =
-                base + Layout::kStagingOffset + (staged_blocks & 1u) * Layout::kStagingBlockBytes;
+                base + Layout::kStagingOffset + (staged_blocks % Layout::kStagingBuffers) * Layout::kStagingBlockBytes;
             ++staged_blocks;
-            if (epi_tid == 0) ptx::bulk_wait_read<1>();  // the block stored two steps ago is drained
+            // the block that last used this staging buffer has been read out by its tensor stores
+            if (epi_tid == 0) ptx::bulk_wait_read<Layout::kStagingBuffers - 1>();
             ptx::named_bar_sync(1, kEpilogueThreads);
             uint32_t acc0[32], acc1[32];
             ptx::tmem_ld_32x32b_x32(taddr + c, acc0);

@@ -22,6 +22,14 @@ struct Operands {
 
 // K-major operand: stored [rows, k] row-major (rows = M for A, N for B), boxed
 // [block_rows x 64].  MN-major operand: stored [k, rows] row-major, boxed [64 x 64].
+// One-byte (E4M3) K-major operand [rows, k]: boxes of block_rows x 128 bytes.
+inline cudaError_t encode_operand_u8(CUtensorMap* map, const void* base, int64_t rows, int64_t k,
+                                     int64_t pitch_bytes, int block_rows) {
+  return host::encode_tensor_map_2d(map, base, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, uint64_t(rows), uint64_t(k),
+                                    uint64_t(pitch_bytes), uint32_t(block_rows), 2 * kBlockK,
+                                    CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
 inline cudaError_t encode_operand(CUtensorMap* map, const void* base, int64_t rows, int64_t k,
                                   int64_t pitch_elements, bool mn_major, int block_rows) {
   if (!mn_major)
@@ -57,38 +65,38 @@ inline void fill_core(FusedParams* p, int m, int n, int k, int block_n, int num_
   p->ldd = ldd;
 }
 
-template <int kMode, bool kTmaEpilogue, bool kAMn, bool kBMn>
+template <int kMode, bool kTmaEpilogue, bool kAMn, bool kBMn, bool kMx = false>
 cudaError_t launch_variant(const Operands& maps, const StoreMaps& stores, const FusedParams& p,
                            int block_n, const DeviceInfo& info, cudaStream_t stream) {
   const int64_t tiles = p.order.count();
   const int compute_capacity = info.sm_count - p.num_comm_ctas;
   const int compute = int(tiles < compute_capacity ? tiles : compute_capacity);
   const int grid = p.num_comm_ctas + compute;
-  const bool cooperative = kMode != kModePlain;
+  const bool cooperative = kMode != kModePlain || kMx;
   if (block_n == 256) {
-    using Layout = SmemLayout<256, 4>;
-    return host::launch_kernel(fused_gemm_kernel<256, 4, kMode, kTmaEpilogue, kAMn, kBMn>, grid, kThreads,
+    using Layout = SmemLayout<256, 4, kMx>;
+    return host::launch_kernel(fused_gemm_kernel<256, 4, kMode, kTmaEpilogue, kAMn, kBMn, kMx>, grid, kThreads,
                                Layout::kDynamicBytes, cooperative, stream, maps.a, maps.b, stores, p);
   }
-  using Layout = SmemLayout<128, 6>;
-  return host::launch_kernel(fused_gemm_kernel<128, 6, kMode, kTmaEpilogue, kAMn, kBMn>, grid, kThreads,
+  using Layout = SmemLayout<128, 6, kMx>;
+  return host::launch_kernel(fused_gemm_kernel<128, 6, kMode, kTmaEpilogue, kAMn, kBMn, kMx>, grid, kThreads,
                              Layout::kDynamicBytes, cooperative, stream, maps.a, maps.b, stores, p);
 }
 
 // The epilogue writes the local output through the copy engine unless the caller asked for the
 // 16-byte vector epilogue or the mode needs it (beta != 0, tile publication to communication
 // CTAs).
-template <int kMode, bool kAMn = false, bool kBMn = false>
+template <int kMode, bool kAMn = false, bool kBMn = false, bool kMx = false>
 cudaError_t launch_mode(const Operands& maps, StoreMaps& stores, const FusedParams& p, int block_n,
                         const DeviceInfo& info, cudaStream_t stream, bool tma_epilogue) {
   if constexpr (kMode != kModeQkvPush) {
     if (tma_epilogue) {
       const cudaError_t status = encode_store_map(&stores.local, p.d, uint64_t(p.m), uint64_t(p.n), p.ldd);
       if (status != cudaSuccess) return status;
-      return launch_variant<kMode, true, kAMn, kBMn>(maps, stores, p, block_n, info, stream);
+      return launch_variant<kMode, true, kAMn, kBMn, kMx>(maps, stores, p, block_n, info, stream);
     }
   }
-  return launch_variant<kMode, false, kAMn, kBMn>(maps, stores, p, block_n, info, stream);
+  return launch_variant<kMode, false, kAMn, kBMn, kMx>(maps, stores, p, block_n, info, stream);
 }
 
 inline bool vector_epilogue_requested(const fuse_b200_options* options) {

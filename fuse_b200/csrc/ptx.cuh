@@ -284,6 +284,14 @@ __device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t tile_addr, uint3
   return start | (lbo << 16) | (sbo << 32) | (uint64_t{1} << 46) | (uint64_t{2} << 61);
 }
 
+// Shared-memory descriptor of one 512-byte scale atom (32 rows x 16 bytes, contiguous, no
+// swizzle): 8-row groups are 128 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc_scale_atom(uint32_t atom_addr) {
+  const uint64_t start = (atom_addr & 0x3FFFFu) >> 4;
+  const uint64_t sbo = 128u >> 4;
+  return start | (sbo << 32) | (uint64_t{1} << 46);
+}
+
 // Instruction descriptor for kind::f16 with BF16 operands and FP32 accumulation.
 __host__ __device__ constexpr uint32_t idesc_bf16_f32(int m, int n, int a_mn_major, int b_mn_major) {
   return (1u << 4) /* D = F32 */ | (1u << 7) /* A = BF16 */ | (1u << 10) /* B = BF16 */ |

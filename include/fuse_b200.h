@@ -287,6 +287,96 @@ FUSE_API int64_t fuse_oproj_backward_ready_elements(const fuse_oproj_backward_da
 FUSE_API int32_t fuse_recommended_qkv_backward_comm_ctas(const fuse_qkv_backward_data_params* params);
 FUSE_API int32_t fuse_recommended_oproj_backward_comm_ctas(const fuse_oproj_backward_data_params* params);
 
+/* ---------------------------------------------------------------------------------------------
+ * MXFP8 forward.  include/fuse/operators/primitives/{gemm_a2a_mxfp8,a2a_gemm_mxfp8}.h
+ * ------------------------------------------------------------------------------------------- */
+/* include/fuse/types.h:22-26 (Mxfp8WeightPreparation). */
+enum { FUSE_MXFP8_PREP_COMM_CTAS = 0, FUSE_MXFP8_PREP_ALL_CTAS = 1, FUSE_MXFP8_PREP_COMM_WARPS = 2 };
+/* include/fuse/types.h:31-35 (Mxfp8Activation): packed row-major E4M3 [rows, K] + native K32
+ * scale storage (512-byte atoms of 128 rows x 4 K-blocks, K atoms before row atoms, rows padded
+ * to 128). */
+typedef struct fuse_mxfp8_activation {
+  const uint8_t* data;
+  const uint8_t* scales;
+  size_t data_bytes, scale_bytes;
+} fuse_mxfp8_activation;
+/* include/fuse/operators/semantics/attention_postprocess.h:19-27; must stay disabled (NULL). */
+typedef struct fuse_qkv_postprocess {
+  const fuse_bf16 *q_gamma, *k_gamma, *cos, *sin;
+  float epsilon;
+} fuse_qkv_postprocess;
+/* gemm_a2a_mxfp8.h:23-39 (Mxfp8GemmA2AParams): prequantised activation, BF16 master weight in
+ * projection.rhs_nt quantised inside the kernel on every call, BF16 routed output.
+ * projection.lhs is unused.  workspace: fuse_gemm_a2a_mxfp8_workspace_size() bytes, 256-byte
+ * aligned, device-local, private to the call. */
+typedef struct fuse_mxfp8_gemm_a2a_params {
+  fuse_gemm_a2a_params projection;
+  void* workspace;
+  size_t workspace_bytes;
+  fuse_mxfp8_activation activation;
+  int32_t weight_preparation;
+  int32_t epilogue_n;
+  fuse_qkv_postprocess postprocess;
+} fuse_mxfp8_gemm_a2a_params;
+
+/* gemm_a2a_mxfp8.h:50-58 / csrc/operators/sm103/api/forward_mxfp8.cuh:553-602. */
+FUSE_API int fuse_gemm_a2a_mxfp8_activation_size(const fuse_gemm_problem* problem, size_t* data_bytes,
+                                        size_t* scale_bytes);
+FUSE_API int fuse_quantize_gemm_a2a_mxfp8_activation(const fuse_gemm_problem* problem, const fuse_bf16* source,
+                                            const fuse_mxfp8_activation* output, fuse_stream stream);
+FUSE_API int fuse_gemm_a2a_mxfp8_workspace_size(const fuse_gemm_problem* problem, size_t* bytes);
+FUSE_API int fuse_launch_gemm_a2a_mxfp8_cutlass(const fuse_mxfp8_gemm_a2a_params* params, fuse_stream stream);
+FUSE_API int fuse_launch_gemm_a2a_mxfp8_cutlass_ex(const fuse_mxfp8_gemm_a2a_params* params,
+                                          const fuse_b200_options* options, fuse_stream stream);
+/* gemm_a2a_mxfp8.h:77-80: weight preparation alone, then GEMM + route on the prepared weight. */
+FUSE_API int fuse_prepare_gemm_a2a_mxfp8(const fuse_mxfp8_gemm_a2a_params* params, fuse_stream stream);
+FUSE_API int fuse_launch_gemm_a2a_mxfp8_prequantized(const fuse_mxfp8_gemm_a2a_params* params, fuse_stream stream);
+FUSE_API int fuse_launch_gemm_a2a_mxfp8_prequantized_ex(const fuse_mxfp8_gemm_a2a_params* params,
+                                               const fuse_b200_options* options, fuse_stream stream);
+/* gemm_a2a_mxfp8.h:93-94: the block-scaled GEMM alone on SMs - num_comm_ctas CTAs, prepared
+ * weight, no quantisation and no communication. */
+FUSE_API int fuse_launch_gemm_a2a_mxfp8_compute_reference(const fuse_mxfp8_gemm_a2a_params* params, fuse_stream stream);
+/* csrc/operators/sm103/detail/quantization.cuh:281-304,350-450: the standalone quantisers.
+ * Row-major BF16 [rows, k] -> E4M3 [rows, k]; BF16 [rows, cols] -> E4M3 [cols, rows] quantised
+ * along the source row axis (rows % 32 == 0).  Scales in native storage of the OUTPUT operand,
+ * fuse_b200_mxfp8_scale_bytes(output rows, output k) bytes. */
+FUSE_API int fuse_b200_quantize_mxfp8(const fuse_bf16* source, int64_t row_stride, int32_t rows, int32_t k,
+                             uint8_t* data, uint8_t* scales, fuse_stream stream);
+FUSE_API int fuse_b200_quantize_mxfp8_transposed(const fuse_bf16* source, int64_t row_stride, int32_t rows,
+                                        int32_t cols, uint8_t* data, uint8_t* scales, fuse_stream stream);
+FUSE_API size_t fuse_b200_mxfp8_scale_bytes(int64_t rows, int64_t k);
+
+/* include/fuse/operators/semantics/attention_postprocess.h:36-42; must stay disabled (NULL). */
+typedef struct fuse_residual_rms_norm {
+  const fuse_bf16* residual;
+  const fuse_bf16* gamma;
+  fuse_bf16* residual_output;
+  float epsilon;
+} fuse_residual_rms_norm;
+/* a2a_gemm_mxfp8.h:25-46 (Mxfp8A2AGemmParams): activation[p] is rank p's prequantised head shard
+ * [B*S_global, K/world] (E4M3 + native scales of THAT shape); the all-to-all copies the bytes and
+ * re-homes the scale atoms into the local [M, K] storage inside `workspace`; the BF16 master
+ * weight projection.rhs_nt is quantised in-kernel; BF16 output.  projection.peer_input,
+ * input_staging and ready are unused. */
+typedef struct fuse_mxfp8_a2a_gemm_params {
+  fuse_a2a_gemm_params projection;
+  fuse_mxfp8_activation activation[FUSE_MAX_WORLD_SIZE];
+  void* workspace;
+  size_t workspace_bytes;
+  int32_t epilogue_n, m_window_tiles, n_group_tiles;
+  fuse_residual_rms_norm postprocess;
+  uint8_t overlap_postnorm;
+  int32_t weight_preparation;
+} fuse_mxfp8_a2a_gemm_params;
+/* a2a_gemm_mxfp8.h:48-61 / csrc/operators/sm103/api/forward_mxfp8.cuh:705-924. */
+FUSE_API int fuse_a2a_gemm_mxfp8_activation_size(const fuse_gemm_problem* problem, const fuse_ulysses_route* route,
+                                        size_t* data_bytes, size_t* scale_bytes);
+FUSE_API int fuse_a2a_gemm_mxfp8_workspace_size(const fuse_gemm_problem* problem, size_t* bytes);
+FUSE_API int fuse_a2a_gemm_mxfp8_staging_view(const fuse_mxfp8_a2a_gemm_params* params, fuse_mxfp8_activation* activation);
+FUSE_API int fuse_launch_a2a_gemm_mxfp8_cutlass(const fuse_mxfp8_a2a_gemm_params* params, fuse_stream stream);
+FUSE_API int fuse_launch_a2a_gemm_mxfp8_cutlass_ex(const fuse_mxfp8_a2a_gemm_params* params,
+                                          const fuse_b200_options* options, fuse_stream stream);
+
 /* The static tile order shared by compute and communication CTAs: linear index -> (m, n) tile
  * for a grid of m_tiles x n_tiles, swizzle in {1,2,4,8}, along_n = 0 (index runs down M inside
  * bands of `swizzle` N tiles) or 1 (transpose).  Same knobs as the reference scheduler
@@ -317,7 +407,8 @@ FUSE_API int fuse_b200_read_status(uint32_t out[16], int clear);
 /* sizeof of the ABI records as compiled: 0 gemm_problem, 1 ulysses_route, 2 gemm_a2a_params,
  * 3 a2a_gemm_params, 4 kernel_traits, 5 options, 6 qkv_backward_data_params,
  * 7 qkv_backward_weight_params, 8 qkv_backward_params, 9 oproj_backward_data_params,
- * 10 oproj_backward_weight_params, 11 oproj_backward_params.  -1 for unknown ids. */
+ * 10 oproj_backward_weight_params, 11 oproj_backward_params, 12 mxfp8_activation,
+ * 13 mxfp8_gemm_a2a_params, 14 mxfp8_a2a_gemm_params.  -1 for unknown ids. */
 FUSE_API int fuse_b200_abi_sizeof(int record);
 /* Number of kernels this library has launched in this process (all entry points). */
 FUSE_API uint64_t fuse_b200_launch_count(void);

@@ -332,6 +332,9 @@ FO_API int64_t fo_mxfp8_scale_bytes(int64_t rows, int64_t width) {
  * scales.  csrc/operators/sm103/detail/quantization.cuh:120-141. */
 FO_API void fo_mxfp8_quantize(const uint16_t* source, int64_t rows, int64_t k, int64_t row_stride,
                               uint8_t* data, uint8_t* scales) {
+  /* rows past the end of the last 128-row atom quantise zeros: scale 2^0 (quantization.cuh:128) */
+  for (int64_t row = rows; row < ((rows + 127) / 128) * 128; ++row)
+    for (int64_t group = 0; group < k / 32; ++group) scales[fo_mxfp8_scale_offset(row, group * 32, k)] = 127;
 #pragma omp parallel for schedule(static)
   for (int64_t row = 0; row < rows; ++row) {
     for (int64_t group = 0; group < k / 32; ++group) {
@@ -353,6 +356,8 @@ FO_API void fo_mxfp8_quantize(const uint16_t* source, int64_t rows, int64_t k, i
  * orientation is re-quantised from its BF16 master along its own K axis. */
 FO_API void fo_mxfp8_quantize_transposed(const uint16_t* source, int64_t rows, int64_t cols,
                                          int64_t row_stride, uint8_t* data, uint8_t* scales) {
+  for (int64_t col = cols; col < ((cols + 127) / 128) * 128; ++col)
+    for (int64_t group = 0; group < rows / 32; ++group) scales[fo_mxfp8_scale_offset(col, group * 32, rows)] = 127;
 #pragma omp parallel for schedule(static)
   for (int64_t col = 0; col < cols; ++col) {
     for (int64_t group = 0; group < rows / 32; ++group) {

@@ -193,3 +193,111 @@ def oproj_backward(world, batch, seq_local, q_heads, head_dim, dy_bits, wo_bits,
         torch.cuda.synchronize()
     check_status()
     return [to_bits(t) for t in da], [to_bits(t) for t in routed], [to_bits(t) for t in dwo]
+
+
+def to_device_u8(a: np.ndarray) -> torch.Tensor:
+    return torch.from_numpy(np.ascontiguousarray(a)).to(DEV)
+
+
+def quantize_mxfp8(source_bits: np.ndarray, transposed: bool = False):
+    """Runs the CUDA quantiser on a [rows, cols] BF16 array.  Returns (data, scales) numpy uint8."""
+    rows, cols = source_bits.shape
+    src = to_device(source_bits)
+    out_rows, out_k = (cols, rows) if transposed else (rows, cols)
+    data = torch.full((out_rows, out_k), 0xAB, dtype=torch.uint8, device=DEV)
+    # zero-filled: K-block slots of a partly used scale atom are never written by the quantiser
+    scales = torch.zeros(api.mxfp8_scale_bytes(out_rows, out_k), dtype=torch.uint8, device=DEV)
+    fn = api.quantize_mxfp8_transposed if transposed else api.quantize_mxfp8
+    rc = fn(src.data_ptr(), cols, rows, cols, data.data_ptr(), scales.data_ptr(), 0)
+    assert rc == 0, f"quantize -> cudaError {rc}"
+    torch.cuda.synchronize()
+    return data.cpu().numpy(), scales.cpu().numpy()
+
+
+def qkv_forward_mxfp8(world, batch, seq_local, q_heads, kv_heads, head_dim, act_data, act_scales, w_bits, comm=4,
+                      alpha=1.0, route="direct", mode="full", swizzle=4, block_n=0):
+    """Runs every rank of the MXFP8 QKV operator.  act_data[r] uint8 [M, K], act_scales[r] native
+    scale bytes; w_bits BF16 master weight [N, K].  mode: "full" (weight quantised in-kernel),
+    "prepared" (prepare + prequantised launch) or "compute" (GEMM only, no routing).
+    Returns (local_outputs, peer_outputs, quantised_weight (data, scales))."""
+    m = batch * seq_local
+    n, k = w_bits.shape
+    rows = batch * seq_local * world
+    w = to_device(w_bits)
+    problem = N.GemmProblem(m, n, k, max_swizzle_size=swizzle)
+    rc, ws_bytes = api.gemm_a2a_mxfp8_workspace_size(problem)
+    assert rc == 0
+    local = [poisoned(m, n) for _ in range(world)]
+    peer = [poisoned(rows * n // world) for _ in range(world)]
+    done = [torch.zeros(world * N.READY_FLAG_STRIDE, dtype=torch.int32, device=DEV) for _ in range(world)]
+    ready = [torch.zeros(api.qkv_ready_elements(problem), dtype=torch.int32, device=DEV) for _ in range(world)]
+    workspaces = []
+    flags = (N.SKIP_PEER_WAIT if world > 1 else 0) | (N.QKV_ROUTE_DIRECT if route == "direct" else N.QKV_ROUTE_COMM_CTAS)
+    for r in range(world):
+        data, scales = to_device_u8(act_data[r]), to_device_u8(act_scales[r])
+        workspace = torch.full((ws_bytes + 256,), 0x5A, dtype=torch.uint8, device=DEV)
+        base = (workspace.data_ptr() + 255) // 256 * 256
+        workspaces.append((workspace, base))
+        route_rec = N.UlyssesRoute(world_size=world, rank=r, batch=batch, global_seq=seq_local * world,
+                                   seq_local=seq_local, q_heads=q_heads, kv_heads=kv_heads, head_dim=head_dim,
+                                   kind=N.ROUTE_QKV_GQA_PACK)
+        proj = N.GemmA2AParams(rhs_nt=w.data_ptr(), local_output=local[r].data_ptr(), ready=ready[r].data_ptr(),
+                               gemm=problem, route=route_rec, num_comm_ctas=comm, epoch=1, alpha=alpha)
+        for q in range(world):
+            proj.peer_output[q] = peer[q].data_ptr()
+            proj.peer_route_done_epoch[q] = done[q].data_ptr()
+        mp = N.Mxfp8GemmA2AParams(projection=proj, workspace=base, workspace_bytes=ws_bytes,
+                                  activation=N.Mxfp8Activation(data=data.data_ptr(), scales=scales.data_ptr(),
+                                                               data_bytes=data.numel(), scale_bytes=scales.numel()))
+        opts = options(flags=flags, block_n=block_n)
+        if mode == "full":
+            rc = api.launch_gemm_a2a_mxfp8_cutlass(mp, 0, opts)
+        else:
+            rc = api.prepare_gemm_a2a_mxfp8(mp, 0)
+            assert rc == 0, f"prepare -> cudaError {rc}"
+            rc = (api.launch_gemm_a2a_mxfp8_prequantized(mp, 0, opts) if mode == "prepared"
+                  else api.launch_gemm_a2a_mxfp8_compute_reference(mp, 0))
+        assert rc == 0, f"mxfp8 launch -> cudaError {rc}"
+        torch.cuda.synchronize()
+    check_status()
+    workspace, base = workspaces[0]
+    offset = base - workspace.data_ptr()
+    wq = workspace[offset:offset + n * k].cpu().numpy().reshape(n, k)
+    sf_off = offset + (n * k + 255) // 256 * 256
+    wsf = workspace[sf_off:sf_off + api.mxfp8_scale_bytes(n, k)].cpu().numpy()
+    return [to_bits(t) for t in local], [to_bits(t) for t in peer], (wq, wsf)
+
+
+def oproj_forward_mxfp8(world, rank, batch, seq_local, peer_data, peer_scales, w_bits, comm=4, causal=False,
+                        cyclic=False, alpha=1.0, block_n=0):
+    """One rank of the MXFP8 output-projection operator.  peer_data[p] uint8 [B*S_global, K/world],
+    peer_scales[p] its native scale bytes.  Returns (staged bytes [M,K], staged scales, output bits)."""
+    n, k = w_bits.shape
+    m = batch * seq_local
+    w = to_device(w_bits)
+    problem = N.GemmProblem(m, n, k, max_swizzle_size=8)
+    rc, ws_bytes = api.a2a_gemm_mxfp8_workspace_size(problem)
+    assert rc == 0
+    workspace = torch.full((ws_bytes + 256,), 0x5A, dtype=torch.uint8, device=DEV)  # garbage scratch
+    base = (workspace.data_ptr() + 255) // 256 * 256
+    out = poisoned(m, n)
+    datas = [to_device_u8(x) for x in peer_data]
+    scales = [to_device_u8(x) for x in peer_scales]
+    route = N.UlyssesRoute(world_size=world, rank=rank, batch=batch, global_seq=seq_local * world,
+                           seq_local=seq_local, kind=N.ROUTE_HEAD_TO_SEQUENCE, direction=N.ROUTE_INVERSE,
+                           causal_load_balanced=int(causal), cyclic_peer_order=int(cyclic))
+    proj = N.A2AGemmParams(rhs_nt=w.data_ptr(), output=out.data_ptr(), gemm=problem, route=route,
+                           num_comm_ctas=comm, epoch=1, alpha=alpha)
+    mp = N.Mxfp8A2AGemmParams(projection=proj, workspace=base, workspace_bytes=ws_bytes)
+    for q in range(world):
+        mp.activation[q] = N.Mxfp8Activation(data=datas[q].data_ptr(), scales=scales[q].data_ptr(),
+                                             data_bytes=datas[q].numel(), scale_bytes=scales[q].numel())
+    rc = api.launch_a2a_gemm_mxfp8_cutlass(mp, 0, options(block_n=block_n))
+    assert rc == 0, f"launch_a2a_gemm_mxfp8_cutlass -> cudaError {rc}"
+    check_status()
+    view = api.a2a_gemm_mxfp8_staging_view(mp)
+    off = view.data - workspace.data_ptr()
+    staged = workspace[off:off + m * k].cpu().numpy().reshape(m, k)
+    soff = view.scales - workspace.data_ptr()
+    staged_scales = workspace[soff:soff + view.scale_bytes].cpu().numpy()
+    return staged, staged_scales, to_bits(out)

@@ -213,8 +213,30 @@ class Mxfp8A2AGemmParams(_Record):
     _defaults_ = {"epilogue_n": 32}
 
 
+class GroupedGemmPolicy(_Record):
+    """include/fuse/operators/primitives/grouped_gemm.h:17-53 of the reference."""
+    _fields_ = [("num_comm_ctas", C.c_int32), ("num_compute_ctas", C.c_int32), ("swizzle", C.c_int32),
+                ("along_n", C.c_uint8), ("tile_n", C.c_int32), ("tile_k", C.c_int32),
+                ("mma_sm_count", C.c_int32), ("dispatch_copy", C.c_int32),
+                ("balance_dispatch_tail", C.c_uint8), ("swap_ab", C.c_uint8), ("trim_swap_tokens", C.c_uint8),
+                ("scheduler", C.c_int32)]
+    _defaults_ = {"num_comm_ctas": 20, "num_compute_ctas": 128, "swizzle": 1, "tile_n": 128, "tile_k": 64,
+                  "mma_sm_count": 1, "trim_swap_tokens": 1}
+
+
+class Bf16GroupedGemmParams(_Record):
+    """include/fuse/operators/primitives/grouped_gemm.h:62-85 of the reference."""
+    _fields_ = [("lhs", C.c_void_p), ("weight_nt", C.c_void_p), ("output", C.c_void_p),
+                ("row_offsets", C.c_void_p), ("source", C.c_void_p),
+                ("peer_input", C.c_void_p * MAX_WORLD_SIZE), ("peer_output", C.c_void_p * MAX_WORLD_SIZE),
+                ("peer_started", C.c_void_p * MAX_WORLD_SIZE), ("peer_done", C.c_void_p * MAX_WORLD_SIZE),
+                ("experts", C.c_int32), ("n", C.c_int32), ("k", C.c_int32), ("expert_row_capacity", C.c_int32),
+                ("rank", C.c_int32), ("world_size", C.c_int32), ("topk", C.c_int32),
+                ("policy", GroupedGemmPolicy), ("dispatch_buffer_rows", C.c_int32)]
+
+
 ABI_RECORDS = {0: GemmProblem, 1: UlyssesRoute, 2: GemmA2AParams, 3: A2AGemmParams,
-               4: KernelTraits, 5: Options, 14: Mxfp8A2AGemmParams, 12: Mxfp8Activation, 13: Mxfp8GemmA2AParams, 6: QkvBackwardDataParams, 7: QkvBackwardWeightParams,
+               4: KernelTraits, 5: Options, 15: GroupedGemmPolicy, 16: Bf16GroupedGemmParams, 14: Mxfp8A2AGemmParams, 12: Mxfp8Activation, 13: Mxfp8GemmA2AParams, 6: QkvBackwardDataParams, 7: QkvBackwardWeightParams,
                8: QkvBackwardParams, 9: OprojBackwardDataParams, 10: OprojBackwardWeightParams,
                11: OprojBackwardParams}
 
@@ -256,6 +278,10 @@ SYMBOLS = {
     "fuse_a2a_gemm_mxfp8_staging_view": (C.c_int, [C.POINTER(Mxfp8A2AGemmParams), C.POINTER(Mxfp8Activation)]),
     "fuse_launch_a2a_gemm_mxfp8_cutlass": (C.c_int, [C.POINTER(Mxfp8A2AGemmParams), _P]),
     "fuse_launch_a2a_gemm_mxfp8_cutlass_ex": (C.c_int, [C.POINTER(Mxfp8A2AGemmParams), C.POINTER(Options), _P]),
+    "fuse_create_bf16_a2a_grouped_gemm": (C.c_int, [C.POINTER(Bf16GroupedGemmParams), C.POINTER(C.c_void_p)]),
+    "fuse_launch_bf16_grouped_gemm": (C.c_int, [C.c_void_p, _P]),
+    "fuse_launch_bf16_grouped_gemm_ex": (C.c_int, [C.c_void_p, C.POINTER(Options), _P]),
+    "fuse_destroy_bf16_grouped_gemm": (C.c_int, [C.c_void_p]),
     "fuse_qkv_cutlass_kernel_traits": (None, [C.POINTER(GemmProblem), C.POINTER(KernelTraits)]),
     "fuse_cutlass_kernel_traits": (None, [C.POINTER(KernelTraits)]),
     "fuse_a2a_lhs_gemm_ready_elements": (C.c_int64, [C.POINTER(GemmProblem), C.POINTER(UlyssesRoute)]),

@@ -217,3 +217,24 @@ def launch_a2a_gemm_mxfp8_cutlass(params: Mxfp8A2AGemmParams, stream: int = 0, o
     if options is None:
         return N.lib().fuse_launch_a2a_gemm_mxfp8_cutlass(C.byref(params), stream)
     return N.lib().fuse_launch_a2a_gemm_mxfp8_cutlass_ex(C.byref(params), _opt(options), stream)
+
+
+# ---- MoE dispatch + grouped GEMM (include/fuse/operators/primitives/grouped_gemm.h) -------------
+from ._native import Bf16GroupedGemmParams, GroupedGemmPolicy  # noqa: E402,F401
+
+
+def create_bf16_a2a_grouped_gemm(params: Bf16GroupedGemmParams):
+    """Returns (cudaError, plan handle).  Allocates private device metadata: call outside capture."""
+    plan = C.c_void_p()
+    rc = N.lib().fuse_create_bf16_a2a_grouped_gemm(C.byref(params), C.byref(plan))
+    return rc, plan.value
+
+
+def launch_bf16_grouped_gemm(plan: int, stream: int = 0, options: Options | None = None) -> int:
+    if options is None:
+        return N.lib().fuse_launch_bf16_grouped_gemm(plan, stream)
+    return N.lib().fuse_launch_bf16_grouped_gemm_ex(plan, _opt(options), stream)
+
+
+def destroy_bf16_grouped_gemm(plan: int) -> int:
+    return N.lib().fuse_destroy_bf16_grouped_gemm(plan)

@@ -329,6 +329,8 @@ int fuse_b200_abi_sizeof(int record) {
     case 12: return int(sizeof(fuse_mxfp8_activation));
     case 13: return int(sizeof(fuse_mxfp8_gemm_a2a_params));
     case 14: return int(sizeof(fuse_mxfp8_a2a_gemm_params));
+    case 15: return int(sizeof(fuse_grouped_gemm_policy));
+    case 16: return int(sizeof(fuse_bf16_grouped_gemm_params));
     default: return -1;
   }
 }

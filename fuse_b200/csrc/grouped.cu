@@ -1,0 +1,165 @@
+// MoE dispatch -> expert FC1 grouped GEMM: plan object and entry points.
+// Interface: include/fuse/operators/primitives/grouped_gemm.h:10-100 of the reference;
+// plan lifetime and validation follow csrc/operators/sm103/api/grouped.cuh:58-428.
+#include <new>
+#include <vector>
+
+#include "grouped.cuh"
+#include "launch.cuh"
+
+struct fuse_bf16_grouped_gemm_plan {
+  fuse_b200::GroupedParams params{};
+  void* metadata = nullptr;  // one private device allocation: tensor maps, flags, epoch, prefix
+  int block_n = 256;
+  int grid = 0;
+  int device = -1;
+};
+
+namespace fuse_b200 {
+namespace {
+
+using namespace launch;
+
+size_t align256(size_t n) { return (n + 255) & ~size_t{255}; }
+
+cudaError_t create_dispatch_plan(const fuse_bf16_grouped_gemm_params& p, fuse_bf16_grouped_gemm_plan** out) {
+  if (out == nullptr) return cudaErrorInvalidValue;
+  *out = nullptr;
+  if (p.lhs == nullptr || p.weight_nt == nullptr || p.output == nullptr || p.row_offsets == nullptr ||
+      p.source == nullptr || p.experts <= 0 || p.n <= 0 || p.k <= 0 || p.expert_row_capacity <= 0 ||
+      p.world_size <= 0 || p.world_size > FUSE_MAX_WORLD_SIZE || p.rank < 0 || p.rank >= p.world_size ||
+      p.topk <= 0 || p.policy.num_comm_ctas <= 0 || p.policy.num_compute_ctas <= 0)
+    return cudaErrorInvalidValue;
+  for (int r = 0; r < p.world_size; ++r)
+    if (!host::aligned16(p.peer_input[r]) || !host::aligned4(p.peer_started[r]) || !host::aligned4(p.peer_done[r]))
+      return cudaErrorInvalidValue;
+  // geometry outside this implementation's domain
+  if (p.n % 8 != 0 || p.k % 8 != 0 || (p.policy.tile_n != 128 && p.policy.tile_n != 256) ||
+      p.policy.mma_sm_count != 1 || p.policy.swap_ab ||
+      (p.dispatch_buffer_rows != 0 && p.dispatch_buffer_rows != p.expert_row_capacity))
+    return cudaErrorNotSupported;
+  DeviceInfo info;
+  cudaError_t status = check_device(&info);
+  if (status != cudaSuccess) return status;
+  if (p.policy.num_comm_ctas >= info.sm_count) return cudaErrorInvalidValue;
+
+  std::vector<void*> lhs(p.experts), weights(p.experts);
+  if ((status = cudaMemcpy(lhs.data(), p.lhs, sizeof(void*) * p.experts, cudaMemcpyDeviceToHost)) != cudaSuccess)
+    return status;
+  if ((status = cudaMemcpy(weights.data(), p.weight_nt, sizeof(void*) * p.experts, cudaMemcpyDeviceToHost)) !=
+      cudaSuccess)
+    return status;
+
+  auto* plan = new (std::nothrow) fuse_bf16_grouped_gemm_plan;
+  if (plan == nullptr) return cudaErrorMemoryAllocation;
+  plan->device = info.device;
+  plan->block_n = p.policy.tile_n;
+  const int cap_tiles = host::ceil_div(p.expert_row_capacity, kBlockM);
+  const size_t maps_bytes = align256(sizeof(CUtensorMap) * size_t(p.experts));
+  const size_t ready_bytes = align256(size_t(p.experts) * cap_tiles * FUSE_READY_FLAG_STRIDE * sizeof(uint32_t));
+  const size_t prefix_bytes = align256(sizeof(int32_t) * size_t(p.experts + 1));
+  const size_t total = 2 * maps_bytes + ready_bytes + 256 + prefix_bytes;
+  if ((status = cudaMalloc(&plan->metadata, total)) != cudaSuccess) {
+    delete plan;
+    return status;
+  }
+  auto fail = [&](cudaError_t error) {
+    cudaFree(plan->metadata);
+    delete plan;
+    return error;
+  };
+  if ((status = cudaMemset(plan->metadata, 0, total)) != cudaSuccess) return fail(status);
+  std::vector<CUtensorMap> maps_a(p.experts), maps_b(p.experts);
+  for (int e = 0; e < p.experts; ++e) {
+    if (!host::aligned16(lhs[e]) || !host::aligned16(weights[e])) return fail(cudaErrorInvalidValue);
+    if ((status = encode_operand(&maps_a[e], lhs[e], p.expert_row_capacity, p.k, p.k, false, kBlockM)) != cudaSuccess)
+      return fail(status);
+    if ((status = encode_operand(&maps_b[e], weights[e], p.n, p.k, p.k, false, plan->block_n)) != cudaSuccess)
+      return fail(status);
+  }
+  uint8_t* base = static_cast<uint8_t*>(plan->metadata);
+  if ((status = cudaMemcpy(base, maps_a.data(), sizeof(CUtensorMap) * p.experts, cudaMemcpyHostToDevice)) != cudaSuccess ||
+      (status = cudaMemcpy(base + maps_bytes, maps_b.data(), sizeof(CUtensorMap) * p.experts,
+                           cudaMemcpyHostToDevice)) != cudaSuccess)
+    return fail(status);
+
+  GroupedParams& g = plan->params;
+  g.experts = p.experts;
+  g.n = p.n;
+  g.k = p.k;
+  g.capacity = p.expert_row_capacity;
+  g.lhs_rows = p.expert_row_capacity;
+  g.rank = p.rank;
+  g.world = p.world_size;
+  g.n_tiles = host::ceil_div(p.n, plan->block_n);
+  g.cap_tiles = cap_tiles;
+  g.num_comm_ctas = p.policy.num_comm_ctas;
+  g.maps_a = reinterpret_cast<const CUtensorMap*>(base);
+  g.maps_b = reinterpret_cast<const CUtensorMap*>(base + maps_bytes);
+  g.lhs = reinterpret_cast<uint16_t* const*>(p.lhs);
+  g.output = reinterpret_cast<uint16_t* const*>(p.output);
+  g.row_offsets = p.row_offsets;
+  g.source = reinterpret_cast<const GroupedTokenSource*>(p.source);
+  g.ready = reinterpret_cast<uint32_t*>(base + 2 * maps_bytes);
+  g.epoch_word = reinterpret_cast<uint32_t*>(base + 2 * maps_bytes + ready_bytes);
+  g.tile_prefix = reinterpret_cast<int32_t*>(base + 2 * maps_bytes + ready_bytes + 256);
+  for (int r = 0; r < p.world_size; ++r) {
+    g.peer_input[r] = p.peer_input[r];
+    g.peer_started[r] = p.peer_started[r];
+    g.peer_done[r] = p.peer_done[r];
+  }
+  const int compute = p.policy.num_compute_ctas < info.sm_count - p.policy.num_comm_ctas
+                          ? p.policy.num_compute_ctas
+                          : info.sm_count - p.policy.num_comm_ctas;
+  plan->grid = p.policy.num_comm_ctas + compute;
+  g.wait.status = info.status;
+  if ((status = cudaDeviceSynchronize()) != cudaSuccess) return fail(status);
+  *out = plan;
+  return cudaSuccess;
+}
+
+cudaError_t launch_plan(fuse_bf16_grouped_gemm_plan* plan, const fuse_b200_options* options, cudaStream_t stream) {
+  if (plan == nullptr) return cudaErrorInvalidValue;
+  GroupedParams g = plan->params;
+  g.flags = options ? options->flags : 0u;
+  g.wait.launch_id = host::next_launch_id();
+  g.wait.epoch = 0;  // read from the device epoch word
+  g.wait.budget_ns = options && options->wait_budget_ns ? options->wait_budget_ns : host::default_wait_budget_ns();
+  grouped_prepare_kernel<<<1, 256, 0, stream>>>(g);
+  cudaError_t status = cudaGetLastError();
+  if (status != cudaSuccess) return status;
+  host::count_launch();
+  if (plan->block_n == 256) {
+    using Layout = SmemLayout<256, 4, false>;
+    return host::launch_kernel(grouped_gemm_kernel<256, 4>, plan->grid, kThreads, Layout::kDynamicBytes, true,
+                               stream, g);
+  }
+  using Layout = SmemLayout<128, 6, false>;
+  return host::launch_kernel(grouped_gemm_kernel<128, 6>, plan->grid, kThreads, Layout::kDynamicBytes, true, stream, g);
+}
+
+}  // namespace
+}  // namespace fuse_b200
+
+extern "C" {
+
+int fuse_create_bf16_a2a_grouped_gemm(const fuse_bf16_grouped_gemm_params* params,
+                                      fuse_bf16_grouped_gemm_plan** plan) {
+  if (params == nullptr) return int(cudaErrorInvalidValue);
+  return int(fuse_b200::create_dispatch_plan(*params, plan));
+}
+int fuse_launch_bf16_grouped_gemm(fuse_bf16_grouped_gemm_plan* plan, fuse_stream stream) {
+  return int(fuse_b200::launch_plan(plan, nullptr, reinterpret_cast<cudaStream_t>(stream)));
+}
+int fuse_launch_bf16_grouped_gemm_ex(fuse_bf16_grouped_gemm_plan* plan, const fuse_b200_options* options,
+                                     fuse_stream stream) {
+  return int(fuse_b200::launch_plan(plan, options, reinterpret_cast<cudaStream_t>(stream)));
+}
+int fuse_destroy_bf16_grouped_gemm(fuse_bf16_grouped_gemm_plan* plan) {
+  if (plan == nullptr) return int(cudaErrorInvalidValue);
+  const cudaError_t status = cudaFree(plan->metadata);
+  delete plan;
+  return int(status);
+}
+
+}  // extern "C"

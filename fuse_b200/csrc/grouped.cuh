@@ -1,0 +1,441 @@
+// MoE dispatch -> expert FC1 grouped GEMM: one persistent kernel.
+//
+// For every local expert e, A_e[M_e, K] is gathered row by row from the ranks that hold the
+// routed tokens (source[row] = {rank, token, slot} -> peer_input[rank][token, :]) into the
+// expert's lhs slab, and D_e[M_e, N] = A_e W_e[N, K]^T.  M_e comes from the DEVICE row_offsets on
+// every launch, so a captured launch can be replayed with new routes.
+//
+//   communication CTAs: the bulk-copy pull pipeline (one row = one chunk) over sub-units of 32
+//       rows of a (expert, 128-row panel), dealt round-robin to the pull warps in panel order;
+//       a panel's flag is published by the arrival that completes it;
+//   compute CTAs: the tcgen05 pipeline of fused_gemm.cuh with a grouped tile decode -- tile ->
+//       (expert, m, n) through the per-launch prefix of tile counts, N fastest so the CTAs of a
+//       wave share a freshly arrived panel -- per-expert tensor maps read from global memory,
+//       the TMA producer gated on the panel flag, and an epilogue that writes only rows < M_e
+//       (the caller's poison in the unused capacity stays).
+//
+// Replaces csrc/operators/sm103/detail/grouped/{a2a_gemm,persistent_gemm,cutlass_pipeline,
+// communication}.cuh of the reference (dispatch direction).
+#pragma once
+
+#include "fused_gemm.cuh"
+
+namespace fuse_b200 {
+
+struct GroupedTokenSource {
+  int32_t rank, token, slot;
+};
+
+struct GroupedParams {
+  int32_t experts, n, k, capacity, lhs_rows;
+  int32_t rank, world;
+  int32_t n_tiles, cap_tiles, num_comm_ctas;
+  const CUtensorMap* maps_a;   // [experts], lhs slabs   [lhs_rows, K]
+  const CUtensorMap* maps_b;   // [experts], weights     [N, K]
+  uint16_t* const* lhs;        // device array of per-expert slab pointers
+  uint16_t* const* output;     // device array of per-expert output pointers [capacity, N]
+  const int64_t* row_offsets;  // device [experts + 1]
+  const GroupedTokenSource* source;
+  const uint16_t* peer_input[kMaxWorldSize];
+  uint32_t* peer_started[kMaxWorldSize];
+  uint32_t* peer_done[kMaxWorldSize];
+  uint32_t* ready;             // [experts * cap_tiles] flag lines: word 0 epoch, word 1 arrivals
+  uint32_t* epoch_word;        // device epoch, advanced by the prepare kernel
+  int32_t* tile_prefix;        // [experts + 1] tiles before each expert, written by prepare
+  uint32_t flags;
+  WaitContext wait;            // wait.epoch is read from epoch_word on the device
+};
+
+// One block per launch: advances the device epoch, derives the tile prefix from the device row
+// counts, clears the panels' arrival counters and tells every peer that this rank's inputs for
+// this invocation are in place (everything earlier on the stream has completed).
+// csrc/operators/sm103/detail/grouped/communication.cuh:137-207.
+__global__ void grouped_prepare_kernel(GroupedParams p) {
+  __shared__ uint32_t epoch;
+  if (threadIdx.x == 0) {
+    epoch = *p.epoch_word + 1u;
+    if (epoch == 0u) epoch = 1u;
+    *p.epoch_word = epoch;
+    int32_t tiles = 0;
+    for (int32_t e = 0; e < p.experts; ++e) {
+      p.tile_prefix[e] = tiles;
+      int64_t rows = p.row_offsets[e + 1] - p.row_offsets[e];
+      if (rows < 0) rows = 0;
+      if (rows > p.capacity) rows = p.capacity;
+      tiles += int32_t((rows + kBlockM - 1) / kBlockM) * p.n_tiles;
+    }
+    p.tile_prefix[p.experts] = tiles;
+  }
+  for (int32_t i = threadIdx.x; i < p.experts * p.cap_tiles; i += blockDim.x)
+    p.ready[int64_t(i) * kReadyFlagStride + 1] = 0u;
+  __syncthreads();
+  if (threadIdx.x < p.world) {
+    __threadfence_system();
+    ptx::st_release_sys(p.peer_started[threadIdx.x] + p.rank * kReadyFlagStride, epoch);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Dispatch pull (communication CTAs).
+// ------------------------------------------------------------------------------------------
+struct DispatchCursor {
+  int32_t sub;       // sub-unit index over (expert, panel, quarter); advances by the pull warps
+  int32_t row;       // row inside the sub-unit = chunk (one row per chunk), times pieces
+  int32_t rows;      // rows of this sub-unit
+  int32_t pieces_done;
+  int32_t flag, needed;
+  int64_t first_row; // index of its first row in `source`
+  uint8_t* dst;      // destination of its first row
+};
+
+__device__ __forceinline__ void dispatch_pull_role(const GroupedParams& p, const WaitContext& w,
+                                                   uint32_t smem_base) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp >= kPullWarps) return;
+  const uint32_t ring = smem_base + uint32_t(warp) * kPullStages * kPullStageBytes;
+  const uint32_t bars = smem_base + kPullWarps * kPullStages * kPullStageBytes +
+                        uint32_t(warp) * kPullStages * 8u;
+  if (lane == 0) {
+    for (int s = 0; s < kPullStages; ++s) ptx::mbar_init(bars + 8u * s, 1);
+    ptx::fence_mbar_init();
+  }
+  __syncwarp();
+
+  const int32_t workers = p.num_comm_ctas * kPullWarps;
+  const int32_t worker = warp * p.num_comm_ctas + int32_t(blockIdx.x);
+  const uint32_t row_bytes = uint32_t(p.k) * 2u;
+  const int32_t pieces = int32_t((row_bytes + kPullStageBytes - 1) / kPullStageBytes);
+  const int32_t subs_per_expert = p.cap_tiles * kPullSubsPerTile;
+  const int32_t subs_total = p.experts * subs_per_expert;
+
+  auto seek = [&](DispatchCursor& c) {
+    for (; c.sub < subs_total; c.sub += workers) {
+      const int32_t e = c.sub / subs_per_expert, within = c.sub - e * subs_per_expert;
+      const int32_t panel = within / kPullSubsPerTile, quarter = within - panel * kPullSubsPerTile;
+      const int64_t begin = p.row_offsets[e];
+      int64_t expert_rows = p.row_offsets[e + 1] - begin;
+      if (expert_rows > p.capacity) expert_rows = p.capacity;
+      const int32_t row0 = panel * kBlockM + quarter * kPullSubRows;
+      if (row0 >= expert_rows) continue;
+      const int32_t panel_rows = int32_t(expert_rows - panel * kBlockM < kBlockM ? expert_rows - panel * kBlockM : kBlockM);
+      c.rows = int32_t(expert_rows - row0 < kPullSubRows ? expert_rows - row0 : kPullSubRows);
+      c.row = 0;
+      c.pieces_done = 0;
+      c.flag = e * p.cap_tiles + panel;
+      c.needed = (panel_rows + kPullSubRows - 1) / kPullSubRows;
+      c.first_row = begin + row0;
+      c.dst = reinterpret_cast<uint8_t*>(p.lhs[e]) + int64_t(row0 % p.lhs_rows) * row_bytes;
+      return true;
+    }
+    return false;
+  };
+  auto advance = [&](DispatchCursor& c) {
+    if (++c.pieces_done < pieces) return true;
+    c.pieces_done = 0;
+    if (++c.row < c.rows) return true;
+    c.sub += workers;
+    return seek(c);
+  };
+
+  uint32_t started_seen = 0;
+  bool ok = true;
+  auto start_load = [&](const DispatchCursor& c, int stage) {  // whole warp
+    GroupedTokenSource src{0, 0, 0};
+    if (lane == 0) src = p.source[c.first_row + c.row];
+    const int32_t src_rank = __shfl_sync(0xffffffffu, src.rank, 0);
+    if (src_rank != p.rank && !(p.flags & kFlagSkipPeerWait) && !((started_seen >> src_rank) & 1u)) {
+      // the peer's tokens are valid once it has entered this invocation
+      uint32_t good = 1u;
+      if (lane == 0)
+        good = flag_wait<true>(p.peer_started[p.rank] + src_rank * kReadyFlagStride, w.epoch, w,
+                               kSitePeerStarted, uint32_t(src_rank)) ? 1u : 0u;
+      good = __shfl_sync(0xffffffffu, good, 0);
+      if (!good) { ok = false; return; }
+      started_seen |= 1u << src_rank;
+    }
+    if (lane == 0) {
+      const uint32_t offset = uint32_t(c.pieces_done) * kPullStageBytes;
+      const uint32_t bytes = row_bytes - offset < kPullStageBytes ? row_bytes - offset : kPullStageBytes;
+      const uint32_t bar = bars + 8u * stage;
+      ptx::mbar_expect_tx(bar, bytes);
+      ptx::bulk_load(ring + uint32_t(stage) * kPullStageBytes,
+                     reinterpret_cast<const uint8_t*>(p.peer_input[src.rank]) + int64_t(src.token) * row_bytes + offset,
+                     bytes, bar);
+    }
+  };
+
+  uint32_t counted_before = 0;
+  int32_t counted_flag = -1, counted_needed = 1;
+  auto publish = [&]() {
+    if (lane == 0 && counted_flag >= 0 && counted_before + 1u == uint32_t(counted_needed))
+      ptx::st_release_gpu(p.ready + int64_t(counted_flag) * kReadyFlagStride, w.epoch);
+    counted_flag = -1;
+  };
+  auto count = [&](int32_t flag, int32_t needed) {
+    publish();
+    if (lane == 0)
+      counted_before = ptx::atom_acq_rel_gpu_add(p.ready + int64_t(flag) * kReadyFlagStride + 1, 1u);
+    counted_flag = flag;
+    counted_needed = needed;
+  };
+
+  DispatchCursor load_cursor{};
+  load_cursor.sub = worker;
+  bool more_loads = seek(load_cursor);
+  if (!more_loads) return;
+  DispatchCursor store_cursor = load_cursor;
+  int32_t issued = 0, consumed = 0;
+  while (issued < kPullStages && more_loads) {
+    start_load(load_cursor, issued % kPullStages);
+    if (!ok) break;
+    more_loads = advance(load_cursor);
+    ++issued;
+  }
+  int32_t lag_flag[kPullLag], lag_needed[kPullLag];
+#pragma unroll
+  for (int i = 0; i < kPullLag; ++i) { lag_flag[i] = -1; lag_needed[i] = 1; }
+  bool more_stores = true;
+  while (ok && more_stores) {
+    const int stage = consumed % kPullStages;
+    uint32_t landed = 1u;
+    if (lane == 0)
+      landed = mbar_wait(bars + 8u * stage, uint32_t(consumed / kPullStages) & 1u, w, kSiteCommStage) ? 1u : 0u;
+    landed = __shfl_sync(0xffffffffu, landed, 0);
+    if (!landed) { ok = false; break; }
+    if (lane == 0) {
+      const uint32_t offset = uint32_t(store_cursor.pieces_done) * kPullStageBytes;
+      const uint32_t bytes = row_bytes - offset < kPullStageBytes ? row_bytes - offset : kPullStageBytes;
+      ptx::bulk_store(store_cursor.dst + int64_t(store_cursor.row) * row_bytes + offset,
+                      ring + uint32_t(stage) * kPullStageBytes, bytes);
+    }
+    ptx::bulk_commit();
+    ++consumed;
+    ptx::bulk_wait_read<0>();
+    __syncwarp();
+    if (more_loads && issued < consumed + kPullStages) {
+      start_load(load_cursor, issued % kPullStages);
+      if (ok) {
+        more_loads = advance(load_cursor);
+        ++issued;
+      }
+    }
+    ptx::bulk_wait<kPullLag>();
+    __syncwarp();
+    if (lag_flag[kPullLag - 1] >= 0) count(lag_flag[kPullLag - 1], lag_needed[kPullLag - 1]);
+#pragma unroll
+    for (int i = kPullLag - 1; i > 0; --i) { lag_flag[i] = lag_flag[i - 1]; lag_needed[i] = lag_needed[i - 1]; }
+    const bool closes = store_cursor.row + 1 == store_cursor.rows && store_cursor.pieces_done + 1 == pieces;
+    lag_flag[0] = closes ? store_cursor.flag : -1;
+    lag_needed[0] = store_cursor.needed;
+    more_stores = advance(store_cursor);
+  }
+  ptx::bulk_wait<0>();
+  __syncwarp();
+  if (ok) {
+#pragma unroll
+    for (int i = kPullLag - 1; i >= 0; --i)
+      if (lag_flag[i] >= 0) count(lag_flag[i], lag_needed[i]);
+    publish();
+  }
+  if (!ok && lane == 0) {
+    for (int32_t i = consumed; i < issued; ++i)
+      mbar_wait(bars + 8u * uint32_t(i % kPullStages), uint32_t(i / kPullStages) & 1u, w, kSiteDrain, false);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// The grouped kernel.
+// ------------------------------------------------------------------------------------------
+template <int kBlockN, int kStages>
+__global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const GroupedParams p) {
+  using Layout = SmemLayout<kBlockN, kStages, false>;
+  constexpr uint32_t kAccumStages = Layout::kAccumStages;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool is_comm = int(blockIdx.x) < p.num_comm_ctas;
+  WaitContext w = p.wait;
+  w.epoch = *p.epoch_word;  // advanced by the prepare kernel earlier on the stream
+
+  if (is_comm) {
+    dispatch_pull_role(p, w, base);
+  } else {
+    const uint32_t bar_base = base + Layout::kBarrierOffset;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+    auto tmem_full_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };
+    auto tmem_empty_bar = [&](int s) { return bar_base + 8u * (2 * kStages + kAccumStages + s); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + Layout::kTmemSlotOffset);
+    constexpr uint32_t kTmemColumns = Layout::kTmemColumns;
+    if (threadIdx.x == 0) {
+      for (int s = 0; s < kStages; ++s) {
+        ptx::mbar_init(full_bar(s), 1);
+        ptx::mbar_init(empty_bar(s), 1);
+      }
+      for (int s = 0; s < int(kAccumStages); ++s) {
+        ptx::mbar_init(tmem_full_bar(s), 1);
+        ptx::mbar_init(tmem_empty_bar(s), kEpilogueThreads);
+      }
+      ptx::fence_mbar_init();
+    }
+    if (warp == 2) {
+      ptx::tmem_alloc(base + Layout::kTmemSlotOffset, kTmemColumns);
+      ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int32_t compute_ctas = int32_t(gridDim.x) - p.num_comm_ctas;
+    const int32_t compute_id = int32_t(blockIdx.x) - p.num_comm_ctas;
+    const int32_t tiles = p.tile_prefix[p.experts];
+    const int32_t k_blocks = (p.k + kBlockK - 1) / kBlockK;
+    // tile -> (expert, m, n); experts only move forward for one CTA
+    auto decode = [&](int32_t t, int32_t& expert, int32_t& mt, int32_t& nt) {
+      while (t >= p.tile_prefix[expert + 1]) ++expert;
+      const int32_t local = t - p.tile_prefix[expert];
+      mt = local / p.n_tiles;
+      nt = local - mt * p.n_tiles;
+    };
+
+    if (warp == 0) {
+      if (lane == 0) {
+        uint32_t stage = 0, phase = 0, issued_mask = 0, issued_parity = 0;
+        int32_t expert = 0;
+        bool ok = true;
+        for (int32_t t = compute_id; ok && t < tiles; t += compute_ctas) {
+          int32_t mt, nt;
+          decode(t, expert, mt, nt);
+          // the whole panel (all of K) arrives as one unit
+          const int64_t flag = (int64_t(expert) * p.cap_tiles + mt) * kReadyFlagStride;
+          ok = flag_wait<false>(p.ready + flag, w.epoch, w, kSitePanelReady, uint32_t(flag / kReadyFlagStride));
+          ptx::fence_proxy_async_global();
+          if (!ok) break;
+          const CUtensorMap* map_a = p.maps_a + expert;
+          const CUtensorMap* map_b = p.maps_b + expert;
+          for (int32_t kb = 0; kb < k_blocks; ++kb) {
+            ok = mbar_wait(empty_bar(stage), phase ^ 1u, w, kSiteSmemEmpty);
+            if (!ok) break;
+            ptx::mbar_expect_tx(full_bar(stage), Layout::kStageBytes);
+            const uint32_t a_dst = base + stage * Layout::kStageBytes;
+            ptx::tma_load_2d(a_dst, map_a, full_bar(stage), kb * kBlockK, (mt * kBlockM) % p.lhs_rows);
+            ptx::tma_load_2d(a_dst + Layout::kABytes, map_b, full_bar(stage), kb * kBlockK, nt * kBlockN);
+            issued_mask |= 1u << stage;
+            issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
+            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          }
+        }
+        if (!ok)
+          for (int s = 0; s < kStages; ++s)
+            if ((issued_mask >> s) & 1u) mbar_wait(full_bar(s), (issued_parity >> s) & 1u, w, kSiteDrain, false);
+      }
+    } else if (warp == 1) {
+      if (lane == 0) {
+        constexpr uint32_t kIdesc = ptx::idesc_bf16_f32(kBlockM, kBlockN, 0, 0);
+        uint32_t stage = 0, phase = 0, accum = 0, accum_phase = 0;
+        bool ok = true;
+        for (int32_t t = compute_id; ok && t < tiles; t += compute_ctas) {
+          ok = mbar_wait(tmem_empty_bar(accum), accum_phase ^ 1u, w, kSiteTmemEmpty);
+          if (!ok) break;
+          ptx::tc_fence_after();
+          const uint32_t d_tmem = tmem_base + accum * kBlockN;
+          for (int32_t kb = 0; kb < k_blocks; ++kb) {
+            ok = mbar_wait(full_bar(stage), phase, w, kSiteSmemFull);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            const uint32_t a_addr = base + stage * Layout::kStageBytes;
+            const uint64_t a_desc = ptx::smem_desc_k_sw128(a_addr);
+            const uint64_t b_desc = ptx::smem_desc_k_sw128(a_addr + Layout::kABytes);
+#pragma unroll
+            for (int k = 0; k < kBlockK / kUmmaK; ++k)
+              ptx::umma_f16(d_tmem, a_desc + uint64_t(2 * k), b_desc + uint64_t(2 * k), kIdesc,
+                            (kb | k) != 0 ? 1u : 0u);
+            ptx::umma_commit(empty_bar(stage));
+            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          }
+          if (!ok) break;
+          ptx::umma_commit(tmem_full_bar(accum));
+          if (++accum == kAccumStages) { accum = 0; accum_phase ^= 1u; }
+        }
+        if (!ok) {
+          ptx::umma_commit(tmem_full_bar(accum));
+          mbar_wait(tmem_full_bar(accum), accum_phase, w, kSiteDrain, false);
+        }
+      }
+    } else if (warp >= 4) {
+      const int quarter = warp & 3;
+      uint32_t accum = 0, accum_phase = 0;
+      int32_t expert = 0;
+      bool ok = true;
+      for (int32_t t = compute_id; ok && t < tiles; t += compute_ctas) {
+        int32_t mt, nt;
+        decode(t, expert, mt, nt);
+        ok = mbar_wait(tmem_full_bar(accum), accum_phase, w, kSiteTmemFull);
+        ok = ptx::named_bar_all(2, kEpilogueThreads, ok);
+        if (!ok) break;
+        ptx::tc_fence_after();
+        int64_t expert_rows = p.row_offsets[expert + 1] - p.row_offsets[expert];
+        if (expert_rows > p.capacity) expert_rows = p.capacity;
+        const int32_t row = mt * kBlockM + quarter * 32 + lane;
+        const bool row_ok = row < expert_rows;  // rows past M_e keep the caller's contents
+        uint16_t* d_row = p.output[expert] + int64_t(row) * p.n + nt * kBlockN;
+        const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + accum * kBlockN;
+#pragma unroll 1
+        for (int c = 0; c < kBlockN; c += 64) {
+          uint32_t acc0[32], acc1[32];
+          ptx::tmem_ld_32x32b_x32(taddr + c, acc0);
+          ptx::tmem_ld_32x32b_x32(taddr + c + 32, acc1);
+          ptx::tmem_wait_ld();
+          if (c + 64 >= kBlockN) {
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(tmem_empty_bar(accum));
+          }
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int32_t col = nt * kBlockN + c + half * 32 + v * 8;
+              if (row_ok && col < p.n) {
+                const uint32_t* a = half == 0 ? &acc0[v * 8] : &acc1[v * 8];
+                uint4 out;
+                __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(a[0]), __uint_as_float(a[1]));
+                out.x = *reinterpret_cast<const uint32_t*>(&pair);
+                pair = __floats2bfloat162_rn(__uint_as_float(a[2]), __uint_as_float(a[3]));
+                out.y = *reinterpret_cast<const uint32_t*>(&pair);
+                pair = __floats2bfloat162_rn(__uint_as_float(a[4]), __uint_as_float(a[5]));
+                out.z = *reinterpret_cast<const uint32_t*>(&pair);
+                pair = __floats2bfloat162_rn(__uint_as_float(a[6]), __uint_as_float(a[7]));
+                out.w = *reinterpret_cast<const uint32_t*>(&pair);
+                ptx::st_v4(d_row + c + half * 32 + v * 8, out);
+              }
+            }
+          }
+        }
+        if (++accum == kAccumStages) { accum = 0; accum_phase ^= 1u; }
+      }
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 2) {
+      ptx::tc_fence_after();
+      ptx::tmem_dealloc(tmem_base, kTmemColumns);
+    }
+  }
+
+  // Every rank tells its peers that it has finished reading their tokens, and leaves only when
+  // all of them have finished reading its own (communication.cuh:237-250).
+  cooperative_groups::this_grid().sync();
+  if (blockIdx.x == 0 && threadIdx.x < 32) {
+    if (lane == 0) ptx::fence_sc_sys();
+    __syncwarp();
+    if (lane < p.world) ptx::st_release_sys(p.peer_done[lane] + p.rank * kReadyFlagStride, w.epoch);
+    __syncwarp();
+    if (lane < p.world && !(p.flags & kFlagSkipPeerWait))
+      flag_wait<true>(p.peer_done[p.rank] + lane * kReadyFlagStride, w.epoch, w, kSitePeerDone, uint32_t(lane));
+  }
+}
+
+}  // namespace fuse_b200

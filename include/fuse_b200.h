@@ -377,6 +377,55 @@ FUSE_API int fuse_launch_a2a_gemm_mxfp8_cutlass(const fuse_mxfp8_a2a_gemm_params
 FUSE_API int fuse_launch_a2a_gemm_mxfp8_cutlass_ex(const fuse_mxfp8_a2a_gemm_params* params,
                                           const fuse_b200_options* options, fuse_stream stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * MoE dispatch -> expert FC1 grouped GEMM.  include/fuse/operators/primitives/grouped_gemm.h
+ * ------------------------------------------------------------------------------------------- */
+/* grouped_gemm.h:10-12 (GroupedTokenSource): where a routed row comes from. */
+typedef struct fuse_grouped_token_source {
+  int32_t rank, token, slot;
+} fuse_grouped_token_source;
+/* grouped_gemm.h:17-53 (GroupedGemmPolicy).  This implementation honours num_comm_ctas,
+ * num_compute_ctas and tile_n (128 or 256); mma_sm_count must be 1 and swap_ab false. */
+typedef struct fuse_grouped_gemm_policy {
+  int32_t num_comm_ctas, num_compute_ctas, swizzle;
+  uint8_t along_n;
+  int32_t tile_n, tile_k;
+  int32_t mma_sm_count;
+  int32_t dispatch_copy;
+  uint8_t balance_dispatch_tail, swap_ab, trim_swap_tokens;
+  int32_t scheduler;
+} fuse_grouped_gemm_policy;
+/* grouped_gemm.h:62-85 (Bf16GroupedGemmParams): device arrays with one pointer per LOCAL expert
+ * (lhs[e] / output[e] slabs of expert_row_capacity rows, weight_nt[e] = W_e[N,K]); row_offsets
+ * (device, experts+1) and source (device) may change between launches; peer_started / peer_done
+ * are caller-owned peer-visible arrays of world_size flags, zeroed once. */
+typedef struct fuse_bf16_grouped_gemm_params {
+  fuse_bf16* const* lhs;
+  const fuse_bf16* const* weight_nt;
+  fuse_bf16* const* output;
+  const int64_t* row_offsets;
+  const fuse_grouped_token_source* source;
+  const fuse_bf16* peer_input[FUSE_MAX_WORLD_SIZE];
+  fuse_bf16* peer_output[FUSE_MAX_WORLD_SIZE];
+  uint32_t* peer_started[FUSE_MAX_WORLD_SIZE];
+  uint32_t* peer_done[FUSE_MAX_WORLD_SIZE];
+  int32_t experts, n, k;
+  int32_t expert_row_capacity;
+  int32_t rank, world_size, topk;
+  fuse_grouped_gemm_policy policy;
+  int32_t dispatch_buffer_rows;
+} fuse_bf16_grouped_gemm_params;
+/* grouped_gemm.h:87-98: opaque plan owning private device metadata; create outside stream
+ * capture (it allocates and synchronises), launch allocates nothing and reads the row counts on
+ * the device, destroy after the last use has finished. */
+typedef struct fuse_bf16_grouped_gemm_plan fuse_bf16_grouped_gemm_plan;
+FUSE_API int fuse_create_bf16_a2a_grouped_gemm(const fuse_bf16_grouped_gemm_params* params,
+                                      fuse_bf16_grouped_gemm_plan** plan);
+FUSE_API int fuse_launch_bf16_grouped_gemm(fuse_bf16_grouped_gemm_plan* plan, fuse_stream stream);
+FUSE_API int fuse_launch_bf16_grouped_gemm_ex(fuse_bf16_grouped_gemm_plan* plan, const fuse_b200_options* options,
+                                     fuse_stream stream);
+FUSE_API int fuse_destroy_bf16_grouped_gemm(fuse_bf16_grouped_gemm_plan* plan);
+
 /* The static tile order shared by compute and communication CTAs: linear index -> (m, n) tile
  * for a grid of m_tiles x n_tiles, swizzle in {1,2,4,8}, along_n = 0 (index runs down M inside
  * bands of `swizzle` N tiles) or 1 (transpose).  Same knobs as the reference scheduler
@@ -408,7 +457,8 @@ FUSE_API int fuse_b200_read_status(uint32_t out[16], int clear);
  * 3 a2a_gemm_params, 4 kernel_traits, 5 options, 6 qkv_backward_data_params,
  * 7 qkv_backward_weight_params, 8 qkv_backward_params, 9 oproj_backward_data_params,
  * 10 oproj_backward_weight_params, 11 oproj_backward_params, 12 mxfp8_activation,
- * 13 mxfp8_gemm_a2a_params, 14 mxfp8_a2a_gemm_params.  -1 for unknown ids. */
+ * 13 mxfp8_gemm_a2a_params, 14 mxfp8_a2a_gemm_params, 15 grouped_gemm_policy,
+ * 16 bf16_grouped_gemm_params.  -1 for unknown ids. */
 FUSE_API int fuse_b200_abi_sizeof(int record);
 /* Number of kernels this library has launched in this process (all entry points). */
 FUSE_API uint64_t fuse_b200_launch_count(void);

@@ -301,3 +301,52 @@ def oproj_forward_mxfp8(world, rank, batch, seq_local, peer_data, peer_scales, w
     soff = view.scales - workspace.data_ptr()
     staged_scales = workspace[soff:soff + view.scale_bytes].cpu().numpy()
     return staged, staged_scales, to_bits(out)
+
+
+def moe_dispatch_fc1(world, rank, experts_local, tokens_bits, weights_bits, row_offsets, sources, capacity,
+                     comm=4, compute=128, tile_n=256, launches=1, second_route=None):
+    """One rank of the MoE dispatch -> FC1 grouped GEMM.  tokens_bits[r] [T, K] per rank;
+    weights_bits [experts_local, N, K]; row_offsets int64 [E+1]; sources int32 [rows, 3].
+    Returns (lhs [E, capacity, K] bits, output [E, capacity, N] bits); unused capacity holds 0x7f7f.
+    With `second_route` = (row_offsets, sources) the same plan is launched again with new device
+    routes (no re-creation), and that launch's results are returned."""
+    e, n, k = weights_bits.shape
+    toks = [to_device(t) for t in tokens_bits]
+    w = to_device(weights_bits)
+    poison = lambda *shape: torch.full(shape, 0x7f7f, dtype=torch.int16, device=DEV).view(torch.bfloat16)
+    lhs, out = poison(e, capacity, k), poison(e, capacity, n)
+    ptrs = lambda t: torch.tensor([t[i].data_ptr() for i in range(e)], dtype=torch.int64, device=DEV)
+    lhs_ptrs, w_ptrs, out_ptrs = ptrs(lhs), ptrs(w), ptrs(out)
+    max_rows = max(int(row_offsets[-1]), int(second_route[0][-1]) if second_route else 0, 1)
+    offs = torch.from_numpy(np.ascontiguousarray(row_offsets, dtype=np.int64)).to(DEV)
+    src = torch.zeros((max_rows, 3), dtype=torch.int32, device=DEV)
+    src[:len(sources)] = torch.from_numpy(np.ascontiguousarray(sources, dtype=np.int32)).to(DEV)
+    started = [torch.zeros(world * N.READY_FLAG_STRIDE, dtype=torch.int32, device=DEV) for _ in range(world)]
+    done = [torch.zeros(world * N.READY_FLAG_STRIDE, dtype=torch.int32, device=DEV) for _ in range(world)]
+    p = N.Bf16GroupedGemmParams(lhs=lhs_ptrs.data_ptr(), weight_nt=w_ptrs.data_ptr(), output=out_ptrs.data_ptr(),
+                                row_offsets=offs.data_ptr(), source=src.data_ptr(), experts=e, n=n, k=k,
+                                expert_row_capacity=capacity, rank=rank, world_size=world, topk=1)
+    p.policy = N.GroupedGemmPolicy(num_comm_ctas=comm, num_compute_ctas=compute, tile_n=tile_n)
+    for r in range(world):
+        p.peer_input[r] = toks[r].data_ptr()
+        p.peer_started[r] = started[r].data_ptr()
+        p.peer_done[r] = done[r].data_ptr()
+    rc, plan = api.create_bf16_a2a_grouped_gemm(p)
+    assert rc == 0, f"create_bf16_a2a_grouped_gemm -> cudaError {rc}"
+    opts = options(flags=N.SKIP_PEER_WAIT if world > 1 else 0)
+    for _ in range(launches):
+        rc = api.launch_bf16_grouped_gemm(plan, 0, opts)
+        assert rc == 0, f"launch_bf16_grouped_gemm -> cudaError {rc}"
+    check_status()
+    if second_route is not None:
+        lhs.view(torch.int16).fill_(0x7f7f)
+        out.view(torch.int16).fill_(0x7f7f)
+        offs.copy_(torch.from_numpy(np.ascontiguousarray(second_route[0], dtype=np.int64)))
+        src[:len(second_route[1])] = torch.from_numpy(np.ascontiguousarray(second_route[1], dtype=np.int32)).to(DEV)
+        rc = api.launch_bf16_grouped_gemm(plan, 0, opts)
+        assert rc == 0
+        check_status()
+    result = to_bits(lhs), to_bits(out)
+    assert int(started[0][rank * N.READY_FLAG_STRIDE]) == launches + (1 if second_route else 0)
+    assert api.destroy_bf16_grouped_gemm(plan) == 0
+    return result

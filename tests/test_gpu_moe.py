@@ -1,0 +1,104 @@
+"""MoE dispatch -> expert FC1 grouped GEMM against the CPU oracle: gathered rows bit for bit,
+GEMM within the reference's grouped tolerance 0.002 + 0.008*|b|
+(benchmarks/sm103/grouped_validation.cuh:119-123), untouched capacity still holding the poison."""
+import numpy as np
+import pytest
+
+from fuse_b200 import synthetic
+from oracle import oracle as O
+
+pytestmark = pytest.mark.gpu
+POISON = 0x7F7F
+
+
+def _routes(world, tokens, experts, topk, seed, zipf=1.1):
+    """Router scores ~ N(0,1) + per-expert Zipf(s) bias under a seeded permutation; top-k distinct
+    experts per token (ties to the lower id); rows of an expert ordered by (rank, token, slot)."""
+    rng = np.random.default_rng(seed)
+    ranks = rng.permutation(experts) + 1
+    bias = np.log(1.0 / ranks.astype(np.float64) ** zipf)
+    bias -= bias.mean()
+    chosen = []
+    for r in range(world):
+        scores = (synthetic.normal_f32((tokens, experts), seed + 17 * r + 1, 1.0) + bias).astype(np.float32)
+        c = np.empty((tokens, topk), dtype=np.int32)
+        O.lib().fo_moe_topk(O.ptr(np.ascontiguousarray(scores)), tokens, experts, topk, O.ptr(c))
+        chosen.append(c)
+    return chosen
+
+
+def _rows_for(world, dest, experts_local, tokens, topk, chosen):
+    offs = np.empty(experts_local + 1, dtype=np.int32)
+    total = O.lib().fo_moe_build_rows(world, dest, experts_local, tokens, topk, O.ptr_array(chosen), O.ptr(offs), None)
+    src = np.empty((max(total, 1), 3), dtype=np.int32)
+    O.lib().fo_moe_build_rows(world, dest, experts_local, tokens, topk, O.ptr_array(chosen), O.ptr(offs), O.ptr(src))
+    return offs.astype(np.int64), src[:total]
+
+
+def _check(world, rank, experts_local, toks, weights, offs, src, capacity, lhs, out):
+    e, n, k = weights.shape
+    want_lhs = np.full((e, capacity, k), POISON, dtype=np.uint16)
+    want_out = np.full((e, capacity, n), POISON, dtype=np.uint16)
+    rc = O.lib().fo_moe_dispatch_fc1(e, O.ptr(offs.astype(np.int32)), O.ptr(np.ascontiguousarray(src, dtype=np.int32)),
+                                     O.ptr_array(toks), O.ptr(np.ascontiguousarray(weights)), n, k, capacity,
+                                     O.ptr(want_lhs), O.ptr(want_out))
+    assert rc == 0
+    assert np.array_equal(lhs.reshape(e, capacity, k), want_lhs), "gathered rows (or untouched capacity) differ"
+    got = out.reshape(e, capacity, n)
+    for ex in range(e):
+        rows = int(offs[ex + 1] - offs[ex])
+        ok, worst, bad = O.within_tolerance(got[ex, :rows], want_out[ex, :rows], 0.002, 0.008)
+        assert ok, f"expert {ex}: {bad} elements outside 0.002+0.008|b| (max abs err {worst})"
+        assert (got[ex, rows:] == POISON).all(), f"expert {ex}: rows past M_e were written"
+
+
+# (world, tokens/rank, experts, topk, K, N, comm, tile_n)
+MOE_CASES = [
+    (1, 96, 4, 2, 256, 512, 2, 256),
+    (2, 160, 8, 2, 512, 768, 4, 256),
+    (4, 128, 16, 4, 1024, 384, 5, 128),     # K row = 2 KiB, N not a tile multiple
+    (2, 64, 4, 2, 9216, 256, 3, 256),       # 18 KiB rows: a row is cut into two pieces
+]
+
+
+@pytest.mark.parametrize("case", MOE_CASES)
+def test_moe_dispatch_fc1_matches_oracle(case):
+    from tests import harness as H
+    world, tokens, experts, topk, k, n, comm, tile_n = case
+    experts_local = experts // world
+    chosen = _routes(world, tokens, experts, topk, synthetic.GROUPED_SEED)
+    toks = [synthetic.normal_bf16((tokens, k), synthetic.GROUPED_SEED + 31 * r + 5, 1.0) for r in range(world)]
+    for rank in sorted({0, world - 1}):
+        weights = synthetic.normal_bf16((experts_local, n, k), synthetic.GROUPED_SEED + 1000 + rank, 0.02)
+        offs, src = _rows_for(world, rank, experts_local, tokens, topk, chosen)
+        capacity = max(256, int(-(-int(np.diff(offs).max()) // 256) * 256))
+        lhs, out = H.moe_dispatch_fc1(world, rank, experts_local, toks, weights, offs, src, capacity, comm=comm,
+                                      tile_n=tile_n)
+        _check(world, rank, experts_local, toks, weights, offs, src, capacity, lhs, out)
+
+
+def test_moe_boundary_row_counts_empty_experts_and_replay_with_new_routes():
+    # Row counts at tile boundaries and empty experts (benchmarks/sm103/grouped_validation.cuh:20-50);
+    # then the same plan replayed with different device routes.
+    from tests import harness as H
+    world, tokens, k, n = 2, 600, 256, 512
+    counts_a = [1, 0, 127, 128, 129, 257, 0, 63]
+    counts_b = [0, 255, 256, 7, 0, 193, 65, 9]
+    e = len(counts_a)
+    toks = [synthetic.normal_bf16((tokens, k), 77 + r, 1.0) for r in range(world)]
+    weights = synthetic.normal_bf16((e, n, k), 99, 0.02)
+    rng = np.random.default_rng(5)
+
+    def make(counts):
+        offs = np.concatenate([[0], np.cumsum(counts)]).astype(np.int64)
+        total = int(offs[-1])
+        src = np.stack([rng.integers(0, world, total), rng.integers(0, tokens, total), rng.integers(0, 2, total)], 1)
+        return offs, src.astype(np.int32)
+
+    first, second = make(counts_a), make(counts_b)
+    capacity = 512
+    lhs, out = H.moe_dispatch_fc1(world, 0, e, toks, weights, first[0], first[1], capacity, comm=3, launches=2)
+    _check(world, 0, e, toks, weights, first[0], first[1], capacity, lhs, out)
+    lhs, out = H.moe_dispatch_fc1(world, 0, e, toks, weights, first[0], first[1], capacity, comm=3,
+                                  second_route=second)
+    _check(world, 0, e, toks, weights, second[0], second[1], capacity, lhs, out)

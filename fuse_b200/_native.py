@@ -235,8 +235,47 @@ class Bf16GroupedGemmParams(_Record):
                 ("policy", GroupedGemmPolicy), ("dispatch_buffer_rows", C.c_int32)]
 
 
+class Mxfp8QkvBackwardInput(_Record):
+    _fields_ = [("grad_q", Mxfp8Activation), ("grad_k", Mxfp8Activation), ("grad_v", Mxfp8Activation),
+                ("master_q", C.c_void_p), ("master_k", C.c_void_p), ("master_v", C.c_void_p)]
+
+
+class Mxfp8QkvBackwardDataParams(_Record):
+    """include/fuse/operators/ulysses/qkv_backward.h:219-224 of the reference."""
+    _fields_ = [("projection", QkvBackwardDataParams), ("peer_input", Mxfp8QkvBackwardInput * MAX_WORLD_SIZE),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+
+
+class Mxfp8QkvBackwardWeightParams(_Record):
+    _fields_ = [("projection", QkvBackwardWeightParams), ("gemm_tuning", BackwardGemmTuning),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+
+
+class Mxfp8QkvBackwardParams(_Record):
+    _fields_ = [("data", Mxfp8QkvBackwardDataParams), ("weight", Mxfp8QkvBackwardWeightParams),
+                ("weight_mode", C.c_int32)]
+
+
+class Mxfp8OprojBackwardDataParams(_Record):
+    """include/fuse/operators/ulysses/oproj_backward.h:191-196 of the reference."""
+    _fields_ = [("projection", OprojBackwardDataParams), ("grad_output", Mxfp8Activation),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+
+
+class Mxfp8OprojBackwardWeightParams(_Record):
+    _fields_ = [("projection", OprojBackwardWeightParams), ("gemm_tuning", BackwardGemmTuning),
+                ("workspace", C.c_void_p), ("workspace_bytes", C.c_size_t)]
+
+
+class Mxfp8OprojBackwardParams(_Record):
+    _fields_ = [("data", Mxfp8OprojBackwardDataParams), ("weight", Mxfp8OprojBackwardWeightParams),
+                ("weight_mode", C.c_int32)]
+
+
 ABI_RECORDS = {0: GemmProblem, 1: UlyssesRoute, 2: GemmA2AParams, 3: A2AGemmParams,
-               4: KernelTraits, 5: Options, 15: GroupedGemmPolicy, 16: Bf16GroupedGemmParams, 14: Mxfp8A2AGemmParams, 12: Mxfp8Activation, 13: Mxfp8GemmA2AParams, 6: QkvBackwardDataParams, 7: QkvBackwardWeightParams,
+               4: KernelTraits, 5: Options, 17: Mxfp8QkvBackwardDataParams, 18: Mxfp8QkvBackwardWeightParams,
+               19: Mxfp8QkvBackwardParams, 20: Mxfp8OprojBackwardDataParams, 21: Mxfp8OprojBackwardWeightParams,
+               22: Mxfp8OprojBackwardParams, 15: GroupedGemmPolicy, 16: Bf16GroupedGemmParams, 14: Mxfp8A2AGemmParams, 12: Mxfp8Activation, 13: Mxfp8GemmA2AParams, 6: QkvBackwardDataParams, 7: QkvBackwardWeightParams,
                8: QkvBackwardParams, 9: OprojBackwardDataParams, 10: OprojBackwardWeightParams,
                11: OprojBackwardParams}
 
@@ -282,6 +321,18 @@ SYMBOLS = {
     "fuse_launch_bf16_grouped_gemm": (C.c_int, [C.c_void_p, _P]),
     "fuse_launch_bf16_grouped_gemm_ex": (C.c_int, [C.c_void_p, C.POINTER(Options), _P]),
     "fuse_destroy_bf16_grouped_gemm": (C.c_int, [C.c_void_p]),
+    "fuse_qkv_backward_mxfp8_data_workspace_size": (C.c_int, [C.POINTER(QkvBackwardDataParams), C.POINTER(C.c_size_t)]),
+    "fuse_qkv_backward_mxfp8_weight_workspace_size": (C.c_int, [C.POINTER(QkvBackwardWeightParams), C.POINTER(C.c_size_t)]),
+    "fuse_launch_qkv_backward_mxfp8_data": (C.c_int, [C.POINTER(Mxfp8QkvBackwardDataParams), _P]),
+    "fuse_launch_qkv_backward_mxfp8_data_ex": (C.c_int, [C.POINTER(Mxfp8QkvBackwardDataParams), C.POINTER(Options), _P]),
+    "fuse_launch_qkv_backward_mxfp8_weight": (C.c_int, [C.POINTER(Mxfp8QkvBackwardWeightParams), _P]),
+    "fuse_launch_qkv_backward_mxfp8": (C.c_int, [C.POINTER(Mxfp8QkvBackwardParams), _P]),
+    "fuse_oproj_backward_mxfp8_data_workspace_size": (C.c_int, [C.POINTER(OprojBackwardDataParams), C.POINTER(C.c_size_t)]),
+    "fuse_oproj_backward_mxfp8_weight_workspace_size": (C.c_int, [C.POINTER(OprojBackwardWeightParams), C.POINTER(C.c_size_t)]),
+    "fuse_launch_oproj_backward_mxfp8_data": (C.c_int, [C.POINTER(Mxfp8OprojBackwardDataParams), _P]),
+    "fuse_launch_oproj_backward_mxfp8_data_ex": (C.c_int, [C.POINTER(Mxfp8OprojBackwardDataParams), C.POINTER(Options), _P]),
+    "fuse_launch_oproj_backward_mxfp8_weight": (C.c_int, [C.POINTER(Mxfp8OprojBackwardWeightParams), _P]),
+    "fuse_launch_oproj_backward_mxfp8": (C.c_int, [C.POINTER(Mxfp8OprojBackwardParams), _P]),
     "fuse_qkv_cutlass_kernel_traits": (None, [C.POINTER(GemmProblem), C.POINTER(KernelTraits)]),
     "fuse_cutlass_kernel_traits": (None, [C.POINTER(KernelTraits)]),
     "fuse_a2a_lhs_gemm_ready_elements": (C.c_int64, [C.POINTER(GemmProblem), C.POINTER(UlyssesRoute)]),

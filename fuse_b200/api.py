@@ -238,3 +238,59 @@ def launch_bf16_grouped_gemm(plan: int, stream: int = 0, options: Options | None
 
 def destroy_bf16_grouped_gemm(plan: int) -> int:
     return N.lib().fuse_destroy_bf16_grouped_gemm(plan)
+
+
+# ---- MXFP8 backward (qkv_backward.h:196-283, oproj_backward.h:186-240 of the reference) ---------
+from ._native import (Mxfp8OprojBackwardDataParams, Mxfp8OprojBackwardParams,  # noqa: E402,F401
+                      Mxfp8OprojBackwardWeightParams, Mxfp8QkvBackwardDataParams, Mxfp8QkvBackwardInput,
+                      Mxfp8QkvBackwardParams, Mxfp8QkvBackwardWeightParams)
+
+
+def _size(fn, params):
+    size = C.c_size_t()
+    rc = fn(C.byref(params), C.byref(size))
+    return rc, size.value
+
+
+def qkv_backward_mxfp8_data_workspace_size(params: QkvBackwardDataParams):
+    return _size(N.lib().fuse_qkv_backward_mxfp8_data_workspace_size, params)
+
+
+def qkv_backward_mxfp8_weight_workspace_size(params: QkvBackwardWeightParams):
+    return _size(N.lib().fuse_qkv_backward_mxfp8_weight_workspace_size, params)
+
+
+def oproj_backward_mxfp8_data_workspace_size(params: OprojBackwardDataParams):
+    return _size(N.lib().fuse_oproj_backward_mxfp8_data_workspace_size, params)
+
+
+def oproj_backward_mxfp8_weight_workspace_size(params: OprojBackwardWeightParams):
+    return _size(N.lib().fuse_oproj_backward_mxfp8_weight_workspace_size, params)
+
+
+def launch_qkv_backward_mxfp8_data(params, stream: int = 0, options: Options | None = None) -> int:
+    if options is None:
+        return N.lib().fuse_launch_qkv_backward_mxfp8_data(C.byref(params), stream)
+    return N.lib().fuse_launch_qkv_backward_mxfp8_data_ex(C.byref(params), _opt(options), stream)
+
+
+def launch_qkv_backward_mxfp8_weight(params, stream: int = 0) -> int:
+    return N.lib().fuse_launch_qkv_backward_mxfp8_weight(C.byref(params), stream)
+
+
+def launch_qkv_backward_mxfp8(params, stream: int = 0) -> int:
+    return N.lib().fuse_launch_qkv_backward_mxfp8(C.byref(params), stream)
+
+
+def launch_oproj_backward_mxfp8_data(params, stream: int = 0, options: Options | None = None) -> int:
+    if options is None:
+        return N.lib().fuse_launch_oproj_backward_mxfp8_data(C.byref(params), stream)
+    return N.lib().fuse_launch_oproj_backward_mxfp8_data_ex(C.byref(params), _opt(options), stream)
+
+
+def launch_oproj_backward_mxfp8_weight(params, stream: int = 0) -> int:
+    return N.lib().fuse_launch_oproj_backward_mxfp8_weight(C.byref(params), stream)
+
+
+def launch_oproj_backward_mxfp8(params, stream: int = 0) -> int:
+    return N.lib().fuse_launch_oproj_backward_mxfp8(C.byref(params), stream)

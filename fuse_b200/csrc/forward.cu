@@ -331,6 +331,12 @@ int fuse_b200_abi_sizeof(int record) {
     case 14: return int(sizeof(fuse_mxfp8_a2a_gemm_params));
     case 15: return int(sizeof(fuse_grouped_gemm_policy));
     case 16: return int(sizeof(fuse_bf16_grouped_gemm_params));
+    case 17: return int(sizeof(fuse_mxfp8_qkv_backward_data_params));
+    case 18: return int(sizeof(fuse_mxfp8_qkv_backward_weight_params));
+    case 19: return int(sizeof(fuse_mxfp8_qkv_backward_params));
+    case 20: return int(sizeof(fuse_mxfp8_oproj_backward_data_params));
+    case 21: return int(sizeof(fuse_mxfp8_oproj_backward_weight_params));
+    case 22: return int(sizeof(fuse_mxfp8_oproj_backward_params));
     default: return -1;
   }
 }

@@ -46,6 +46,9 @@ enum FusedMode : int {
                       // in the owning peer's planar Q|K|V; no communication CTAs, no tile flags
   kModeHeadGate = 4,  // QKV backward data: comm CTAs push this rank's planar dQ/dK/dV into every
                       // destination's packed staging; the GEMM's K loop is gated per (M tile, head)
+  kModeGradPull = 5,  // MXFP8 QKV backward data: comm CTAs pull the owners' prequantised planar
+                      // gradients (bytes + scale atoms) into the packed lhs, and their BF16
+                      // masters into the staging kept for the weight gradient; same head gate
 };
 
 enum LaunchFlags : uint32_t {
@@ -102,6 +105,14 @@ struct GradRoute {
   const uint16_t* grad[3];                          // dQ, dK, dV planes of this rank
   uint16_t* peer_staging[kMaxWorldSize];
   uint32_t* peer_ready[kMaxWorldSize];              // [m_tiles * (q + 2 kv)] flags on each peer
+  // Receiver pull of prequantised gradients (head_dim == 128: one scale atom per head and
+  // 128-row group): every owner's planes as E4M3 bytes, native scales and BF16 masters.
+  const uint8_t* peer_bytes[kMaxWorldSize][3];
+  const uint8_t* peer_scales[kMaxWorldSize][3];
+  const uint16_t* peer_master[kMaxWorldSize][3];
+  uint8_t* lhs_bytes;                               // packed [M, (q + 2 kv) * 128] E4M3
+  uint8_t* lhs_scales;                              // its native scale storage
+  uint16_t* master_staging;                         // packed BF16 [M, (q + 2 kv) * 128]
 };
 
 struct FusedParams {
@@ -730,6 +741,59 @@ __device__ __forceinline__ void grad_push_role(const FusedParams& p) {
   __threadfence_system();
 }
 
+// ------------------------------------------------------------------------------------------
+// Communication role: MXFP8 QKV backward reverse route, receiver pull.
+//
+// Unit of work = (M tile, logical head): from the owner's planar gradient the 128 x 128 E4M3
+// block, its 512-byte scale atom and the 128 x 128 BF16 master block are copied with 16-byte
+// accesses into the packed lhs bytes / scale storage (consumed by the block-scaled GEMM) and
+// the packed BF16 staging (kept for the weight gradient), then ready[m_tile*heads + head] =
+// epoch is released (csrc/operators/sm103/detail/backward.cuh:423-552).
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void grad_pull_role(const FusedParams& p) {
+  const GradRoute& g = p.grad;
+  const int tid = threadIdx.x;
+  const int32_t m_tiles = (g.m + kBlockM - 1) / kBlockM;
+  const int32_t heads_total = g.q_heads + 2 * g.kv_heads;
+  const int32_t width = heads_total * 128;
+  const int64_t units = int64_t(m_tiles) * heads_total;
+  for (int64_t u = blockIdx.x; u < units; u += p.num_comm_ctas) {
+    const int32_t mt = int32_t(u / heads_total), head = int32_t(u % heads_total);
+    const int32_t segment = head < g.q_heads ? 0 : (head < g.q_heads + g.kv_heads ? 1 : 2);
+    const int32_t seg_head = head - (segment == 0 ? 0 : g.q_heads + (segment == 2 ? g.kv_heads : 0));
+    const int32_t seg_local = (segment == 0 ? g.q_heads : g.kv_heads) / g.world;
+    const int32_t owner = seg_head / seg_local, local_head = seg_head - owner * seg_local;
+    const int64_t plane_width = int64_t(seg_local) * 128;
+    const int32_t m0 = mt * kBlockM;
+    const int32_t rows = g.m - m0 < kBlockM ? g.m - m0 : kBlockM;
+    const uint8_t* src8 = g.peer_bytes[owner][segment] + int64_t(local_head) * 128;
+    const uint16_t* src16 = g.peer_master[owner][segment] + int64_t(local_head) * 128;
+    // E4M3 bytes: 8 chunks per row; BF16 masters: 16 chunks per row
+    for (int32_t i = tid; i < rows * 24; i += kThreads) {
+      const int32_t row = i / 24, c = i - row * 24;
+      const int64_t src_row = global_row(g.world, g.rank, g.seq_local, g.global_seq, g.causal != 0, m0 + row);
+      if (c < 8) {
+        const uint4 v = ptx::ld_cg_v4(src8 + src_row * plane_width + c * 16);
+        ptx::st_v4(g.lhs_bytes + int64_t(m0 + row) * width + int64_t(head) * 128 + c * 16, v);
+      } else {
+        const uint4 v = ptx::ld_cg_v4(src16 + src_row * plane_width + (c - 8) * 8);
+        ptx::st_v4(g.master_staging + int64_t(m0 + row) * width + int64_t(head) * 128 + (c - 8) * 8, v);
+      }
+    }
+    if (tid < 32) {  // the (128-row group, head) scale atom
+      const int64_t src_row0 = global_row(g.world, g.rank, g.seq_local, g.global_seq, g.causal != 0, m0);
+      const uint4 v = ptx::ld_cg_v4(g.peer_scales[owner][segment] + ((src_row0 >> 7) * seg_local + local_head) * 512 + tid * 16);
+      ptx::st_v4(g.lhs_scales + (int64_t(mt) * heads_total + head) * 512 + tid * 16, v);
+    }
+    __syncthreads();
+    if (tid == 0) {
+      __threadfence();
+      ptx::fence_proxy_async_global();
+      ptx::st_release_gpu(p.ready + (int64_t(mt) * heads_total + head) * kReadyFlagStride, p.wait.epoch);
+    }
+  }
+}
+
 // 32 FP32 accumulators of one output row -> alpha (and beta * old D) -> BF16 -> four 16-byte
 // stores.  `col` is the global column of acc[0]; vectors past N are skipped (N % 8 == 0).
 struct PeerRow {
@@ -913,6 +977,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       else lhs_pull_bulk_role(p, base);
     }
     if constexpr (kMode == kModeHeadGate) grad_push_role(p);
+    if constexpr (kMode == kModeGradPull) grad_pull_role(p);
   } else {
     const uint32_t bar_base = base + Layout::kBarrierOffset;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -961,13 +1026,14 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           p.order.decode(t, mt, nt);
           int32_t gated_upto = -1;  // highest K shard already acquired for this tile
           for (int32_t kb = 0; kb < k_blocks; ++kb) {
-            if constexpr (kMode == kModeLhsPull || kMode == kModeHeadGate) {
+            if constexpr (kMode == kModeLhsPull || kMode == kModeHeadGate || kMode == kModeGradPull) {
               // K groups whose rows arrive separately: peers' shards (forward pull, flags set by
               // this GPU's communication CTAs) or Q/K/V heads (backward, flags set by the
               // sending GPUs at system scope).
               constexpr bool kRemoteWriter = kMode == kModeHeadGate;
-              const int32_t group_width = kRemoteWriter ? p.grad.head_dim : p.lhs.shard_width;
-              const int32_t groups = kRemoteWriter ? p.grad.q_heads + 2 * p.grad.kv_heads : p.lhs.world;
+              constexpr bool kHeads = kMode != kModeLhsPull;
+              const int32_t group_width = kHeads ? p.grad.head_dim : p.lhs.shard_width;
+              const int32_t groups = kHeads ? p.grad.q_heads + 2 * p.grad.kv_heads : p.lhs.world;
               int32_t last = (kb * kBlockElems + kBlockElems - 1) / group_width;
               if (last >= groups) last = groups - 1;
               while (ok && gated_upto < last) {
@@ -1224,7 +1290,8 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   }
 
-  if constexpr (kMode == kModeQkvPush || kMode == kModeQkvDirect || kMode == kModeHeadGate) {
+  if constexpr (kMode == kModeQkvPush || kMode == kModeQkvDirect || kMode == kModeHeadGate ||
+                kMode == kModeGradPull) {
     cooperative_groups::this_grid().sync();
     qkv_finalize(p);
   }

@@ -426,6 +426,71 @@ FUSE_API int fuse_launch_bf16_grouped_gemm_ex(fuse_bf16_grouped_gemm_plan* plan,
                                      fuse_stream stream);
 FUSE_API int fuse_destroy_bf16_grouped_gemm(fuse_bf16_grouped_gemm_plan* plan);
 
+/* ---------------------------------------------------------------------------------------------
+ * MXFP8 backward.  include/fuse/operators/ulysses/qkv_backward.h:196-283, oproj_backward.h:186-240
+ * ------------------------------------------------------------------------------------------- */
+/* qkv_backward.h:199-204 (Mxfp8QkvBackwardInput): one source rank's prequantised planar dQ, dK,
+ * dV (each with native scales of its OWN planar width) and their BF16 masters. */
+typedef struct fuse_mxfp8_qkv_backward_input {
+  fuse_mxfp8_activation grad_q, grad_k, grad_v;
+  const fuse_bf16 *master_q, *master_k, *master_v;
+} fuse_mxfp8_qkv_backward_input;
+/* qkv_backward.h:219-224 (Mxfp8QkvBackwardDataParams): only projection.peer_dqkv_staging[rank]
+ * and peer_ready[rank] are used locally; peer_input supplies the reads; head_dim must be 128. */
+typedef struct fuse_mxfp8_qkv_backward_data_params {
+  fuse_qkv_backward_data_params projection;
+  fuse_mxfp8_qkv_backward_input peer_input[FUSE_MAX_WORLD_SIZE];
+  void* workspace;
+  size_t workspace_bytes;
+} fuse_mxfp8_qkv_backward_data_params;
+/* qkv_backward.h:241-246 (Mxfp8QkvBackwardWeightParams). */
+typedef struct fuse_mxfp8_qkv_backward_weight_params {
+  fuse_qkv_backward_weight_params projection;
+  fuse_backward_gemm_tuning gemm_tuning;
+  void* workspace;
+  size_t workspace_bytes;
+} fuse_mxfp8_qkv_backward_weight_params;
+typedef struct fuse_mxfp8_qkv_backward_params {
+  fuse_mxfp8_qkv_backward_data_params data;
+  fuse_mxfp8_qkv_backward_weight_params weight;
+  int32_t weight_mode;
+} fuse_mxfp8_qkv_backward_params;
+/* oproj_backward.h:191-196 (Mxfp8OprojBackwardDataParams): grad_output is the prequantised dY. */
+typedef struct fuse_mxfp8_oproj_backward_data_params {
+  fuse_oproj_backward_data_params projection;
+  fuse_mxfp8_activation grad_output;
+  void* workspace;
+  size_t workspace_bytes;
+} fuse_mxfp8_oproj_backward_data_params;
+/* oproj_backward.h:205-210 (Mxfp8OprojBackwardWeightParams). */
+typedef struct fuse_mxfp8_oproj_backward_weight_params {
+  fuse_oproj_backward_weight_params projection;
+  fuse_backward_gemm_tuning gemm_tuning;
+  void* workspace;
+  size_t workspace_bytes;
+} fuse_mxfp8_oproj_backward_weight_params;
+typedef struct fuse_mxfp8_oproj_backward_params {
+  fuse_mxfp8_oproj_backward_data_params data;
+  fuse_mxfp8_oproj_backward_weight_params weight;
+  int32_t weight_mode;
+} fuse_mxfp8_oproj_backward_params;
+/* qkv_backward.h:252-280 / csrc/operators/sm103/api/backward_mxfp8.cuh:404-497. */
+FUSE_API int fuse_qkv_backward_mxfp8_data_workspace_size(const fuse_qkv_backward_data_params* params, size_t* bytes);
+FUSE_API int fuse_qkv_backward_mxfp8_weight_workspace_size(const fuse_qkv_backward_weight_params* params, size_t* bytes);
+FUSE_API int fuse_launch_qkv_backward_mxfp8_data(const fuse_mxfp8_qkv_backward_data_params* params, fuse_stream stream);
+FUSE_API int fuse_launch_qkv_backward_mxfp8_data_ex(const fuse_mxfp8_qkv_backward_data_params* params,
+                                           const fuse_b200_options* options, fuse_stream stream);
+FUSE_API int fuse_launch_qkv_backward_mxfp8_weight(const fuse_mxfp8_qkv_backward_weight_params* params, fuse_stream stream);
+FUSE_API int fuse_launch_qkv_backward_mxfp8(const fuse_mxfp8_qkv_backward_params* params, fuse_stream stream);
+/* oproj_backward.h:222-237. */
+FUSE_API int fuse_oproj_backward_mxfp8_data_workspace_size(const fuse_oproj_backward_data_params* params, size_t* bytes);
+FUSE_API int fuse_oproj_backward_mxfp8_weight_workspace_size(const fuse_oproj_backward_weight_params* params, size_t* bytes);
+FUSE_API int fuse_launch_oproj_backward_mxfp8_data(const fuse_mxfp8_oproj_backward_data_params* params, fuse_stream stream);
+FUSE_API int fuse_launch_oproj_backward_mxfp8_data_ex(const fuse_mxfp8_oproj_backward_data_params* params,
+                                             const fuse_b200_options* options, fuse_stream stream);
+FUSE_API int fuse_launch_oproj_backward_mxfp8_weight(const fuse_mxfp8_oproj_backward_weight_params* params, fuse_stream stream);
+FUSE_API int fuse_launch_oproj_backward_mxfp8(const fuse_mxfp8_oproj_backward_params* params, fuse_stream stream);
+
 /* The static tile order shared by compute and communication CTAs: linear index -> (m, n) tile
  * for a grid of m_tiles x n_tiles, swizzle in {1,2,4,8}, along_n = 0 (index runs down M inside
  * bands of `swizzle` N tiles) or 1 (transpose).  Same knobs as the reference scheduler
@@ -458,7 +523,9 @@ FUSE_API int fuse_b200_read_status(uint32_t out[16], int clear);
  * 7 qkv_backward_weight_params, 8 qkv_backward_params, 9 oproj_backward_data_params,
  * 10 oproj_backward_weight_params, 11 oproj_backward_params, 12 mxfp8_activation,
  * 13 mxfp8_gemm_a2a_params, 14 mxfp8_a2a_gemm_params, 15 grouped_gemm_policy,
- * 16 bf16_grouped_gemm_params.  -1 for unknown ids. */
+ * 16 bf16_grouped_gemm_params, 17 mxfp8_qkv_backward_data_params, 18 mxfp8_qkv_backward_weight_params,
+ * 19 mxfp8_qkv_backward_params, 20 mxfp8_oproj_backward_data_params, 21 mxfp8_oproj_backward_weight_params,
+ * 22 mxfp8_oproj_backward_params.  -1 for unknown ids. */
 FUSE_API int fuse_b200_abi_sizeof(int record);
 /* Number of kernels this library has launched in this process (all entry points). */
 FUSE_API uint64_t fuse_b200_launch_count(void);

@@ -350,3 +350,105 @@ def moe_dispatch_fc1(world, rank, experts_local, tokens_bits, weights_bits, row_
     assert int(started[0][rank * N.READY_FLAG_STRIDE]) == launches + (1 if second_route else 0)
     assert api.destroy_bf16_grouped_gemm(plan) == 0
     return result
+
+
+def _aligned_scratch(nbytes):
+    buf = torch.full((nbytes + 256,), 0x5A, dtype=torch.uint8, device=DEV)
+    return buf, (buf.data_ptr() + 255) // 256 * 256
+
+
+def _activation(data_t, scales_t):
+    return N.Mxfp8Activation(data=data_t.data_ptr(), scales=scales_t.data_ptr(), data_bytes=data_t.numel(),
+                             scale_bytes=scales_t.numel())
+
+
+def qkv_backward_mxfp8(world, rank, batch, seq_local, q_heads, kv_heads, planes_bits, planes_q, w_bits, x_bits,
+                       comm=4, causal=False, alpha=1.0, beta=0.0, dw_init_bits=None):
+    """One rank of the MXFP8 QKV backward (data + weight).  planes_bits[r] = BF16 (dQ, dK, dV) masters of
+    rank r, planes_q[r] = their ((data, scales), ...) quantisations.  Returns (staging, dX, dW) bits."""
+    d = 128
+    m = batch * seq_local
+    width = (q_heads + 2 * kv_heads) * d
+    hidden = w_bits.shape[1]
+    w, x = to_device(w_bits), to_device(x_bits)
+    masters = [[to_device(pl) for pl in planes_bits[r]] for r in range(world)]
+    quant = [[(to_device_u8(q[0]), to_device_u8(q[1])) for q in planes_q[r]] for r in range(world)]
+    staging, dx = poisoned(m, width), poisoned(m, hidden)
+    dw = to_device(dw_init_bits) if dw_init_bits is not None else poisoned(width, hidden)
+    done = [torch.zeros(world * N.READY_FLAG_STRIDE, dtype=torch.int32, device=DEV) for _ in range(world)]
+    proj = N.QkvBackwardDataParams(weight=w.data_ptr(), grad_input=dx.data_ptr(), local_tokens=m, hidden=hidden,
+                                   batch=batch, q_heads=q_heads, kv_heads=kv_heads, head_dim=d, world_size=world,
+                                   rank=rank, num_comm_ctas=comm, epoch=1, causal_load_balanced=int(causal), alpha=alpha)
+    proj.gemm_tuning.max_swizzle_size = 4
+    ready = torch.zeros(api.qkv_backward_ready_elements(proj), dtype=torch.int32, device=DEV)
+    proj.peer_dqkv_staging[rank] = staging.data_ptr()
+    proj.peer_ready[rank] = ready.data_ptr()
+    for peer in range(world):
+        proj.peer_done_epoch[peer] = done[peer].data_ptr()
+    rc, ws_bytes = api.qkv_backward_mxfp8_data_workspace_size(proj)
+    assert rc == 0
+    scratch, base = _aligned_scratch(ws_bytes)
+    mp = N.Mxfp8QkvBackwardDataParams(projection=proj, workspace=base, workspace_bytes=ws_bytes)
+    for peer in range(world):
+        mp.peer_input[peer] = N.Mxfp8QkvBackwardInput(
+            grad_q=_activation(*quant[peer][0]), grad_k=_activation(*quant[peer][1]), grad_v=_activation(*quant[peer][2]),
+            master_q=masters[peer][0].data_ptr(), master_k=masters[peer][1].data_ptr(), master_v=masters[peer][2].data_ptr())
+    rc = api.launch_qkv_backward_mxfp8_data(mp, 0, options(flags=N.SKIP_PEER_WAIT if world > 1 else 0))
+    assert rc == 0, f"launch_qkv_backward_mxfp8_data -> cudaError {rc}"
+    check_status()
+    wproj = N.QkvBackwardWeightParams(dqkv_staging=staging.data_ptr(), saved_input=x.data_ptr(),
+                                      grad_weight=dw.data_ptr(), local_tokens=m, hidden=hidden, q_heads=q_heads,
+                                      kv_heads=kv_heads, head_dim=d, alpha=alpha, beta=beta)
+    rc, ws2 = api.qkv_backward_mxfp8_weight_workspace_size(wproj)
+    assert rc == 0
+    scratch2, base2 = _aligned_scratch(ws2)
+    wp = N.Mxfp8QkvBackwardWeightParams(projection=wproj, workspace=base2, workspace_bytes=ws2)
+    rc = api.launch_qkv_backward_mxfp8_weight(wp, 0)
+    assert rc == 0, f"launch_qkv_backward_mxfp8_weight -> cudaError {rc}"
+    check_status()
+    del scratch, scratch2
+    return to_bits(staging), to_bits(dx), to_bits(dw)
+
+
+def oproj_backward_mxfp8(world, batch, seq_local, q_heads, dy_bits, dy_q, wo_bits, attn_bits, causal=False,
+                         alpha=1.0):
+    """Every rank of the MXFP8 output-projection backward.  Returns (dA list, routed list, dWo list)."""
+    d = 128
+    m, a = batch * seq_local, q_heads * d
+    hidden = wo_bits.shape[0]
+    rows = batch * seq_local * world
+    wo = to_device(wo_bits)
+    da = [poisoned(m, a) for _ in range(world)]
+    routed = [poisoned(rows * (a // world)) for _ in range(world)]
+    dwo = [poisoned(hidden, a) for _ in range(world)]
+    done = [torch.zeros(world * N.READY_FLAG_STRIDE, dtype=torch.int32, device=DEV) for _ in range(world)]
+    for r in range(world):
+        dy, attn = to_device(dy_bits[r]), to_device(attn_bits[r])
+        dq = (to_device_u8(dy_q[r][0]), to_device_u8(dy_q[r][1]))
+        proj = N.OprojBackwardDataParams(weight=wo.data_ptr(), local_grad_attention=da[r].data_ptr(), local_tokens=m,
+                                         hidden=hidden, batch=batch, q_heads=q_heads, head_dim=d, world_size=world,
+                                         rank=r, num_comm_ctas=4, epoch=1, causal_load_balanced=int(causal), alpha=alpha)
+        proj.gemm_tuning.max_swizzle_size = 4
+        for peer in range(world):
+            proj.peer_grad_attention[peer] = routed[peer].data_ptr()
+            proj.peer_done_epoch[peer] = done[peer].data_ptr()
+        rc, ws = api.oproj_backward_mxfp8_data_workspace_size(proj)
+        assert rc == 0
+        scratch, base = _aligned_scratch(ws)
+        mp = N.Mxfp8OprojBackwardDataParams(projection=proj, grad_output=_activation(*dq), workspace=base,
+                                            workspace_bytes=ws)
+        rc = api.launch_oproj_backward_mxfp8_data(mp, 0, options(flags=N.SKIP_PEER_WAIT if world > 1 else 0))
+        assert rc == 0, f"launch_oproj_backward_mxfp8_data -> cudaError {rc}"
+        wproj = N.OprojBackwardWeightParams(grad_output=dy.data_ptr(), saved_attention=attn.data_ptr(),
+                                            grad_weight=dwo[r].data_ptr(), local_tokens=m, hidden=hidden,
+                                            q_heads=q_heads, head_dim=d, alpha=alpha)
+        rc, ws2 = api.oproj_backward_mxfp8_weight_workspace_size(wproj)
+        assert rc == 0
+        scratch2, base2 = _aligned_scratch(ws2)
+        wp = N.Mxfp8OprojBackwardWeightParams(projection=wproj, workspace=base2, workspace_bytes=ws2)
+        rc = api.launch_oproj_backward_mxfp8_weight(wp, 0)
+        assert rc == 0, f"launch_oproj_backward_mxfp8_weight -> cudaError {rc}"
+        torch.cuda.synchronize()
+        del scratch, scratch2
+    check_status()
+    return [to_bits(t) for t in da], [to_bits(t) for t in routed], [to_bits(t) for t in dwo]

@@ -17,6 +17,7 @@ RASTER_HEURISTIC, RASTER_ALONG_M, RASTER_ALONG_N = 0, 1, 2
 DTYPE_BF16, DTYPE_E4M3 = 0, 1
 ROUTE_HEAD_TO_SEQUENCE, ROUTE_QKV_GQA_PACK = 0, 2
 ROUTE_FORWARD, ROUTE_INVERSE = 0, 1
+STATIC_SCRATCH_BYTES = 8 << 20
 SKIP_PEER_WAIT = 1
 QKV_ROUTE_COMM_CTAS = 2
 QKV_ROUTE_DIRECT = 4
@@ -309,6 +310,7 @@ SYMBOLS = {
     "fuse_launch_gemm_a2a_mxfp8_prequantized": (C.c_int, [C.POINTER(Mxfp8GemmA2AParams), _P]),
     "fuse_launch_gemm_a2a_mxfp8_prequantized_ex": (C.c_int, [C.POINTER(Mxfp8GemmA2AParams), C.POINTER(Options), _P]),
     "fuse_launch_gemm_a2a_mxfp8_compute_reference": (C.c_int, [C.POINTER(Mxfp8GemmA2AParams), _P]),
+    "fuse_b200_launch_gemm_a2a_mxfp8_static": (C.c_int, [C.POINTER(Mxfp8GemmA2AParams), _P]),
     "fuse_b200_quantize_mxfp8": (C.c_int, [_P, C.c_int64, C.c_int32, C.c_int32, _P, _P, _P]),
     "fuse_b200_quantize_mxfp8_transposed": (C.c_int, [_P, C.c_int64, C.c_int32, C.c_int32, _P, _P, _P]),
     "fuse_b200_mxfp8_scale_bytes": (C.c_size_t, [C.c_int64, C.c_int64]),

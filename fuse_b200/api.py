@@ -294,3 +294,9 @@ def launch_oproj_backward_mxfp8_weight(params, stream: int = 0) -> int:
 
 def launch_oproj_backward_mxfp8(params, stream: int = 0) -> int:
     return N.lib().fuse_launch_oproj_backward_mxfp8(C.byref(params), stream)
+
+
+def launch_gemm_a2a_mxfp8_static(params: Mxfp8GemmA2AParams, stream: int = 0) -> int:
+    """MXFP8 QKV operator with the library's built-in weight scratch (allocates nothing;
+    weights whose scratch exceeds N.STATIC_SCRATCH_BYTES are rejected)."""
+    return N.lib().fuse_b200_launch_gemm_a2a_mxfp8_static(C.byref(params), stream)

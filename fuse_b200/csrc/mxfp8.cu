@@ -4,6 +4,9 @@
 // Interface: include/fuse/operators/primitives/gemm_a2a_mxfp8.h and a2a_gemm_mxfp8.h of the
 // reference; quantisation arithmetic and scale storage: csrc/operators/sm103/detail/
 // quantization.cuh:91-141,350-450 and benchmarks/sm103/fused_mxfp8.cuh:13-16.
+#include <cstdio>
+#include <mutex>
+
 #include "launch.cuh"
 
 namespace fuse_b200 {
@@ -441,3 +444,65 @@ int fuse_launch_a2a_gemm_mxfp8_cutlass(const fuse_mxfp8_a2a_gemm_params* p, fuse
 }
 
 }  // extern "C"
+
+// ------------------------------------------------------------------------------------------
+// Entry point that allocates nothing.
+//
+// Some callers of the MXFP8 QKV operator cannot hand over scratch memory: code running inside a
+// CUDA-graph capture or a real-time serving loop must not call cudaMalloc (it synchronises the
+// device and is illegal during capture), and plug-ins whose host framework owns the device
+// allocator have nothing of their own to carve scratch from.  For them the quantised-weight
+// scratch lives in this fixed array inside the library image.  Every GPU that loads the library
+// holds these bytes until the process exits, which is why the limit is modest.
+// ------------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_weight_scratch[FUSE_B200_STATIC_SCRATCH_BYTES];
+
+namespace fuse_b200 {
+namespace {
+
+// Device address of the array on each device.  In host code the array's name is only a
+// stand-in for the symbol: the address a kernel can use comes from cudaGetSymbolAddress, asked
+// once per device with that device current.
+std::mutex g_static_scratch_mutex;
+void* g_static_scratch_address[64] = {};
+
+cudaError_t static_scratch(void** address) {
+  int device = -1;
+  cudaError_t status = cudaGetDevice(&device);
+  if (status != cudaSuccess) return status;
+  if (device < 0 || device >= 64) return cudaErrorInvalidDevice;
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_address[device] == nullptr) {
+    void* ptr = nullptr;
+    status = cudaGetSymbolAddress(&ptr, g_static_weight_scratch);
+    if (status != cudaSuccess) return status;
+    g_static_scratch_address[device] = ptr;
+  }
+  *address = g_static_scratch_address[device];
+  return cudaSuccess;
+}
+
+}  // namespace
+}  // namespace fuse_b200
+
+extern "C" int fuse_b200_launch_gemm_a2a_mxfp8_static(const fuse_mxfp8_gemm_a2a_params* params, fuse_stream stream) {
+  if (params == nullptr) return int(cudaErrorInvalidValue);
+  const fuse_gemm_problem& g = params->projection.gemm;
+  if (g.n <= 0 || g.k <= 0) return int(cudaErrorInvalidValue);
+  const size_t need = fuse_b200::weight_scratch(g, nullptr).bytes;
+  if (need > size_t(FUSE_B200_STATIC_SCRATCH_BYTES)) {
+    std::fprintf(stderr,
+                 "fuse_b200_launch_gemm_a2a_mxfp8_static: weight [%d, %d] needs %zu bytes of scratch, the "
+                 "built-in scratch holds %zu; use fuse_launch_gemm_a2a_mxfp8_cutlass with caller scratch\n",
+                 g.n, g.k, need, size_t(FUSE_B200_STATIC_SCRATCH_BYTES));
+    return int(cudaErrorInvalidValue);
+  }
+  void* scratch = nullptr;
+  const cudaError_t status = fuse_b200::static_scratch(&scratch);
+  if (status != cudaSuccess) return int(status);
+  fuse_mxfp8_gemm_a2a_params with_scratch = *params;
+  with_scratch.workspace = scratch;
+  with_scratch.workspace_bytes = size_t(FUSE_B200_STATIC_SCRATCH_BYTES);
+  return int(fuse_b200::qkv_forward_mxfp8(with_scratch, nullptr, reinterpret_cast<cudaStream_t>(stream),
+                                          fuse_b200::MxPhase::kFull));
+}

@@ -336,6 +336,21 @@ FUSE_API int fuse_launch_gemm_a2a_mxfp8_prequantized_ex(const fuse_mxfp8_gemm_a2
 /* gemm_a2a_mxfp8.h:93-94: the block-scaled GEMM alone on SMs - num_comm_ctas CTAs, prepared
  * weight, no quantisation and no communication. */
 FUSE_API int fuse_launch_gemm_a2a_mxfp8_compute_reference(const fuse_mxfp8_gemm_a2a_params* params, fuse_stream stream);
+/* No counterpart in the reference.  The MXFP8 QKV operator for callers that cannot supply
+ * scratch memory -- code inside a stream capture or a latency-critical loop, where cudaMalloc is
+ * illegal or stalls the device, and plug-ins whose host owns the allocator.  Same operator and
+ * result as fuse_launch_gemm_a2a_mxfp8_cutlass, but params->workspace and workspace_bytes are
+ * ignored: the quantised weight goes to a fixed array of FUSE_B200_STATIC_SCRATCH_BYTES inside
+ * the library image (held by every GPU that loads the library, until exit).  The call allocates
+ * and frees nothing.  A weight whose scratch (N*K bytes plus N*K/32 scale bytes, each rounded
+ * up to 256) exceeds the array is rejected with cudaErrorInvalidValue and one line on stderr.
+ * The first call on each device looks the array's device address up; make that call before
+ * starting a stream capture.  All calls share the array and it keeps the previous call's
+ * contents; nothing in it has to start at zero (each call rewrites every byte it later reads),
+ * but two calls that overlap on the GPU race on it: keep them on one stream or order them. */
+#define FUSE_B200_STATIC_SCRATCH_BYTES (8u << 20)
+FUSE_API int fuse_b200_launch_gemm_a2a_mxfp8_static(const fuse_mxfp8_gemm_a2a_params* params, fuse_stream stream);
+
 /* csrc/operators/sm103/detail/quantization.cuh:281-304,350-450: the standalone quantisers.
  * Row-major BF16 [rows, k] -> E4M3 [rows, k]; BF16 [rows, cols] -> E4M3 [cols, rows] quantised
  * along the source row axis (rows % 32 == 0).  Scales in native storage of the OUTPUT operand,

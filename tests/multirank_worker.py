@@ -96,6 +96,89 @@ def main():
     ok, worst, bad = O.within_tolerance(bits(out), want_out)
     assert ok, ("oproj", worst, bad)
     dist.barrier()  # peers' inputs stay immutable until every rank is done
+
+    # ---- QKV backward: sender push into the peers' staging, flags released on the destination ----
+    hidden = 384
+    planes_all = [tuple(synthetic.normal_bf16((rows, heads // world * d), synthetic.rank_seed(r) + 100 * seg + 101, 0.01)
+                        for seg, heads in enumerate((q, kv, kv))) for r in range(world)]
+    wb = synthetic.normal_bf16((n, hidden), synthetic.BASE_SEED + 23, 0.02)
+    bp = N.QkvBackwardDataParams(local_tokens=m, hidden=hidden, batch=batch, q_heads=q, kv_heads=kv, head_dim=d,
+                                 world_size=world, rank=rank, num_comm_ctas=8, epoch=1, alpha=1.0)
+    bsym = w.allocate({"bwd_staging": m * n * 2, "bwd_ready": api.qkv_backward_ready_elements(bp) * 4,
+                       "bwd_done": world * N.READY_FLAG_STRIDE * 4})
+    mine = [to_dev(pl) for pl in planes_all[rank]]
+    wb_d = to_dev(wb)
+    dx = torch.full((m, hidden), -1, dtype=torch.int16, device=dev).view(torch.bfloat16)
+    bp.grad_q, bp.grad_k, bp.grad_v = (t.data_ptr() for t in mine)
+    bp.weight, bp.grad_input = wb_d.data_ptr(), dx.data_ptr()
+    for r in range(world):
+        bp.peer_dqkv_staging[r] = bsym["bwd_staging"].peer_ptrs[r]
+        bp.peer_ready[r] = bsym["bwd_ready"].peer_ptrs[r]
+        bp.peer_done_epoch[r] = bsym["bwd_done"].peer_ptrs[r]
+    torch.cuda.synchronize()
+    dist.barrier()
+    assert api.launch_qkv_backward_data(bp, 0, opts) == 0
+    torch.cuda.synchronize()
+    status = api.read_status()
+    assert status[0] == 0, status[:8]
+    want_staging, want_dx, _ = O.qkv_backward(world, rank, batch, s, q, kv, d, planes_all, wb,
+                                              synthetic.normal_bf16((m, hidden), 1, 1.0))
+    assert np.array_equal(bits(bsym["bwd_staging"].view(torch.bfloat16)).reshape(m, n), want_staging), "bwd staging"
+    ok, worst, bad = O.within_tolerance(bits(dx), want_dx, 0.02, 0.02)
+    assert ok, ("dX", worst, bad)
+    dist.barrier()
+
+    # ---- MoE dispatch: entry/exit handshakes with every peer, row gather across ranks ------------
+    experts_local, tokens, topk, mk, mn = 4, 96, 2, 512, 256
+    rng = np.random.default_rng(11)
+    chosen = [rng.integers(0, experts_local * world, (tokens, topk)).astype(np.int32) for _ in range(world)]
+    for c in chosen:
+        c[:, 1] = (c[:, 0] + 1 + c[:, 1] % (experts_local * world - 1)) % (experts_local * world)  # distinct experts
+    offs = np.empty(experts_local + 1, dtype=np.int32)
+    total = O.lib().fo_moe_build_rows(world, rank, experts_local, tokens, topk, O.ptr_array(chosen), O.ptr(offs), None)
+    src = np.empty((max(total, 1), 3), dtype=np.int32)
+    O.lib().fo_moe_build_rows(world, rank, experts_local, tokens, topk, O.ptr_array(chosen), O.ptr(offs), O.ptr(src))
+    toks_all = [synthetic.normal_bf16((tokens, mk), synthetic.GROUPED_SEED + 31 * r, 1.0) for r in range(world)]
+    ew = synthetic.normal_bf16((experts_local, mn, mk), synthetic.GROUPED_SEED + 1000 + rank, 0.02)
+    cap = 256
+    msym = w.allocate({"moe_tokens": tokens * mk * 2, "moe_started": world * N.READY_FLAG_STRIDE * 4,
+                       "moe_done": world * N.READY_FLAG_STRIDE * 4})
+    msym["moe_tokens"].view(torch.bfloat16).copy_(to_dev(toks_all[rank]).reshape(-1))
+    ew_d = to_dev(ew)
+    lhs = torch.full((experts_local, cap, mk), 0x7f7f, dtype=torch.int16, device=dev).view(torch.bfloat16)
+    eo = torch.full((experts_local, cap, mn), 0x7f7f, dtype=torch.int16, device=dev).view(torch.bfloat16)
+    ptrs = lambda t: torch.tensor([t[i].data_ptr() for i in range(experts_local)], dtype=torch.int64, device=dev)
+    lp, wp, op = ptrs(lhs), ptrs(ew_d), ptrs(eo)
+    offs_d = torch.from_numpy(offs.astype(np.int64)).to(dev)
+    src_d = torch.from_numpy(src).to(dev)
+    gp = N.Bf16GroupedGemmParams(lhs=lp.data_ptr(), weight_nt=wp.data_ptr(), output=op.data_ptr(),
+                                 row_offsets=offs_d.data_ptr(), source=src_d.data_ptr(), experts=experts_local,
+                                 n=mn, k=mk, expert_row_capacity=cap, rank=rank, world_size=world, topk=topk)
+    gp.policy = N.GroupedGemmPolicy(num_comm_ctas=6, num_compute_ctas=128, tile_n=256)
+    for r in range(world):
+        gp.peer_input[r] = msym["moe_tokens"].peer_ptrs[r]
+        gp.peer_started[r] = msym["moe_started"].peer_ptrs[r]
+        gp.peer_done[r] = msym["moe_done"].peer_ptrs[r]
+    rc, plan = api.create_bf16_a2a_grouped_gemm(gp)
+    assert rc == 0, rc
+    torch.cuda.synchronize()
+    dist.barrier()
+    for _ in range(2):
+        assert api.launch_bf16_grouped_gemm(plan, 0, opts) == 0
+    torch.cuda.synchronize()
+    status = api.read_status()
+    assert status[0] == 0, status[:8]
+    want_lhs = np.full((experts_local, cap, mk), 0x7f7f, dtype=np.uint16)
+    want_eo = np.full((experts_local, cap, mn), 0x7f7f, dtype=np.uint16)
+    assert O.lib().fo_moe_dispatch_fc1(experts_local, O.ptr(offs), O.ptr(src), O.ptr_array(toks_all), O.ptr(ew), mn, mk,
+                                       cap, O.ptr(want_lhs), O.ptr(want_eo)) == 0
+    assert np.array_equal(bits(lhs), want_lhs), "dispatched rows"
+    for e in range(experts_local):
+        cnt = int(offs[e + 1] - offs[e])
+        ok, worst, bad = O.within_tolerance(bits(eo)[e, :cnt], want_eo[e, :cnt], 0.002, 0.008)
+        assert ok, ("moe", e, worst, bad)
+    assert api.destroy_bf16_grouped_gemm(plan) == 0
+    dist.barrier()
     w.close()
     dist.destroy_process_group()
     print(f"MULTIRANK PASS rank {rank}/{world} route={route_mode}", flush=True)

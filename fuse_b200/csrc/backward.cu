@@ -94,6 +94,25 @@ cudaError_t qkv_backward_data(const fuse_qkv_backward_data_params& p, const fuse
     f.grad.peer_ready[peer] = p.peer_ready[peer];
     f.qkv.peer_done[peer] = p.peer_done_epoch[peer];
   }
+  // Tensor-copy push when a head is one 128-column box and 64-row boxes never straddle a
+  // sequence block; otherwise the register (16-byte) push.
+  const int row_block = p.causal_load_balanced ? seq_local / 2 : seq_local;
+  if (p.head_dim == 128 && row_block % 64 == 0 && !(options && (options->flags & FUSE_B200_VECTOR_PULL))) {
+    GradPushMaps push{};
+    bool encoded = true;
+    const fuse_bf16* planes[3] = {p.grad_q, p.grad_k, p.grad_v};
+    const int heads[3] = {p.q_heads, p.kv_heads, p.kv_heads};
+    const uint64_t rows_global = uint64_t(p.batch) * uint64_t(seq_local) * uint64_t(p.world_size);
+    for (int s = 0; s < 3 && encoded; ++s)
+      encoded = encode_copy_map(&push.plane[s], planes[s], 2, rows_global, uint64_t(heads[s] / p.world_size) * 128, 64, 128) ==
+                cudaSuccess;
+    for (int peer = 0; peer < p.world_size && encoded; ++peer)
+      encoded = encode_copy_map(&push.staging[peer], p.peer_dqkv_staging[peer], 2, uint64_t(m), uint64_t(k), 64, 128) ==
+                cudaSuccess;
+    if (encoded)
+      return launch_mode<kModeHeadGate, false, true, false, GradPushMaps>(maps, push, f, block_n, info, stream,
+                                                                          !vector_epilogue_requested(options));
+  }
   StoreMaps stores{};
   return launch_mode<kModeHeadGate, false, true>(maps, stores, f, block_n, info, stream,
                                                  !vector_epilogue_requested(options));

@@ -168,6 +168,25 @@ cudaError_t qkv_data(const fuse_mxfp8_qkv_backward_data_params& mp, const fuse_b
     }
     f.qkv.peer_done[peer] = p.peer_done_epoch[peer];
   }
+  if (!(options && (options->flags & FUSE_B200_VECTOR_PULL))) {
+    GradPullMaps pull{};
+    const uint64_t rows_global = uint64_t(p.batch) * uint64_t(seq_local) * uint64_t(p.world_size);
+    const int heads[3] = {p.q_heads, p.kv_heads, p.kv_heads};
+    bool encoded = encode_copy_map(&pull.lhs, lhs.data, 1, uint64_t(m), uint64_t(k), 128, 128) == cudaSuccess &&
+                   encode_copy_map(&pull.master, p.peer_dqkv_staging[p.rank], 2, uint64_t(m), uint64_t(k), 64, 128) ==
+                       cudaSuccess;
+    for (int peer = 0; peer < p.world_size && encoded; ++peer)
+      for (int s = 0; s < 3 && encoded; ++s) {
+        const uint64_t plane_width = uint64_t(heads[s] / p.world_size) * 128;
+        encoded = encode_copy_map(&pull.bytes[peer][s], f.grad.peer_bytes[peer][s], 1, rows_global, plane_width, 128, 128) ==
+                      cudaSuccess &&
+                  encode_copy_map(&pull.masters[peer][s], f.grad.peer_master[peer][s], 2, rows_global, plane_width, 64, 128) ==
+                      cudaSuccess;
+      }
+    if (encoded)
+      return launch_mode<kModeGradPull, false, false, true, GradPullMaps>(maps, pull, f, block_n, info, stream,
+                                                                          !vector_epilogue_requested(options));
+  }
   StoreMaps stores{};
   return launch_mode<kModeGradPull, false, false, true>(maps, stores, f, block_n, info, stream,
                                                         !vector_epilogue_requested(options));

@@ -21,6 +21,8 @@
 // detail/cutlass_pipeline.cuh:335-814) with hand-written tcgen05/TMEM code.
 #pragma once
 
+#include <type_traits>
+
 #include <cooperative_groups.h>
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
@@ -69,6 +71,23 @@ enum LaunchFlags : uint32_t {
 struct alignas(64) StoreMaps {
   CUtensorMap local;
   CUtensorMap peer[kMaxWorldSize][3];
+};
+// Tensor maps of the QKV backward sender push: this rank's planar dQ, dK, dV
+// ([B*S_global, local_heads*128] BF16, boxes of 128 columns x 64 rows, no swizzle) and every
+// destination's packed staging ([M, (q+2kv)*128], same boxes).
+struct alignas(64) GradPushMaps {
+  CUtensorMap local;
+  CUtensorMap plane[3];
+  CUtensorMap staging[kMaxWorldSize];
+};
+// Tensor maps of the MXFP8 QKV backward receiver pull: every owner's planes as E4M3 bytes
+// (boxes of 128 bytes x 128 rows) and as BF16 masters (128 columns x 64 rows), the local packed
+// lhs bytes and the local packed BF16 staging.
+struct alignas(64) GradPullMaps {
+  CUtensorMap local;
+  CUtensorMap lhs, master;
+  CUtensorMap bytes[kMaxWorldSize][3];
+  CUtensorMap masters[kMaxWorldSize][3];
 };
 
 struct QkvRoute {
@@ -794,6 +813,212 @@ __device__ __forceinline__ void grad_pull_role(const FusedParams& p) {
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Chunk pipeline shared by the tensor-copy communication roles.
+//
+// Every pull/push warp of a communication CTA walks its units chunk by chunk (a chunk fits one
+// kPullStageBytes stage): loads run kPullStages ahead into the warp's shared-memory ring and
+// complete on mbarriers; as a chunk lands its store is issued and committed as one bulk group;
+// the stage is reused once that store has read it; a unit is reported (`Policy::publish`) when
+// the group holding its last chunk has completed, checked kPullLag chunks late.  The policy
+// supplies the unit/chunk walk and the copy instructions.
+// ------------------------------------------------------------------------------------------
+template <class Policy>
+__device__ __forceinline__ void run_chunk_pipeline(Policy& policy, const WaitContext& w, uint32_t smem_base,
+                                                   int32_t num_comm_ctas) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp >= kPullWarps) return;
+  const uint32_t ring = smem_base + uint32_t(warp) * kPullStages * kPullStageBytes;
+  const uint32_t bars = smem_base + kPullWarps * kPullStages * kPullStageBytes + uint32_t(warp) * kPullStages * 8u;
+  if (lane == 0) {
+    for (int s = 0; s < kPullStages; ++s) ptx::mbar_init(bars + 8u * s, 1);
+    ptx::fence_mbar_init();
+  }
+  __syncwarp();
+  const int32_t workers = num_comm_ctas * kPullWarps;
+  const int32_t worker = warp * num_comm_ctas + int32_t(blockIdx.x);
+
+  typename Policy::Cursor load_cursor, store_cursor;
+  bool more_loads = policy.first(load_cursor, worker, workers);
+  if (!more_loads) return;
+  store_cursor = load_cursor;
+  int32_t issued = 0, consumed = 0;
+  while (issued < kPullStages && more_loads) {
+    policy.load(load_cursor, ring + uint32_t(issued % kPullStages) * kPullStageBytes,
+                bars + 8u * uint32_t(issued % kPullStages), lane);
+    more_loads = policy.next(load_cursor, workers);
+    ++issued;
+  }
+  int64_t lag_unit[kPullLag];
+#pragma unroll
+  for (int i = 0; i < kPullLag; ++i) lag_unit[i] = -1;
+  bool ok = true, more_stores = true;
+  while (ok && more_stores) {
+    const int stage = consumed % kPullStages;
+    uint32_t landed = 1u;
+    if (lane == 0)
+      landed = mbar_wait(bars + 8u * stage, uint32_t(consumed / kPullStages) & 1u, w, kSiteCommStage) ? 1u : 0u;
+    landed = __shfl_sync(0xffffffffu, landed, 0);
+    if (!landed) { ok = false; break; }
+    policy.store(store_cursor, ring + uint32_t(stage) * kPullStageBytes, lane);
+    ptx::bulk_commit();
+    ++consumed;
+    ptx::bulk_wait_read<0>();
+    __syncwarp();
+    if (more_loads && issued < consumed + kPullStages) {
+      policy.load(load_cursor, ring + uint32_t(issued % kPullStages) * kPullStageBytes,
+                  bars + 8u * uint32_t(issued % kPullStages), lane);
+      more_loads = policy.next(load_cursor, workers);
+      ++issued;
+    }
+    ptx::bulk_wait<kPullLag>();
+    __syncwarp();
+    if (lag_unit[kPullLag - 1] >= 0) policy.publish(lag_unit[kPullLag - 1], lane);
+#pragma unroll
+    for (int i = kPullLag - 1; i > 0; --i) lag_unit[i] = lag_unit[i - 1];
+    lag_unit[0] = policy.closes(store_cursor) ? policy.unit(store_cursor) : -1;
+    more_stores = policy.next(store_cursor, workers);
+  }
+  ptx::bulk_wait<0>();
+  __syncwarp();
+  if (ok) {
+#pragma unroll
+    for (int i = kPullLag - 1; i >= 0; --i)
+      if (lag_unit[i] >= 0) policy.publish(lag_unit[i], lane);
+  }
+  if (!ok && lane == 0)
+    for (int32_t i = consumed; i < issued; ++i)
+      mbar_wait(bars + 8u * uint32_t(i % kPullStages), uint32_t(i / kPullStages) & 1u, w, kSiteDrain, false);
+}
+
+// QKV backward sender push with tensor copies (head_dim 128): unit = (destination M tile,
+// destination, local head), two chunks of 64 rows x 128 columns.  Destinations rotate from the
+// next rank on.  The destination's flag is released at system scope once both chunks' stores
+// have completed.
+struct GradPushPolicy {
+  struct Cursor { int64_t unit; int32_t chunk; };
+  const FusedParams& p;
+  const GradPushMaps& maps;
+  int32_t m_tiles, local_heads, heads_total, q_local, kv_local;
+  int64_t units;
+  __device__ GradPushPolicy(const FusedParams& params, const GradPushMaps& m) : p(params), maps(m) {
+    const GradRoute& g = p.grad;
+    m_tiles = (g.m + kBlockM - 1) / kBlockM;
+    q_local = g.q_heads / g.world;
+    kv_local = g.kv_heads / g.world;
+    local_heads = q_local + 2 * kv_local;
+    heads_total = g.q_heads + 2 * g.kv_heads;
+    units = int64_t(m_tiles) * g.world * local_heads;
+  }
+  struct Where { int32_t dest, mt, segment, local_head, head; };
+  __device__ Where where(int64_t u) const {
+    const GradRoute& g = p.grad;
+    Where x;
+    const int32_t slot = int32_t(u % local_heads), rest = int32_t(u / local_heads);
+    x.dest = (g.rank + 1 + rest % g.world) % g.world;
+    x.mt = rest / g.world;
+    x.segment = slot < q_local ? 0 : (slot < q_local + kv_local ? 1 : 2);
+    x.local_head = slot - (x.segment == 0 ? 0 : q_local + (x.segment == 2 ? kv_local : 0));
+    const int32_t seg_local = x.segment == 0 ? q_local : kv_local;
+    x.head = (x.segment == 0 ? 0 : g.q_heads + (x.segment == 2 ? g.kv_heads : 0)) + g.rank * seg_local + x.local_head;
+    return x;
+  }
+  __device__ bool first(Cursor& c, int32_t worker, int32_t) const { c.unit = worker; c.chunk = 0; return c.unit < units; }
+  __device__ bool next(Cursor& c, int32_t workers) const {
+    if (++c.chunk < 2 && p.grad.m - where(c.unit).mt * kBlockM > 64) return true;
+    c.chunk = 0;
+    c.unit += workers;
+    return c.unit < units;
+  }
+  __device__ void load(const Cursor& c, uint32_t smem, uint32_t bar, int lane) const {
+    if (lane != 0) return;
+    const GradRoute& g = p.grad;
+    const Where x = where(c.unit);
+    const int64_t src_row = global_row(g.world, x.dest, g.seq_local, g.global_seq, g.causal != 0, x.mt * kBlockM + c.chunk * 64);
+    ptx::mbar_expect_tx(bar, 64u * 256u);
+    ptx::tma_load_2d(smem, &maps.plane[x.segment], bar, x.local_head * 128, int32_t(src_row));
+  }
+  __device__ void store(const Cursor& c, uint32_t smem, int lane) const {
+    if (lane != 0) return;
+    const Where x = where(c.unit);
+    ptx::tma_store_2d(&maps.staging[x.dest], smem, x.head * 128, x.mt * kBlockM + c.chunk * 64);
+  }
+  __device__ bool closes(const Cursor& c) const { return c.chunk == 1 || p.grad.m - where(c.unit).mt * kBlockM <= 64; }
+  __device__ int64_t unit(const Cursor& c) const { return c.unit; }
+  __device__ void publish(int64_t u, int lane) const {
+    if (lane != 0) return;
+    const Where x = where(u);
+    __threadfence_system();
+    ptx::st_release_sys(p.grad.peer_ready[x.dest] + (int64_t(x.mt) * heads_total + x.head) * kReadyFlagStride,
+                        p.wait.epoch);
+  }
+};
+
+// MXFP8 QKV backward receiver pull with tensor copies: unit = (M tile, logical head), four
+// chunks: the 128 x 128 E4M3 block, two 64-row halves of the BF16 master block, the scale atom.
+struct GradPullPolicy {
+  struct Cursor { int64_t unit; int32_t chunk; };
+  const FusedParams& p;
+  const GradPullMaps& maps;
+  int32_t heads_total;
+  int64_t units;
+  __device__ GradPullPolicy(const FusedParams& params, const GradPullMaps& m) : p(params), maps(m) {
+    heads_total = p.grad.q_heads + 2 * p.grad.kv_heads;
+    units = int64_t((p.grad.m + kBlockM - 1) / kBlockM) * heads_total;
+  }
+  struct Where { int32_t mt, head, segment, owner, local_head, seg_local; int64_t src_row; };
+  __device__ Where where(int64_t u) const {
+    const GradRoute& g = p.grad;
+    Where x;
+    x.mt = int32_t(u / heads_total);
+    x.head = int32_t(u % heads_total);
+    x.segment = x.head < g.q_heads ? 0 : (x.head < g.q_heads + g.kv_heads ? 1 : 2);
+    const int32_t seg_head = x.head - (x.segment == 0 ? 0 : g.q_heads + (x.segment == 2 ? g.kv_heads : 0));
+    x.seg_local = (x.segment == 0 ? g.q_heads : g.kv_heads) / g.world;
+    x.owner = seg_head / x.seg_local;
+    x.local_head = seg_head - x.owner * x.seg_local;
+    x.src_row = global_row(g.world, g.rank, g.seq_local, g.global_seq, g.causal != 0, x.mt * kBlockM);
+    return x;
+  }
+  __device__ bool first(Cursor& c, int32_t worker, int32_t) const { c.unit = worker; c.chunk = 0; return c.unit < units; }
+  __device__ bool next(Cursor& c, int32_t workers) const {
+    if (++c.chunk < 4) return true;
+    c.chunk = 0;
+    c.unit += workers;
+    return c.unit < units;
+  }
+  __device__ void load(const Cursor& c, uint32_t smem, uint32_t bar, int lane) const {
+    if (lane != 0) return;
+    const Where x = where(c.unit);
+    if (c.chunk == 0) {
+      ptx::mbar_expect_tx(bar, 128u * 128u);
+      ptx::tma_load_2d(smem, &maps.bytes[x.owner][x.segment], bar, x.local_head * 128, int32_t(x.src_row));
+    } else if (c.chunk < 3) {
+      ptx::mbar_expect_tx(bar, 64u * 256u);
+      ptx::tma_load_2d(smem, &maps.masters[x.owner][x.segment], bar, x.local_head * 128,
+                       int32_t(x.src_row) + (c.chunk - 1) * 64);
+    } else {
+      ptx::mbar_expect_tx(bar, 512u);
+      ptx::bulk_load(smem, p.grad.peer_scales[x.owner][x.segment] + ((x.src_row >> 7) * x.seg_local + x.local_head) * 512,
+                     512u, bar);
+    }
+  }
+  __device__ void store(const Cursor& c, uint32_t smem, int lane) const {
+    if (lane != 0) return;
+    const Where x = where(c.unit);
+    if (c.chunk == 0) ptx::tma_store_2d(&maps.lhs, smem, x.head * 128, x.mt * kBlockM);
+    else if (c.chunk < 3) ptx::tma_store_2d(&maps.master, smem, x.head * 128, x.mt * kBlockM + (c.chunk - 1) * 64);
+    else ptx::bulk_store(p.grad.lhs_scales + (int64_t(x.mt) * heads_total + x.head) * 512, smem, 512u);
+  }
+  __device__ bool closes(const Cursor& c) const { return c.chunk == 3; }
+  __device__ int64_t unit(const Cursor& c) const { return c.unit; }
+  __device__ void publish(int64_t u, int lane) const {
+    if (lane != 0) return;
+    __threadfence();
+    ptx::st_release_gpu(p.ready + u * kReadyFlagStride, p.wait.epoch);
+  }
+};
+
 // 32 FP32 accumulators of one output row -> alpha (and beta * old D) -> BF16 -> four 16-byte
 // stores.  `col` is the global column of acc[0]; vectors past N are skipped (N % 8 == 0).
 struct PeerRow {
@@ -938,11 +1163,11 @@ __device__ __forceinline__ void mxfp8_quantize_rows(const uint16_t* source, int6
 // each a [64 K rows x 128 bytes] swizzled box (the data-gradient GEMMs read the forward weight
 // as stored, the weight-gradient GEMMs read both operands along the token axis).
 template <int kBlockN, int kStages, int kMode, bool kTmaEpilogue, bool kAMn = false, bool kBMn = false,
-          bool kMx = false>
+          bool kMx = false, class Maps = StoreMaps>
 __global__ void __launch_bounds__(kThreads, 1)
 fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b,
-                  const __grid_constant__ StoreMaps store_maps, const FusedParams p) {
+                  const __grid_constant__ Maps store_maps, const FusedParams p) {
   using Layout = SmemLayout<kBlockN, kStages, kMx>;
   constexpr uint32_t kAccumStages = Layout::kAccumStages;
   static_assert(!kMx || (!kAMn && !kBMn), "block-scaled operands are K-major");
@@ -976,8 +1201,23 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if (p.flags & kFlagVectorPull) lhs_pull_role(p, smem);
       else lhs_pull_bulk_role(p, base);
     }
-    if constexpr (kMode == kModeHeadGate) grad_push_role(p);
-    if constexpr (kMode == kModeGradPull) grad_pull_role(p);
+    if constexpr (kMode == kModeHeadGate) {
+      if constexpr (std::is_same<Maps, GradPushMaps>::value) {
+        GradPushPolicy policy(p, store_maps);
+        run_chunk_pipeline(policy, p.wait, base, p.num_comm_ctas);
+        __threadfence_system();
+      } else {
+        grad_push_role(p);
+      }
+    }
+    if constexpr (kMode == kModeGradPull) {
+      if constexpr (std::is_same<Maps, GradPullMaps>::value) {
+        GradPullPolicy policy(p, store_maps);
+        run_chunk_pipeline(policy, p.wait, base, p.num_comm_ctas);
+      } else {
+        grad_pull_role(p);
+      }
+    }
   } else {
     const uint32_t bar_base = base + Layout::kBarrierOffset;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };

@@ -65,8 +65,8 @@ inline void fill_core(FusedParams* p, int m, int n, int k, int block_n, int num_
   p->ldd = ldd;
 }
 
-template <int kMode, bool kTmaEpilogue, bool kAMn, bool kBMn, bool kMx = false>
-cudaError_t launch_variant(const Operands& maps, const StoreMaps& stores, const FusedParams& p,
+template <int kMode, bool kTmaEpilogue, bool kAMn, bool kBMn, bool kMx = false, class Maps = StoreMaps>
+cudaError_t launch_variant(const Operands& maps, const Maps& stores, const FusedParams& p,
                            int block_n, const DeviceInfo& info, cudaStream_t stream) {
   const int64_t tiles = p.order.count();
   const int compute_capacity = info.sm_count - p.num_comm_ctas;
@@ -75,28 +75,38 @@ cudaError_t launch_variant(const Operands& maps, const StoreMaps& stores, const 
   const bool cooperative = kMode != kModePlain || kMx;
   if (block_n == 256) {
     using Layout = SmemLayout<256, 4, kMx>;
-    return host::launch_kernel(fused_gemm_kernel<256, 4, kMode, kTmaEpilogue, kAMn, kBMn, kMx>, grid, kThreads,
+    return host::launch_kernel(fused_gemm_kernel<256, 4, kMode, kTmaEpilogue, kAMn, kBMn, kMx, Maps>, grid, kThreads,
                                Layout::kDynamicBytes, cooperative, stream, maps.a, maps.b, stores, p);
   }
   using Layout = SmemLayout<128, 6, kMx>;
-  return host::launch_kernel(fused_gemm_kernel<128, 6, kMode, kTmaEpilogue, kAMn, kBMn, kMx>, grid, kThreads,
+  return host::launch_kernel(fused_gemm_kernel<128, 6, kMode, kTmaEpilogue, kAMn, kBMn, kMx, Maps>, grid, kThreads,
                              Layout::kDynamicBytes, cooperative, stream, maps.a, maps.b, stores, p);
 }
 
 // The epilogue writes the local output through the copy engine unless the caller asked for the
 // 16-byte vector epilogue or the mode needs it (beta != 0, tile publication to communication
 // CTAs).
-template <int kMode, bool kAMn = false, bool kBMn = false, bool kMx = false>
-cudaError_t launch_mode(const Operands& maps, StoreMaps& stores, const FusedParams& p, int block_n,
+template <int kMode, bool kAMn = false, bool kBMn = false, bool kMx = false, class Maps = StoreMaps>
+cudaError_t launch_mode(const Operands& maps, Maps& stores, const FusedParams& p, int block_n,
                         const DeviceInfo& info, cudaStream_t stream, bool tma_epilogue) {
   if constexpr (kMode != kModeQkvPush) {
     if (tma_epilogue) {
       const cudaError_t status = encode_store_map(&stores.local, p.d, uint64_t(p.m), uint64_t(p.n), p.ldd);
       if (status != cudaSuccess) return status;
-      return launch_variant<kMode, true, kAMn, kBMn, kMx>(maps, stores, p, block_n, info, stream);
+      return launch_variant<kMode, true, kAMn, kBMn, kMx, Maps>(maps, stores, p, block_n, info, stream);
     }
   }
-  return launch_variant<kMode, false, kAMn, kBMn, kMx>(maps, stores, p, block_n, info, stream);
+  return launch_variant<kMode, false, kAMn, kBMn, kMx, Maps>(maps, stores, p, block_n, info, stream);
+}
+
+// Row-major [rows, cols] tensor of `element_bytes`-wide elements boxed box_rows x box_cols
+// without swizzle: the copy boxes of the gradient routes.
+inline cudaError_t encode_copy_map(CUtensorMap* map, const void* base, uint32_t element_bytes, uint64_t rows,
+                                   uint64_t cols, uint32_t box_rows, uint32_t box_cols) {
+  return host::encode_tensor_map_2d(map, base,
+                                    element_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8,
+                                    element_bytes, rows, cols, cols * element_bytes, box_rows, box_cols,
+                                    CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
 inline bool vector_epilogue_requested(const fuse_b200_options* options) {

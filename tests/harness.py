@@ -107,7 +107,7 @@ def oproj_forward(world, rank, batch, seq_local, peer_bits, w_bits, comm=4, caus
 
 
 def qkv_backward(world, batch, seq_local, q_heads, kv_heads, head_dim, planes_bits, w_bits, x_bits, comm=4,
-                 causal=False, alpha=1.0, beta=0.0, dw_init_bits=None, block_n=0, tuning=(1, False)):
+                 causal=False, alpha=1.0, beta=0.0, dw_init_bits=None, block_n=0, tuning=(1, False), vector=False):
     """Runs every rank of the QKV backward (data + weight).  planes_bits[r] = (dQ, dK, dV) of rank r.
     Several ranks on one GPU: every rank's communication CTAs push first (COMM_ONLY), then every
     rank's GEMM runs (COMPUTE_ONLY).  Returns per rank (staging, dX, dW) bits."""
@@ -142,7 +142,8 @@ def qkv_backward(world, batch, seq_local, q_heads, kv_heads, head_dim, planes_bi
     phases = [0] if world == 1 else [N.COMM_ONLY, N.COMPUTE_ONLY]
     for phase in phases:
         for p in params:
-            opts = options(flags=phase | (N.SKIP_PEER_WAIT if world > 1 else 0), block_n=block_n)
+            opts = options(flags=phase | (N.SKIP_PEER_WAIT if world > 1 else 0) | (N.VECTOR_PULL if vector else 0),
+                           block_n=block_n)
             rc = api.launch_qkv_backward_data(p, 0, opts)
             assert rc == 0, f"launch_qkv_backward_data -> cudaError {rc}"
     check_status()
@@ -363,7 +364,7 @@ def _activation(data_t, scales_t):
 
 
 def qkv_backward_mxfp8(world, rank, batch, seq_local, q_heads, kv_heads, planes_bits, planes_q, w_bits, x_bits,
-                       comm=4, causal=False, alpha=1.0, beta=0.0, dw_init_bits=None):
+                       comm=4, causal=False, alpha=1.0, beta=0.0, dw_init_bits=None, vector=False):
     """One rank of the MXFP8 QKV backward (data + weight).  planes_bits[r] = BF16 (dQ, dK, dV) masters of
     rank r, planes_q[r] = their ((data, scales), ...) quantisations.  Returns (staging, dX, dW) bits."""
     d = 128
@@ -393,7 +394,8 @@ def qkv_backward_mxfp8(world, rank, batch, seq_local, q_heads, kv_heads, planes_
         mp.peer_input[peer] = N.Mxfp8QkvBackwardInput(
             grad_q=_activation(*quant[peer][0]), grad_k=_activation(*quant[peer][1]), grad_v=_activation(*quant[peer][2]),
             master_q=masters[peer][0].data_ptr(), master_k=masters[peer][1].data_ptr(), master_v=masters[peer][2].data_ptr())
-    rc = api.launch_qkv_backward_mxfp8_data(mp, 0, options(flags=N.SKIP_PEER_WAIT if world > 1 else 0))
+    rc = api.launch_qkv_backward_mxfp8_data(mp, 0, options(flags=(N.SKIP_PEER_WAIT if world > 1 else 0) |
+                                                            (N.VECTOR_PULL if vector else 0)))
     assert rc == 0, f"launch_qkv_backward_mxfp8_data -> cudaError {rc}"
     check_status()
     wproj = N.QkvBackwardWeightParams(dqkv_staging=staging.data_ptr(), saved_input=x.data_ptr(),

@@ -25,8 +25,9 @@ QKV_BWD_CASES = [
 ]
 
 
+@pytest.mark.parametrize("vector", [False, True])
 @pytest.mark.parametrize("case", QKV_BWD_CASES)
-def test_qkv_backward_matches_oracle(case):
+def test_qkv_backward_matches_oracle(case, vector):
     from tests import harness as H
     world, batch, s, q, kv, d, hidden, comm, causal = case
     m, width, rows = batch * s, (q + 2 * kv) * d, batch * s * world
@@ -37,7 +38,7 @@ def test_qkv_backward_matches_oracle(case):
     xs = [synthetic.normal_bf16((m, hidden), synthetic.rank_seed(r) + 1000, 1.0) for r in range(world)]
     dw0 = [synthetic.normal_bf16((width, hidden), synthetic.rank_seed(r) + 7, 0.05) for r in range(world)]
     got = H.qkv_backward(world, batch, s, q, kv, d, planes, w, xs, comm=comm, causal=causal, alpha=0.5,
-                         beta=1.0, dw_init_bits=dw0)
+                         beta=1.0, dw_init_bits=dw0, vector=vector)
     for r in range(world):
         staging, dx, dw = O.qkv_backward(world, r, batch, s, q, kv, d, planes, w, xs[r], causal=causal,
                                          alpha=0.5, beta=1.0, grad_weight=dw0[r])

@@ -35,8 +35,9 @@ CASES = [
 ]
 
 
+@pytest.mark.parametrize("vector", [False, True])
 @pytest.mark.parametrize("case", CASES)
-def test_qkv_backward_mxfp8_matches_oracle(case):
+def test_qkv_backward_mxfp8_matches_oracle(case, vector):
     from tests import harness as H
     world, batch, s, q, kv, hidden, comm, causal = case
     d = 128
@@ -50,7 +51,7 @@ def test_qkv_backward_mxfp8_matches_oracle(case):
         x = synthetic.normal_bf16((m, hidden), synthetic.rank_seed(rank) + 1000, 1.0)
         dw0 = synthetic.normal_bf16((width, hidden), synthetic.rank_seed(rank) + 7, 0.05)
         staging, dx, dw = H.qkv_backward_mxfp8(world, rank, batch, s, q, kv, planes, planes_q, w, x, comm=comm,
-                                               causal=causal, alpha=0.5, beta=1.0, dw_init_bits=dw0)
+                                               causal=causal, alpha=0.5, beta=1.0, dw_init_bits=dw0, vector=vector)
         want_staging, _, _ = O.qkv_backward(world, rank, batch, s, q, kv, d, planes, w, x, causal=causal)
         assert np.array_equal(staging, want_staging), "BF16 masters routed for the weight gradient differ"
         # packed lhs of the data GEMM: owners' bytes and scale atoms, element by element

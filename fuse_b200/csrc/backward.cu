@@ -94,6 +94,7 @@ cudaError_t qkv_backward_data(const fuse_qkv_backward_data_params& p, const fuse
     f.grad.peer_ready[peer] = p.peer_ready[peer];
     f.qkv.peer_done[peer] = p.peer_done_epoch[peer];
   }
+  plan_join(&f, block_n, info.sm_count, double(m) * k * 2.0, false);
   // Tensor-copy push when a head is one 128-column box and 64-row boxes never straddle a
   // sequence block; otherwise the register (16-byte) push.
   const int row_block = p.causal_load_balanced ? seq_local / 2 : seq_local;

@@ -168,6 +168,7 @@ cudaError_t qkv_data(const fuse_mxfp8_qkv_backward_data_params& mp, const fuse_b
     }
     f.qkv.peer_done[peer] = p.peer_done_epoch[peer];
   }
+  plan_join(&f, block_n, info.sm_count, double(m) * k * (3.0 + 1.0 / 32), true);
   if (!(options && (options->flags & FUSE_B200_VECTOR_PULL))) {
     GradPullMaps pull{};
     const uint64_t rows_global = uint64_t(p.batch) * uint64_t(seq_local) * uint64_t(p.world_size);

@@ -206,6 +206,7 @@ cudaError_t oproj_forward(const fuse_a2a_gemm_params& p, const fuse_b200_options
     k.lhs.peer_input[peer] = p.peer_input[peer];
     k.lhs.peer_input_ready[peer] = p.peer_input_ready[peer];
   }
+  plan_join(&k, block_n, info.sm_count, double(p.gemm.m) * p.gemm.k * 2.0, false);
   StoreMaps stores{};
   return launch_mode<kModeLhsPull>(maps, stores, k, block_n, info, stream,
                                    !vector_epilogue_requested(options));

@@ -157,6 +157,10 @@ struct FusedParams {
   uint32_t* clear_words;
   int64_t clear_count;
   uint32_t* ready;            // tile flags (QkvPush) or (m-tile, k-shard) flags (LhsPull)
+  // Tiles [join_tile, tiles) are dealt round-robin to ALL CTAs of the grid: communication CTAs
+  // whose transfers are finished by then run the GEMM pipeline on their share (pull and
+  // gradient modes).  join_tile == tiles: communication CTAs never compute.
+  int64_t join_tile;
   uint32_t flags;
   // Optional %globaltimer trace: CTA `trace_cta` appends (site, timestamp) pairs until the
   // buffer holds trace_capacity records; word 0 of the buffer is the record count.
@@ -494,25 +498,30 @@ __device__ __forceinline__ void lhs_pull_bulk_role(const FusedParams& p, uint32_
       pieces == 1 ? (int32_t(kPullStageBytes / shard_bytes) < kPullSubRows ? int32_t(kPullStageBytes / shard_bytes)
                                                                           : kPullSubRows)
                   : 1;
-  const int32_t subs_total = p.order.m_tiles * r.world * kPullSubsPerTile;
+  // A sub-unit is at most two chunks, so that the first units the GEMM waits for are spread
+  // over every pull warp (wide rows: a few rows; 1 KiB rows: 32 rows).
+  int32_t sub_rows = 2 * rows_per_chunk < kPullSubRows ? 2 * rows_per_chunk : kPullSubRows;
+  while (kBlockM % sub_rows != 0) --sub_rows;
+  const int32_t subs_per_tile = kBlockM / sub_rows;
+  const int32_t subs_total = p.order.m_tiles * r.world * subs_per_tile;
   const int32_t row_block = r.causal ? r.seq_local / 2 : r.seq_local;  // rows consecutive at the source
   const int64_t dst_pitch = r.lda * r.element_bytes;
 
   // Positions `c` on the first sub-unit at or after c.sub that has rows; false past the end.
   auto seek = [&](PullCursor& c) {
     for (; c.sub < subs_total; c.sub += workers) {
-      const int32_t unit = c.sub / kPullSubsPerTile, quarter = c.sub - unit * kPullSubsPerTile;
+      const int32_t unit = c.sub / subs_per_tile, quarter = c.sub - unit * subs_per_tile;
       const int32_t mt = unit / r.world, shard = unit - mt * r.world;
       const int32_t rows_in_unit = p.m - mt * kBlockM < kBlockM ? p.m - mt * kBlockM : kBlockM;
-      const int32_t row0 = quarter * kPullSubRows;
+      const int32_t row0 = quarter * sub_rows;
       if (row0 >= rows_in_unit) continue;
-      c.rows = rows_in_unit - row0 < kPullSubRows ? rows_in_unit - row0 : kPullSubRows;
+      c.rows = rows_in_unit - row0 < sub_rows ? rows_in_unit - row0 : sub_rows;
       c.row = mt * kBlockM + row0;
       c.chunk = 0;
       c.data_chunks = ((c.rows + rows_per_chunk - 1) / rows_per_chunk) * pieces;
       c.chunks = c.data_chunks + (quarter == 0 ? scale_chunks : 0);
       c.flag = unit;
-      c.needed = (rows_in_unit + kPullSubRows - 1) / kPullSubRows;
+      c.needed = (rows_in_unit + sub_rows - 1) / sub_rows;
       c.peer = r.cyclic ? (r.rank + shard) % r.world : shard;
       c.contiguous = (c.row % row_block) + c.rows <= row_block;
       c.src = reinterpret_cast<const uint8_t*>(r.peer_input[c.peer]) +
@@ -1158,6 +1167,35 @@ __device__ __forceinline__ void mxfp8_quantize_rows(const uint16_t* source, int6
   }
 }
 
+// The tile sequence of one CTA: compute CTAs first take every compute_ctas-th tile below
+// join_tile, then every CTA of the grid (communication CTAs included) takes every
+// all_ctas-th tile from join_tile on.
+struct TileWalk {
+  int64_t t, join_tile, tiles;
+  int32_t compute_id, all_id, compute_ctas, all_ctas;
+  bool joined;
+  __device__ int64_t first() {
+    joined = compute_id < 0;
+    t = joined ? join_tile + all_id : compute_id;
+    if (!joined && t >= join_tile) {
+      joined = true;
+      t = join_tile + all_id;
+    }
+    return t < tiles ? t : -1;
+  }
+  __device__ int64_t next() {
+    if (!joined) {
+      t += compute_ctas;
+      if (t < join_tile) return t;
+      joined = true;
+      t = join_tile + all_id;
+    } else {
+      t += all_ctas;
+    }
+    return t < tiles ? t : -1;
+  }
+};
+
 // kAMn / kBMn: the operand is stored with its M (resp. N) axis contiguous -- [K, M] / [K, N]
 // row-major -- and is fed to the tensor core as an MN-major tile: 64-element groups along MN,
 // each a [64 K rows x 128 bytes] swizzled box (the data-gradient GEMMs read the forward weight
@@ -1193,9 +1231,9 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     }
   }
 
-  if (skip_role) {
-    // nothing: this launch runs the other role only
-  } else if (is_comm) {
+  constexpr bool kCommJoins = kMode == kModeLhsPull || kMode == kModeHeadGate || kMode == kModeGradPull;
+  const bool joins_compute = kCommJoins && is_comm && p.join_tile < p.order.count();
+  if (is_comm && !skip_role) {
     if constexpr (kMode == kModeQkvPush) qkv_push_role<kBlockN>(p, smem);
     if constexpr (kMode == kModeLhsPull) {
       if (p.flags & kFlagVectorPull) lhs_pull_role(p, smem);
@@ -1218,7 +1256,9 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         grad_pull_role(p);
       }
     }
-  } else {
+  }
+  if (joins_compute) __syncthreads();  // the transfer pipeline's shared memory is free again
+  if ((!is_comm || joins_compute) && !(p.flags & kFlagCommOnly)) {
     const uint32_t bar_base = base + Layout::kBarrierOffset;
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
@@ -1250,8 +1290,15 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     const uint32_t tmem_base = *tmem_slot;
 
     const int32_t compute_ctas = int32_t(gridDim.x) - p.num_comm_ctas;
-    const int32_t compute_id = int32_t(blockIdx.x) - p.num_comm_ctas;
+    const int32_t compute_id = int32_t(blockIdx.x) - p.num_comm_ctas;  // negative on communication CTAs
     const int64_t tiles = p.order.count();
+    TileWalk walk_template;
+    walk_template.join_tile = p.join_tile < tiles ? p.join_tile : tiles;
+    walk_template.tiles = tiles;
+    walk_template.compute_id = compute_id;
+    walk_template.all_id = compute_id >= 0 ? compute_id : compute_ctas + int32_t(blockIdx.x);
+    walk_template.compute_ctas = compute_ctas;
+    walk_template.all_ctas = int32_t(gridDim.x);
     constexpr int32_t kBlockElems = kMx ? 2 * kBlockK : kBlockK;  // K elements per 128-byte row
     const int32_t k_blocks = (p.k + kBlockElems - 1) / kBlockElems;
 
@@ -1261,7 +1308,8 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t stage = 0, phase = 0;
         uint32_t issued_mask = 0, issued_parity = 0;  // last armed phase per stage (for the drain)
         bool ok = true;
-        for (int64_t t = compute_id; ok && t < tiles; t += compute_ctas) {
+        TileWalk walk = walk_template;
+        for (int64_t t = walk.first(); ok && t >= 0; t = walk.next()) {
           int32_t mt, nt;
           p.order.decode(t, mt, nt);
           int32_t gated_upto = -1;  // highest K shard already acquired for this tile
@@ -1278,10 +1326,12 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
               if (last >= groups) last = groups - 1;
               while (ok && gated_upto < last) {
                 ++gated_upto;
+                trace_event(p, 10);  // gate wait begins
                 const int64_t flag = (int64_t(mt) * groups + gated_upto) * kReadyFlagStride;
                 ok = flag_wait<kRemoteWriter>(p.ready + flag, p.wait.epoch, p.wait, kSiteLhsReady,
                                               uint32_t(flag / kReadyFlagStride));
                 ptx::fence_proxy_async_global();
+                trace_event(p, 11);  // gate passed
               }
               if (!ok) break;
             }
@@ -1345,7 +1395,8 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t sf_parity = 0;
         (void)sf_parity;
         bool ok = true;
-        for (int64_t t = compute_id; ok && t < tiles; t += compute_ctas) {
+        TileWalk walk = walk_template;
+        for (int64_t t = walk.first(); ok && t >= 0; t = walk.next()) {
           ok = mbar_wait(tmem_empty_bar(accum), accum_phase ^ 1u, p.wait, kSiteTmemEmpty);
           if (!ok) break;
           ptx::tc_fence_after();
@@ -1408,7 +1459,8 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       constexpr int kChunks = kBlockN / 8;
       uint32_t table = 0;  // which of the two route tables this tile uses
       uint32_t staged_blocks = 0;  // 64-column blocks staged so far (selects the staging buffer)
-      for (int64_t t = compute_id; ok && t < tiles; t += compute_ctas) {
+      TileWalk walk = walk_template;
+      for (int64_t t = walk.first(); ok && t >= 0; t = walk.next()) {
         int32_t mt, nt;
         p.order.decode(t, mt, nt);
         PeerRow peer{};

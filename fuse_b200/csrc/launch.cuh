@@ -63,6 +63,40 @@ inline void fill_core(FusedParams* p, int m, int n, int k, int block_n, int num_
   p->beta = beta;
   p->d = static_cast<uint16_t*>(d);
   p->ldd = ldd;
+  p->join_tile = p->order.count();
+}
+
+// Host plan for the tail share of tiles that communication CTAs compute once their transfers are
+// done (pull and gradient modes).  Calibration on B200: one SM sustains about 10.3 TFLOP/s of
+// BF16 UMMA (17 TFLOP/s block-scaled E4M3) inside these kernels and one communication CTA moves
+// about 35 GB/s through its copy pipeline.  With tau the time of one tile and t_c the time the
+// transfers take, the plan tries every whole number of compute-only waves w1: the first
+// w1 * compute_ctas tiles go to the compute CTAs alone, the rest is dealt to the whole grid, and
+// the split with the smallest makespan max((w1 + w2) * tau, t_c + w2 * tau) wins, w2 being the
+// waves of the shared part.  FUSE_B200_JOIN_WAVES=0 keeps the communication CTAs out of the GEMM.
+inline void plan_join(FusedParams* p, int block_n, int sm_count, double comm_bytes, bool block_scaled) {
+  const int64_t tiles = p->order.count();
+  const int comm = p->num_comm_ctas;
+  if (comm <= 0 || tiles <= 0) return;
+  if (const char* text = std::getenv("FUSE_B200_JOIN_WAVES"))
+    if (std::atoll(text) == 0) return;
+  const int64_t compute = tiles < sm_count - comm ? tiles : sm_count - comm;
+  const int64_t all = comm + compute;
+  const double tau = 2.0 * kBlockM * block_n * double(p->k) / (block_scaled ? 17.0e12 : 10.3e12);
+  const double t_c = 25.0e-6 + comm_bytes / (comm * 35.0e9);
+  double best = double((tiles + compute - 1) / compute) * tau;  // no sharing
+  int64_t best_join = tiles;
+  for (int64_t w1 = 0; w1 * compute < tiles; ++w1) {
+    const int64_t join = w1 * compute, rest = tiles - join;
+    const int64_t w2 = (rest + all - 1) / all;
+    const double compute_side = double(w1 + w2) * tau, comm_side = t_c + double(w2) * tau;
+    const double makespan = compute_side > comm_side ? compute_side : comm_side;
+    if (makespan < best - 1.0e-9) {
+      best = makespan;
+      best_join = join;
+    }
+  }
+  p->join_tile = best_join;
 }
 
 template <int kMode, bool kTmaEpilogue, bool kAMn, bool kBMn, bool kMx = false, class Maps = StoreMaps>

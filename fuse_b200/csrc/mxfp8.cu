@@ -334,6 +334,7 @@ cudaError_t oproj_forward_mxfp8(const fuse_mxfp8_a2a_gemm_params& mp, const fuse
     f.lhs.peer_scales[peer] = mp.activation[peer].scales;
     f.lhs.peer_input_ready[peer] = p.peer_input_ready[peer];
   }
+  plan_join(&f, block_n, info.sm_count, double(g.m) * g.k * (1.0 + 1.0 / 32), true);
   StoreMaps stores{};
   return launch_mode<kModeLhsPull, false, false, true>(maps, stores, f, block_n, info, stream,
                                                        !vector_epilogue_requested(options));

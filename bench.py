@@ -40,9 +40,9 @@ FLOPS_PER_RANK = 2.0 * TOKENS_PER_RANK * HIDDEN * (QKV_N + OPROJ_K)
 QKV_FLOPS = 2.0 * TOKENS_PER_RANK * HIDDEN * QKV_N
 
 # DRAM bytes (read + write) of one launch of the dominant kernel (the fused QKV kernel at this
-# workload), from the ncu capture summarised in profiles/qkv_forward_c2_ncu.md; None until
-# such a capture exists.
-QKV_DRAM_TRAFFIC_BYTES = None
+# workload, context-parallel size 1, direct route), dram__bytes_read.sum + dram__bytes_write.sum
+# of the ncu capture summarised in profiles/fused_gemm_kernel_forward_c2_ncu.md.
+QKV_DRAM_TRAFFIC_BYTES = 836_608_768
 
 
 def measured_peaks():

@@ -335,6 +335,9 @@ SYMBOLS = {
     "fuse_launch_oproj_backward_mxfp8_data_ex": (C.c_int, [C.POINTER(Mxfp8OprojBackwardDataParams), C.POINTER(Options), _P]),
     "fuse_launch_oproj_backward_mxfp8_weight": (C.c_int, [C.POINTER(Mxfp8OprojBackwardWeightParams), _P]),
     "fuse_launch_oproj_backward_mxfp8": (C.c_int, [C.POINTER(Mxfp8OprojBackwardParams), _P]),
+    "fuse_a2a_gemm_mxfp8_workspace_size_for_params": (C.c_int, [C.POINTER(Mxfp8A2AGemmParams), C.POINTER(C.c_size_t)]),
+    "fuse_mxfp8_qkv_cutlass_kernel_traits": (None, [C.c_int32, C.POINTER(KernelTraits)]),
+    "fuse_mxfp8_oproj_cutlass_kernel_traits": (None, [C.c_int32, C.c_uint8, C.POINTER(KernelTraits)]),
     "fuse_qkv_cutlass_kernel_traits": (None, [C.POINTER(GemmProblem), C.POINTER(KernelTraits)]),
     "fuse_cutlass_kernel_traits": (None, [C.POINTER(KernelTraits)]),
     "fuse_a2a_lhs_gemm_ready_elements": (C.c_int64, [C.POINTER(GemmProblem), C.POINTER(UlyssesRoute)]),

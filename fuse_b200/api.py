@@ -198,10 +198,29 @@ def a2a_gemm_mxfp8_activation_size(problem: GemmProblem, route: UlyssesRoute):
     return rc, data.value, scales.value
 
 
-def a2a_gemm_mxfp8_workspace_size(problem: GemmProblem):
+def a2a_gemm_mxfp8_workspace_size(problem):
+    """Both reference overloads (include/fuse/operators/primitives/a2a_gemm_mxfp8.h:50-51): a
+    GemmProblem or a whole Mxfp8A2AGemmParams record."""
     size = C.c_size_t()
-    rc = N.lib().fuse_a2a_gemm_mxfp8_workspace_size(C.byref(problem), C.byref(size))
+    if isinstance(problem, Mxfp8A2AGemmParams):
+        rc = N.lib().fuse_a2a_gemm_mxfp8_workspace_size_for_params(C.byref(problem), C.byref(size))
+    else:
+        rc = N.lib().fuse_a2a_gemm_mxfp8_workspace_size(C.byref(problem), C.byref(size))
     return rc, size.value
+
+
+def mxfp8_qkv_cutlass_kernel_traits(epilogue_n: int = 64) -> KernelTraits:
+    """include/fuse/operators/primitives/gemm_a2a_mxfp8.h:41."""
+    out = KernelTraits()
+    N.lib().fuse_mxfp8_qkv_cutlass_kernel_traits(epilogue_n, C.byref(out))
+    return out
+
+
+def mxfp8_oproj_cutlass_kernel_traits(epilogue_n: int = 32, overlap_postnorm: bool = False) -> KernelTraits:
+    """include/fuse/operators/primitives/a2a_gemm_mxfp8.h:52."""
+    out = KernelTraits()
+    N.lib().fuse_mxfp8_oproj_cutlass_kernel_traits(epilogue_n, int(overlap_postnorm), C.byref(out))
+    return out
 
 
 def a2a_gemm_mxfp8_staging_view(params: Mxfp8A2AGemmParams) -> Mxfp8Activation:

@@ -426,6 +426,22 @@ int fuse_a2a_gemm_mxfp8_workspace_size(const fuse_gemm_problem* g, size_t* bytes
   *bytes = lhs_scratch(*g, nullptr).bytes;
   return 0;
 }
+int fuse_a2a_gemm_mxfp8_workspace_size_for_params(const fuse_mxfp8_a2a_gemm_params* p, size_t* bytes) {
+  if (p == nullptr) return int(cudaErrorInvalidValue);
+  return fuse_a2a_gemm_mxfp8_workspace_size(&p->projection.gemm, bytes);
+}
+static void mx_traits(int32_t epilogue_n, fuse_kernel_traits* out) {
+  if (out == nullptr) return;
+  *out = {};
+  if (epilogue_n != 32 && epilogue_n != 64) return;
+  using Layout = fuse_b200::SmemLayout<256, 4, true>;
+  *out = {fuse_b200::kBlockM, 256, 128, fuse_b200::kThreads, int32_t(Layout::kDynamicBytes)};
+}
+void fuse_mxfp8_qkv_cutlass_kernel_traits(int32_t epilogue_n, fuse_kernel_traits* out) { mx_traits(epilogue_n, out); }
+void fuse_mxfp8_oproj_cutlass_kernel_traits(int32_t epilogue_n, uint8_t overlap_postnorm, fuse_kernel_traits* out) {
+  (void)overlap_postnorm;
+  mx_traits(epilogue_n, out);
+}
 int fuse_a2a_gemm_mxfp8_staging_view(const fuse_mxfp8_a2a_gemm_params* p, fuse_mxfp8_activation* out) {
   if (p == nullptr || out == nullptr || p->workspace == nullptr) return int(cudaErrorInvalidValue);
   const LhsScratch w = lhs_scratch(p->projection.gemm, p->workspace);

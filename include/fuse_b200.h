@@ -387,6 +387,16 @@ typedef struct fuse_mxfp8_a2a_gemm_params {
 FUSE_API int fuse_a2a_gemm_mxfp8_activation_size(const fuse_gemm_problem* problem, const fuse_ulysses_route* route,
                                         size_t* data_bytes, size_t* scale_bytes);
 FUSE_API int fuse_a2a_gemm_mxfp8_workspace_size(const fuse_gemm_problem* problem, size_t* bytes);
+/* a2a_gemm_mxfp8.h:51: the overload that takes the whole parameter record (same answer for
+ * params->projection.gemm; C has no overloads, hence the suffix). */
+FUSE_API int fuse_a2a_gemm_mxfp8_workspace_size_for_params(const fuse_mxfp8_a2a_gemm_params* params, size_t* bytes);
+/* gemm_a2a_mxfp8.h:41 and a2a_gemm_mxfp8.h:52: tile geometry of the block-scaled kernels (for
+ * sizing `ready`).  epilogue_n and overlap_postnorm select among the reference's kernel
+ * instances; this library has one tile shape per operand type, so both are accepted and
+ * ignored (values outside {32, 64} leave *out zeroed, as the reference returns {}). */
+FUSE_API void fuse_mxfp8_qkv_cutlass_kernel_traits(int32_t epilogue_n, fuse_kernel_traits* out);
+FUSE_API void fuse_mxfp8_oproj_cutlass_kernel_traits(int32_t epilogue_n, uint8_t overlap_postnorm,
+                                                     fuse_kernel_traits* out);
 FUSE_API int fuse_a2a_gemm_mxfp8_staging_view(const fuse_mxfp8_a2a_gemm_params* params, fuse_mxfp8_activation* activation);
 FUSE_API int fuse_launch_a2a_gemm_mxfp8_cutlass(const fuse_mxfp8_a2a_gemm_params* params, fuse_stream stream);
 FUSE_API int fuse_launch_a2a_gemm_mxfp8_cutlass_ex(const fuse_mxfp8_a2a_gemm_params* params,

@@ -73,6 +73,21 @@ def test_ready_sizes():
     assert api.a2a_lhs_gemm_ready_elements(N.GemmProblem(130, 4096, 4096), route) == 2 * 8 * 32
 
 
+def test_mxfp8_traits_and_workspace_overloads():
+    for traits in (api.mxfp8_qkv_cutlass_kernel_traits(64), api.mxfp8_qkv_cutlass_kernel_traits(32),
+                   api.mxfp8_oproj_cutlass_kernel_traits(32, False), api.mxfp8_oproj_cutlass_kernel_traits(64, True)):
+        assert (traits.block_m, traits.block_n, traits.block_k, traits.threads) == (128, 256, 128, 256)
+        assert 114 * 1024 < traits.dynamic_smem_bytes <= 227 * 1024
+    # the reference returns an empty record for an epilogue width it has no kernel for
+    assert api.mxfp8_qkv_cutlass_kernel_traits(48).block_m == 0
+    prob = N.GemmProblem(4096, 8192, 8192)
+    params = N.Mxfp8A2AGemmParams()
+    params.projection.gemm = prob
+    by_problem = api.a2a_gemm_mxfp8_workspace_size(prob)
+    assert by_problem[0] == 0 and by_problem[1] > 0
+    assert api.a2a_gemm_mxfp8_workspace_size(params) == by_problem
+
+
 def test_tile_order_is_a_bijection_and_bands_are_compact():
     lib = N.lib()
     for (mt, nt) in [(1, 1), (7, 5), (128, 24), (16, 3), (3, 16), (9, 9)]:

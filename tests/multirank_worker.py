@@ -179,6 +179,151 @@ def main():
         assert ok, ("moe", e, worst, bad)
     assert api.destroy_bf16_grouped_gemm(plan) == 0
     dist.barrier()
+
+    # ---- MXFP8 output projection: bytes and scale bytes pulled from every peer ------------------
+    to_dev_u8 = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
+    shard = ko // world
+    mx_n = 512
+    quant = [O.mxfp8_quantize(a) for a in attn_all]
+    wmx = synthetic.normal_bf16((mx_n, ko), synthetic.BASE_SEED + 17, 0.02)
+    want_wq, want_wsf = O.mxfp8_quantize(wmx)
+    xsym = w.allocate({"mx_data": rows * shard, "mx_scales": len(quant[0][1])})
+    xsym["mx_data"].local.copy_(to_dev_u8(quant[rank][0]).reshape(-1))
+    xsym["mx_scales"].local.copy_(to_dev_u8(quant[rank][1]))
+    wmx_d = to_dev(wmx)
+    mx_problem = N.GemmProblem(m, mx_n, ko, max_swizzle_size=8)
+    rc, ws_bytes = api.a2a_gemm_mxfp8_workspace_size(mx_problem)
+    assert rc == 0
+    scratch = torch.full((ws_bytes + 256,), 0x5A, dtype=torch.uint8, device=dev)
+    base = (scratch.data_ptr() + 255) // 256 * 256
+    mx_out = torch.full((m, mx_n), -1, dtype=torch.int16, device=dev).view(torch.bfloat16)
+    mproj = N.A2AGemmParams(rhs_nt=wmx_d.data_ptr(), output=mx_out.data_ptr(), gemm=mx_problem, route=o_route,
+                            num_comm_ctas=8, epoch=1)
+    mxp = N.Mxfp8A2AGemmParams(projection=mproj, workspace=base, workspace_bytes=ws_bytes)
+    for r in range(world):
+        mxp.activation[r] = N.Mxfp8Activation(data=xsym["mx_data"].peer_ptrs[r], scales=xsym["mx_scales"].peer_ptrs[r],
+                                              data_bytes=rows * shard, scale_bytes=len(quant[0][1]))
+    torch.cuda.synchronize()
+    dist.barrier()
+    assert api.launch_a2a_gemm_mxfp8_cutlass(mxp, 0, opts) == 0
+    torch.cuda.synchronize()
+    status = api.read_status()
+    assert status[0] == 0, status[:8]
+    want_data = np.empty((m, ko), dtype=np.uint8)
+    want_scales = np.zeros(O.lib().fo_mxfp8_scale_bytes(m, ko), dtype=np.uint8)
+    for row in range(m):
+        src_row = O.lib().fo_global_row(world, rank, s, 0, row)
+        for j in range(world):
+            want_data[row, j * shard:(j + 1) * shard] = quant[j][0][src_row]
+            for kk in range(0, shard, 32):
+                want_scales[O.lib().fo_mxfp8_scale_offset(row, j * shard + kk, ko)] = \
+                    quant[j][1][O.lib().fo_mxfp8_scale_offset(src_row, kk, shard)]
+    view = api.a2a_gemm_mxfp8_staging_view(mxp)
+    off = view.data - scratch.data_ptr()
+    assert np.array_equal(scratch[off:off + m * ko].cpu().numpy().reshape(m, ko), want_data), "mxfp8 gathered bytes"
+    soff = view.scales - scratch.data_ptr()
+    assert np.array_equal(scratch[soff:soff + view.scale_bytes].cpu().numpy(), want_scales), "mxfp8 gathered scales"
+    ok, worst, bad = O.within_tolerance(bits(mx_out), O.gemm_mxfp8(want_data, want_scales, want_wq, want_wsf))
+    assert ok, ("mxfp8 oproj", worst, bad)
+    dist.barrier()
+
+    # ---- MXFP8 QKV backward data: quantised gradients, scale atoms and BF16 masters pulled -------
+    planes_q = [tuple(O.mxfp8_quantize(pl) for pl in planes_all[r]) for r in range(world)]
+    names = ("q", "k", "v")
+    spec = {}
+    for seg, name in enumerate(names):
+        spec[f"g{name}_data"] = planes_q[0][seg][0].size
+        spec[f"g{name}_scales"] = planes_q[0][seg][1].size
+        spec[f"g{name}_master"] = planes_all[0][seg].size * 2
+    spec["mxb_done"] = world * N.READY_FLAG_STRIDE * 4
+    gsym = w.allocate(spec)
+    for seg, name in enumerate(names):
+        gsym[f"g{name}_data"].local.copy_(to_dev_u8(planes_q[rank][seg][0]).reshape(-1))
+        gsym[f"g{name}_scales"].local.copy_(to_dev_u8(planes_q[rank][seg][1]))
+        gsym[f"g{name}_master"].view(torch.bfloat16).copy_(to_dev(planes_all[rank][seg]).reshape(-1))
+    mx_staging = torch.full((m, n), -1, dtype=torch.int16, device=dev).view(torch.bfloat16)
+    mx_dx = torch.full((m, hidden), -1, dtype=torch.int16, device=dev).view(torch.bfloat16)
+    bproj = N.QkvBackwardDataParams(weight=wb_d.data_ptr(), grad_input=mx_dx.data_ptr(), local_tokens=m, hidden=hidden,
+                                    batch=batch, q_heads=q, kv_heads=kv, head_dim=d, world_size=world, rank=rank,
+                                    num_comm_ctas=8, epoch=1, alpha=1.0)
+    bproj.gemm_tuning.max_swizzle_size = 4
+    mx_ready = torch.zeros(api.qkv_backward_ready_elements(bproj), dtype=torch.int32, device=dev)
+    bproj.peer_dqkv_staging[rank] = mx_staging.data_ptr()
+    bproj.peer_ready[rank] = mx_ready.data_ptr()
+    for r in range(world):
+        bproj.peer_done_epoch[r] = gsym["mxb_done"].peer_ptrs[r]
+    rc, ws_bytes = api.qkv_backward_mxfp8_data_workspace_size(bproj)
+    assert rc == 0
+    scratch2 = torch.full((ws_bytes + 256,), 0x5A, dtype=torch.uint8, device=dev)
+    mbp = N.Mxfp8QkvBackwardDataParams(projection=bproj, workspace=(scratch2.data_ptr() + 255) // 256 * 256,
+                                       workspace_bytes=ws_bytes)
+    act = lambda r, name, seg: N.Mxfp8Activation(
+        data=gsym[f"g{name}_data"].peer_ptrs[r], scales=gsym[f"g{name}_scales"].peer_ptrs[r],
+        data_bytes=planes_q[0][seg][0].size, scale_bytes=planes_q[0][seg][1].size)
+    for r in range(world):
+        mbp.peer_input[r] = N.Mxfp8QkvBackwardInput(
+            grad_q=act(r, "q", 0), grad_k=act(r, "k", 1), grad_v=act(r, "v", 2),
+            master_q=gsym["gq_master"].peer_ptrs[r], master_k=gsym["gk_master"].peer_ptrs[r],
+            master_v=gsym["gv_master"].peer_ptrs[r])
+    torch.cuda.synchronize()
+    dist.barrier()
+    assert api.launch_qkv_backward_mxfp8_data(mbp, 0, opts) == 0
+    torch.cuda.synchronize()
+    status = api.read_status()
+    assert status[0] == 0, status[:8]
+    assert np.array_equal(bits(mx_staging), want_staging), "mxfp8 backward: routed BF16 masters"
+    import ctypes as C
+    packed = np.empty((m, n), dtype=np.uint8)
+    packed_s = np.zeros(O.lib().fo_mxfp8_scale_bytes(m, n), dtype=np.uint8)
+    owner, seg_out, off_out = C.c_int32(), C.c_int32(), C.c_int64()
+    for row in range(m):
+        for head in range(q + 2 * kv):
+            O.lib().fo_qkv_backward_source(world, rank, s, q, kv, d, 0, row, head * d, C.byref(owner), C.byref(seg_out),
+                                           C.byref(off_out))
+            data, scales = planes_q[owner.value][seg_out.value]
+            pw = data.shape[1]
+            src_row, src_col = off_out.value // pw, off_out.value % pw
+            packed[row, head * d:(head + 1) * d] = data[src_row, src_col:src_col + d]
+            for kk in range(0, d, 32):
+                packed_s[O.lib().fo_mxfp8_scale_offset(row, head * d + kk, n)] = \
+                    scales[O.lib().fo_mxfp8_scale_offset(src_row, src_col + kk, pw)]
+    wt_q, wt_s = O.mxfp8_quantize_transposed(wb)
+    ok, worst, bad = O.within_tolerance(bits(mx_dx), O.gemm_mxfp8(packed, packed_s, wt_q, wt_s))
+    assert ok, ("mxfp8 dX", worst, bad)
+    dist.barrier()
+
+    # ---- BF16 output-projection backward: dA = dY Wo, pushed sequence -> head to every peer ------
+    ob_hidden = 256
+    dys = [synthetic.normal_bf16((m, ob_hidden), synthetic.rank_seed(r) + 301, 0.01) for r in range(world)]
+    wob = synthetic.normal_bf16((ob_hidden, ko), synthetic.BASE_SEED + 17, 0.02)
+    osym = w.allocate({"ob_routed": rows * (ko // world) * 2, "ob_done": world * N.READY_FLAG_STRIDE * 4})
+    osym["ob_routed"].view(torch.int16).fill_(-1)
+    dy_d, wob_d = to_dev(dys[rank]), to_dev(wob)
+    da = torch.full((m, ko), -1, dtype=torch.int16, device=dev).view(torch.bfloat16)
+    obp = N.OprojBackwardDataParams(grad_output=dy_d.data_ptr(), weight=wob_d.data_ptr(),
+                                    local_grad_attention=da.data_ptr(), local_tokens=m, hidden=ob_hidden, batch=batch,
+                                    q_heads=q, head_dim=d, world_size=world, rank=rank, num_comm_ctas=8, epoch=1,
+                                    alpha=1.0)
+    obp.gemm_tuning.max_swizzle_size = 4
+    ob_ready = torch.zeros(api.oproj_backward_ready_elements(obp), dtype=torch.int32, device=dev)
+    obp.ready = ob_ready.data_ptr()
+    for r in range(world):
+        obp.peer_grad_attention[r] = osym["ob_routed"].peer_ptrs[r]
+        obp.peer_done_epoch[r] = osym["ob_done"].peer_ptrs[r]
+    torch.cuda.synchronize()
+    dist.barrier()
+    assert api.launch_oproj_backward_data(obp, 0, opts) == 0
+    torch.cuda.synchronize()
+    status = api.read_status()
+    assert status[0] == 0, status[:8]
+    want_da, want_routed, _ = O.oproj_backward(world, batch, s, q, d, dys, wob,
+                                               [np.zeros((m, ko), dtype=np.uint16)] * world)
+    ok, worst, bad = O.within_tolerance(bits(da), want_da[rank], 0.02, 0.02)
+    assert ok, ("dA", worst, bad)
+    ok, worst, bad = O.within_tolerance(bits(osym["ob_routed"].view(torch.bfloat16)), want_routed[rank].reshape(-1),
+                                        0.02, 0.02)
+    assert ok, ("routed dA", worst, bad)
+    dist.barrier()
     w.close()
     dist.destroy_process_group()
     print(f"MULTIRANK PASS rank {rank}/{world} route={route_mode}", flush=True)

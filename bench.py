@@ -45,6 +45,18 @@ QKV_FLOPS = 2.0 * TOKENS_PER_RANK * HIDDEN * QKV_N
 QKV_DRAM_TRAFFIC_BYTES = 836_608_768
 
 
+_RESULT_FD = None
+
+
+def emit(line: dict) -> None:
+    data = (json.dumps(line) + "\n").encode()
+    if _RESULT_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_RESULT_FD, data)
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -113,7 +125,7 @@ def run_reference_arm(args):
         "e2e": {"value": value, "unit": "PFLOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def workload_config(n_gpus):
@@ -130,12 +142,30 @@ def workload_config(n_gpus):
 # --------------------------------------------------------------------------------------------
 
 class ClockSampler:
+    """Reads (never sets) SM clock, power and clock-event reasons of one GPU every 2 ms through
+    NVML while the timed region runs, so that even a 50 ms region gets a few dozen samples;
+    falls back to an `nvidia-smi -lms` child when the NVML python module is missing."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
+                   "sw_power_cap": 0x4}
 
     def __init__(self, uuid: str | None):
-        self.samples, self.proc, self.thread = [], None, None
+        self.samples, self.proc, self.thread, self.nvml, self.handle = [], None, None, None, None
+        self.stop_flag = threading.Event()
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.handle = (pynvml.nvmlDeviceGetHandleByUUID(uuid.encode() if hasattr(uuid, "encode") else uuid)
+                           if uuid else pynvml.nvmlDeviceGetHandleByIndex(0))
+            self.smax = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.nvml = pynvml
+            self.thread = threading.Thread(target=self._poll, daemon=True)
+            self.thread.start()
+            return
+        except Exception:  # noqa: BLE001 - any NVML problem selects the fallback
+            self.nvml = None
         cmd = ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50"]
         if uuid:
             cmd += ["-i", uuid]
@@ -146,31 +176,51 @@ class ClockSampler:
         except OSError:
             self.proc = None
 
+    def _poll(self):
+        nv = self.nvml
+        while not self.stop_flag.is_set():
+            try:
+                sm = float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+                self.samples.append((time.perf_counter(), (sm, self.smax, mask)))
+            except Exception:  # noqa: BLE001
+                pass
+            time.sleep(0.002)
+
     def _read(self):
         for line in self.proc.stdout:
             self.samples.append((time.perf_counter(), line.strip()))
 
     def stop(self, t0, t1):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.12)
-        self.proc.terminate()
-        rows = [s for (t, s) in self.samples if t0 - 0.05 <= t <= t1 + 0.05] or [s for (_, s) in self.samples]
-        sm, smax, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for row in rows:
-            cells = [c.strip() for c in row.split(",")]
-            try:
-                sm.append(float(cells[0]))
-                smax.append(float(cells[1]))
-            except (ValueError, IndexError):
-                continue
-            for name, cell in zip(names, cells[3:7]):
-                if cell == "Active":
-                    reasons.add(name)
+        sm, smax, reasons = [], [], set()
+        if self.nvml is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=1.0)
+            rows = [s for (t, s) in self.samples if t0 <= t <= t1] or [s for (_, s) in self.samples[-3:]]
+            for clock, top, mask in rows:
+                sm.append(clock)
+                smax.append(top)
+                reasons.update(name for name in names if mask & self.REASON_BITS[name])
+            source = "nvml"
+        elif self.proc is not None:
+            time.sleep(0.12)
+            self.proc.terminate()
+            rows = [s for (t, s) in self.samples if t0 - 0.05 <= t <= t1 + 0.05] or [s for (_, s) in self.samples]
+            for row in rows:
+                cells = [c.strip() for c in row.split(",")]
+                try:
+                    sm.append(float(cells[0]))
+                    smax.append(float(cells[1]))
+                except (ValueError, IndexError):
+                    continue
+                reasons.update(name for name, cell in zip(names, cells[3:7]) if cell == "Active")
+            source = "nvidia-smi"
+        else:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no clock source available"]}
         sm.sort()
         return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(smax) if smax else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "source": source}
 
 
 # --------------------------------------------------------------------------------------------
@@ -405,7 +455,7 @@ def run_gpu_arm(args):
             cpu_s = (time.perf_counter() - tc) / reps
             line["cpu_baseline"] = {"value": flops / cpu_s / 1e15, "unit": "PFLOPS", "cores": cores,
                                     "kind": "port", "sample": sample}
-        print(json.dumps(line), flush=True)
+        emit(line)
     barrier()
     world.close()
     if world_size > 1:
@@ -429,6 +479,12 @@ def main():
     parser.add_argument("--skip-pure", action="store_true")
     args = parser.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl != "reference" else args.warmup
+    # Standard output carries the one JSON line and nothing else: whatever libraries print there
+    # (NCCL's version banner, for one) goes to standard error instead.
+    global _RESULT_FD
+    sys.stdout.flush()
+    _RESULT_FD = os.dup(1)
+    os.dup2(2, 1)
     if args.impl == "reference":
         run_reference_arm(args)
     else:

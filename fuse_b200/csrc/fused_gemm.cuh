@@ -1279,6 +1279,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         ptx::mbar_init(tmem_empty_bar(s), kEpilogueThreads);
       }
       ptx::fence_mbar_init();
+      *reinterpret_cast<volatile uint32_t*>(smem + Layout::kTmemSlotOffset + 8) = 0u;  // gate progress
     }
     if (warp == 2) {
       ptx::tmem_alloc(base + Layout::kTmemSlotOffset, kTmemColumns);
@@ -1300,6 +1301,11 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     walk_template.compute_ctas = compute_ctas;
     walk_template.all_ctas = int32_t(gridDim.x);
     constexpr int32_t kBlockElems = kMx ? 2 * kBlockK : kBlockK;  // K elements per 128-byte row
+    constexpr bool kGated = kMode == kModeLhsPull || kMode == kModeHeadGate || kMode == kModeGradPull;
+    // Gate progress word: (tiles this CTA has walked) * kGateSeqStep + complete groups of the current one.
+    constexpr uint32_t kGateSeqStep = 65536u;
+    const uint32_t gate_word = base + Layout::kTmemSlotOffset + 8u;
+    (void)gate_word;
     const int32_t k_blocks = (p.k + kBlockElems - 1) / kBlockElems;
 
     if (warp == 0) {
@@ -1309,29 +1315,28 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t issued_mask = 0, issued_parity = 0;  // last armed phase per stage (for the drain)
         bool ok = true;
         TileWalk walk = walk_template;
-        for (int64_t t = walk.first(); ok && t >= 0; t = walk.next()) {
+        uint32_t tile_seq = 0;
+        for (int64_t t = walk.first(); ok && t >= 0; t = walk.next(), ++tile_seq) {
           int32_t mt, nt;
           p.order.decode(t, mt, nt);
-          int32_t gated_upto = -1;  // highest K shard already acquired for this tile
+          int32_t gated_upto = -1;  // highest K group already acquired for this tile
           for (int32_t kb = 0; kb < k_blocks; ++kb) {
-            if constexpr (kMode == kModeLhsPull || kMode == kModeHeadGate || kMode == kModeGradPull) {
-              // K groups whose rows arrive separately: peers' shards (forward pull, flags set by
-              // this GPU's communication CTAs) or Q/K/V heads (backward, flags set by the
-              // sending GPUs at system scope).
-              constexpr bool kRemoteWriter = kMode == kModeHeadGate;
+            if constexpr (kGated) {
+              // K groups whose rows arrive separately: peers' shards (forward pull) or Q/K/V heads
+              // (backward).  The gate scout (warp 3) polls the flags, 32 at a time and ahead of
+              // this thread, and posts how far this tile's groups are complete.
               constexpr bool kHeads = kMode != kModeLhsPull;
               const int32_t group_width = kHeads ? p.grad.head_dim : p.lhs.shard_width;
               const int32_t groups = kHeads ? p.grad.q_heads + 2 * p.grad.kv_heads : p.lhs.world;
               int32_t last = (kb * kBlockElems + kBlockElems - 1) / group_width;
               if (last >= groups) last = groups - 1;
-              while (ok && gated_upto < last) {
-                ++gated_upto;
+              if (gated_upto < last) {
                 trace_event(p, 10);  // gate wait begins
-                const int64_t flag = (int64_t(mt) * groups + gated_upto) * kReadyFlagStride;
-                ok = flag_wait<kRemoteWriter>(p.ready + flag, p.wait.epoch, p.wait, kSiteLhsReady,
-                                              uint32_t(flag / kReadyFlagStride));
+                ok = progress_wait(gate_word, tile_seq * kGateSeqStep + uint32_t(last) + 1u, p.wait, kSiteLhsReady,
+                                   uint32_t(mt * groups + last));
                 ptx::fence_proxy_async_global();
                 trace_event(p, 11);  // gate passed
+                gated_upto = last;
               }
               if (!ok) break;
             }
@@ -1376,6 +1381,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           }
           (void)gated_upto;
         }
+        (void)tile_seq;
         if (!ok) {
           // Unwinding: let every copy this thread started land before shared memory goes away.
           for (int s = 0; s < kStages; ++s)
@@ -1448,6 +1454,60 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           mbar_wait(tmem_full_bar(accum), accum_phase, p.wait, kSiteDrain, false);
         }
       }
+    } else if (warp == 3) {
+      // ------------------------------------------------------------------ gate scout
+      // Walks this CTA's tiles in the producer's order; every lane acquires one group's flag of
+      // the current tile, the complete prefix is posted to shared memory for the producer.  The
+      // scout runs ahead of the producer, so in steady state the producer never sees flag latency.
+      if constexpr (kGated) {
+        constexpr bool kRemoteWriter = kMode == kModeHeadGate;  // flags released by the sending GPUs
+        constexpr bool kHeads = kMode != kModeLhsPull;
+        const int32_t groups = kHeads ? p.grad.q_heads + 2 * p.grad.kv_heads : p.lhs.world;
+        TileWalk walk = walk_template;
+        uint32_t tile_seq = 0;
+        bool ok = true;
+        for (int64_t t = walk.first(); ok && t >= 0; t = walk.next(), ++tile_seq) {
+          int32_t mt, nt;
+          p.order.decode(t, mt, nt);
+          const uint32_t* flags = p.ready + int64_t(mt) * groups * kReadyFlagStride;
+          int32_t prefix = 0;
+          uint32_t spin = 0;
+          uint64_t start = 0;
+          while (prefix < groups) {
+            // while stalled only the next few flags are polled
+            const int32_t g = prefix + lane;
+            uint32_t seen = 0u;
+            if (g < groups && (spin == 0u || lane < 4)) {
+              const uint32_t* flag = flags + int64_t(g) * kReadyFlagStride;
+              seen = kRemoteWriter ? ptx::ld_acquire_sys(flag) : ptx::ld_acquire_gpu(flag);
+            }
+            const uint32_t complete = __ballot_sync(0xffffffffu, seen >= p.wait.epoch);
+            const int32_t n = complete == 0xffffffffu ? 32 : __ffs(int(~complete)) - 1;
+            if (n > 0) {
+              prefix = prefix + n < groups ? prefix + n : groups;
+              __syncwarp();  // every lane's acquire is ordered before the release below
+              if (lane == 0) ptx::st_release_cta_shared(gate_word, tile_seq * kGateSeqStep + uint32_t(prefix));
+              spin = 0u;
+              continue;
+            }
+            if (spin == 0u) start = ptx::globaltimer();
+            __nanosleep(64);
+            if ((++spin & 15u) == 0u) {
+              uint32_t stop = 0u;
+              if (lane == 0) {
+                if (aborted(p.wait)) {
+                  stop = 1u;
+                } else if (ptx::globaltimer() - start > p.wait.budget_ns) {
+                  report_timeout(p.wait, kRemoteWriter ? kStatusPeerTimeout : kStatusFlagTimeout, kSiteLhsReady,
+                                 uint32_t(mt * groups + prefix), seen, p.wait.epoch);
+                  stop = 1u;
+                }
+              }
+              if (__shfl_sync(0xffffffffu, stop, 0)) { ok = false; break; }
+            }
+          }
+        }
+      }
     } else if (warp >= 4) {
       // ------------------------------------------------------------------ epilogue
       const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
@@ -1498,44 +1558,88 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           // them: one tensor store into the local output and, for the direct QKV push, one into
           // the owning peer's planar tensor (full-line writes over NVLink).
           const int32_t row_in_tile = quarter * 32 + lane;
-#pragma unroll 1
-          for (int c = 0; c < kBlockN; c += 64) {
-            const uint32_t staging =
-                base + Layout::kStagingOffset + (staged_blocks % Layout::kStagingBuffers) * Layout::kStagingBlockBytes;
-            ++staged_blocks;
-            // the block that last used this staging buffer has been read out by its tensor stores
-            if (epi_tid == 0) ptx::bulk_wait_read<Layout::kStagingBuffers - 1>();
-            ptx::named_bar_sync(1, kEpilogueThreads);
-            uint32_t acc0[32], acc1[32];
-            ptx::tmem_ld_32x32b_x32(taddr + c, acc0);
-            ptx::tmem_ld_32x32b_x32(taddr + c + 32, acc1);
-            ptx::tmem_wait_ld();
-            if (c + 64 >= kBlockN) {
-              ptx::tc_fence_before();
-              ptx::mbar_arrive(tmem_empty_bar(accum));
-            }
-            const uint32_t row_addr = staging + uint32_t(row_in_tile) * 128u;
-            stage_accumulators(acc0, row_addr, 0, row_in_tile, p.alpha);
-            stage_accumulators(acc1, row_addr, 4, row_in_tile, p.alpha);
-            ptx::fence_proxy_async_shared();
-            ptx::named_bar_sync(1, kEpilogueThreads);
-            if (epi_tid == 0) {
-              const int32_t col = nt * kBlockN + c;
-              if (col < p.n) {
-                ptx::tma_store_2d(&store_maps.local, staging, col, mt * kBlockM);
-                if constexpr (kMode == kModeQkvDirect) {
-                  const QkvRoute& r = p.qkv;
-                  const int32_t q_width = r.q_heads * r.head_dim, kv_width = r.kv_heads * r.head_dim;
-                  const int32_t segment = col < q_width ? 0 : (col < q_width + kv_width ? 1 : 2);
-                  const int32_t within = col - (segment == 0 ? 0 : q_width + (segment == 2 ? kv_width : 0));
-                  const int32_t local_width = (segment == 0 ? q_width : kv_width) / r.world;
-                  const int32_t owner = within / local_width;  // segment > 0 only when kv_heads > 0
-                  ptx::tma_store_2d(&store_maps.peer[owner][segment], staging, within - owner * local_width,
-                                    int32_t(global_row(r.world, r.rank, r.seq_local, r.global_seq,
-                                                       r.causal != 0, mt * kBlockM)));
-                }
+          // One thread hands a staged 64-column block to the copy engine.
+          auto issue_stores = [&](int c, uint32_t staging) {
+            const int32_t col = nt * kBlockN + c;
+            if (col < p.n) {
+              ptx::tma_store_2d(&store_maps.local, staging, col, mt * kBlockM);
+              if constexpr (kMode == kModeQkvDirect) {
+                const QkvRoute& r = p.qkv;
+                const int32_t q_width = r.q_heads * r.head_dim, kv_width = r.kv_heads * r.head_dim;
+                const int32_t segment = col < q_width ? 0 : (col < q_width + kv_width ? 1 : 2);
+                const int32_t within = col - (segment == 0 ? 0 : q_width + (segment == 2 ? kv_width : 0));
+                const int32_t local_width = (segment == 0 ? q_width : kv_width) / r.world;
+                const int32_t owner = within / local_width;  // segment > 0 only when kv_heads > 0
+                ptx::tma_store_2d(&store_maps.peer[owner][segment], staging, within - owner * local_width,
+                                  int32_t(global_row(r.world, r.rank, r.seq_local, r.global_seq,
+                                                     r.causal != 0, mt * kBlockM)));
               }
-              ptx::bulk_commit();
+            }
+            ptx::bulk_commit();
+          };
+          if constexpr (kAccumStages == 1) {
+            // Single accumulator: drain it whole into packed BF16 registers and hand TMEM back
+            // before any staging, so the next tile's UMMAs overlap the stores.
+            uint32_t packed[kBlockN / 2];
+#pragma unroll
+            for (int c = 0; c < kBlockN; c += 64) {
+              uint32_t acc0[32], acc1[32];
+              ptx::tmem_ld_32x32b_x32(taddr + c, acc0);
+              ptx::tmem_ld_32x32b_x32(taddr + c + 32, acc1);
+              ptx::tmem_wait_ld();
+#pragma unroll
+              for (int e = 0; e < 16; ++e) {
+                __nv_bfloat162 pair = __floats2bfloat162_rn(p.alpha * __uint_as_float(acc0[2 * e]),
+                                                            p.alpha * __uint_as_float(acc0[2 * e + 1]));
+                packed[c / 2 + e] = *reinterpret_cast<const uint32_t*>(&pair);
+                pair = __floats2bfloat162_rn(p.alpha * __uint_as_float(acc1[2 * e]),
+                                             p.alpha * __uint_as_float(acc1[2 * e + 1]));
+                packed[c / 2 + 16 + e] = *reinterpret_cast<const uint32_t*>(&pair);
+              }
+            }
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(tmem_empty_bar(accum));
+#pragma unroll
+            for (int c = 0; c < kBlockN; c += 64) {
+              const uint32_t staging =
+                  base + Layout::kStagingOffset + (staged_blocks % Layout::kStagingBuffers) * Layout::kStagingBlockBytes;
+              ++staged_blocks;
+              if (epi_tid == 0) ptx::bulk_wait_read<Layout::kStagingBuffers - 1>();
+              ptx::named_bar_sync(1, kEpilogueThreads);
+              const uint32_t row_addr = staging + uint32_t(row_in_tile) * 128u;
+#pragma unroll
+              for (int v = 0; v < 8; ++v) {
+                const uint4 out = make_uint4(packed[c / 2 + v * 4], packed[c / 2 + v * 4 + 1],
+                                             packed[c / 2 + v * 4 + 2], packed[c / 2 + v * 4 + 3]);
+                ptx::st_shared_v4(row_addr + uint32_t((v ^ (row_in_tile & 7)) * 16), out);
+              }
+              ptx::fence_proxy_async_shared();
+              ptx::named_bar_sync(1, kEpilogueThreads);
+              if (epi_tid == 0) issue_stores(c, staging);
+            }
+          } else {
+#pragma unroll 1
+            for (int c = 0; c < kBlockN; c += 64) {
+              const uint32_t staging =
+                  base + Layout::kStagingOffset + (staged_blocks % Layout::kStagingBuffers) * Layout::kStagingBlockBytes;
+              ++staged_blocks;
+              // the block that last used this staging buffer has been read out by its tensor stores
+              if (epi_tid == 0) ptx::bulk_wait_read<Layout::kStagingBuffers - 1>();
+              ptx::named_bar_sync(1, kEpilogueThreads);
+              uint32_t acc0[32], acc1[32];
+              ptx::tmem_ld_32x32b_x32(taddr + c, acc0);
+              ptx::tmem_ld_32x32b_x32(taddr + c + 32, acc1);
+              ptx::tmem_wait_ld();
+              if (c + 64 >= kBlockN) {
+                ptx::tc_fence_before();
+                ptx::mbar_arrive(tmem_empty_bar(accum));
+              }
+              const uint32_t row_addr = staging + uint32_t(row_in_tile) * 128u;
+              stage_accumulators(acc0, row_addr, 0, row_in_tile, p.alpha);
+              stage_accumulators(acc1, row_addr, 4, row_in_tile, p.alpha);
+              ptx::fence_proxy_async_shared();
+              ptx::named_bar_sync(1, kEpilogueThreads);
+              if (epi_tid == 0) issue_stores(c, staging);
             }
           }
         } else {

@@ -84,6 +84,7 @@ cudaError_t qkv_backward_data(const fuse_qkv_backward_data_params& p, const fuse
   f.grad.kv_heads = p.kv_heads;
   f.grad.head_dim = p.head_dim;
   f.grad.causal = p.causal_load_balanced ? 1 : 0;
+  f.grad.m_group = wave_m_group(f, info.sm_count);
   f.grad.grad[0] = p.grad_q;
   f.grad.grad[1] = p.grad_k;
   f.grad.grad[2] = p.grad_v;

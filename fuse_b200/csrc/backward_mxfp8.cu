@@ -152,6 +152,7 @@ cudaError_t qkv_data(const fuse_mxfp8_qkv_backward_data_params& mp, const fuse_b
   f.grad.kv_heads = p.kv_heads;
   f.grad.head_dim = p.head_dim;
   f.grad.causal = p.causal_load_balanced ? 1 : 0;
+  f.grad.m_group = wave_m_group(f, info.sm_count);
   f.grad.lhs_bytes = lhs.data;
   f.grad.lhs_scales = lhs.scales;
   f.grad.master_staging = p.peer_dqkv_staging[p.rank];

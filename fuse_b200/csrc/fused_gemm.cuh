@@ -121,6 +121,7 @@ struct LhsRoute {
 struct GradRoute {
   int32_t world, rank, seq_local, global_seq, m;   // m = rows per rank (same on every rank)
   int32_t q_heads, kv_heads, head_dim, causal;
+  int32_t m_group;                                  // M tiles one GEMM wave works on together (>= 1)
   const uint16_t* grad[3];                          // dQ, dK, dV planes of this rank
   uint16_t* peer_staging[kMaxWorldSize];
   uint32_t* peer_ready[kMaxWorldSize];              // [m_tiles * (q + 2 kv)] flags on each peer
@@ -181,7 +182,7 @@ constexpr int kPullLag = 4;
 constexpr int kPullSubRows = 32;
 constexpr int kPullSubsPerTile = kBlockM / kPullSubRows;
 // Shared memory a communication CTA needs for it: the warps' rings plus their mbarriers.
-constexpr uint32_t kPullSmemBytes = kPullWarps * kPullStages * (kPullStageBytes + 8u);
+constexpr uint32_t kPullSmemBytes = kPullWarps * kPullStages * (kPullStageBytes + 8u) + 512u;  // + unit queues
 
 // kMx: block-scaled E4M3 operands (one UE8M0 scale per 32 K values).  A K block is then 128
 // one-byte elements (the same 128-byte swizzle rows), each stage also carries the 512-byte scale
@@ -825,18 +826,89 @@ __device__ __forceinline__ void grad_pull_role(const FusedParams& p) {
 // ------------------------------------------------------------------------------------------
 // Chunk pipeline shared by the tensor-copy communication roles.
 //
-// Every pull/push warp of a communication CTA walks its units chunk by chunk (a chunk fits one
-// kPullStageBytes stage): loads run kPullStages ahead into the warp's shared-memory ring and
-// complete on mbarriers; as a chunk lands its store is issued and committed as one bulk group;
-// the stage is reused once that store has read it; a unit is reported (`Policy::publish`) when
-// the group holding its last chunk has completed, checked kPullLag chunks late.  The policy
-// supplies the unit/chunk walk and the copy instructions.
+// Warps 0..kPullWarps-1 of a communication CTA each walk their units chunk by chunk (a chunk
+// fits one kPullStageBytes stage): loads run kPullStages ahead into the warp's shared-memory
+// ring and complete on mbarriers; as a chunk lands its store is issued and committed as one bulk
+// group; the stage is reused once that store has read it; a unit is complete when the group
+// holding its last chunk has completed, checked kPullLag chunks late.  Completed units go into a
+// small per-warp queue in shared memory; the last warp of the CTA (the publisher) drains the
+// queues and releases the units' flags -- one memory fence per batch of units, so the
+// microseconds a GPU- or system-scope fence takes are never on a copy warp's path.  The policy
+// supplies the unit/chunk walk, the copy instructions, the fence and the flag store.
 // ------------------------------------------------------------------------------------------
+constexpr int kPublishDepth = 16;                 // queue entries per copy warp
+constexpr uint32_t kPublishSentinel = 0xffffffffu;  // "this warp has no more units"
+constexpr uint32_t kPublishQueueBytes = kPullWarps * (kPublishDepth + 2) * 4u;
+static_assert(kPublishQueueBytes <= 512u, "the unit queues live in the 512 bytes after the copy rings");
+static_assert(kThreads / 32 > kPullWarps, "one warp beyond the copy warps publishes");
+
+template <class Policy>
+__device__ __forceinline__ void run_unit_publisher(Policy& policy, const WaitContext& w, uint32_t queue,
+                                                   uint32_t heads, uint32_t tails, int lane) {
+  uint32_t tail = 0, idle = 0;
+  bool finished = lane >= kPullWarps;  // lane l drains the queue of copy warp l
+  uint64_t idle_since = 0;
+  for (;;) {
+    uint32_t units[4];
+    int n = 0;
+    if (!finished) {
+      const uint32_t head = ptx::ld_acquire_cta_shared(heads + 4u * uint32_t(lane));
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        units[i] = 0u;
+        if (!finished && tail != head) {
+          const uint32_t u = ptx::ld_acquire_cta_shared(queue + (uint32_t(lane) * kPublishDepth + tail % kPublishDepth) * 4u);
+          ++tail;
+          if (u == kPublishSentinel) finished = true;
+          else { units[i] = u; n = i + 1; }
+        }
+      }
+    }
+    if (__any_sync(0xffffffffu, n > 0)) {
+      policy.publish_fence();
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (i < n) policy.publish_flag(int64_t(units[i]));
+      if (lane < kPullWarps) ptx::st_release_cta_shared(tails + 4u * uint32_t(lane), tail);
+      idle = 0;
+      continue;
+    }
+    if (lane < kPullWarps) ptx::st_release_cta_shared(tails + 4u * uint32_t(lane), tail);
+    if (__all_sync(0xffffffffu, finished)) break;
+    if (idle == 0u) idle_since = ptx::globaltimer();
+    __nanosleep(100);
+    if ((++idle & 63u) == 0u) {
+      // Copy warps end with a sentinel whatever happens to them; this limit only covers a warp
+      // that never ran.
+      uint32_t stop = 0u;
+      if (lane == 0) {
+        if (aborted(w) && ptx::globaltimer() - idle_since > w.budget_ns) stop = 1u;
+        if (ptx::globaltimer() - idle_since > 2 * w.budget_ns) {
+          report_timeout(w, kStatusFlagTimeout, kSiteCommStage, 0u, 0u, 0u);
+          stop = 1u;
+        }
+      }
+      if (__shfl_sync(0xffffffffu, stop, 0)) break;
+    }
+  }
+}
+
 template <class Policy>
 __device__ __forceinline__ void run_chunk_pipeline(Policy& policy, const WaitContext& w, uint32_t smem_base,
                                                    int32_t num_comm_ctas) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (warp >= kPullWarps) return;
+  const uint32_t queue = smem_base + kPullWarps * kPullStages * (kPullStageBytes + 8u);
+  const uint32_t heads = queue + kPullWarps * kPublishDepth * 4u, tails = heads + kPullWarps * 4u;
+  if (threadIdx.x < kPullWarps) {
+    ptx::st_release_cta_shared(heads + 4u * threadIdx.x, 0u);
+    ptx::st_release_cta_shared(tails + 4u * threadIdx.x, 0u);
+  }
+  __syncthreads();  // every thread of the communication CTA comes through here
+  if (warp == kPullWarps) {
+    run_unit_publisher(policy, w, queue, heads, tails, lane);
+    return;
+  }
+  if (warp > kPullWarps) return;
   const uint32_t ring = smem_base + uint32_t(warp) * kPullStages * kPullStageBytes;
   const uint32_t bars = smem_base + kPullWarps * kPullStages * kPullStageBytes + uint32_t(warp) * kPullStages * 8u;
   if (lane == 0) {
@@ -847,9 +919,26 @@ __device__ __forceinline__ void run_chunk_pipeline(Policy& policy, const WaitCon
   const int32_t workers = num_comm_ctas * kPullWarps;
   const int32_t worker = warp * num_comm_ctas + int32_t(blockIdx.x);
 
+  // Lane 0 appends a completed unit (or the sentinel) to this warp's queue; a full queue waits
+  // for the publisher, giving up only when the launch is being aborted.
+  uint32_t posted = 0;
+  auto post = [&](uint32_t unit) {
+    if (lane != 0) return;
+    const uint32_t my_tail = tails + 4u * uint32_t(warp);
+    if (posted - ptx::ld_acquire_cta_shared(my_tail) >= uint32_t(kPublishDepth)) {
+      if (!progress_wait(my_tail, posted - uint32_t(kPublishDepth) + 1u, w, kSiteCommStage, uint32_t(warp))) return;
+    }
+    ptx::st_release_cta_shared(queue + (uint32_t(warp) * kPublishDepth + posted % kPublishDepth) * 4u, unit);
+    ++posted;
+    ptx::st_release_cta_shared(heads + 4u * uint32_t(warp), posted);
+  };
+
   typename Policy::Cursor load_cursor, store_cursor;
   bool more_loads = policy.first(load_cursor, worker, workers);
-  if (!more_loads) return;
+  if (!more_loads) {
+    post(kPublishSentinel);
+    return;
+  }
   store_cursor = load_cursor;
   int32_t issued = 0, consumed = 0;
   while (issued < kPullStages && more_loads) {
@@ -865,15 +954,20 @@ __device__ __forceinline__ void run_chunk_pipeline(Policy& policy, const WaitCon
   while (ok && more_stores) {
     const int stage = consumed % kPullStages;
     uint32_t landed = 1u;
-    if (lane == 0)
+    if (lane == 0) {
+      trace_event(policy.p, 30);  // waiting for the chunk to land
       landed = mbar_wait(bars + 8u * stage, uint32_t(consumed / kPullStages) & 1u, w, kSiteCommStage) ? 1u : 0u;
+      trace_event(policy.p, 31);
+    }
     landed = __shfl_sync(0xffffffffu, landed, 0);
     if (!landed) { ok = false; break; }
     policy.store(store_cursor, ring + uint32_t(stage) * kPullStageBytes, lane);
     ptx::bulk_commit();
     ++consumed;
+    if (lane == 0) trace_event(policy.p, 32);  // store issued
     ptx::bulk_wait_read<0>();
     __syncwarp();
+    if (lane == 0) trace_event(policy.p, 33);  // store has read the stage
     if (more_loads && issued < consumed + kPullStages) {
       policy.load(load_cursor, ring + uint32_t(issued % kPullStages) * kPullStageBytes,
                   bars + 8u * uint32_t(issued % kPullStages), lane);
@@ -882,7 +976,9 @@ __device__ __forceinline__ void run_chunk_pipeline(Policy& policy, const WaitCon
     }
     ptx::bulk_wait<kPullLag>();
     __syncwarp();
-    if (lag_unit[kPullLag - 1] >= 0) policy.publish(lag_unit[kPullLag - 1], lane);
+    if (lane == 0) trace_event(policy.p, 34);  // older stores complete
+    if (lag_unit[kPullLag - 1] >= 0) post(uint32_t(lag_unit[kPullLag - 1]));
+    if (lane == 0) trace_event(policy.p, 35);  // unit queued for publication
 #pragma unroll
     for (int i = kPullLag - 1; i > 0; --i) lag_unit[i] = lag_unit[i - 1];
     lag_unit[0] = policy.closes(store_cursor) ? policy.unit(store_cursor) : -1;
@@ -893,11 +989,12 @@ __device__ __forceinline__ void run_chunk_pipeline(Policy& policy, const WaitCon
   if (ok) {
 #pragma unroll
     for (int i = kPullLag - 1; i >= 0; --i)
-      if (lag_unit[i] >= 0) policy.publish(lag_unit[i], lane);
+      if (lag_unit[i] >= 0) post(uint32_t(lag_unit[i]));
   }
   if (!ok && lane == 0)
     for (int32_t i = consumed; i < issued; ++i)
       mbar_wait(bars + 8u * uint32_t(i % kPullStages), uint32_t(i / kPullStages) & 1u, w, kSiteDrain, false);
+  post(kPublishSentinel);
 }
 
 // QKV backward sender push with tensor copies (head_dim 128): unit = (destination M tile,
@@ -905,7 +1002,8 @@ __device__ __forceinline__ void run_chunk_pipeline(Policy& policy, const WaitCon
 // next rank on.  The destination's flag is released at system scope once both chunks' stores
 // have completed.
 struct GradPushPolicy {
-  struct Cursor { int64_t unit; int32_t chunk; };
+  struct Where { int32_t dest, mt, segment, local_head, head; };
+  struct Cursor { int64_t unit; int32_t chunk; Where x; };
   const FusedParams& p;
   const GradPushMaps& maps;
   int32_t m_tiles, local_heads, heads_total, q_local, kv_local;
@@ -919,46 +1017,57 @@ struct GradPushPolicy {
     heads_total = g.q_heads + 2 * g.kv_heads;
     units = int64_t(m_tiles) * g.world * local_heads;
   }
-  struct Where { int32_t dest, mt, segment, local_head, head; };
+  // Units are ordered so that the M tiles one GEMM wave works on (a group of m_group tiles)
+  // advance through the heads together: group, then local head, then destination, then M tile.
   __device__ Where where(int64_t u) const {
     const GradRoute& g = p.grad;
     Where x;
-    const int32_t slot = int32_t(u % local_heads), rest = int32_t(u / local_heads);
-    x.dest = (g.rank + 1 + rest % g.world) % g.world;
-    x.mt = rest / g.world;
+    const int64_t per_group = int64_t(g.m_group) * g.world * local_heads;
+    const int32_t group = int32_t(u / per_group);
+    const int32_t mt0 = group * g.m_group;
+    const int32_t size = m_tiles - mt0 < g.m_group ? m_tiles - mt0 : g.m_group;
+    const int32_t within = int32_t(u - group * per_group);
+    const int32_t slot = within / (g.world * size), rest = within - slot * (g.world * size);
+    x.dest = (g.rank + 1 + rest / size) % g.world;
+    x.mt = mt0 + rest % size;
     x.segment = slot < q_local ? 0 : (slot < q_local + kv_local ? 1 : 2);
     x.local_head = slot - (x.segment == 0 ? 0 : q_local + (x.segment == 2 ? kv_local : 0));
     const int32_t seg_local = x.segment == 0 ? q_local : kv_local;
     x.head = (x.segment == 0 ? 0 : g.q_heads + (x.segment == 2 ? g.kv_heads : 0)) + g.rank * seg_local + x.local_head;
     return x;
   }
-  __device__ bool first(Cursor& c, int32_t worker, int32_t) const { c.unit = worker; c.chunk = 0; return c.unit < units; }
+  __device__ bool first(Cursor& c, int32_t worker, int32_t) const {
+    c.unit = worker;
+    c.chunk = 0;
+    if (c.unit >= units) return false;
+    c.x = where(c.unit);
+    return true;
+  }
   __device__ bool next(Cursor& c, int32_t workers) const {
-    if (++c.chunk < 2 && p.grad.m - where(c.unit).mt * kBlockM > 64) return true;
+    if (++c.chunk < 2 && p.grad.m - c.x.mt * kBlockM > 64) return true;
     c.chunk = 0;
     c.unit += workers;
-    return c.unit < units;
+    if (c.unit >= units) return false;
+    c.x = where(c.unit);
+    return true;
   }
   __device__ void load(const Cursor& c, uint32_t smem, uint32_t bar, int lane) const {
     if (lane != 0) return;
     const GradRoute& g = p.grad;
-    const Where x = where(c.unit);
-    const int64_t src_row = global_row(g.world, x.dest, g.seq_local, g.global_seq, g.causal != 0, x.mt * kBlockM + c.chunk * 64);
+    const int64_t src_row = global_row(g.world, c.x.dest, g.seq_local, g.global_seq, g.causal != 0, c.x.mt * kBlockM + c.chunk * 64);
     ptx::mbar_expect_tx(bar, 64u * 256u);
-    ptx::tma_load_2d(smem, &maps.plane[x.segment], bar, x.local_head * 128, int32_t(src_row));
+    ptx::tma_load_2d(smem, &maps.plane[c.x.segment], bar, c.x.local_head * 128, int32_t(src_row));
   }
   __device__ void store(const Cursor& c, uint32_t smem, int lane) const {
     if (lane != 0) return;
-    const Where x = where(c.unit);
-    ptx::tma_store_2d(&maps.staging[x.dest], smem, x.head * 128, x.mt * kBlockM + c.chunk * 64);
+    ptx::tma_store_2d(&maps.staging[c.x.dest], smem, c.x.head * 128, c.x.mt * kBlockM + c.chunk * 64);
   }
-  __device__ bool closes(const Cursor& c) const { return c.chunk == 1 || p.grad.m - where(c.unit).mt * kBlockM <= 64; }
+  __device__ bool closes(const Cursor& c) const { return c.chunk == 1 || p.grad.m - c.x.mt * kBlockM <= 64; }
   __device__ int64_t unit(const Cursor& c) const { return c.unit; }
-  __device__ void publish(int64_t u, int lane) const {
-    if (lane != 0) return;
+  __device__ void publish_fence() const { ptx::fence_acq_rel_sys(); }
+  __device__ void publish_flag(int64_t u) const {
     const Where x = where(u);
-    __threadfence_system();
-    ptx::st_release_sys(p.grad.peer_ready[x.dest] + (int64_t(x.mt) * heads_total + x.head) * kReadyFlagStride,
+    ptx::st_relaxed_sys(p.grad.peer_ready[x.dest] + (int64_t(x.mt) * heads_total + x.head) * kReadyFlagStride,
                         p.wait.epoch);
   }
 };
@@ -966,7 +1075,8 @@ struct GradPushPolicy {
 // MXFP8 QKV backward receiver pull with tensor copies: unit = (M tile, logical head), four
 // chunks: the 128 x 128 E4M3 block, two 64-row halves of the BF16 master block, the scale atom.
 struct GradPullPolicy {
-  struct Cursor { int64_t unit; int32_t chunk; };
+  struct Where { int32_t mt, head, segment, owner, local_head, seg_local; int64_t src_row; };
+  struct Cursor { int64_t unit; int32_t chunk; Where x; };
   const FusedParams& p;
   const GradPullMaps& maps;
   int32_t heads_total;
@@ -975,12 +1085,18 @@ struct GradPullPolicy {
     heads_total = p.grad.q_heads + 2 * p.grad.kv_heads;
     units = int64_t((p.grad.m + kBlockM - 1) / kBlockM) * heads_total;
   }
-  struct Where { int32_t mt, head, segment, owner, local_head, seg_local; int64_t src_row; };
   __device__ Where where(int64_t u) const {
     const GradRoute& g = p.grad;
     Where x;
-    x.mt = int32_t(u / heads_total);
-    x.head = int32_t(u % heads_total);
+    // group of m_group M tiles, then head, then M tile: a GEMM wave's tiles advance together
+    const int32_t m_tiles = (g.m + kBlockM - 1) / kBlockM;
+    const int64_t per_group = int64_t(g.m_group) * heads_total;
+    const int32_t group = int32_t(u / per_group);
+    const int32_t mt0 = group * g.m_group;
+    const int32_t size = m_tiles - mt0 < g.m_group ? m_tiles - mt0 : g.m_group;
+    const int32_t within = int32_t(u - group * per_group);
+    x.head = within / size;
+    x.mt = mt0 + within % size;
     x.segment = x.head < g.q_heads ? 0 : (x.head < g.q_heads + g.kv_heads ? 1 : 2);
     const int32_t seg_head = x.head - (x.segment == 0 ? 0 : g.q_heads + (x.segment == 2 ? g.kv_heads : 0));
     x.seg_local = (x.segment == 0 ? g.q_heads : g.kv_heads) / g.world;
@@ -989,16 +1105,24 @@ struct GradPullPolicy {
     x.src_row = global_row(g.world, g.rank, g.seq_local, g.global_seq, g.causal != 0, x.mt * kBlockM);
     return x;
   }
-  __device__ bool first(Cursor& c, int32_t worker, int32_t) const { c.unit = worker; c.chunk = 0; return c.unit < units; }
+  __device__ bool first(Cursor& c, int32_t worker, int32_t) const {
+    c.unit = worker;
+    c.chunk = 0;
+    if (c.unit >= units) return false;
+    c.x = where(c.unit);
+    return true;
+  }
   __device__ bool next(Cursor& c, int32_t workers) const {
     if (++c.chunk < 4) return true;
     c.chunk = 0;
     c.unit += workers;
-    return c.unit < units;
+    if (c.unit >= units) return false;
+    c.x = where(c.unit);
+    return true;
   }
   __device__ void load(const Cursor& c, uint32_t smem, uint32_t bar, int lane) const {
     if (lane != 0) return;
-    const Where x = where(c.unit);
+    const Where& x = c.x;
     if (c.chunk == 0) {
       ptx::mbar_expect_tx(bar, 128u * 128u);
       ptx::tma_load_2d(smem, &maps.bytes[x.owner][x.segment], bar, x.local_head * 128, int32_t(x.src_row));
@@ -1014,17 +1138,17 @@ struct GradPullPolicy {
   }
   __device__ void store(const Cursor& c, uint32_t smem, int lane) const {
     if (lane != 0) return;
-    const Where x = where(c.unit);
+    const Where& x = c.x;
     if (c.chunk == 0) ptx::tma_store_2d(&maps.lhs, smem, x.head * 128, x.mt * kBlockM);
     else if (c.chunk < 3) ptx::tma_store_2d(&maps.master, smem, x.head * 128, x.mt * kBlockM + (c.chunk - 1) * 64);
     else ptx::bulk_store(p.grad.lhs_scales + (int64_t(x.mt) * heads_total + x.head) * 512, smem, 512u);
   }
   __device__ bool closes(const Cursor& c) const { return c.chunk == 3; }
   __device__ int64_t unit(const Cursor& c) const { return c.unit; }
-  __device__ void publish(int64_t u, int lane) const {
-    if (lane != 0) return;
-    __threadfence();
-    ptx::st_release_gpu(p.ready + u * kReadyFlagStride, p.wait.epoch);
+  __device__ void publish_fence() const { ptx::fence_acq_rel_gpu(); }
+  __device__ void publish_flag(int64_t u) const {
+    const Where x = where(u);
+    ptx::st_relaxed_gpu(p.ready + (int64_t(x.mt) * heads_total + x.head) * kReadyFlagStride, p.wait.epoch);
   }
 };
 
@@ -1331,12 +1455,14 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
               int32_t last = (kb * kBlockElems + kBlockElems - 1) / group_width;
               if (last >= groups) last = groups - 1;
               if (gated_upto < last) {
-                trace_event(p, 10);  // gate wait begins
+                if (kb == 0) trace_event(p, 10);  // first gate wait of the tile begins
+                uint32_t seen = 0;
                 ok = progress_wait(gate_word, tile_seq * kGateSeqStep + uint32_t(last) + 1u, p.wait, kSiteLhsReady,
-                                   uint32_t(mt * groups + last));
+                                   uint32_t(mt * groups + last), &seen);
+                // One proxy fence covers every group the scout has posted so far.
                 ptx::fence_proxy_async_global();
-                trace_event(p, 11);  // gate passed
-                gated_upto = last;
+                if (kb == 0) trace_event(p, 11);  // first gate passed
+                gated_upto = (seen / kGateSeqStep) > tile_seq ? groups - 1 : int32_t(seen % kGateSeqStep) - 1;
               }
               if (!ok) break;
             }
@@ -1670,6 +1796,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 p.ready + (int64_t(mt) * p.order.n_tiles + nt) * kReadyFlagStride, p.wait.epoch);
           }
         }
+        if (epi_tid == 0) trace_event(p, 13);  // tile handed to the copy engine
         if (++accum == kAccumStages) { accum = 0; accum_phase ^= 1u; }
       }
       if constexpr (kTmaEpilogue) {

@@ -74,6 +74,16 @@ inline void fill_core(FusedParams* p, int m, int n, int k, int block_n, int num_
 // w1 * compute_ctas tiles go to the compute CTAs alone, the rest is dealt to the whole grid, and
 // the split with the smallest makespan max((w1 + w2) * tau, t_c + w2 * tau) wins, w2 being the
 // waves of the shared part.  FUSE_B200_JOIN_WAVES=0 keeps the communication CTAs out of the GEMM.
+// M tiles that one wave of compute CTAs works on at the same time under the launch's tile order:
+// a band of `swizzle` M tiles with the N raster, compute_ctas / band width with the M raster.
+inline int32_t wave_m_group(const FusedParams& p, int sm_count) {
+  const int32_t compute = sm_count - p.num_comm_ctas;
+  const int32_t swizzle = p.order.swizzle > 0 ? p.order.swizzle : 1;
+  int32_t group = p.order.along_n ? swizzle : (compute + swizzle - 1) / swizzle;
+  if (group > p.order.m_tiles) group = p.order.m_tiles;
+  return group < 1 ? 1 : group;
+}
+
 inline void plan_join(FusedParams* p, int block_n, int sm_count, double comm_bytes, bool block_scaled) {
   const int64_t tiles = p->order.count();
   const int comm = p->num_comm_ctas;

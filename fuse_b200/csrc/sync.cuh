@@ -118,11 +118,14 @@ __device__ __forceinline__ bool flag_wait(const uint32_t* flag, uint32_t expecte
 // ordinary budget and reports what it was waiting for; this wait learns of that through the
 // abort word, and its own (doubled) budget only covers a writer that never ran.
 __device__ __forceinline__ bool progress_wait(uint32_t smem_word, uint32_t expected, const WaitContext& w,
-                                              uint32_t site, uint32_t index) {
-  if (ptx::ld_acquire_cta_shared(smem_word) >= expected) return true;
+                                              uint32_t site, uint32_t index, uint32_t* observed = nullptr) {
+  uint32_t seen = ptx::ld_acquire_cta_shared(smem_word);
+  if (observed != nullptr) *observed = seen;
+  if (seen >= expected) return true;
   const uint64_t start = ptx::globaltimer();
   for (uint32_t spin = 1;; ++spin) {
-    const uint32_t seen = ptx::ld_acquire_cta_shared(smem_word);
+    seen = ptx::ld_acquire_cta_shared(smem_word);
+    if (observed != nullptr) *observed = seen;
     if (seen >= expected) return true;
     if ((spin & 63u) == 0u) {
       if (aborted(w)) return false;

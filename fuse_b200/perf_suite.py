@@ -35,6 +35,8 @@ def main():
     ap.add_argument("--scale", type=float, default=1.0, help="scale rows per rank of c3/c4/c5")
     ap.add_argument("--only", default="", help="comma list of c2,c3,c4,c5,bwd")
     ap.add_argument("--comm", type=int, default=16)
+    ap.add_argument("--bwd-along-m", type=int, default=0, help="tile raster of the data-gradient GEMMs")
+    ap.add_argument("--bwd-swizzle", type=int, default=8)
     args = ap.parse_args()
     world_size = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -145,7 +147,8 @@ def main():
                                    "b_gattn": rows * (k_o // cp) * 2})
             bp = N.QkvBackwardDataParams(local_tokens=m, hidden=hid, batch=1, q_heads=q, kv_heads=kv, head_dim=d,
                                          world_size=cp, rank=rank, num_comm_ctas=args.comm, epoch=0)
-            bp.gemm_tuning.max_swizzle_size = 8
+            bp.gemm_tuning.max_swizzle_size = args.bwd_swizzle
+            bp.gemm_tuning.along_m = args.bwd_along_m
             bready = world.allocate({"b_ready": api.qkv_backward_ready_elements(bp) * 4})
             planes = [gen((rows, h // cp * d), seed + 100 * i + 101, 0.01) for i, h in enumerate((q, kv, kv))]
             dx = torch.empty((m, hid), dtype=bf16, device=dev)
@@ -171,7 +174,8 @@ def main():
             op = N.OprojBackwardDataParams(grad_output=dy.data_ptr(), weight=wo.data_ptr(), local_grad_attention=da.data_ptr(),
                                            local_tokens=m, hidden=hid, batch=1, q_heads=q, head_dim=d, world_size=cp,
                                            rank=rank, num_comm_ctas=args.comm, epoch=0)
-            op.gemm_tuning.max_swizzle_size = 8
+            op.gemm_tuning.max_swizzle_size = args.bwd_swizzle
+            op.gemm_tuning.along_m = args.bwd_along_m
             for r in range(cp):
                 op.peer_grad_attention[r] = bsym["b_gattn"].peer_ptrs[r]
                 op.peer_done_epoch[r] = bsym["b_done2"].peer_ptrs[r]

@@ -206,7 +206,16 @@ cudaError_t oproj_forward(const fuse_a2a_gemm_params& p, const fuse_b200_options
     k.lhs.peer_input[peer] = p.peer_input[peer];
     k.lhs.peer_input_ready[peer] = p.peer_input_ready[peer];
   }
+  plan_lhs_slices(&k, info.sm_count);
   plan_join(&k, block_n, info.sm_count, double(p.gemm.m) * p.gemm.k * 2.0, false);
+  if (!(k.flags & kFlagVectorPull)) {
+    LhsPullMaps pull{};
+    if (encode_lhs_pull_maps(&pull, k, uint64_t(p.route.batch) * uint64_t(p.route.global_seq)))
+      return launch_mode<kModeLhsPull, false, false, false, LhsPullMaps>(maps, pull, k, block_n, info, stream,
+                                                                         !vector_epilogue_requested(options));
+  }
+  k.lhs.virt = 1;  // bulk-copy or vector pull: one gate per shard
+  k.lhs.virt_width = k.lhs.shard_width;
   StoreMaps stores{};
   return launch_mode<kModeLhsPull>(maps, stores, k, block_n, info, stream,
                                    !vector_epilogue_requested(options));

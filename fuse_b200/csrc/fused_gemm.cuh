@@ -90,6 +90,16 @@ struct alignas(64) GradPullMaps {
   CUtensorMap masters[kMaxWorldSize][3];
 };
 
+// Tensor maps of the forward lhs pull: every peer's head shard ([B*S_global, K/world]) and the
+// local staging ([M, K]), both typed as 32-bit words so that a box row can be 1 KiB wide; boxes of
+// `piece_bytes` x `rows_per_chunk` (one pipeline stage), no swizzle.
+struct alignas(64) LhsPullMaps {
+  CUtensorMap local;
+  CUtensorMap staging;
+  CUtensorMap peer[kMaxWorldSize];
+  int32_t piece_bytes, rows_per_chunk;
+};
+
 struct QkvRoute {
   int32_t world, rank, batch, seq_local, global_seq;
   int32_t q_heads, kv_heads, head_dim;
@@ -113,6 +123,11 @@ struct LhsRoute {
   const uint8_t* peer_scales[kMaxWorldSize];
   uint8_t* local_scales;
   int32_t k_atoms, shard_atoms;  // K/128 and (K/world)/128
+  // Gate granularity: every shard is cut into `virt` column slices of virt_width elements, each
+  // with its own flag (word 2v of the shard's flag line) and arrival counter (word 2v + 1), so
+  // that a GEMM tile starts on the first slice instead of the whole shard.  m_group: M tiles one
+  // GEMM wave works on together; their slices are delivered side by side.
+  int32_t virt, virt_width, m_group;
 };
 
 // QKV backward reverse route (head -> sequence), sender side: this rank holds planar
@@ -179,6 +194,7 @@ constexpr int kPullWarps = 7;
 constexpr int kPullStages = 2;
 constexpr uint32_t kPullStageBytes = 16384;
 constexpr int kPullLag = 4;
+constexpr int kPullEagerChunks = 4;  // chunks per warp reported without lag at start-up
 constexpr int kPullSubRows = 32;
 constexpr int kPullSubsPerTile = kBlockM / kPullSubRows;
 // Shared memory a communication CTA needs for it: the warps' rings plus their mbarriers.
@@ -435,8 +451,8 @@ __device__ __forceinline__ void lhs_pull_role(const FusedParams& p, uint8_t* sme
     if (tid == 0) {
       __threadfence();                    // ... and ordered before the flag at GPU scope,
       ptx::fence_proxy_async_global();    // also for the TMA (async proxy) reads that follow
-      ptx::st_release_gpu(p.ready + (int64_t(mt) * r.world + shard) * kReadyFlagStride,
-                          p.wait.epoch);
+      for (int32_t v = 0; v < r.virt; ++v)
+        ptx::st_release_gpu(p.ready + (int64_t(mt) * r.world + shard) * kReadyFlagStride + 2 * v, p.wait.epoch);
     }
   }
 }
@@ -466,6 +482,7 @@ struct PullCursor {
   int32_t row;        // rank-local row of its first row
   int32_t flag, needed, peer;
   bool contiguous;    // its source rows are consecutive in the peer's tensor
+  uint32_t src_col;   // byte offset of its column slice inside a source row
   const uint8_t* src; // source of its first row (valid when contiguous)
   uint8_t* dst;       // destination of its first row
   int32_t data_chunks;       // chunks [data_chunks, chunks) carry the unit's scale atoms
@@ -488,23 +505,26 @@ __device__ __forceinline__ void lhs_pull_bulk_role(const FusedParams& p, uint32_
 
   const int32_t workers = p.num_comm_ctas * kPullWarps;
   const int32_t worker = warp * p.num_comm_ctas + int32_t(blockIdx.x);  // neighbours on different SMs
-  const uint32_t shard_bytes = uint32_t(r.shard_width) * uint32_t(r.element_bytes);
-  const int32_t pieces = int32_t((shard_bytes + kPullStageBytes - 1) / kPullStageBytes);
+  const uint32_t shard_bytes = uint32_t(r.shard_width) * uint32_t(r.element_bytes);  // source row pitch
+  const uint32_t unit_bytes = uint32_t(r.virt_width) * uint32_t(r.element_bytes);    // one column slice
+  const int32_t unit_atoms = r.virt_width / 128;
+  const int32_t gates = r.world * r.virt;  // column slices of one M tile
+  const int32_t pieces = int32_t((unit_bytes + kPullStageBytes - 1) / kPullStageBytes);
   // Scale atoms of one unit travel as extra chunks of its first sub-unit: the K atoms of one
   // 128-row group are contiguous at the source and at the destination.
   const bool with_scales = r.local_scales != nullptr;
   constexpr int32_t kAtomsPerChunk = int32_t(kPullStageBytes / 512);
-  const int32_t scale_chunks = with_scales ? (r.shard_atoms + kAtomsPerChunk - 1) / kAtomsPerChunk : 0;
+  const int32_t scale_chunks = with_scales ? (unit_atoms + kAtomsPerChunk - 1) / kAtomsPerChunk : 0;
   const int32_t rows_per_chunk =
-      pieces == 1 ? (int32_t(kPullStageBytes / shard_bytes) < kPullSubRows ? int32_t(kPullStageBytes / shard_bytes)
-                                                                          : kPullSubRows)
+      pieces == 1 ? (int32_t(kPullStageBytes / unit_bytes) < kPullSubRows ? int32_t(kPullStageBytes / unit_bytes)
+                                                                         : kPullSubRows)
                   : 1;
   // A sub-unit is at most two chunks, so that the first units the GEMM waits for are spread
   // over every pull warp (wide rows: a few rows; 1 KiB rows: 32 rows).
   int32_t sub_rows = 2 * rows_per_chunk < kPullSubRows ? 2 * rows_per_chunk : kPullSubRows;
   while (kBlockM % sub_rows != 0) --sub_rows;
   const int32_t subs_per_tile = kBlockM / sub_rows;
-  const int32_t subs_total = p.order.m_tiles * r.world * subs_per_tile;
+  const int32_t subs_total = p.order.m_tiles * gates * subs_per_tile;
   const int32_t row_block = r.causal ? r.seq_local / 2 : r.seq_local;  // rows consecutive at the source
   const int64_t dst_pitch = r.lda * r.element_bytes;
 
@@ -512,7 +532,13 @@ __device__ __forceinline__ void lhs_pull_bulk_role(const FusedParams& p, uint32_
   auto seek = [&](PullCursor& c) {
     for (; c.sub < subs_total; c.sub += workers) {
       const int32_t unit = c.sub / subs_per_tile, quarter = c.sub - unit * subs_per_tile;
-      const int32_t mt = unit / r.world, shard = unit - mt * r.world;
+      // unit order: group of m_group M tiles, then column slice, then M tile of the group
+      const int32_t per_group = r.m_group * gates;
+      const int32_t group = unit / per_group, mt0 = group * r.m_group;
+      const int32_t group_size = p.order.m_tiles - mt0 < r.m_group ? p.order.m_tiles - mt0 : r.m_group;
+      const int32_t within = unit - group * per_group;
+      const int32_t gate = within / group_size, mt = mt0 + within - gate * group_size;
+      const int32_t shard = gate / r.virt, slice = gate - shard * r.virt;
       const int32_t rows_in_unit = p.m - mt * kBlockM < kBlockM ? p.m - mt * kBlockM : kBlockM;
       const int32_t row0 = quarter * sub_rows;
       if (row0 >= rows_in_unit) continue;
@@ -521,18 +547,20 @@ __device__ __forceinline__ void lhs_pull_bulk_role(const FusedParams& p, uint32_
       c.chunk = 0;
       c.data_chunks = ((c.rows + rows_per_chunk - 1) / rows_per_chunk) * pieces;
       c.chunks = c.data_chunks + (quarter == 0 ? scale_chunks : 0);
-      c.flag = unit;
+      c.flag = (mt * r.world + shard) * kReadyFlagStride + 2 * slice;  // word offset of the slice's flag
       c.needed = (rows_in_unit + sub_rows - 1) / sub_rows;
       c.peer = r.cyclic ? (r.rank + shard) % r.world : shard;
-      c.contiguous = (c.row % row_block) + c.rows <= row_block;
+      c.contiguous = r.virt == 1 && (c.row % row_block) + c.rows <= row_block;
+      c.src_col = uint32_t(slice) * unit_bytes;
       c.src = reinterpret_cast<const uint8_t*>(r.peer_input[c.peer]) +
-              global_row(r.world, r.rank, r.seq_local, r.global_seq, r.causal != 0, c.row) * shard_bytes;
+              global_row(r.world, r.rank, r.seq_local, r.global_seq, r.causal != 0, c.row) * shard_bytes + c.src_col;
       c.dst = reinterpret_cast<uint8_t*>(r.staging) + int64_t(c.row) * dst_pitch +
-              int64_t(shard) * shard_bytes;
+              int64_t(shard) * shard_bytes + c.src_col;
       if (with_scales) {
         const int64_t src_row = global_row(r.world, r.rank, r.seq_local, r.global_seq, r.causal != 0, mt * kBlockM);
-        c.scale_src = r.peer_scales[c.peer] + (src_row >> 7) * int64_t(r.shard_atoms) * 512;
-        c.scale_dst = r.local_scales + (int64_t(mt) * r.k_atoms + int64_t(shard) * r.shard_atoms) * 512;
+        c.scale_src = r.peer_scales[c.peer] + ((src_row >> 7) * int64_t(r.shard_atoms) + int64_t(slice) * unit_atoms) * 512;
+        c.scale_dst = r.local_scales +
+                      (int64_t(mt) * r.k_atoms + int64_t(shard) * r.shard_atoms + int64_t(slice) * unit_atoms) * 512;
       }
       return true;
     }
@@ -549,7 +577,7 @@ __device__ __forceinline__ void lhs_pull_bulk_role(const FusedParams& p, uint32_
     Chunk k;
     if (c.chunk >= c.data_chunks) {  // scale atoms: one contiguous run, described as a single row
       const int32_t first_atom = (c.chunk - c.data_chunks) * kAtomsPerChunk;
-      const int32_t atoms = r.shard_atoms - first_atom < kAtomsPerChunk ? r.shard_atoms - first_atom : kAtomsPerChunk;
+      const int32_t atoms = unit_atoms - first_atom < kAtomsPerChunk ? unit_atoms - first_atom : kAtomsPerChunk;
       k.row_off = 0;
       k.rows = 1;
       k.col_off = uint32_t(first_atom) * 512u;
@@ -560,12 +588,12 @@ __device__ __forceinline__ void lhs_pull_bulk_role(const FusedParams& p, uint32_
       k.row_off = c.chunk * rows_per_chunk;
       k.rows = c.rows - k.row_off < rows_per_chunk ? c.rows - k.row_off : rows_per_chunk;
       k.col_off = 0;
-      k.bytes_per_row = shard_bytes;
+      k.bytes_per_row = unit_bytes;
     } else {
       k.row_off = c.chunk / pieces;
       k.rows = 1;
       k.col_off = uint32_t(c.chunk - k.row_off * pieces) * kPullStageBytes;
-      k.bytes_per_row = shard_bytes - k.col_off < kPullStageBytes ? shard_bytes - k.col_off : kPullStageBytes;
+      k.bytes_per_row = unit_bytes - k.col_off < kPullStageBytes ? unit_bytes - k.col_off : kPullStageBytes;
     }
     return k;
   };
@@ -602,7 +630,7 @@ __device__ __forceinline__ void lhs_pull_bulk_role(const FusedParams& p, uint32_
         const int64_t src_row = global_row(r.world, r.rank, r.seq_local, r.global_seq, r.causal != 0,
                                            c.row + k.row_off + row);
         ptx::bulk_load(dst + uint32_t(row) * k.bytes_per_row,
-                       reinterpret_cast<const uint8_t*>(r.peer_input[c.peer]) + src_row * shard_bytes + k.col_off,
+                       reinterpret_cast<const uint8_t*>(r.peer_input[c.peer]) + src_row * shard_bytes + c.src_col + k.col_off,
                        k.bytes_per_row, bar);
       }
     }
@@ -617,13 +645,13 @@ __device__ __forceinline__ void lhs_pull_bulk_role(const FusedParams& p, uint32_
   int32_t counted_flag = -1, counted_needed = 1;
   auto publish = [&]() {
     if (lane == 0 && counted_flag >= 0 && (counted_before + 1u) % uint32_t(counted_needed) == 0u)
-      ptx::st_release_gpu(p.ready + int64_t(counted_flag) * kReadyFlagStride, p.wait.epoch);
+      ptx::st_release_gpu(p.ready + counted_flag, p.wait.epoch);
     counted_flag = -1;
   };
   auto count = [&](int32_t flag, int32_t needed) {
     publish();
     if (lane == 0)
-      counted_before = ptx::atom_acq_rel_gpu_add(p.ready + int64_t(flag) * kReadyFlagStride + 1, 1u);
+      counted_before = ptx::atom_acq_rel_gpu_add(p.ready + flag + 1, 1u);
     counted_flag = flag;
     counted_needed = needed;
   };
@@ -941,16 +969,21 @@ __device__ __forceinline__ void run_chunk_pipeline(Policy& policy, const WaitCon
   }
   store_cursor = load_cursor;
   int32_t issued = 0, consumed = 0;
-  while (issued < kPullStages && more_loads) {
-    policy.load(load_cursor, ring + uint32_t(issued % kPullStages) * kPullStageBytes,
-                bars + 8u * uint32_t(issued % kPullStages), lane);
+  bool ok = true, more_stores = true;
+  // Starts the copy of the chunk under the load cursor; false when the policy had to give up
+  // (an upstream flag that never came), in which case nothing was started.
+  auto start_load = [&]() {
+    uint32_t good = policy.load(load_cursor, ring + uint32_t(issued % kPullStages) * kPullStageBytes,
+                                bars + 8u * uint32_t(issued % kPullStages), lane) ? 1u : 0u;
+    good = __shfl_sync(0xffffffffu, good, 0);
+    if (!good) { ok = false; return; }
     more_loads = policy.next(load_cursor, workers);
     ++issued;
-  }
+  };
+  while (ok && issued < kPullStages && more_loads) start_load();
   int64_t lag_unit[kPullLag];
 #pragma unroll
   for (int i = 0; i < kPullLag; ++i) lag_unit[i] = -1;
-  bool ok = true, more_stores = true;
   while (ok && more_stores) {
     const int stage = consumed % kPullStages;
     uint32_t landed = 1u;
@@ -968,20 +1001,28 @@ __device__ __forceinline__ void run_chunk_pipeline(Policy& policy, const WaitCon
     ptx::bulk_wait_read<0>();
     __syncwarp();
     if (lane == 0) trace_event(policy.p, 33);  // store has read the stage
-    if (more_loads && issued < consumed + kPullStages) {
-      policy.load(load_cursor, ring + uint32_t(issued % kPullStages) * kPullStageBytes,
-                  bars + 8u * uint32_t(issued % kPullStages), lane);
-      more_loads = policy.next(load_cursor, workers);
-      ++issued;
-    }
-    ptx::bulk_wait<kPullLag>();
-    __syncwarp();
-    if (lane == 0) trace_event(policy.p, 34);  // older stores complete
-    if (lag_unit[kPullLag - 1] >= 0) post(uint32_t(lag_unit[kPullLag - 1]));
-    if (lane == 0) trace_event(policy.p, 35);  // unit queued for publication
+    if (more_loads && issued < consumed + kPullStages) start_load();
+    if (consumed <= kPullEagerChunks) {
+      // The first chunks feed GEMM tiles that are already waiting: report them as soon as their
+      // stores have completed instead of kPullLag chunks later.
+      ptx::bulk_wait<0>();
+      __syncwarp();
 #pragma unroll
-    for (int i = kPullLag - 1; i > 0; --i) lag_unit[i] = lag_unit[i - 1];
-    lag_unit[0] = policy.closes(store_cursor) ? policy.unit(store_cursor) : -1;
+      for (int i = kPullLag - 1; i >= 0; --i) {
+        if (lag_unit[i] >= 0) post(uint32_t(lag_unit[i]));
+        lag_unit[i] = -1;
+      }
+      if (policy.closes(store_cursor)) post(uint32_t(policy.unit(store_cursor)));
+    } else {
+      ptx::bulk_wait<kPullLag>();
+      __syncwarp();
+      if (lane == 0) trace_event(policy.p, 34);  // older stores complete
+      if (lag_unit[kPullLag - 1] >= 0) post(uint32_t(lag_unit[kPullLag - 1]));
+      if (lane == 0) trace_event(policy.p, 35);  // unit queued for publication
+#pragma unroll
+      for (int i = kPullLag - 1; i > 0; --i) lag_unit[i] = lag_unit[i - 1];
+      lag_unit[0] = policy.closes(store_cursor) ? policy.unit(store_cursor) : -1;
+    }
     more_stores = policy.next(store_cursor, workers);
   }
   ptx::bulk_wait<0>();
@@ -996,6 +1037,145 @@ __device__ __forceinline__ void run_chunk_pipeline(Policy& policy, const WaitCon
       mbar_wait(bars + 8u * uint32_t(i % kPullStages), uint32_t(i / kPullStages) & 1u, w, kSiteDrain, false);
   post(kPublishSentinel);
 }
+
+// Forward lhs pull with tensor copies.  A (M tile, column slice) unit -- 128 rows of one slice of
+// one peer's shard, plus (block-scaled operands) the slice's scale atoms -- is cut into chunks of
+// rows_per_chunk rows x piece_bytes (one stage) and the chunks into sub-units of two, dealt round
+// robin to the copy warps in the GEMM's first-use order (wave group, slice, M tile).  Each
+// chunk is one tensor load from the peer and one tensor store into the staging; a finished
+// sub-unit is counted in word 2v+1 of the shard's flag line and the arrival that completes the
+// unit publishes word 2v = epoch (arrival counting as in
+// csrc/operators/sm103/detail/a2a_gemm.cuh:466-642, but the epoch need not advance by one).
+struct LhsPullPolicy {
+  struct Cursor {
+    int32_t sub, chunk;                       // global sub-unit index, chunk inside it (0 or 1)
+    int32_t mt, shard, slice, peer;           // decoded unit
+    int32_t first_chunk, chunks_here, data_chunks, flag, needed;
+    int64_t src_row0;                         // source row of the M tile's first row
+  };
+  const FusedParams& p;
+  const LhsPullMaps& maps;
+  int32_t gates, pieces, rows_per_chunk, piece_bytes, unit_bytes, unit_atoms, scale_chunks;
+  int32_t subs_per_unit, subs_total;
+  uint32_t shard_bytes;
+  bool tile_rows_consecutive;  // the 128 rows of every M tile are consecutive at the source
+  mutable uint32_t upstream_seen = 0;
+  static constexpr int32_t kAtomsPerChunk = int32_t(kPullStageBytes / 512);
+  __device__ LhsPullPolicy(const FusedParams& params, const LhsPullMaps& m) : p(params), maps(m) {
+    const LhsRoute& r = p.lhs;
+    shard_bytes = uint32_t(r.shard_width) * uint32_t(r.element_bytes);
+    unit_bytes = r.virt_width * r.element_bytes;
+    unit_atoms = r.virt_width / 128;
+    gates = r.world * r.virt;
+    piece_bytes = m.piece_bytes;
+    rows_per_chunk = m.rows_per_chunk;
+    pieces = unit_bytes / piece_bytes;
+    scale_chunks = r.local_scales != nullptr ? (unit_atoms + kAtomsPerChunk - 1) / kAtomsPerChunk : 0;
+    const int32_t chunks_full = (kBlockM / rows_per_chunk) * pieces + scale_chunks;
+    subs_per_unit = (chunks_full + 1) / 2;
+    subs_total = p.order.m_tiles * gates * subs_per_unit;
+    tile_rows_consecutive = (r.causal ? r.seq_local / 2 : r.seq_local) % kBlockM == 0;
+  }
+  // Decodes sub-unit c.sub; false when it holds no chunk (a short last M tile).
+  __device__ bool decode(Cursor& c) const {
+    const LhsRoute& r = p.lhs;
+    const int32_t unit = c.sub / subs_per_unit, q = c.sub - unit * subs_per_unit;
+    const int32_t per_group = r.m_group * gates;
+    const int32_t group = unit / per_group, mt0 = group * r.m_group;
+    const int32_t group_size = p.order.m_tiles - mt0 < r.m_group ? p.order.m_tiles - mt0 : r.m_group;
+    const int32_t within = unit - group * per_group;
+    const int32_t gate = within / group_size;
+    c.mt = mt0 + within - gate * group_size;
+    c.shard = gate / r.virt;
+    c.slice = gate - c.shard * r.virt;
+    const int32_t rows = p.m - c.mt * kBlockM < kBlockM ? p.m - c.mt * kBlockM : kBlockM;
+    c.data_chunks = ((rows + rows_per_chunk - 1) / rows_per_chunk) * pieces;
+    const int32_t total = c.data_chunks + scale_chunks;
+    c.first_chunk = 2 * q;
+    if (c.first_chunk >= total) return false;
+    c.chunks_here = total - c.first_chunk < 2 ? total - c.first_chunk : 2;
+    c.needed = (total + 1) / 2;
+    c.flag = (c.mt * r.world + c.shard) * kReadyFlagStride + 2 * c.slice;
+    c.peer = r.cyclic ? (r.rank + c.shard) % r.world : c.shard;
+    c.src_row0 = global_row(r.world, r.rank, r.seq_local, r.global_seq, r.causal != 0, c.mt * kBlockM);
+    c.chunk = 0;
+    return true;
+  }
+  __device__ bool seek(Cursor& c, int32_t workers) const {
+    for (; c.sub < subs_total; c.sub += workers)
+      if (decode(c)) return true;
+    return false;
+  }
+  __device__ bool first(Cursor& c, int32_t worker, int32_t workers) const {
+    c.sub = worker;
+    return seek(c, workers);
+  }
+  __device__ bool next(Cursor& c, int32_t workers) const {
+    if (++c.chunk < c.chunks_here) return true;
+    c.sub += workers;
+    return seek(c, workers);
+  }
+  __device__ bool load(const Cursor& c, uint32_t smem, uint32_t bar, int lane) const {
+    if (lane != 0) return true;
+    const LhsRoute& r = p.lhs;
+    if (r.peer_input_ready[c.peer] != nullptr && !((upstream_seen >> c.peer) & 1u)) {
+      // the peer's producer (attention) publishes one epoch per tensor
+      if (!flag_wait<true>(r.peer_input_ready[c.peer], r.input_epoch, p.wait, kSiteUpstreamReady, uint32_t(c.peer)))
+        return false;
+      upstream_seen |= 1u << c.peer;
+    }
+    const int32_t k = c.first_chunk + c.chunk;
+    if (k < c.data_chunks) {
+      const int32_t row_block = pieces == 1 ? k : k / pieces, piece = k - row_block * pieces;
+      // rows of one chunk are consecutive at the source: chunks never straddle a sequence block
+      const int64_t src_row = tile_rows_consecutive
+                                  ? c.src_row0 + row_block * rows_per_chunk
+                                  : global_row(r.world, r.rank, r.seq_local, r.global_seq, r.causal != 0,
+                                               c.mt * kBlockM + row_block * rows_per_chunk);
+      ptx::mbar_expect_tx(bar, uint32_t(rows_per_chunk) * uint32_t(piece_bytes));
+      ptx::tma_load_2d(smem, &maps.peer[c.peer], bar, (c.slice * unit_bytes + piece * piece_bytes) / 4, int32_t(src_row));
+    } else {
+      const int32_t first_atom = (k - c.data_chunks) * kAtomsPerChunk;
+      const int32_t atoms = unit_atoms - first_atom < kAtomsPerChunk ? unit_atoms - first_atom : kAtomsPerChunk;
+      ptx::mbar_expect_tx(bar, uint32_t(atoms) * 512u);
+      ptx::bulk_load(smem,
+                     r.peer_scales[c.peer] +
+                         ((c.src_row0 >> 7) * int64_t(r.shard_atoms) + int64_t(c.slice) * unit_atoms + first_atom) * 512,
+                     uint32_t(atoms) * 512u, bar);
+    }
+    return true;
+  }
+  __device__ void store(const Cursor& c, uint32_t smem, int lane) const {
+    if (lane != 0) return;
+    const LhsRoute& r = p.lhs;
+    const int32_t k = c.first_chunk + c.chunk;
+    if (k < c.data_chunks) {
+      const int32_t row_block = pieces == 1 ? k : k / pieces, piece = k - row_block * pieces;
+      ptx::tma_store_2d(&maps.staging, smem,
+                        int32_t((uint32_t(c.shard) * shard_bytes + uint32_t(c.slice * unit_bytes + piece * piece_bytes)) / 4u),
+                        c.mt * kBlockM + row_block * rows_per_chunk);
+    } else {
+      const int32_t first_atom = (k - c.data_chunks) * kAtomsPerChunk;
+      const int32_t atoms = unit_atoms - first_atom < kAtomsPerChunk ? unit_atoms - first_atom : kAtomsPerChunk;
+      ptx::bulk_store(r.local_scales + (int64_t(c.mt) * r.k_atoms + int64_t(c.shard) * r.shard_atoms +
+                                        int64_t(c.slice) * unit_atoms + first_atom) * 512,
+                      smem, uint32_t(atoms) * 512u);
+    }
+  }
+  __device__ bool closes(const Cursor& c) const { return c.chunk + 1 == c.chunks_here; }
+  __device__ int64_t unit(const Cursor& c) const { return c.sub; }
+  __device__ void publish_fence() const {}
+  // The acq_rel read-modify-write orders the completed copies (observed by the copy warp and
+  // handed over through shared memory) before the count; the consumer fences the proxies after
+  // its acquire.
+  __device__ void publish_flag(int64_t sub) const {
+    Cursor c;
+    c.sub = int32_t(sub);
+    if (!decode(c)) return;
+    const uint32_t before = ptx::atom_acq_rel_gpu_add(p.ready + c.flag + 1, 1u);
+    if ((before + 1u) % uint32_t(c.needed) == 0u) ptx::st_release_gpu(p.ready + c.flag, p.wait.epoch);
+  }
+};
 
 // QKV backward sender push with tensor copies (head_dim 128): unit = (destination M tile,
 // destination, local head), two chunks of 64 rows x 128 columns.  Destinations rotate from the
@@ -1051,12 +1231,13 @@ struct GradPushPolicy {
     c.x = where(c.unit);
     return true;
   }
-  __device__ void load(const Cursor& c, uint32_t smem, uint32_t bar, int lane) const {
-    if (lane != 0) return;
+  __device__ bool load(const Cursor& c, uint32_t smem, uint32_t bar, int lane) const {
+    if (lane != 0) return true;
     const GradRoute& g = p.grad;
     const int64_t src_row = global_row(g.world, c.x.dest, g.seq_local, g.global_seq, g.causal != 0, c.x.mt * kBlockM + c.chunk * 64);
     ptx::mbar_expect_tx(bar, 64u * 256u);
     ptx::tma_load_2d(smem, &maps.plane[c.x.segment], bar, c.x.local_head * 128, int32_t(src_row));
+    return true;
   }
   __device__ void store(const Cursor& c, uint32_t smem, int lane) const {
     if (lane != 0) return;
@@ -1120,8 +1301,8 @@ struct GradPullPolicy {
     c.x = where(c.unit);
     return true;
   }
-  __device__ void load(const Cursor& c, uint32_t smem, uint32_t bar, int lane) const {
-    if (lane != 0) return;
+  __device__ bool load(const Cursor& c, uint32_t smem, uint32_t bar, int lane) const {
+    if (lane != 0) return true;
     const Where& x = c.x;
     if (c.chunk == 0) {
       ptx::mbar_expect_tx(bar, 128u * 128u);
@@ -1135,6 +1316,7 @@ struct GradPullPolicy {
       ptx::bulk_load(smem, p.grad.peer_scales[x.owner][x.segment] + ((x.src_row >> 7) * x.seg_local + x.local_head) * 512,
                      512u, bar);
     }
+    return true;
   }
   __device__ void store(const Cursor& c, uint32_t smem, int lane) const {
     if (lane != 0) return;
@@ -1360,8 +1542,13 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
   if (is_comm && !skip_role) {
     if constexpr (kMode == kModeQkvPush) qkv_push_role<kBlockN>(p, smem);
     if constexpr (kMode == kModeLhsPull) {
-      if (p.flags & kFlagVectorPull) lhs_pull_role(p, smem);
-      else lhs_pull_bulk_role(p, base);
+      if constexpr (std::is_same<Maps, LhsPullMaps>::value) {
+        LhsPullPolicy policy(p, store_maps);
+        run_chunk_pipeline(policy, p.wait, base, p.num_comm_ctas);
+      } else {
+        if (p.flags & kFlagVectorPull) lhs_pull_role(p, smem);
+        else lhs_pull_bulk_role(p, base);
+      }
     }
     if constexpr (kMode == kModeHeadGate) {
       if constexpr (std::is_same<Maps, GradPushMaps>::value) {
@@ -1450,8 +1637,8 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
               // (backward).  The gate scout (warp 3) polls the flags, 32 at a time and ahead of
               // this thread, and posts how far this tile's groups are complete.
               constexpr bool kHeads = kMode != kModeLhsPull;
-              const int32_t group_width = kHeads ? p.grad.head_dim : p.lhs.shard_width;
-              const int32_t groups = kHeads ? p.grad.q_heads + 2 * p.grad.kv_heads : p.lhs.world;
+              const int32_t group_width = kHeads ? p.grad.head_dim : p.lhs.virt_width;
+              const int32_t groups = kHeads ? p.grad.q_heads + 2 * p.grad.kv_heads : p.lhs.world * p.lhs.virt;
               int32_t last = (kb * kBlockElems + kBlockElems - 1) / group_width;
               if (last >= groups) last = groups - 1;
               if (gated_upto < last) {
@@ -1588,14 +1775,15 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
       if constexpr (kGated) {
         constexpr bool kRemoteWriter = kMode == kModeHeadGate;  // flags released by the sending GPUs
         constexpr bool kHeads = kMode != kModeLhsPull;
-        const int32_t groups = kHeads ? p.grad.q_heads + 2 * p.grad.kv_heads : p.lhs.world;
+        const int32_t groups = kHeads ? p.grad.q_heads + 2 * p.grad.kv_heads : p.lhs.world * p.lhs.virt;
+        const int32_t virt = kHeads ? 1 : p.lhs.virt;  // column slices sharing one flag line
         TileWalk walk = walk_template;
         uint32_t tile_seq = 0;
         bool ok = true;
         for (int64_t t = walk.first(); ok && t >= 0; t = walk.next(), ++tile_seq) {
           int32_t mt, nt;
           p.order.decode(t, mt, nt);
-          const uint32_t* flags = p.ready + int64_t(mt) * groups * kReadyFlagStride;
+          const uint32_t* flags = p.ready + int64_t(mt) * (groups / virt) * kReadyFlagStride;
           int32_t prefix = 0;
           uint32_t spin = 0;
           uint64_t start = 0;
@@ -1604,7 +1792,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const int32_t g = prefix + lane;
             uint32_t seen = 0u;
             if (g < groups && (spin == 0u || lane < 4)) {
-              const uint32_t* flag = flags + int64_t(g) * kReadyFlagStride;
+              const uint32_t* flag = flags + int64_t(g / virt) * kReadyFlagStride + 2 * (g % virt);
               seen = kRemoteWriter ? ptx::ld_acquire_sys(flag) : ptx::ld_acquire_gpu(flag);
             }
             const uint32_t complete = __ballot_sync(0xffffffffu, seen >= p.wait.epoch);

@@ -84,6 +84,17 @@ inline int32_t wave_m_group(const FusedParams& p, int sm_count) {
   return group < 1 ? 1 : group;
 }
 
+// Column slices of the lhs pull: the largest power of two (at most 16, the pairs of words a flag
+// line holds) that keeps a slice at least 1 KiB wide and a whole number of 128-byte K blocks.
+inline void plan_lhs_slices(FusedParams* p, int sm_count) {
+  const int64_t shard_bytes = int64_t(p->lhs.shard_width) * p->lhs.element_bytes;
+  int virt = 1;
+  while (virt < 16 && shard_bytes % (2 * virt * 128) == 0 && shard_bytes / (2 * virt) >= 1024) virt *= 2;
+  p->lhs.virt = virt;
+  p->lhs.virt_width = p->lhs.shard_width / virt;
+  p->lhs.m_group = wave_m_group(*p, sm_count);
+}
+
 inline void plan_join(FusedParams* p, int block_n, int sm_count, double comm_bytes, bool block_scaled) {
   const int64_t tiles = p->order.count();
   const int comm = p->num_comm_ctas;
@@ -151,6 +162,33 @@ inline cudaError_t encode_copy_map(CUtensorMap* map, const void* base, uint32_t 
                                     element_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8,
                                     element_bytes, rows, cols, cols * element_bytes, box_rows, box_cols,
                                     CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
+// Tensor maps of the forward lhs pull (LhsPullPolicy).  False when the geometry does not fit the
+// tensor copies (the caller then runs the bulk-copy pull with one gate per shard): a slice must
+// be a whole number of power-of-two pieces of at most 1 KiB, and the rows of one chunk must be
+// consecutive in the peer's tensor.
+inline bool encode_lhs_pull_maps(LhsPullMaps* maps, const FusedParams& f, uint64_t source_rows) {
+  const LhsRoute& r = f.lhs;
+  const uint32_t unit_bytes = uint32_t(r.virt_width) * uint32_t(r.element_bytes);
+  const uint64_t shard_bytes = uint64_t(r.shard_width) * uint64_t(r.element_bytes);
+  const uint64_t staging_pitch = uint64_t(r.lda) * uint64_t(r.element_bytes);
+  uint32_t piece = 1024;
+  while (piece >= 128 && unit_bytes % piece != 0) piece /= 2;
+  if (piece < 128 || shard_bytes % 16 != 0 || staging_pitch % 16 != 0) return false;
+  const uint32_t rows_per_chunk = kPullStageBytes / piece < uint32_t(kBlockM) ? kPullStageBytes / piece : uint32_t(kBlockM);
+  const int32_t row_block = r.causal ? r.seq_local / 2 : r.seq_local;
+  if (row_block % int32_t(rows_per_chunk) != 0) return false;
+  maps->piece_bytes = int32_t(piece);
+  maps->rows_per_chunk = int32_t(rows_per_chunk);
+  for (int peer = 0; peer < r.world; ++peer)
+    if (host::encode_tensor_map_2d(&maps->peer[peer], r.peer_input[peer], CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, source_rows,
+                                   shard_bytes / 4, shard_bytes, rows_per_chunk, piece / 4,
+                                   CU_TENSOR_MAP_SWIZZLE_NONE) != cudaSuccess)
+      return false;
+  return host::encode_tensor_map_2d(&maps->staging, r.staging, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, uint64_t(f.m),
+                                    uint64_t(f.k) * uint64_t(r.element_bytes) / 4, staging_pitch, rows_per_chunk,
+                                    piece / 4, CU_TENSOR_MAP_SWIZZLE_NONE) == cudaSuccess;
 }
 
 inline bool vector_epilogue_requested(const fuse_b200_options* options) {

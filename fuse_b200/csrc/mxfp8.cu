@@ -334,7 +334,16 @@ cudaError_t oproj_forward_mxfp8(const fuse_mxfp8_a2a_gemm_params& mp, const fuse
     f.lhs.peer_scales[peer] = mp.activation[peer].scales;
     f.lhs.peer_input_ready[peer] = p.peer_input_ready[peer];
   }
+  plan_lhs_slices(&f, info.sm_count);
   plan_join(&f, block_n, info.sm_count, double(g.m) * g.k * (1.0 + 1.0 / 32), true);
+  if (!(f.flags & kFlagVectorPull)) {
+    LhsPullMaps pull{};
+    if (launch::encode_lhs_pull_maps(&pull, f, uint64_t(r.batch) * uint64_t(r.global_seq)))
+      return launch_mode<kModeLhsPull, false, false, true, LhsPullMaps>(maps, pull, f, block_n, info, stream,
+                                                                        !vector_epilogue_requested(options));
+  }
+  f.lhs.virt = 1;  // bulk-copy or vector pull: one gate per shard
+  f.lhs.virt_width = f.lhs.shard_width;
   StoreMaps stores{};
   return launch_mode<kModeLhsPull, false, false, true>(maps, stores, f, block_n, info, stream,
                                                        !vector_epilogue_requested(options));

@@ -6,6 +6,7 @@
 #include <cstring>
 
 #include "launch.cuh"
+#include "pair_gemm.cuh"
 
 namespace fuse_b200 {
 namespace {
@@ -59,6 +60,33 @@ bool qkv_direct_push(const fuse_b200_options* options) {
   return false;
 }
 
+// CTA-pair tiles (256 x 256 on two SMs, pair_gemm.cuh) are used wherever the shape allows;
+// the environment switch FUSE_B200_PAIR=0 (read on every launch) selects the one-CTA tiles.
+bool pair_tiles_requested() {
+  const char* text = std::getenv("FUSE_B200_PAIR");
+  return text == nullptr || std::atoi(text) != 0;
+}
+
+// Launches pair_gemm_kernel over `k` (whose tile order is re-planned for 256-row tiles).
+template <bool kDirect>
+cudaError_t launch_pair(const void* a, int64_t lda, const void* b, int64_t ldb, const fuse_gemm_problem& g,
+                        StoreMaps& stores, FusedParams k, const DeviceInfo& info, cudaStream_t stream) {
+  Operands maps;
+  cudaError_t status = encode_operand(&maps.a, a, g.m, g.k, lda, false, kBlockM);
+  if (status != cudaSuccess) return status;
+  if ((status = encode_operand(&maps.b, b, g.n, g.k, ldb, false, PairLayout::kBlockN / 2)) != cudaSuccess) return status;
+  if ((status = encode_store_map(&stores.local, k.d, uint64_t(k.m), uint64_t(k.n), k.ldd)) != cudaSuccess) return status;
+  k.order.m_tiles = host::ceil_div(g.m, 2 * kBlockM);
+  k.order.n_tiles = host::ceil_div(g.n, PairLayout::kBlockN);
+  k.order.swizzle = select_swizzle(g.max_swizzle_size, k.order.m_tiles, k.order.n_tiles);
+  if (kDirect) k.order.n_shift = int32_t(int64_t(k.qkv.rank) * k.order.n_tiles / k.qkv.world);
+  k.join_tile = k.order.count();
+  const int64_t tiles = k.order.count();
+  const int pairs = int(tiles < info.sm_count / 2 ? tiles : info.sm_count / 2);
+  return host::launch_kernel(pair_gemm_kernel<kDirect>, 2 * pairs, kThreads, PairLayout::kDynamicBytes, kDirect, stream,
+                             maps.a, maps.b, stores, k);
+}
+
 // detail/gemm_a2a.cuh:237-299 (can_implement) for the plain QKV GQA pack route.
 cudaError_t check_qkv_route(const fuse_gemm_a2a_params& p) {
   const fuse_ulysses_route& r = p.route;
@@ -109,6 +137,8 @@ cudaError_t qkv_forward(const fuse_gemm_a2a_params& p, const fuse_b200_options* 
   k.ready = p.ready;
   k.flags = options ? options->flags : 0u;
   k.wait = host::make_wait(info, p.epoch, options ? options->wait_budget_ns : 0);
+  // ranks start at different column tiles so that their pushes go to different owners
+  k.order.n_shift = int32_t(int64_t(p.route.rank) * k.order.n_tiles / p.route.world_size);
   k.qkv.world = p.route.world_size;
   k.qkv.rank = p.route.rank;
   k.qkv.batch = p.route.batch;
@@ -133,6 +163,9 @@ cudaError_t qkv_forward(const fuse_gemm_a2a_params& p, const fuse_b200_options* 
                                  int64_t(r.q_heads) / r.world_size * r.head_dim,
                                  int64_t(r.kv_heads) / r.world_size * r.head_dim);
   }
+  if (tma && block_n == 256 && pair_tiles_requested())
+    return launch_pair<true>(p.lhs, packed_or(p.gemm.stride_a.row, p.gemm.k), p.rhs_nt,
+                             packed_or(p.gemm.stride_b.row, p.gemm.k), p.gemm, stores, k, info, stream);
   return launch_mode<kModeQkvDirect>(maps, stores, k, block_n, info, stream, tma);
 }
 
@@ -216,6 +249,7 @@ cudaError_t oproj_forward(const fuse_a2a_gemm_params& p, const fuse_b200_options
   }
   k.lhs.virt = 1;  // bulk-copy or vector pull: one gate per shard
   k.lhs.virt_width = k.lhs.shard_width;
+  if (k.lhs.gate_start != 0) k.lhs.gate_start = k.lhs.rank;
   StoreMaps stores{};
   return launch_mode<kModeLhsPull>(maps, stores, k, block_n, info, stream,
                                    !vector_epilogue_requested(options));
@@ -243,6 +277,9 @@ cudaError_t plain_gemm(const fuse_gemm_problem& g, const void* a, const void* b,
   DeviceInfo reduced = info;
   reduced.sm_count = info.sm_count - reserved_comm_ctas;
   StoreMaps stores{};
+  if (block_n == 256 && pair_tiles_requested())
+    return launch_pair<false>(a, packed_or(g.stride_a.row, g.k), b, packed_or(g.stride_b.row, g.k), g, stores, k,
+                              reduced, stream);
   return launch_mode<kModePlain>(maps, stores, k, block_n, reduced, stream, true);
 }
 

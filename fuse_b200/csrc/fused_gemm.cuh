@@ -128,6 +128,10 @@ struct LhsRoute {
   // that a GEMM tile starts on the first slice instead of the whole shard.  m_group: M tiles one
   // GEMM wave works on together; their slices are delivered side by side.
   int32_t virt, virt_width, m_group;
+  // The GEMM walks K starting at this rank's own shard (gate_start = first column slice of it,
+  // k_block_start the matching K block) and wraps around: the first K blocks need no transfer,
+  // and at any moment every rank pulls from a different peer.
+  int32_t gate_start, k_block_start;
 };
 
 // QKV backward reverse route (head -> sequence), sender side: this rank holds planar
@@ -537,7 +541,8 @@ __device__ __forceinline__ void lhs_pull_bulk_role(const FusedParams& p, uint32_
       const int32_t group = unit / per_group, mt0 = group * r.m_group;
       const int32_t group_size = p.order.m_tiles - mt0 < r.m_group ? p.order.m_tiles - mt0 : r.m_group;
       const int32_t within = unit - group * per_group;
-      const int32_t gate = within / group_size, mt = mt0 + within - gate * group_size;
+      const int32_t position = within / group_size, mt = mt0 + within - position * group_size;
+      const int32_t gate = position + r.gate_start < gates ? position + r.gate_start : position + r.gate_start - gates;
       const int32_t shard = gate / r.virt, slice = gate - shard * r.virt;
       const int32_t rows_in_unit = p.m - mt * kBlockM < kBlockM ? p.m - mt * kBlockM : kBlockM;
       const int32_t row0 = quarter * sub_rows;
@@ -1084,8 +1089,9 @@ struct LhsPullPolicy {
     const int32_t group = unit / per_group, mt0 = group * r.m_group;
     const int32_t group_size = p.order.m_tiles - mt0 < r.m_group ? p.order.m_tiles - mt0 : r.m_group;
     const int32_t within = unit - group * per_group;
-    const int32_t gate = within / group_size;
-    c.mt = mt0 + within - gate * group_size;
+    const int32_t position = within / group_size;  // in the GEMM's (rotated) K order
+    c.mt = mt0 + within - position * group_size;
+    const int32_t gate = position + r.gate_start < gates ? position + r.gate_start : position + r.gate_start - gates;
     c.shard = gate / r.virt;
     c.slice = gate - c.shard * r.virt;
     const int32_t rows = p.m - c.mt * kBlockM < kBlockM ? p.m - c.mt * kBlockM : kBlockM;
@@ -1631,7 +1637,13 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           int32_t mt, nt;
           p.order.decode(t, mt, nt);
           int32_t gated_upto = -1;  // highest K group already acquired for this tile
-          for (int32_t kb = 0; kb < k_blocks; ++kb) {
+          for (int32_t ki = 0; ki < k_blocks; ++ki) {
+            // K block loaded at step ki: the lhs pull starts at this rank's own shard and wraps.
+            int32_t kb = ki;
+            if constexpr (kMode == kModeLhsPull) {
+              kb += p.lhs.k_block_start;
+              if (kb >= k_blocks) kb -= k_blocks;
+            }
             if constexpr (kGated) {
               // K groups whose rows arrive separately: peers' shards (forward pull) or Q/K/V heads
               // (backward).  The gate scout (warp 3) polls the flags, 32 at a time and ahead of
@@ -1639,16 +1651,16 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
               constexpr bool kHeads = kMode != kModeLhsPull;
               const int32_t group_width = kHeads ? p.grad.head_dim : p.lhs.virt_width;
               const int32_t groups = kHeads ? p.grad.q_heads + 2 * p.grad.kv_heads : p.lhs.world * p.lhs.virt;
-              int32_t last = (kb * kBlockElems + kBlockElems - 1) / group_width;
+              int32_t last = (ki * kBlockElems + kBlockElems - 1) / group_width;  // position in K order
               if (last >= groups) last = groups - 1;
               if (gated_upto < last) {
-                if (kb == 0) trace_event(p, 10);  // first gate wait of the tile begins
+                if (ki == 0) trace_event(p, 10);  // first gate wait of the tile begins
                 uint32_t seen = 0;
                 ok = progress_wait(gate_word, tile_seq * kGateSeqStep + uint32_t(last) + 1u, p.wait, kSiteLhsReady,
                                    uint32_t(mt * groups + last), &seen);
                 // One proxy fence covers every group the scout has posted so far.
                 ptx::fence_proxy_async_global();
-                if (kb == 0) trace_event(p, 11);  // first gate passed
+                if (ki == 0) trace_event(p, 11);  // first gate passed
                 gated_upto = (seen / kGateSeqStep) > tile_seq ? groups - 1 : int32_t(seen % kGateSeqStep) - 1;
               }
               if (!ok) break;
@@ -1792,7 +1804,12 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             const int32_t g = prefix + lane;
             uint32_t seen = 0u;
             if (g < groups && (spin == 0u || lane < 4)) {
-              const uint32_t* flag = flags + int64_t(g / virt) * kReadyFlagStride + 2 * (g % virt);
+              int32_t gate = g;  // position g of the GEMM's K order -> gate index
+              if constexpr (!kHeads) {
+                gate += p.lhs.gate_start;
+                if (gate >= groups) gate -= groups;
+              }
+              const uint32_t* flag = flags + int64_t(gate / virt) * kReadyFlagStride + 2 * (gate % virt);
               seen = kRemoteWriter ? ptx::ld_acquire_sys(flag) : ptx::ld_acquire_gpu(flag);
             }
             const uint32_t complete = __ballot_sync(0xffffffffu, seen >= p.wait.epoch);

@@ -93,6 +93,12 @@ inline void plan_lhs_slices(FusedParams* p, int sm_count) {
   p->lhs.virt = virt;
   p->lhs.virt_width = p->lhs.shard_width / virt;
   p->lhs.m_group = wave_m_group(*p, sm_count);
+  // K rotation: start at this rank's own shard when shards are whole K blocks.
+  const int block_elems = p->lhs.element_bytes == 1 ? 2 * kBlockK : kBlockK;
+  const bool rotate = p->lhs.shard_width % block_elems == 0 && p->k == p->lhs.shard_width * p->lhs.world;
+  const int shard_first = p->lhs.cyclic ? 0 : p->lhs.rank;  // cyclic order already puts the own shard first
+  p->lhs.gate_start = rotate ? shard_first * virt : 0;
+  p->lhs.k_block_start = rotate ? shard_first * (p->lhs.shard_width / block_elems) : 0;
 }
 
 inline void plan_join(FusedParams* p, int block_n, int sm_count, double comm_bytes, bool block_scaled) {

@@ -344,6 +344,7 @@ cudaError_t oproj_forward_mxfp8(const fuse_mxfp8_a2a_gemm_params& mp, const fuse
   }
   f.lhs.virt = 1;  // bulk-copy or vector pull: one gate per shard
   f.lhs.virt_width = f.lhs.shard_width;
+  if (f.lhs.gate_start != 0) f.lhs.gate_start = f.lhs.rank;
   StoreMaps stores{};
   return launch_mode<kModeLhsPull, false, false, true>(maps, stores, f, block_n, info, stream,
                                                        !vector_epilogue_requested(options));

@@ -1,0 +1,242 @@
+// BF16 NT GEMM on CTA pairs: two CTAs of a cluster, resident on the two SMs of one TPC, work on
+// one 256 x 256 output tile with `tcgen05.mma.cta_group::2`.
+//
+// Each CTA keeps the A rows of its half of the tile (128 x 64 per K block) and HALF of the B tile
+// (128 of the 256 weight rows); the tensor cores of both SMs read both halves, so a CTA moves and
+// holds 32 KiB per K block instead of 48 KiB -- six pipeline stages instead of four, and a third
+// less shared-memory traffic per FLOP, which is what bounds the one-CTA 128 x 256 tile.  The
+// accumulator rows of each CTA stay in its own TMEM (two stages of 256 columns).
+//
+// Roles per CTA: warp 0 TMA producer (its own A and B halves; the byte counts of both CTAs land
+// on the LEADER's full barrier), warp 1 UMMA issuer (leader CTA only; its commits arrive on the
+// empty / accumulator-full barriers of both CTAs), warp 2 TMEM allocator (same warp in both
+// CTAs), warps 4-7 epilogue (both CTAs; the peer's epilogue threads release the accumulator on
+// the leader's barrier through the cluster's shared-memory window).
+//
+// Modes: plain GEMM, and the QKV projection whose epilogue stores every 64-column block into the
+// local output and into the owning peer's planar Q | K | V tensor (no communication CTAs).
+// Replaces the 2-SM instances of csrc/operators/sm103/detail/cutlass_pipeline.cuh of the
+// reference (tile m256n256k64), written directly against the instructions.
+#pragma once
+
+#include <cooperative_groups.h>
+
+#include "fused_gemm.cuh"
+
+namespace fuse_b200 {
+
+struct PairLayout {
+  static constexpr int kStages = 6;
+  static constexpr int kAccumStages = 2;
+  static constexpr int kBlockN = 256;                                  // of the pair's tile
+  static constexpr uint32_t kABytes = kBlockM * kBlockK * 2;           // this CTA's 128 rows
+  static constexpr uint32_t kBBytes = (kBlockN / 2) * kBlockK * 2;     // this CTA's half of B
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr uint32_t kStagingBuffers = 2;
+  static constexpr uint32_t kStagingBlockBytes = kBlockM * 64 * 2;
+  static constexpr uint32_t kStagingOffset = kStages * kStageBytes;
+  static constexpr uint32_t kBarrierOffset = kStagingOffset + kStagingBuffers * kStagingBlockBytes;
+  static constexpr uint32_t kNumBarriers = 2 * kStages + 2 * kAccumStages;
+  static constexpr uint32_t kTmemSlotOffset = kBarrierOffset + kNumBarriers * 8;
+  static constexpr uint32_t kBytes = kTmemSlotOffset + 16;
+  static constexpr uint32_t kDynamicBytes = kBytes + 1024;
+  static constexpr uint32_t kTmemColumns = 512;
+  static_assert(kDynamicBytes <= 227 * 1024, "shared memory budget");
+  static_assert(kDynamicBytes > 114 * 1024, "must force one CTA per SM");
+};
+
+// kDirect: QKV projection with the direct route (FusedParams::qkv, StoreMaps::peer).
+template <bool kDirect>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ StoreMaps store_maps, const FusedParams p) {
+  using Layout = PairLayout;
+  constexpr int kStages = Layout::kStages;
+  constexpr int kBlockN = Layout::kBlockN;
+  constexpr uint32_t kAccumStages = Layout::kAccumStages;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;  // the same offset in both CTAs of the pair
+  uint8_t* smem = smem_raw + (base - raw_addr);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();  // 0: leader (issues the UMMAs)
+  const bool leader = rank == 0;
+
+  const uint32_t bar_base = base + Layout::kBarrierOffset;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+  auto tmem_full_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };
+  auto tmem_empty_bar = [&](int s) { return bar_base + 8u * (2 * kStages + kAccumStages + s); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + Layout::kTmemSlotOffset);
+
+  if (threadIdx.x == 0) {
+    ptx::prefetch_tensormap(&tmap_a);
+    ptx::prefetch_tensormap(&tmap_b);
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(full_bar(s), 1);   // the leader's expect_tx arrival; bytes from both CTAs
+      ptx::mbar_init(empty_bar(s), 1);  // one commit arrival per phase, in each CTA
+    }
+    for (int s = 0; s < int(kAccumStages); ++s) {
+      ptx::mbar_init(tmem_full_bar(s), 1);                      // commit arrival, in each CTA
+      ptx::mbar_init(tmem_empty_bar(s), 2 * kEpilogueThreads);  // both CTAs' epilogues (leader's copy is used)
+    }
+    ptx::fence_mbar_init();
+  }
+  if (warp == 2) {
+    ptx::tmem_alloc_pair(base + Layout::kTmemSlotOffset, Layout::kTmemColumns);
+    ptx::tmem_relinquish_pair();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync();  // barriers of both CTAs exist before anything arrives on them
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int32_t pairs = int32_t(gridDim.x) / 2, pair_id = int32_t(blockIdx.x) / 2;
+  const int64_t tiles = p.order.count();  // tiles of 256 x 256
+  const int32_t k_blocks = (p.k + kBlockK - 1) / kBlockK;
+  bool unwound = false;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int64_t t = pair_id; ok && t < tiles; t += pairs) {
+        int32_t mp, nt;
+        p.order.decode(t, mp, nt);
+        const int32_t row0 = mp * 2 * kBlockM + int32_t(rank) * kBlockM;          // this CTA's A rows
+        const int32_t wrow0 = nt * kBlockN + int32_t(rank) * (kBlockN / 2);      // this CTA's half of B
+        for (int32_t kb = 0; kb < k_blocks; ++kb) {
+          ok = mbar_wait(empty_bar(stage), phase ^ 1u, p.wait, kSiteSmemEmpty);
+          if (!ok) break;
+          const uint32_t a_dst = base + stage * Layout::kStageBytes;
+          const uint32_t leader_full = ptx::map_to_cta(full_bar(stage), 0);
+          if (leader) ptx::mbar_expect_tx(full_bar(stage), 2 * Layout::kStageBytes);
+          ptx::tma_load_2d_pair(a_dst, &tmap_a, leader_full, kb * kBlockK, row0);
+          ptx::tma_load_2d_pair(a_dst + Layout::kABytes, &tmap_b, leader_full, kb * kBlockK, wrow0);
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      unwound = !ok;
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ UMMA issuer (leader CTA)
+    if (lane == 0 && leader) {
+      constexpr uint32_t kIdesc = ptx::idesc_bf16_f32(2 * kBlockM, kBlockN, 0, 0);
+      uint32_t stage = 0, phase = 0, accum = 0, accum_phase = 0;
+      bool ok = true;
+      for (int64_t t = pair_id; ok && t < tiles; t += pairs) {
+        ok = mbar_wait(tmem_empty_bar(accum), accum_phase ^ 1u, p.wait, kSiteTmemEmpty);
+        if (!ok) break;
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + accum * kBlockN;
+        for (int32_t kb = 0; kb < k_blocks; ++kb) {
+          ok = mbar_wait(full_bar(stage), phase, p.wait, kSiteSmemFull);
+          if (!ok) break;
+          ptx::tc_fence_after();
+          const uint32_t a_addr = base + stage * Layout::kStageBytes;
+          const uint64_t a_desc = ptx::smem_desc_k_sw128(a_addr);
+          const uint64_t b_desc = ptx::smem_desc_k_sw128(a_addr + Layout::kABytes);
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k)
+            ptx::umma_f16_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+          ptx::umma_commit_pair(empty_bar(stage), 3);  // frees the stage in both CTAs
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        ptx::umma_commit_pair(tmem_full_bar(accum), 3);
+        if (++accum == kAccumStages) { accum = 0; accum_phase ^= 1u; }
+      }
+      if (!ok) {
+        // Unwinding: UMMAs already issued must retire before TMEM is released.
+        ptx::umma_commit_pair(tmem_full_bar(accum), 3);
+        mbar_wait(tmem_full_bar(accum), accum_phase, p.wait, kSiteDrain, false);
+      }
+      unwound = !ok;
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ epilogue (both CTAs)
+    const int quarter = warp & 3;
+    const int epi_tid = threadIdx.x - 128;
+    const uint32_t leader_tmem_empty0 = ptx::map_to_cta(tmem_empty_bar(0), 0);
+    const uint32_t leader_tmem_empty1 = ptx::map_to_cta(tmem_empty_bar(1), 0);
+    uint32_t accum = 0, accum_phase = 0, staged_blocks = 0;
+    bool ok = true;
+    for (int64_t t = pair_id; ok && t < tiles; t += pairs) {
+      int32_t mp, nt;
+      p.order.decode(t, mp, nt);
+      const int32_t mt = mp * 2 + int32_t(rank);  // this CTA's 128-row tile
+      ok = mbar_wait(tmem_full_bar(accum), accum_phase, p.wait, kSiteTmemFull);
+      ok = ptx::named_bar_all(2, kEpilogueThreads, ok);
+      if (!ok) break;
+      ptx::tc_fence_after();
+      const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + accum * kBlockN;
+      const int32_t row_in_tile = quarter * 32 + lane;
+#pragma unroll 1
+      for (int c = 0; c < kBlockN; c += 64) {
+        const uint32_t staging =
+            base + Layout::kStagingOffset + (staged_blocks % Layout::kStagingBuffers) * Layout::kStagingBlockBytes;
+        ++staged_blocks;
+        if (epi_tid == 0) ptx::bulk_wait_read<Layout::kStagingBuffers - 1>();
+        ptx::named_bar_sync(1, kEpilogueThreads);
+        uint32_t acc0[32], acc1[32];
+        ptx::tmem_ld_32x32b_x32(taddr + c, acc0);
+        ptx::tmem_ld_32x32b_x32(taddr + c + 32, acc1);
+        ptx::tmem_wait_ld();
+        if (c + 64 >= kBlockN) {
+          // Accumulator read: hand the stage back to the leader's UMMA issuer.
+          ptx::tc_fence_before();
+          ptx::mbar_arrive_cluster(accum ? leader_tmem_empty1 : leader_tmem_empty0);
+        }
+        const uint32_t row_addr = staging + uint32_t(row_in_tile) * 128u;
+        stage_accumulators(acc0, row_addr, 0, row_in_tile, p.alpha);
+        stage_accumulators(acc1, row_addr, 4, row_in_tile, p.alpha);
+        ptx::fence_proxy_async_shared();
+        ptx::named_bar_sync(1, kEpilogueThreads);
+        if (epi_tid == 0) {
+          const int32_t col = nt * kBlockN + c;
+          if (col < p.n && mt * kBlockM < p.m) {
+            ptx::tma_store_2d(&store_maps.local, staging, col, mt * kBlockM);
+            if constexpr (kDirect) {
+              const QkvRoute& r = p.qkv;
+              const int32_t q_width = r.q_heads * r.head_dim, kv_width = r.kv_heads * r.head_dim;
+              const int32_t segment = col < q_width ? 0 : (col < q_width + kv_width ? 1 : 2);
+              const int32_t within = col - (segment == 0 ? 0 : q_width + (segment == 2 ? kv_width : 0));
+              const int32_t local_width = (segment == 0 ? q_width : kv_width) / r.world;
+              const int32_t owner = within / local_width;
+              ptx::tma_store_2d(&store_maps.peer[owner][segment], staging, within - owner * local_width,
+                                int32_t(global_row(r.world, r.rank, r.seq_local, r.global_seq, r.causal != 0,
+                                                   mt * kBlockM)));
+            }
+          }
+          ptx::bulk_commit();
+        }
+      }
+      if (++accum == kAccumStages) { accum = 0; accum_phase ^= 1u; }
+    }
+    if (epi_tid == 0) ptx::bulk_wait<0>();  // every tensor store of this CTA is performed
+    unwound = !ok;
+  }
+
+  if (unwound) {
+    // A wait gave up: copies that were started may still be landing in either CTA's shared
+    // memory.  Give them time before the pair is torn down (error path only).
+    const uint64_t start = ptx::globaltimer();
+    while (ptx::globaltimer() - start < 200000ull) __nanosleep(1000);
+  }
+  if constexpr (kDirect) __threadfence_system();  // peer stores performed
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync();  // neither CTA leaves (or frees TMEM) while the other may still touch it
+  if (warp == 2) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc_pair(tmem_base, Layout::kTmemColumns);
+  }
+  if constexpr (kDirect) {
+    cooperative_groups::this_grid().sync();
+    qkv_finalize(p);
+  }
+}
+
+}  // namespace fuse_b200

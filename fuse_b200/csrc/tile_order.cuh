@@ -18,6 +18,10 @@ struct TileOrder {
   int32_t n_tiles = 0;
   int32_t swizzle = 1;    // 1, 2, 4 or 8
   int32_t along_n = 0;    // 0: linear index runs along M first; 1: along N first
+  // Every rank of a context-parallel group walks the same order; shifting the N coordinate by a
+  // rank-dependent number of tiles makes the ranks work on different column ranges -- and thus
+  // push to different owners -- at any moment, instead of all writing to the same peer.
+  int32_t n_shift = 0;
 
   __host__ __device__ int64_t count() const { return int64_t(m_tiles) * n_tiles; }
 
@@ -33,11 +37,19 @@ struct TileOrder {
     const int32_t b = band_begin + within % width;  // position along the minor axis
     m = along_n ? b : a;
     n = along_n ? a : b;
+    if (n_shift != 0) {
+      n += n_shift;
+      if (n >= n_tiles) n -= n_tiles;
+    }
   }
 
   __host__ __device__ int64_t linear(int32_t m, int32_t n) const {
     const int32_t major = along_n ? n_tiles : m_tiles;
     const int32_t minor = along_n ? m_tiles : n_tiles;
+    if (n_shift != 0) {
+      n -= n_shift;
+      if (n < 0) n += n_tiles;
+    }
     const int32_t a = along_n ? n : m, b = along_n ? m : n;
     const int32_t band = b / swizzle, band_begin = band * swizzle;
     const int32_t width = minor - band_begin < swizzle ? minor - band_begin : swizzle;

@@ -67,10 +67,10 @@ bool pair_tiles_requested() {
   return text == nullptr || std::atoi(text) != 0;
 }
 
-// Launches pair_gemm_kernel over `k` (whose tile order is re-planned for 256-row tiles).
-template <bool kDirect>
+// Launches pair_gemm_kernel over `k`, whose tile order is re-planned for 256-row tiles.
+template <int kMode, class Maps>
 cudaError_t launch_pair(const void* a, int64_t lda, const void* b, int64_t ldb, const fuse_gemm_problem& g,
-                        StoreMaps& stores, FusedParams k, const DeviceInfo& info, cudaStream_t stream) {
+                        Maps& stores, FusedParams k, const DeviceInfo& info, cudaStream_t stream, double comm_bytes = 0.0) {
   Operands maps;
   cudaError_t status = encode_operand(&maps.a, a, g.m, g.k, lda, false, kBlockM);
   if (status != cudaSuccess) return status;
@@ -79,12 +79,13 @@ cudaError_t launch_pair(const void* a, int64_t lda, const void* b, int64_t ldb, 
   k.order.m_tiles = host::ceil_div(g.m, 2 * kBlockM);
   k.order.n_tiles = host::ceil_div(g.n, PairLayout::kBlockN);
   k.order.swizzle = select_swizzle(g.max_swizzle_size, k.order.m_tiles, k.order.n_tiles);
-  if (kDirect) k.order.n_shift = int32_t(int64_t(k.qkv.rank) * k.order.n_tiles / k.qkv.world);
+  if (kMode == kModeQkvDirect) k.order.n_shift = int32_t(int64_t(k.qkv.rank) * k.order.n_tiles / k.qkv.world);
   k.join_tile = k.order.count();
+  if (kMode == kModeLhsPull) plan_join(&k, PairLayout::kBlockN, info.sm_count, comm_bytes, false, 2);
   const int64_t tiles = k.order.count();
-  const int pairs = int(tiles < info.sm_count / 2 ? tiles : info.sm_count / 2);
-  return host::launch_kernel(pair_gemm_kernel<kDirect>, 2 * pairs, kThreads, PairLayout::kDynamicBytes, kDirect, stream,
-                             maps.a, maps.b, stores, k);
+  const int compute_pairs = int(tiles < (info.sm_count - k.num_comm_ctas) / 2 ? tiles : (info.sm_count - k.num_comm_ctas) / 2);
+  return host::launch_kernel(pair_gemm_kernel<kMode, Maps>, k.num_comm_ctas + 2 * compute_pairs, kThreads,
+                             PairLayout::kDynamicBytes, kMode != kModePlain, stream, maps.a, maps.b, stores, k);
 }
 
 // detail/gemm_a2a.cuh:237-299 (can_implement) for the plain QKV GQA pack route.
@@ -164,7 +165,7 @@ cudaError_t qkv_forward(const fuse_gemm_a2a_params& p, const fuse_b200_options* 
                                  int64_t(r.kv_heads) / r.world_size * r.head_dim);
   }
   if (tma && block_n == 256 && pair_tiles_requested())
-    return launch_pair<true>(p.lhs, packed_or(p.gemm.stride_a.row, p.gemm.k), p.rhs_nt,
+    return launch_pair<kModeQkvDirect>(p.lhs, packed_or(p.gemm.stride_a.row, p.gemm.k), p.rhs_nt,
                              packed_or(p.gemm.stride_b.row, p.gemm.k), p.gemm, stores, k, info, stream);
   return launch_mode<kModeQkvDirect>(maps, stores, k, block_n, info, stream, tma);
 }
@@ -243,6 +244,16 @@ cudaError_t oproj_forward(const fuse_a2a_gemm_params& p, const fuse_b200_options
   plan_join(&k, block_n, info.sm_count, double(p.gemm.m) * p.gemm.k * 2.0, false);
   if (!(k.flags & kFlagVectorPull)) {
     LhsPullMaps pull{};
+    if (encode_lhs_pull_maps(&pull, k, uint64_t(p.route.batch) * uint64_t(p.route.global_seq))) {
+      // CTA pairs: whole pairs of communication CTAs, 256-row tiles (the slices of the M tiles of
+      // one wave are then delivered for twice as many 128-row tiles)
+      if (block_n == 256 && num_comm_ctas % 2 == 0 && info.sm_count % 2 == 0 && pair_tiles_requested()) {
+        FusedParams pk = k;
+        pk.lhs.m_group = 2 * wave_m_group_pairs(pk, info.sm_count);
+        return launch_pair<kModeLhsPull>(p.input_staging, lda, p.rhs_nt, packed_or(p.gemm.stride_b.row, p.gemm.k), p.gemm,
+                                         pull, pk, info, stream, double(p.gemm.m) * p.gemm.k * 2.0);
+      }
+    }
     if (encode_lhs_pull_maps(&pull, k, uint64_t(p.route.batch) * uint64_t(p.route.global_seq)))
       return launch_mode<kModeLhsPull, false, false, false, LhsPullMaps>(maps, pull, k, block_n, info, stream,
                                                                          !vector_epilogue_requested(options));
@@ -278,7 +289,7 @@ cudaError_t plain_gemm(const fuse_gemm_problem& g, const void* a, const void* b,
   reduced.sm_count = info.sm_count - reserved_comm_ctas;
   StoreMaps stores{};
   if (block_n == 256 && pair_tiles_requested())
-    return launch_pair<false>(a, packed_or(g.stride_a.row, g.k), b, packed_or(g.stride_b.row, g.k), g, stores, k,
+    return launch_pair<kModePlain>(a, packed_or(g.stride_a.row, g.k), b, packed_or(g.stride_b.row, g.k), g, stores, k,
                               reduced, stream);
   return launch_mode<kModePlain>(maps, stores, k, block_n, reduced, stream, true);
 }

@@ -1061,7 +1061,7 @@ struct LhsPullPolicy {
   const FusedParams& p;
   const LhsPullMaps& maps;
   int32_t gates, pieces, rows_per_chunk, piece_bytes, unit_bytes, unit_atoms, scale_chunks;
-  int32_t subs_per_unit, subs_total;
+  int32_t subs_per_unit, subs_total, m_tiles;  // m_tiles: 128-row tiles (the launch's tile order may use taller ones)
   uint32_t shard_bytes;
   bool tile_rows_consecutive;  // the 128 rows of every M tile are consecutive at the source
   mutable uint32_t upstream_seen = 0;
@@ -1078,7 +1078,8 @@ struct LhsPullPolicy {
     scale_chunks = r.local_scales != nullptr ? (unit_atoms + kAtomsPerChunk - 1) / kAtomsPerChunk : 0;
     const int32_t chunks_full = (kBlockM / rows_per_chunk) * pieces + scale_chunks;
     subs_per_unit = (chunks_full + 1) / 2;
-    subs_total = p.order.m_tiles * gates * subs_per_unit;
+    m_tiles = (p.m + kBlockM - 1) / kBlockM;
+    subs_total = m_tiles * gates * subs_per_unit;
     tile_rows_consecutive = (r.causal ? r.seq_local / 2 : r.seq_local) % kBlockM == 0;
   }
   // Decodes sub-unit c.sub; false when it holds no chunk (a short last M tile).
@@ -1087,7 +1088,7 @@ struct LhsPullPolicy {
     const int32_t unit = c.sub / subs_per_unit, q = c.sub - unit * subs_per_unit;
     const int32_t per_group = r.m_group * gates;
     const int32_t group = unit / per_group, mt0 = group * r.m_group;
-    const int32_t group_size = p.order.m_tiles - mt0 < r.m_group ? p.order.m_tiles - mt0 : r.m_group;
+    const int32_t group_size = m_tiles - mt0 < r.m_group ? m_tiles - mt0 : r.m_group;
     const int32_t within = unit - group * per_group;
     const int32_t position = within / group_size;  // in the GEMM's (rotated) K order
     c.mt = mt0 + within - position * group_size;
@@ -1482,6 +1483,56 @@ __device__ __forceinline__ void mxfp8_quantize_rows(const uint16_t* source, int6
 // The tile sequence of one CTA: compute CTAs first take every compute_ctas-th tile below
 // join_tile, then every CTA of the grid (communication CTAs included) takes every
 // all_ctas-th tile from join_tile on.
+// Gate scout, one tile: the lanes of one warp acquire the flags of the tile's K groups (32 at a
+// time, in the GEMM's K order, which starts at `gate_start` and wraps) and lane 0 posts the
+// complete prefix, plus `progress_base`, to the shared-memory word the TMA producer watches.
+// `virt` groups share one flag line (words 0, 2, 4, ...).  False when the wait gave up.
+constexpr uint32_t kGateSeqStep = 65536u;  // progress word = tiles walked * step + complete groups
+template <bool kRemoteWriter>
+__device__ __forceinline__ bool scout_tile(const WaitContext& w, const uint32_t* flags, int32_t groups, int32_t virt,
+                                           int32_t gate_start, uint32_t gate_word, uint32_t progress_base, int lane,
+                                           uint32_t index_base) {
+  int32_t prefix = 0;
+  uint32_t spin = 0;
+  uint64_t start = 0;
+  while (prefix < groups) {
+    // while stalled only the next few flags are polled
+    const int32_t g = prefix + lane;
+    uint32_t seen = 0u;
+    if (g < groups && (spin == 0u || lane < 4)) {
+      int32_t gate = g + gate_start;  // position g of the K order -> gate index
+      if (gate >= groups) gate -= groups;
+      const uint32_t* flag = flags + int64_t(gate / virt) * kReadyFlagStride + 2 * (gate % virt);
+      seen = kRemoteWriter ? ptx::ld_acquire_sys(flag) : ptx::ld_acquire_gpu(flag);
+    }
+    const uint32_t complete = __ballot_sync(0xffffffffu, seen >= w.epoch);
+    const int32_t n = complete == 0xffffffffu ? 32 : __ffs(int(~complete)) - 1;
+    if (n > 0) {
+      prefix = prefix + n < groups ? prefix + n : groups;
+      __syncwarp();  // every lane's acquire is ordered before the release below
+      if (lane == 0) ptx::st_release_cta_shared(gate_word, progress_base + uint32_t(prefix));
+      spin = 0u;
+      continue;
+    }
+    if (spin == 0u) start = ptx::globaltimer();
+    __nanosleep(64);
+    if ((++spin & 15u) == 0u) {
+      uint32_t stop = 0u;
+      if (lane == 0) {
+        if (aborted(w)) {
+          stop = 1u;
+        } else if (ptx::globaltimer() - start > w.budget_ns) {
+          report_timeout(w, kRemoteWriter ? kStatusPeerTimeout : kStatusFlagTimeout, kSiteLhsReady,
+                         index_base + uint32_t(prefix), seen, w.epoch);
+          stop = 1u;
+        }
+      }
+      if (__shfl_sync(0xffffffffu, stop, 0)) return false;
+    }
+  }
+  return true;
+}
+
 struct TileWalk {
   int64_t t, join_tile, tiles;
   int32_t compute_id, all_id, compute_ctas, all_ctas;
@@ -1620,7 +1671,6 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     constexpr int32_t kBlockElems = kMx ? 2 * kBlockK : kBlockK;  // K elements per 128-byte row
     constexpr bool kGated = kMode == kModeLhsPull || kMode == kModeHeadGate || kMode == kModeGradPull;
     // Gate progress word: (tiles this CTA has walked) * kGateSeqStep + complete groups of the current one.
-    constexpr uint32_t kGateSeqStep = 65536u;
     const uint32_t gate_word = base + Layout::kTmemSlotOffset + 8u;
     (void)gate_word;
     const int32_t k_blocks = (p.k + kBlockElems - 1) / kBlockElems;
@@ -1796,47 +1846,8 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           int32_t mt, nt;
           p.order.decode(t, mt, nt);
           const uint32_t* flags = p.ready + int64_t(mt) * (groups / virt) * kReadyFlagStride;
-          int32_t prefix = 0;
-          uint32_t spin = 0;
-          uint64_t start = 0;
-          while (prefix < groups) {
-            // while stalled only the next few flags are polled
-            const int32_t g = prefix + lane;
-            uint32_t seen = 0u;
-            if (g < groups && (spin == 0u || lane < 4)) {
-              int32_t gate = g;  // position g of the GEMM's K order -> gate index
-              if constexpr (!kHeads) {
-                gate += p.lhs.gate_start;
-                if (gate >= groups) gate -= groups;
-              }
-              const uint32_t* flag = flags + int64_t(gate / virt) * kReadyFlagStride + 2 * (gate % virt);
-              seen = kRemoteWriter ? ptx::ld_acquire_sys(flag) : ptx::ld_acquire_gpu(flag);
-            }
-            const uint32_t complete = __ballot_sync(0xffffffffu, seen >= p.wait.epoch);
-            const int32_t n = complete == 0xffffffffu ? 32 : __ffs(int(~complete)) - 1;
-            if (n > 0) {
-              prefix = prefix + n < groups ? prefix + n : groups;
-              __syncwarp();  // every lane's acquire is ordered before the release below
-              if (lane == 0) ptx::st_release_cta_shared(gate_word, tile_seq * kGateSeqStep + uint32_t(prefix));
-              spin = 0u;
-              continue;
-            }
-            if (spin == 0u) start = ptx::globaltimer();
-            __nanosleep(64);
-            if ((++spin & 15u) == 0u) {
-              uint32_t stop = 0u;
-              if (lane == 0) {
-                if (aborted(p.wait)) {
-                  stop = 1u;
-                } else if (ptx::globaltimer() - start > p.wait.budget_ns) {
-                  report_timeout(p.wait, kRemoteWriter ? kStatusPeerTimeout : kStatusFlagTimeout, kSiteLhsReady,
-                                 uint32_t(mt * groups + prefix), seen, p.wait.epoch);
-                  stop = 1u;
-                }
-              }
-              if (__shfl_sync(0xffffffffu, stop, 0)) { ok = false; break; }
-            }
-          }
+          ok = scout_tile<kRemoteWriter>(p.wait, flags, groups, virt, kHeads ? 0 : p.lhs.gate_start, gate_word,
+                                         tile_seq * kGateSeqStep, lane, uint32_t(mt * groups));
         }
       }
     } else if (warp >= 4) {

@@ -84,6 +84,19 @@ inline int32_t wave_m_group(const FusedParams& p, int sm_count) {
   return group < 1 ? 1 : group;
 }
 
+// The same for CTA pairs (256-row tiles): result in 256-row tiles.
+inline int32_t wave_m_group_pairs(const FusedParams& p, int sm_count) {
+  const int32_t compute = (sm_count - p.num_comm_ctas) / 2;
+  const int32_t m_tiles = (p.m + 2 * kBlockM - 1) / (2 * kBlockM);
+  const int32_t n_tiles = (p.n + 255) / 256;
+  const int32_t smaller = m_tiles < n_tiles ? m_tiles : n_tiles;
+  int32_t swizzle = p.order.swizzle > 0 ? p.order.swizzle : 1;
+  while (swizzle > 1 && swizzle > smaller) swizzle /= 2;
+  int32_t group = p.order.along_n ? swizzle : (compute + swizzle - 1) / swizzle;
+  if (group > m_tiles) group = m_tiles;
+  return group < 1 ? 1 : group;
+}
+
 // Column slices of the lhs pull: the largest power of two (at most 16, the pairs of words a flag
 // line holds) that keeps a slice at least 1 KiB wide and a whole number of 128-byte K blocks.
 inline void plan_lhs_slices(FusedParams* p, int sm_count) {
@@ -101,16 +114,21 @@ inline void plan_lhs_slices(FusedParams* p, int sm_count) {
   p->lhs.k_block_start = rotate ? shard_first * (p->lhs.shard_width / block_elems) : 0;
 }
 
-inline void plan_join(FusedParams* p, int block_n, int sm_count, double comm_bytes, bool block_scaled) {
+// `group` = CTAs that work on one tile together (2 for CTA pairs: `order` then counts 256-row
+// tiles and the waves are waves of pairs).
+inline void plan_join(FusedParams* p, int block_n, int sm_count, double comm_bytes, bool block_scaled,
+                      int group = 1) {
   const int64_t tiles = p->order.count();
-  const int comm = p->num_comm_ctas;
+  const int comm = p->num_comm_ctas / group;
   if (comm <= 0 || tiles <= 0) return;
   if (const char* text = std::getenv("FUSE_B200_JOIN_WAVES"))
     if (std::atoll(text) == 0) return;
-  const int64_t compute = tiles < sm_count - comm ? tiles : sm_count - comm;
+  const int64_t units = sm_count / group;
+  const int64_t compute = tiles < units - comm ? tiles : units - comm;
   const int64_t all = comm + compute;
-  const double tau = 2.0 * kBlockM * block_n * double(p->k) / (block_scaled ? 17.0e12 : 10.3e12);
-  const double t_c = 25.0e-6 + comm_bytes / (comm * 35.0e9);
+  // one tile per unit: a pair does twice the rows on twice the SMs
+  const double tau = 2.0 * kBlockM * block_n * double(p->k) / (block_scaled ? 17.0e12 : (group == 2 ? 11.0e12 : 10.3e12));
+  const double t_c = 25.0e-6 + comm_bytes / (p->num_comm_ctas * 35.0e9);
   double best = double((tiles + compute - 1) / compute) * tau;  // no sharing
   int64_t best_join = tiles;
   for (int64_t w1 = 0; w1 * compute < tiles; ++w1) {

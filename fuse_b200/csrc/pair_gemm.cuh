@@ -13,8 +13,11 @@
 // CTAs), warps 4-7 epilogue (both CTAs; the peer's epilogue threads release the accumulator on
 // the leader's barrier through the cluster's shared-memory window).
 //
-// Modes: plain GEMM, and the QKV projection whose epilogue stores every 64-column block into the
-// local output and into the owning peer's planar Q | K | V tensor (no communication CTAs).
+// Modes: plain GEMM; the QKV projection whose epilogue stores every 64-column block into the
+// local output and into the owning peer's planar Q | K | V tensor (no communication CTAs); and
+// the output projection fed by the lhs pull (communication CTAs, launched as whole pairs, run the
+// tensor-copy pull and join the GEMM afterwards; each compute CTA gates its own A rows on the
+// column-slice flags through its gate scout warp).
 // Replaces the 2-SM instances of csrc/operators/sm103/detail/cutlass_pipeline.cuh of the
 // reference (tile m256n256k64), written directly against the instructions.
 #pragma once
@@ -38,18 +41,24 @@ struct PairLayout {
   static constexpr uint32_t kBarrierOffset = kStagingOffset + kStagingBuffers * kStagingBlockBytes;
   static constexpr uint32_t kNumBarriers = 2 * kStages + 2 * kAccumStages;
   static constexpr uint32_t kTmemSlotOffset = kBarrierOffset + kNumBarriers * 8;
-  static constexpr uint32_t kBytes = kTmemSlotOffset + 16;
+  static constexpr uint32_t kComputeBytes = kTmemSlotOffset + 16;
+  // communication pairs lay the copy pipeline over the same allocation
+  static constexpr uint32_t kBytes = kComputeBytes > kPullSmemBytes ? kComputeBytes : kPullSmemBytes;
   static constexpr uint32_t kDynamicBytes = kBytes + 1024;
   static constexpr uint32_t kTmemColumns = 512;
   static_assert(kDynamicBytes <= 227 * 1024, "shared memory budget");
   static_assert(kDynamicBytes > 114 * 1024, "must force one CTA per SM");
 };
 
-// kDirect: QKV projection with the direct route (FusedParams::qkv, StoreMaps::peer).
-template <bool kDirect>
+// kMode: kModePlain, kModeQkvDirect (FusedParams::qkv, StoreMaps::peer) or kModeLhsPull
+// (FusedParams::lhs, LhsPullMaps; num_comm_ctas even).
+template <int kMode, class Maps>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ StoreMaps store_maps, const FusedParams p) {
+                 const __grid_constant__ Maps store_maps, const FusedParams p) {
+  static_assert(kMode == kModePlain || kMode == kModeQkvDirect || kMode == kModeLhsPull, "modes of the pair kernel");
+  constexpr bool kDirect = kMode == kModeQkvDirect;
+  constexpr bool kGated = kMode == kModeLhsPull;
   using Layout = PairLayout;
   constexpr int kStages = Layout::kStages;
   constexpr int kBlockN = Layout::kBlockN;
@@ -68,6 +77,24 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   auto tmem_full_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };
   auto tmem_empty_bar = [&](int s) { return bar_base + 8u * (2 * kStages + kAccumStages + s); };
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + Layout::kTmemSlotOffset);
+  const uint32_t gate_word = base + Layout::kTmemSlotOffset + 8u;
+
+  // Communication pairs first move the lhs; they take part in the GEMM afterwards when the
+  // host planned a share of tiles for them, and leave otherwise.
+  const bool is_comm = int(blockIdx.x) < p.num_comm_ctas;
+  const int64_t tiles = p.order.count();  // tiles of 256 x 256
+  if constexpr (kGated) {
+    if (is_comm) {
+      if (!(p.flags & kFlagComputeOnly)) {
+        LhsPullPolicy policy(p, store_maps);
+        run_chunk_pipeline(policy, p.wait, base, p.num_comm_ctas);
+      }
+      if (p.join_tile >= tiles || (p.flags & kFlagCommOnly)) return;  // both CTAs of the pair alike
+      __syncthreads();  // the copy pipeline's shared memory is free again
+    } else if (p.flags & kFlagCommOnly) {
+      return;
+    }
+  }
 
   if (threadIdx.x == 0) {
     ptx::prefetch_tensormap(&tmap_a);
@@ -81,6 +108,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       ptx::mbar_init(tmem_empty_bar(s), 2 * kEpilogueThreads);  // both CTAs' epilogues (leader's copy is used)
     }
     ptx::fence_mbar_init();
+    *reinterpret_cast<volatile uint32_t*>(smem + Layout::kTmemSlotOffset + 8) = 0u;  // gate progress
   }
   if (warp == 2) {
     ptx::tmem_alloc_pair(base + Layout::kTmemSlotOffset, Layout::kTmemColumns);
@@ -92,8 +120,15 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  const int32_t pairs = int32_t(gridDim.x) / 2, pair_id = int32_t(blockIdx.x) / 2;
-  const int64_t tiles = p.order.count();  // tiles of 256 x 256
+  // Tile walk in units of pairs: compute pairs own the tiles before join_tile, every pair shares
+  // the rest.
+  TileWalk walk_template;
+  walk_template.join_tile = p.join_tile < tiles ? p.join_tile : tiles;
+  walk_template.tiles = tiles;
+  walk_template.compute_ctas = (int32_t(gridDim.x) - p.num_comm_ctas) / 2;
+  walk_template.all_ctas = int32_t(gridDim.x) / 2;
+  walk_template.compute_id = is_comm ? -1 : (int32_t(blockIdx.x) - p.num_comm_ctas) / 2;
+  walk_template.all_id = is_comm ? walk_template.compute_ctas + int32_t(blockIdx.x) / 2 : walk_template.compute_id;
   const int32_t k_blocks = (p.k + kBlockK - 1) / kBlockK;
   bool unwound = false;
 
@@ -102,12 +137,32 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
-      for (int64_t t = pair_id; ok && t < tiles; t += pairs) {
+      TileWalk walk = walk_template;
+      uint32_t tile_seq = 0;
+      for (int64_t t = walk.first(); ok && t >= 0; t = walk.next(), ++tile_seq) {
         int32_t mp, nt;
         p.order.decode(t, mp, nt);
         const int32_t row0 = mp * 2 * kBlockM + int32_t(rank) * kBlockM;          // this CTA's A rows
         const int32_t wrow0 = nt * kBlockN + int32_t(rank) * (kBlockN / 2);      // this CTA's half of B
-        for (int32_t kb = 0; kb < k_blocks; ++kb) {
+        int32_t gated_upto = -1;
+        for (int32_t ki = 0; ki < k_blocks; ++ki) {
+          int32_t kb = ki;
+          if constexpr (kGated) {
+            // K starts at this rank's own shard and wraps; this CTA's rows arrive slice by slice
+            kb += p.lhs.k_block_start;
+            if (kb >= k_blocks) kb -= k_blocks;
+            const int32_t groups = p.lhs.world * p.lhs.virt;
+            int32_t last = (ki * kBlockK + kBlockK - 1) / p.lhs.virt_width;
+            if (last >= groups) last = groups - 1;
+            if (gated_upto < last) {
+              uint32_t seen = 0;
+              ok = progress_wait(gate_word, tile_seq * kGateSeqStep + uint32_t(last) + 1u, p.wait, kSiteLhsReady,
+                                 uint32_t((mp * 2 + int32_t(rank)) * groups + last), &seen);
+              ptx::fence_proxy_async_global();
+              gated_upto = (seen / kGateSeqStep) > tile_seq ? groups - 1 : int32_t(seen % kGateSeqStep) - 1;
+            }
+            if (!ok) break;
+          }
           ok = mbar_wait(empty_bar(stage), phase ^ 1u, p.wait, kSiteSmemEmpty);
           if (!ok) break;
           const uint32_t a_dst = base + stage * Layout::kStageBytes;
@@ -117,7 +172,9 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           ptx::tma_load_2d_pair(a_dst + Layout::kABytes, &tmap_b, leader_full, kb * kBlockK, wrow0);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
+        (void)gated_upto;
       }
+      (void)tile_seq;
       unwound = !ok;
     }
   } else if (warp == 1) {
@@ -126,7 +183,8 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       constexpr uint32_t kIdesc = ptx::idesc_bf16_f32(2 * kBlockM, kBlockN, 0, 0);
       uint32_t stage = 0, phase = 0, accum = 0, accum_phase = 0;
       bool ok = true;
-      for (int64_t t = pair_id; ok && t < tiles; t += pairs) {
+      TileWalk walk = walk_template;
+      for (int64_t t = walk.first(); ok && t >= 0; t = walk.next()) {
         ok = mbar_wait(tmem_empty_bar(accum), accum_phase ^ 1u, p.wait, kSiteTmemEmpty);
         if (!ok) break;
         ptx::tc_fence_after();
@@ -155,6 +213,26 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       }
       unwound = !ok;
     }
+  } else if (warp == 3) {
+    // ------------------------------------------------------------------ gate scout (both CTAs)
+    if constexpr (kGated) {
+      const int32_t groups = p.lhs.world * p.lhs.virt;
+      TileWalk walk = walk_template;
+      uint32_t tile_seq = 0;
+      bool ok = true;
+      for (int64_t t = walk.first(); ok && t >= 0; t = walk.next(), ++tile_seq) {
+        int32_t mp, nt;
+        p.order.decode(t, mp, nt);
+        const int32_t mt = mp * 2 + int32_t(rank);
+        if (mt * kBlockM >= p.m) {  // no rows in this half: nothing to wait for, the loads read zeros
+          if (lane == 0) ptx::st_release_cta_shared(gate_word, (tile_seq + 1u) * kGateSeqStep);
+          continue;
+        }
+        const uint32_t* flags = p.ready + int64_t(mt) * p.lhs.world * kReadyFlagStride;
+        ok = scout_tile<false>(p.wait, flags, groups, p.lhs.virt, p.lhs.gate_start, gate_word,
+                               tile_seq * kGateSeqStep, lane, uint32_t(mt * groups));
+      }
+    }
   } else if (warp >= 4) {
     // ------------------------------------------------------------------ epilogue (both CTAs)
     const int quarter = warp & 3;
@@ -163,7 +241,8 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const uint32_t leader_tmem_empty1 = ptx::map_to_cta(tmem_empty_bar(1), 0);
     uint32_t accum = 0, accum_phase = 0, staged_blocks = 0;
     bool ok = true;
-    for (int64_t t = pair_id; ok && t < tiles; t += pairs) {
+    TileWalk walk = walk_template;
+    for (int64_t t = walk.first(); ok && t >= 0; t = walk.next()) {
       int32_t mp, nt;
       p.order.decode(t, mp, nt);
       const int32_t mt = mp * 2 + int32_t(rank);  // this CTA's 128-row tile

@@ -142,8 +142,9 @@ def workload_config(n_gpus):
 # --------------------------------------------------------------------------------------------
 
 class ClockSampler:
-    """Reads (never sets) SM clock, power and clock-event reasons of one GPU every 2 ms through
-    NVML while the timed region runs, so that even a 50 ms region gets a few dozen samples;
+    """Reads (never sets) SM clock and clock-event reasons of one GPU through NVML every few
+    milliseconds while the timed region runs (a 50 ms region gets several samples; polling much
+    faster than that delays this process's own kernel launches);
     falls back to an `nvidia-smi -lms` child when the NVML python module is missing."""
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -151,7 +152,8 @@ class ClockSampler:
     REASON_BITS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20,
                    "sw_power_cap": 0x4}
 
-    def __init__(self, uuid: str | None):
+    def __init__(self, uuid: str | None, period_s: float = 0.01):
+        self.period_s = period_s
         self.samples, self.proc, self.thread, self.nvml, self.handle = [], None, None, None, None
         self.stop_flag = threading.Event()
         try:
@@ -185,7 +187,7 @@ class ClockSampler:
                 self.samples.append((time.perf_counter(), (sm, self.smax, mask)))
             except Exception:  # noqa: BLE001
                 pass
-            time.sleep(0.002)
+            time.sleep(self.period_s)
 
     def _read(self):
         for line in self.proc.stdout:
@@ -327,14 +329,17 @@ def run_gpu_arm(args):
             raise RuntimeError(f"device wait gave up during {where}: {status[:8]}")
 
     # ---- device-resident throughput ----------------------------------------------------------
+    # The clock sampler starts before the warm-up: opening NVML takes milliseconds, and a rank that
+    # entered the timed region late would make every other rank wait in its first launch.
+    sampler = (ClockSampler("GPU-" + str(torch.cuda.get_device_properties(local_rank).uuid), args.clock_period_ms * 1e-3)
+               if rank == 0 else None)
+    events = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 1)]
     barrier()
     for _ in range(args.warmup):
         step()
-    barrier()
     check_status("warm-up")
-    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(local_rank).uuid)) if rank == 0 else None
+    barrier()
     launches_before = api.launch_count()
-    events = [torch.cuda.Event(enable_timing=True) for _ in range(2 * args.steps + 1)]
     t0 = time.perf_counter()
     events[0].record(stream)
     for i in range(args.steps):
@@ -475,6 +480,7 @@ def main():
                         help="QKV routing from communication CTAs or from the GEMM epilogue")
     parser.add_argument("--e2e-steps", type=int, default=5)
     parser.add_argument("--cpu-rows", type=int, default=1024)
+    parser.add_argument("--clock-period-ms", type=float, default=10.0)
     parser.add_argument("--skip-cpu", action="store_true")
     parser.add_argument("--skip-pure", action="store_true")
     args = parser.parse_args()

@@ -474,7 +474,7 @@ def main():
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="fuse_b200", choices=["fuse_b200", "reference"])
     parser.add_argument("--qkv-comm", type=int, default=16)
-    parser.add_argument("--oproj-comm", type=int, default=16)
+    parser.add_argument("--oproj-comm", type=int, default=20)
     parser.add_argument("--swizzle", type=int, default=8)
     parser.add_argument("--qkv-route", default="direct", choices=["comm", "direct"],
                         help="QKV routing from communication CTAs or from the GEMM epilogue")

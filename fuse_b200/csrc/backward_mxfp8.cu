@@ -67,6 +67,16 @@ cudaError_t mx_gemm(const Quantised& a, const Quantised& b, fuse_bf16* d, int m,
   f.k_atoms = k / 128;
   f.wait = host::make_wait(info, 1, 0);
   StoreMaps stores{};
+  if (block_n == 256 && beta == 0.0f && k % 128 == 0 && info.sm_count % 2 == 0 && launch::pair_tiles_requested()) {
+    // CTA pairs: B boxed by half tiles, scale storage read through tensor maps
+    Operands pair_maps = maps;
+    CUtensorMap sfa_map, sfb_map;
+    if (encode_operand_u8(&pair_maps.b, b.data, n, k, k, 128) == cudaSuccess &&
+        launch::encode_scale_atoms(&sfa_map, a.scales, m, k) == cudaSuccess &&
+        launch::encode_scale_atoms(&sfb_map, b.scales, n, k) == cudaSuccess)
+      return launch::launch_pair_kernel<kModePlain, StoreMaps, true>(pair_maps, sfa_map, sfb_map, stores, f,
+                                                                     max_swizzle ? max_swizzle : 8, info, stream, 0.0);
+  }
   return launch_mode<kModePlain, false, false, true>(maps, stores, f, block_n, info, stream, beta == 0.0f);
 }
 
@@ -185,6 +195,20 @@ cudaError_t qkv_data(const fuse_mxfp8_qkv_backward_data_params& mp, const fuse_b
                   encode_copy_map(&pull.masters[peer][s], f.grad.peer_master[peer][s], 2, rows_global, plane_width, 64, 128) ==
                       cudaSuccess;
       }
+    if (encoded && block_n == 256 && p.num_comm_ctas % 2 == 0 && info.sm_count % 2 == 0 &&
+        !vector_epilogue_requested(options) && launch::pair_tiles_requested()) {
+      // CTA pairs: whole pairs of communication CTAs, 256-row tiles
+      Operands pair_maps = maps;
+      CUtensorMap sfa_map, sfb_map;
+      FusedParams pf = f;
+      pf.grad.m_group = 2 * launch::wave_m_group_pairs(pf, info.sm_count);
+      if (encode_operand_u8(&pair_maps.b, wq.data, n, k, k, 128) == cudaSuccess &&
+          launch::encode_scale_atoms(&sfa_map, f.sfa, m, k) == cudaSuccess &&
+          launch::encode_scale_atoms(&sfb_map, f.sfb, n, k) == cudaSuccess)
+        return launch::launch_pair_kernel<kModeGradPull, GradPullMaps, true>(
+            pair_maps, sfa_map, sfb_map, pull, pf, p.gemm_tuning.max_swizzle_size ? p.gemm_tuning.max_swizzle_size : 1, info,
+            stream, double(m) * k * (3.0 + 1.0 / 32));
+    }
     if (encoded)
       return launch_mode<kModeGradPull, false, false, true, GradPullMaps>(maps, pull, f, block_n, info, stream,
                                                                           !vector_epilogue_requested(options));

@@ -6,7 +6,6 @@
 #include <cstring>
 
 #include "launch.cuh"
-#include "pair_gemm.cuh"
 
 namespace fuse_b200 {
 namespace {
@@ -60,32 +59,17 @@ bool qkv_direct_push(const fuse_b200_options* options) {
   return false;
 }
 
-// CTA-pair tiles (256 x 256 on two SMs, pair_gemm.cuh) are used wherever the shape allows;
-// the environment switch FUSE_B200_PAIR=0 (read on every launch) selects the one-CTA tiles.
-bool pair_tiles_requested() {
-  const char* text = std::getenv("FUSE_B200_PAIR");
-  return text == nullptr || std::atoi(text) != 0;
-}
-
-// Launches pair_gemm_kernel over `k`, whose tile order is re-planned for 256-row tiles.
+// BF16 operands of the pair kernel: A boxes of 128 rows, B boxes of 128 rows (half a tile).
 template <int kMode, class Maps>
 cudaError_t launch_pair(const void* a, int64_t lda, const void* b, int64_t ldb, const fuse_gemm_problem& g,
-                        Maps& stores, FusedParams k, const DeviceInfo& info, cudaStream_t stream, double comm_bytes = 0.0) {
+                        Maps& stores, const FusedParams& k, const DeviceInfo& info, cudaStream_t stream,
+                        double comm_bytes = 0.0) {
   Operands maps;
   cudaError_t status = encode_operand(&maps.a, a, g.m, g.k, lda, false, kBlockM);
   if (status != cudaSuccess) return status;
   if ((status = encode_operand(&maps.b, b, g.n, g.k, ldb, false, PairLayout::kBlockN / 2)) != cudaSuccess) return status;
-  if ((status = encode_store_map(&stores.local, k.d, uint64_t(k.m), uint64_t(k.n), k.ldd)) != cudaSuccess) return status;
-  k.order.m_tiles = host::ceil_div(g.m, 2 * kBlockM);
-  k.order.n_tiles = host::ceil_div(g.n, PairLayout::kBlockN);
-  k.order.swizzle = select_swizzle(g.max_swizzle_size, k.order.m_tiles, k.order.n_tiles);
-  if (kMode == kModeQkvDirect) k.order.n_shift = int32_t(int64_t(k.qkv.rank) * k.order.n_tiles / k.qkv.world);
-  k.join_tile = k.order.count();
-  if (kMode == kModeLhsPull) plan_join(&k, PairLayout::kBlockN, info.sm_count, comm_bytes, false, 2);
-  const int64_t tiles = k.order.count();
-  const int compute_pairs = int(tiles < (info.sm_count - k.num_comm_ctas) / 2 ? tiles : (info.sm_count - k.num_comm_ctas) / 2);
-  return host::launch_kernel(pair_gemm_kernel<kMode, Maps>, k.num_comm_ctas + 2 * compute_pairs, kThreads,
-                             PairLayout::kDynamicBytes, kMode != kModePlain, stream, maps.a, maps.b, stores, k);
+  return launch::launch_pair_kernel<kMode, Maps, false>(maps, maps.a, maps.a, stores, k, g.max_swizzle_size, info, stream,
+                                                        comm_bytes);
 }
 
 // detail/gemm_a2a.cuh:237-299 (can_implement) for the plain QKV GQA pack route.

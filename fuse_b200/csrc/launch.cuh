@@ -7,6 +7,7 @@
 
 #include "fuse_b200.h"
 #include "fused_gemm.cuh"
+#include "pair_gemm.cuh"
 #include "host.cuh"
 
 namespace fuse_b200 {
@@ -213,6 +214,43 @@ inline bool encode_lhs_pull_maps(LhsPullMaps* maps, const FusedParams& f, uint64
   return host::encode_tensor_map_2d(&maps->staging, r.staging, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, uint64_t(f.m),
                                     uint64_t(f.k) * uint64_t(r.element_bytes) / 4, staging_pitch, rows_per_chunk,
                                     piece / 4, CU_TENSOR_MAP_SWIZZLE_NONE) == cudaSuccess;
+}
+
+// Launches pair_gemm_kernel (CTA pairs, 256 x 256 tiles) over `k`, whose tile order is re-planned
+// for 256-row tiles.  `maps.b` must box 128 rows (half a tile); sfa / sfb are only read by the
+// block-scaled variant.
+template <int kMode, class Maps, bool kMx>
+cudaError_t launch_pair_kernel(const Operands& maps, const CUtensorMap& sfa, const CUtensorMap& sfb, Maps& stores,
+                               FusedParams k, int max_swizzle, const DeviceInfo& info, cudaStream_t stream,
+                               double comm_bytes) {
+  using Layout = PairLayoutT<kMx>;
+  cudaError_t status = encode_store_map(&stores.local, k.d, uint64_t(k.m), uint64_t(k.n), k.ldd);
+  if (status != cudaSuccess) return status;
+  k.order.m_tiles = host::ceil_div(k.m, 2 * kBlockM);
+  k.order.n_tiles = host::ceil_div(k.n, Layout::kBlockN);
+  k.order.swizzle = select_swizzle(max_swizzle, k.order.m_tiles, k.order.n_tiles);
+  if (kMode == kModeQkvDirect) k.order.n_shift = int32_t(int64_t(k.qkv.rank) * k.order.n_tiles / k.qkv.world);
+  k.join_tile = k.order.count();
+  if (kMode == kModeLhsPull || kMode == kModeGradPull) plan_join(&k, Layout::kBlockN, info.sm_count, comm_bytes, kMx, 2);
+  const int64_t tiles = k.order.count();
+  const int compute_pairs = int(tiles < (info.sm_count - k.num_comm_ctas) / 2 ? tiles : (info.sm_count - k.num_comm_ctas) / 2);
+  return host::launch_kernel(pair_gemm_kernel<kMode, Maps, kMx>, k.num_comm_ctas + 2 * compute_pairs, kThreads,
+                             Layout::kDynamicBytes, kMode != kModePlain || kMx, stream, maps.a, maps.b, sfa, sfb, stores, k);
+}
+
+// Scale storage of a block-scaled operand ([rows, K] elements) as a tensor of 512-byte atoms,
+// one atom per row of 128 32-bit words.
+inline cudaError_t encode_scale_atoms(CUtensorMap* map, const void* scales, int64_t rows, int64_t k) {
+  const uint64_t atoms = uint64_t((rows + 127) / 128) * uint64_t((k + 127) / 128);
+  return host::encode_tensor_map_2d(map, scales, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, atoms, 128, 512, 1, 128,
+                                    CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
+// CTA-pair tiles are used wherever the shape allows; the environment switch FUSE_B200_PAIR=0
+// (read on every launch) selects the one-CTA tiles.
+inline bool pair_tiles_requested() {
+  const char* text = std::getenv("FUSE_B200_PAIR");
+  return text == nullptr || std::atoi(text) != 0;
 }
 
 inline bool vector_epilogue_requested(const fuse_b200_options* options) {

@@ -204,6 +204,15 @@ cudaError_t qkv_forward_mxfp8(const fuse_mxfp8_gemm_a2a_params& mp, const fuse_b
   if (!routed) {
     DeviceInfo reduced = info;
     reduced.sm_count = info.sm_count - p.num_comm_ctas;  // compute budget of the fused kernel
+    if (block_n == 256 && g.k % 128 == 0 && reduced.sm_count % 2 == 0 && launch::pair_tiles_requested()) {
+      Operands pair_maps = maps;
+      CUtensorMap sfa_map, sfb_map;
+      if (encode_operand_u8(&pair_maps.b, w.data, g.n, g.k, g.k, 128) == cudaSuccess &&
+          launch::encode_scale_atoms(&sfa_map, f.sfa, g.m, g.k) == cudaSuccess &&
+          launch::encode_scale_atoms(&sfb_map, f.sfb, g.n, g.k) == cudaSuccess)
+        return launch::launch_pair_kernel<kModePlain, StoreMaps, true>(pair_maps, sfa_map, sfb_map, stores, f,
+                                                                       g.max_swizzle_size, reduced, stream, 0.0);
+    }
     return launch_mode<kModePlain, false, false, true>(maps, stores, f, block_n, reduced, stream, true);
   }
   f.qkv.world = r.world_size;
@@ -338,6 +347,21 @@ cudaError_t oproj_forward_mxfp8(const fuse_mxfp8_a2a_gemm_params& mp, const fuse
   plan_join(&f, block_n, info.sm_count, double(g.m) * g.k * (1.0 + 1.0 / 32), true);
   if (!(f.flags & kFlagVectorPull)) {
     LhsPullMaps pull{};
+    if (launch::encode_lhs_pull_maps(&pull, f, uint64_t(r.batch) * uint64_t(r.global_seq))) {
+      if (block_n == 256 && g.k % 128 == 0 && p.num_comm_ctas % 2 == 0 && info.sm_count % 2 == 0 &&
+          launch::pair_tiles_requested()) {
+        // CTA pairs: whole pairs of communication CTAs, 256-row tiles
+        Operands pair_maps = maps;
+        CUtensorMap sfa_map, sfb_map;
+        FusedParams pf = f;
+        pf.lhs.m_group = 2 * launch::wave_m_group_pairs(pf, info.sm_count);
+        if (encode_operand_u8(&pair_maps.b, w.weights.data, g.n, g.k, g.k, 128) == cudaSuccess &&
+            launch::encode_scale_atoms(&sfa_map, f.sfa, g.m, g.k) == cudaSuccess &&
+            launch::encode_scale_atoms(&sfb_map, f.sfb, g.n, g.k) == cudaSuccess)
+          return launch::launch_pair_kernel<kModeLhsPull, LhsPullMaps, true>(
+              pair_maps, sfa_map, sfb_map, pull, pf, g.max_swizzle_size, info, stream, double(g.m) * g.k * (1.0 + 1.0 / 32));
+      }
+    }
     if (launch::encode_lhs_pull_maps(&pull, f, uint64_t(r.batch) * uint64_t(r.global_seq)))
       return launch_mode<kModeLhsPull, false, false, true, LhsPullMaps>(maps, pull, f, block_n, info, stream,
                                                                         !vector_epilogue_requested(options));

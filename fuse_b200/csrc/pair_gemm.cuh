@@ -28,16 +28,23 @@
 
 namespace fuse_b200 {
 
-struct PairLayout {
+// kMx: block-scaled E4M3 operands.  A K block is then 128 one-byte elements (the same 128-byte
+// rows); every stage also carries the 512-byte scale atom of this CTA's A rows and the two atoms
+// of ALL 256 B rows (each CTA's tensor core needs the scales of the whole B tile); the
+// accumulator is single-buffered (TMEM also holds the scales) and drained whole by the epilogue.
+template <bool kMx>
+struct PairLayoutT {
   static constexpr int kStages = 6;
-  static constexpr int kAccumStages = 2;
+  static constexpr int kAccumStages = kMx ? 1 : 2;
   static constexpr int kBlockN = 256;                                  // of the pair's tile
   static constexpr uint32_t kABytes = kBlockM * kBlockK * 2;           // this CTA's 128 rows
   static constexpr uint32_t kBBytes = (kBlockN / 2) * kBlockK * 2;     // this CTA's half of B
   static constexpr uint32_t kStageBytes = kABytes + kBBytes;
-  static constexpr uint32_t kStagingBuffers = 2;
+  static constexpr uint32_t kSfStageBytes = kMx ? 512u * 3u : 0u;      // SFA, SFB rows 0-127, SFB rows 128-255
+  static constexpr uint32_t kSfOffset = kStages * kStageBytes;
+  static constexpr uint32_t kStagingBuffers = kMx ? 1 : 2;
   static constexpr uint32_t kStagingBlockBytes = kBlockM * 64 * 2;
-  static constexpr uint32_t kStagingOffset = kStages * kStageBytes;
+  static constexpr uint32_t kStagingOffset = kSfOffset + ((kStages * kSfStageBytes + 1023u) & ~1023u);
   static constexpr uint32_t kBarrierOffset = kStagingOffset + kStagingBuffers * kStagingBlockBytes;
   static constexpr uint32_t kNumBarriers = 2 * kStages + 2 * kAccumStages;
   static constexpr uint32_t kTmemSlotOffset = kBarrierOffset + kNumBarriers * 8;
@@ -46,21 +53,33 @@ struct PairLayout {
   static constexpr uint32_t kBytes = kComputeBytes > kPullSmemBytes ? kComputeBytes : kPullSmemBytes;
   static constexpr uint32_t kDynamicBytes = kBytes + 1024;
   static constexpr uint32_t kTmemColumns = 512;
+  // TMEM: accumulator stage(s), then (kMx) two alternating sets of scale columns: 4 for A, 8 for B.
+  static constexpr uint32_t kSfColumns = kMx ? 12u : 0u;
+  static constexpr uint32_t kTmemSfOffset = kAccumStages * kBlockN;
+  static_assert(kTmemSfOffset + 2 * kSfColumns <= kTmemColumns, "TMEM budget");
   static_assert(kDynamicBytes <= 227 * 1024, "shared memory budget");
   static_assert(kDynamicBytes > 114 * 1024, "must force one CTA per SM");
 };
+using PairLayout = PairLayoutT<false>;
 
 // kMode: kModePlain, kModeQkvDirect (FusedParams::qkv, StoreMaps::peer) or kModeLhsPull
 // (FusedParams::lhs, LhsPullMaps; num_comm_ctas even).
-template <int kMode, class Maps>
+// kMx: block-scaled E4M3 (tmap_sfa / tmap_sfb: the operands' scale storage as rows of one 512-byte
+// atom, 128 32-bit words); FusedParams::wq_* / clear_* request the weight quantisation prologue.
+template <int kMode, class Maps, bool kMx = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                  const __grid_constant__ Maps store_maps, const FusedParams p) {
-  static_assert(kMode == kModePlain || kMode == kModeQkvDirect || kMode == kModeLhsPull, "modes of the pair kernel");
+  static_assert(kMode == kModePlain || kMode == kModeQkvDirect || kMode == kModeLhsPull || kMode == kModeGradPull,
+                "modes of the pair kernel");
+  static_assert(kMode != kModeGradPull || kMx, "the gradient pull feeds the block-scaled GEMM");
   constexpr bool kDirect = kMode == kModeQkvDirect;
-  constexpr bool kGated = kMode == kModeLhsPull;
-  using Layout = PairLayout;
+  constexpr bool kGated = kMode == kModeLhsPull || kMode == kModeGradPull;
+  constexpr bool kHeads = kMode == kModeGradPull;  // K groups are Q/K/V heads, one flag line each
+  using Layout = PairLayoutT<kMx>;
   constexpr int kStages = Layout::kStages;
+  constexpr int32_t kBlockElems = kMx ? 2 * kBlockK : kBlockK;  // K elements per 128-byte row
   constexpr int kBlockN = Layout::kBlockN;
   constexpr uint32_t kAccumStages = Layout::kAccumStages;
   extern __shared__ uint8_t smem_raw[];
@@ -79,22 +98,47 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + Layout::kTmemSlotOffset);
   const uint32_t gate_word = base + Layout::kTmemSlotOffset + 8u;
 
+  if constexpr (kMx) {
+    // Preparation by every CTA of the (cooperative) grid, then one grid-wide join: quantise the
+    // BF16 master weight into the workspace, clear the library-owned flag words.
+    if (p.wq_source != nullptr || p.clear_words != nullptr) {
+      const int64_t first = int64_t(blockIdx.x) * kThreads + threadIdx.x;
+      const int64_t step = int64_t(gridDim.x) * kThreads;
+      if (p.wq_source != nullptr)
+        mxfp8_quantize_rows(p.wq_source, p.wq_stride, p.wq_rows, p.wq_k, p.wq_data, p.wq_scales, first, step);
+      for (int64_t i = first; i < p.clear_count; i += step) p.clear_words[i] = 0u;
+      __threadfence();
+      ptx::fence_proxy_async_global();  // the quantised bytes are read by TMA after the join
+      cooperative_groups::this_grid().sync();
+    }
+  }
+
   // Communication pairs first move the lhs; they take part in the GEMM afterwards when the
   // host planned a share of tiles for them, and leave otherwise.
   const bool is_comm = int(blockIdx.x) < p.num_comm_ctas;
   const int64_t tiles = p.order.count();  // tiles of 256 x 256
+  bool do_compute = true;
   if constexpr (kGated) {
     if (is_comm) {
       if (!(p.flags & kFlagComputeOnly)) {
-        LhsPullPolicy policy(p, store_maps);
-        run_chunk_pipeline(policy, p.wait, base, p.num_comm_ctas);
+        if constexpr (kHeads) {
+          GradPullPolicy policy(p, store_maps);
+          run_chunk_pipeline(policy, p.wait, base, p.num_comm_ctas);
+        } else {
+          LhsPullPolicy policy(p, store_maps);
+          run_chunk_pipeline(policy, p.wait, base, p.num_comm_ctas);
+        }
       }
-      if (p.join_tile >= tiles || (p.flags & kFlagCommOnly)) return;  // both CTAs of the pair alike
-      __syncthreads();  // the copy pipeline's shared memory is free again
+      if (p.join_tile >= tiles || (p.flags & kFlagCommOnly)) do_compute = false;  // both CTAs of the pair alike
+      // The copy pipelines of BOTH CTAs of the pair are done before either re-uses its shared
+      // memory for the GEMM: the pair's TMEM allocation and barriers involve both CTAs.
+      __syncthreads();
+      ptx::cluster_sync();
     } else if (p.flags & kFlagCommOnly) {
-      return;
+      do_compute = false;
     }
   }
+  if (do_compute) {
 
   if (threadIdx.x == 0) {
     ptx::prefetch_tensormap(&tmap_a);
@@ -129,7 +173,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   walk_template.all_ctas = int32_t(gridDim.x) / 2;
   walk_template.compute_id = is_comm ? -1 : (int32_t(blockIdx.x) - p.num_comm_ctas) / 2;
   walk_template.all_id = is_comm ? walk_template.compute_ctas + int32_t(blockIdx.x) / 2 : walk_template.compute_id;
-  const int32_t k_blocks = (p.k + kBlockK - 1) / kBlockK;
+  const int32_t k_blocks = (p.k + kBlockElems - 1) / kBlockElems;
   bool unwound = false;
 
   if (warp == 0) {
@@ -148,11 +192,15 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int32_t ki = 0; ki < k_blocks; ++ki) {
           int32_t kb = ki;
           if constexpr (kGated) {
-            // K starts at this rank's own shard and wraps; this CTA's rows arrive slice by slice
-            kb += p.lhs.k_block_start;
-            if (kb >= k_blocks) kb -= k_blocks;
-            const int32_t groups = p.lhs.world * p.lhs.virt;
-            int32_t last = (ki * kBlockK + kBlockK - 1) / p.lhs.virt_width;
+            // forward pull: K starts at this rank's own shard and wraps; this CTA's rows arrive
+            // slice by slice.  Gradient pull: head by head, in order.
+            if constexpr (!kHeads) {
+              kb += p.lhs.k_block_start;
+              if (kb >= k_blocks) kb -= k_blocks;
+            }
+            const int32_t groups = kHeads ? p.grad.q_heads + 2 * p.grad.kv_heads : p.lhs.world * p.lhs.virt;
+            const int32_t group_width = kHeads ? p.grad.head_dim : p.lhs.virt_width;
+            int32_t last = (ki * kBlockElems + kBlockElems - 1) / group_width;
             if (last >= groups) last = groups - 1;
             if (gated_upto < last) {
               uint32_t seen = 0;
@@ -167,9 +215,18 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (!ok) break;
           const uint32_t a_dst = base + stage * Layout::kStageBytes;
           const uint32_t leader_full = ptx::map_to_cta(full_bar(stage), 0);
-          if (leader) ptx::mbar_expect_tx(full_bar(stage), 2 * Layout::kStageBytes);
-          ptx::tma_load_2d_pair(a_dst, &tmap_a, leader_full, kb * kBlockK, row0);
-          ptx::tma_load_2d_pair(a_dst + Layout::kABytes, &tmap_b, leader_full, kb * kBlockK, wrow0);
+          if (leader) ptx::mbar_expect_tx(full_bar(stage), 2 * (Layout::kStageBytes + Layout::kSfStageBytes));
+          ptx::tma_load_2d_pair(a_dst, &tmap_a, leader_full, kb * kBlockElems, row0);
+          ptx::tma_load_2d_pair(a_dst + Layout::kABytes, &tmap_b, leader_full, kb * kBlockElems, wrow0);
+          if constexpr (kMx) {
+            // scale atoms of this K block: this CTA's A rows, and both 128-row halves of the B tile
+            // (rows past the operand read zeros: the tensor map clips)
+            const uint32_t sf_dst = base + Layout::kSfOffset + stage * Layout::kSfStageBytes;
+            const int32_t mt = mp * 2 + int32_t(rank);
+            ptx::tma_load_2d_pair(sf_dst, &tmap_sfa, leader_full, 0, mt * p.k_atoms + kb);
+            ptx::tma_load_2d_pair(sf_dst + 512u, &tmap_sfb, leader_full, 0, (nt * 2) * p.k_atoms + kb);
+            ptx::tma_load_2d_pair(sf_dst + 1024u, &tmap_sfb, leader_full, 0, (nt * 2 + 1) * p.k_atoms + kb);
+          }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
         (void)gated_upto;
@@ -182,6 +239,9 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     if (lane == 0 && leader) {
       constexpr uint32_t kIdesc = ptx::idesc_bf16_f32(2 * kBlockM, kBlockN, 0, 0);
       uint32_t stage = 0, phase = 0, accum = 0, accum_phase = 0;
+      uint32_t sf_parity = 0;
+      (void)sf_parity;
+      (void)kIdesc;
       bool ok = true;
       TileWalk walk = walk_template;
       for (int64_t t = walk.first(); ok && t >= 0; t = walk.next()) {
@@ -196,9 +256,25 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t a_addr = base + stage * Layout::kStageBytes;
           const uint64_t a_desc = ptx::smem_desc_k_sw128(a_addr);
           const uint64_t b_desc = ptx::smem_desc_k_sw128(a_addr + Layout::kABytes);
+          if constexpr (kMx) {
+            // scale atoms shared -> TMEM in both CTAs, then four K = 32 UMMAs; UMMA k reads byte k
+            // of every 32-bit scale column; two sets of scale columns alternate
+            const uint32_t sf_smem = base + Layout::kSfOffset + stage * Layout::kSfStageBytes;
+            const uint32_t sf_tmem = tmem_base + Layout::kTmemSfOffset + (sf_parity ? Layout::kSfColumns : 0u);
+            sf_parity ^= 1u;
+            ptx::tmem_cp_32x128b_warpx4_pair(sf_tmem, ptx::smem_desc_scale_atom(sf_smem));
+            ptx::tmem_cp_32x128b_warpx4_pair(sf_tmem + 4u, ptx::smem_desc_scale_atom(sf_smem + 512u));
+            ptx::tmem_cp_32x128b_warpx4_pair(sf_tmem + 8u, ptx::smem_desc_scale_atom(sf_smem + 1024u));
 #pragma unroll
-          for (int k = 0; k < kBlockK / kUmmaK; ++k)
-            ptx::umma_f16_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < 4; ++k)
+              ptx::umma_mxf8_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k,
+                                  ptx::idesc_mxf8_e4m3(2 * kBlockM, kBlockN, k, k), sf_tmem, sf_tmem + 4u,
+                                  (kb | k) != 0 ? 1u : 0u);
+          } else {
+#pragma unroll
+            for (int k = 0; k < kBlockK / kUmmaK; ++k)
+              ptx::umma_f16_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+          }
           ptx::umma_commit_pair(empty_bar(stage), 3);  // frees the stage in both CTAs
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
@@ -216,7 +292,8 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else if (warp == 3) {
     // ------------------------------------------------------------------ gate scout (both CTAs)
     if constexpr (kGated) {
-      const int32_t groups = p.lhs.world * p.lhs.virt;
+      const int32_t groups = kHeads ? p.grad.q_heads + 2 * p.grad.kv_heads : p.lhs.world * p.lhs.virt;
+      const int32_t virt = kHeads ? 1 : p.lhs.virt;
       TileWalk walk = walk_template;
       uint32_t tile_seq = 0;
       bool ok = true;
@@ -228,8 +305,8 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (lane == 0) ptx::st_release_cta_shared(gate_word, (tile_seq + 1u) * kGateSeqStep);
           continue;
         }
-        const uint32_t* flags = p.ready + int64_t(mt) * p.lhs.world * kReadyFlagStride;
-        ok = scout_tile<false>(p.wait, flags, groups, p.lhs.virt, p.lhs.gate_start, gate_word,
+        const uint32_t* flags = p.ready + int64_t(mt) * (groups / virt) * kReadyFlagStride;
+        ok = scout_tile<false>(p.wait, flags, groups, virt, kHeads ? 0 : p.lhs.gate_start, gate_word,
                                tile_seq * kGateSeqStep, lane, uint32_t(mt * groups));
       }
     }
@@ -238,7 +315,8 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int quarter = warp & 3;
     const int epi_tid = threadIdx.x - 128;
     const uint32_t leader_tmem_empty0 = ptx::map_to_cta(tmem_empty_bar(0), 0);
-    const uint32_t leader_tmem_empty1 = ptx::map_to_cta(tmem_empty_bar(1), 0);
+    const uint32_t leader_tmem_empty1 = ptx::map_to_cta(tmem_empty_bar(kAccumStages - 1), 0);
+    (void)leader_tmem_empty1;
     uint32_t accum = 0, accum_phase = 0, staged_blocks = 0;
     bool ok = true;
     TileWalk walk = walk_template;
@@ -252,44 +330,87 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       ptx::tc_fence_after();
       const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + accum * kBlockN;
       const int32_t row_in_tile = quarter * 32 + lane;
-#pragma unroll 1
-      for (int c = 0; c < kBlockN; c += 64) {
-        const uint32_t staging =
-            base + Layout::kStagingOffset + (staged_blocks % Layout::kStagingBuffers) * Layout::kStagingBlockBytes;
-        ++staged_blocks;
-        if (epi_tid == 0) ptx::bulk_wait_read<Layout::kStagingBuffers - 1>();
-        ptx::named_bar_sync(1, kEpilogueThreads);
-        uint32_t acc0[32], acc1[32];
-        ptx::tmem_ld_32x32b_x32(taddr + c, acc0);
-        ptx::tmem_ld_32x32b_x32(taddr + c + 32, acc1);
-        ptx::tmem_wait_ld();
-        if (c + 64 >= kBlockN) {
-          // Accumulator read: hand the stage back to the leader's UMMA issuer.
-          ptx::tc_fence_before();
-          ptx::mbar_arrive_cluster(accum ? leader_tmem_empty1 : leader_tmem_empty0);
-        }
-        const uint32_t row_addr = staging + uint32_t(row_in_tile) * 128u;
-        stage_accumulators(acc0, row_addr, 0, row_in_tile, p.alpha);
-        stage_accumulators(acc1, row_addr, 4, row_in_tile, p.alpha);
-        ptx::fence_proxy_async_shared();
-        ptx::named_bar_sync(1, kEpilogueThreads);
-        if (epi_tid == 0) {
-          const int32_t col = nt * kBlockN + c;
-          if (col < p.n && mt * kBlockM < p.m) {
-            ptx::tma_store_2d(&store_maps.local, staging, col, mt * kBlockM);
-            if constexpr (kDirect) {
-              const QkvRoute& r = p.qkv;
-              const int32_t q_width = r.q_heads * r.head_dim, kv_width = r.kv_heads * r.head_dim;
-              const int32_t segment = col < q_width ? 0 : (col < q_width + kv_width ? 1 : 2);
-              const int32_t within = col - (segment == 0 ? 0 : q_width + (segment == 2 ? kv_width : 0));
-              const int32_t local_width = (segment == 0 ? q_width : kv_width) / r.world;
-              const int32_t owner = within / local_width;
-              ptx::tma_store_2d(&store_maps.peer[owner][segment], staging, within - owner * local_width,
-                                int32_t(global_row(r.world, r.rank, r.seq_local, r.global_seq, r.causal != 0,
-                                                   mt * kBlockM)));
-            }
+      // One thread hands a staged 64-column block to the copy engine.
+      auto issue_stores = [&](int c, uint32_t staging) {
+        const int32_t col = nt * kBlockN + c;
+        if (col < p.n && mt * kBlockM < p.m) {
+          ptx::tma_store_2d(&store_maps.local, staging, col, mt * kBlockM);
+          if constexpr (kDirect) {
+            const QkvRoute& r = p.qkv;
+            const int32_t q_width = r.q_heads * r.head_dim, kv_width = r.kv_heads * r.head_dim;
+            const int32_t segment = col < q_width ? 0 : (col < q_width + kv_width ? 1 : 2);
+            const int32_t within = col - (segment == 0 ? 0 : q_width + (segment == 2 ? kv_width : 0));
+            const int32_t local_width = (segment == 0 ? q_width : kv_width) / r.world;
+            const int32_t owner = within / local_width;
+            ptx::tma_store_2d(&store_maps.peer[owner][segment], staging, within - owner * local_width,
+                              int32_t(global_row(r.world, r.rank, r.seq_local, r.global_seq, r.causal != 0,
+                                                 mt * kBlockM)));
           }
-          ptx::bulk_commit();
+        }
+        ptx::bulk_commit();
+      };
+      if constexpr (kAccumStages == 1) {
+        // Single accumulator: drain it whole into packed BF16 registers and hand TMEM back
+        // before any staging, so the next tile's UMMAs overlap the stores.
+        uint32_t packed[kBlockN / 2];
+#pragma unroll
+        for (int c = 0; c < kBlockN; c += 64) {
+          uint32_t acc0[32], acc1[32];
+          ptx::tmem_ld_32x32b_x32(taddr + c, acc0);
+          ptx::tmem_ld_32x32b_x32(taddr + c + 32, acc1);
+          ptx::tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            __nv_bfloat162 pair = __floats2bfloat162_rn(p.alpha * __uint_as_float(acc0[2 * e]),
+                                                        p.alpha * __uint_as_float(acc0[2 * e + 1]));
+            packed[c / 2 + e] = *reinterpret_cast<const uint32_t*>(&pair);
+            pair = __floats2bfloat162_rn(p.alpha * __uint_as_float(acc1[2 * e]), p.alpha * __uint_as_float(acc1[2 * e + 1]));
+            packed[c / 2 + 16 + e] = *reinterpret_cast<const uint32_t*>(&pair);
+          }
+        }
+        ptx::tc_fence_before();
+        ptx::mbar_arrive_cluster(leader_tmem_empty0);
+#pragma unroll
+        for (int c = 0; c < kBlockN; c += 64) {
+          const uint32_t staging =
+              base + Layout::kStagingOffset + (staged_blocks % Layout::kStagingBuffers) * Layout::kStagingBlockBytes;
+          ++staged_blocks;
+          if (epi_tid == 0) ptx::bulk_wait_read<Layout::kStagingBuffers - 1>();
+          ptx::named_bar_sync(1, kEpilogueThreads);
+          const uint32_t row_addr = staging + uint32_t(row_in_tile) * 128u;
+#pragma unroll
+          for (int v = 0; v < 8; ++v) {
+            const uint4 out = make_uint4(packed[c / 2 + v * 4], packed[c / 2 + v * 4 + 1], packed[c / 2 + v * 4 + 2],
+                                         packed[c / 2 + v * 4 + 3]);
+            ptx::st_shared_v4(row_addr + uint32_t((v ^ (row_in_tile & 7)) * 16), out);
+          }
+          ptx::fence_proxy_async_shared();
+          ptx::named_bar_sync(1, kEpilogueThreads);
+          if (epi_tid == 0) issue_stores(c, staging);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < kBlockN; c += 64) {
+          const uint32_t staging =
+              base + Layout::kStagingOffset + (staged_blocks % Layout::kStagingBuffers) * Layout::kStagingBlockBytes;
+          ++staged_blocks;
+          if (epi_tid == 0) ptx::bulk_wait_read<Layout::kStagingBuffers - 1>();
+          ptx::named_bar_sync(1, kEpilogueThreads);
+          uint32_t acc0[32], acc1[32];
+          ptx::tmem_ld_32x32b_x32(taddr + c, acc0);
+          ptx::tmem_ld_32x32b_x32(taddr + c + 32, acc1);
+          ptx::tmem_wait_ld();
+          if (c + 64 >= kBlockN) {
+            // Accumulator read: hand the stage back to the leader's UMMA issuer.
+            ptx::tc_fence_before();
+            ptx::mbar_arrive_cluster(accum ? leader_tmem_empty1 : leader_tmem_empty0);
+          }
+          const uint32_t row_addr = staging + uint32_t(row_in_tile) * 128u;
+          stage_accumulators(acc0, row_addr, 0, row_in_tile, p.alpha);
+          stage_accumulators(acc1, row_addr, 4, row_in_tile, p.alpha);
+          ptx::fence_proxy_async_shared();
+          ptx::named_bar_sync(1, kEpilogueThreads);
+          if (epi_tid == 0) issue_stores(c, staging);
         }
       }
       if (++accum == kAccumStages) { accum = 0; accum_phase ^= 1u; }
@@ -312,7 +433,9 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     ptx::tc_fence_after();
     ptx::tmem_dealloc_pair(tmem_base, Layout::kTmemColumns);
   }
-  if constexpr (kDirect) {
+  }  // do_compute
+  if constexpr (kDirect || kMode == kModeGradPull) {
+    // every rank's transfers are complete before any rank's inputs or outputs may change
     cooperative_groups::this_grid().sync();
     qkv_finalize(p);
   }

@@ -11,6 +11,7 @@ struct fuse_bf16_grouped_gemm_plan {
   fuse_b200::GroupedParams params{};
   void* metadata = nullptr;  // one private device allocation: tensor maps, flags, epoch, prefix
   int block_n = 256;
+  bool pair = false;  // CTA pairs (policy.mma_sm_count == 2)
   int grid = 0;
   int device = -1;
 };
@@ -35,7 +36,7 @@ cudaError_t create_dispatch_plan(const fuse_bf16_grouped_gemm_params& p, fuse_bf
       return cudaErrorInvalidValue;
   // geometry outside this implementation's domain
   if (p.n % 8 != 0 || p.k % 8 != 0 || (p.policy.tile_n != 128 && p.policy.tile_n != 256) ||
-      p.policy.mma_sm_count != 1 || p.policy.swap_ab ||
+      (p.policy.mma_sm_count != 1 && p.policy.mma_sm_count != 2) || p.policy.swap_ab ||
       (p.dispatch_buffer_rows != 0 && p.dispatch_buffer_rows != p.expert_row_capacity))
     return cudaErrorNotSupported;
   DeviceInfo info;
@@ -54,6 +55,13 @@ cudaError_t create_dispatch_plan(const fuse_bf16_grouped_gemm_params& p, fuse_bf
   if (plan == nullptr) return cudaErrorMemoryAllocation;
   plan->device = info.device;
   plan->block_n = p.policy.tile_n;
+  // mma_sm_count 2: CTA pairs (256 x 256 tiles); needs the 256-wide tile, whole pairs of
+  // communication and compute CTAs, and is otherwise outside this implementation's domain.
+  plan->pair = p.policy.mma_sm_count == 2;
+  if (plan->pair && (p.policy.tile_n != 256 || p.policy.num_comm_ctas % 2 != 0 || info.sm_count % 2 != 0)) {
+    delete plan;
+    return cudaErrorNotSupported;
+  }
   const int cap_tiles = host::ceil_div(p.expert_row_capacity, kBlockM);
   const size_t maps_bytes = align256(sizeof(CUtensorMap) * size_t(p.experts));
   const size_t ready_bytes = align256(size_t(p.experts) * cap_tiles * FUSE_READY_FLAG_STRIDE * sizeof(uint32_t));
@@ -74,7 +82,8 @@ cudaError_t create_dispatch_plan(const fuse_bf16_grouped_gemm_params& p, fuse_bf
     if (!host::aligned16(lhs[e]) || !host::aligned16(weights[e])) return fail(cudaErrorInvalidValue);
     if ((status = encode_operand(&maps_a[e], lhs[e], p.expert_row_capacity, p.k, p.k, false, kBlockM)) != cudaSuccess)
       return fail(status);
-    if ((status = encode_operand(&maps_b[e], weights[e], p.n, p.k, p.k, false, plan->block_n)) != cudaSuccess)
+    if ((status = encode_operand(&maps_b[e], weights[e], p.n, p.k, p.k, false, plan->pair ? 128 : plan->block_n)) !=
+        cudaSuccess)
       return fail(status);
   }
   uint8_t* base = static_cast<uint8_t*>(plan->metadata);
@@ -93,6 +102,7 @@ cudaError_t create_dispatch_plan(const fuse_bf16_grouped_gemm_params& p, fuse_bf
   g.world = p.world_size;
   g.n_tiles = host::ceil_div(p.n, plan->block_n);
   g.cap_tiles = cap_tiles;
+  g.tile_m = plan->pair ? 2 * kBlockM : kBlockM;
   g.num_comm_ctas = p.policy.num_comm_ctas;
   g.maps_a = reinterpret_cast<const CUtensorMap*>(base);
   g.maps_b = reinterpret_cast<const CUtensorMap*>(base + maps_bytes);
@@ -111,7 +121,7 @@ cudaError_t create_dispatch_plan(const fuse_bf16_grouped_gemm_params& p, fuse_bf
   const int compute = p.policy.num_compute_ctas < info.sm_count - p.policy.num_comm_ctas
                           ? p.policy.num_compute_ctas
                           : info.sm_count - p.policy.num_comm_ctas;
-  plan->grid = p.policy.num_comm_ctas + compute;
+  plan->grid = p.policy.num_comm_ctas + (plan->pair ? compute / 2 * 2 : compute);
   g.wait.status = info.status;
   if ((status = cudaDeviceSynchronize()) != cudaSuccess) return fail(status);
   *out = plan;
@@ -129,6 +139,9 @@ cudaError_t launch_plan(fuse_bf16_grouped_gemm_plan* plan, const fuse_b200_optio
   cudaError_t status = cudaGetLastError();
   if (status != cudaSuccess) return status;
   host::count_launch();
+  if (plan->pair)
+    return host::launch_kernel(grouped_pair_kernel, plan->grid, kThreads, PairLayoutT<false>::kDynamicBytes, true, stream,
+                               g);
   if (plan->block_n == 256) {
     using Layout = SmemLayout<256, 4, false>;
     return host::launch_kernel(grouped_gemm_kernel<256, 4>, plan->grid, kThreads, Layout::kDynamicBytes, true,

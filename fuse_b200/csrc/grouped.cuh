@@ -19,6 +19,7 @@
 #pragma once
 
 #include "fused_gemm.cuh"
+#include "pair_gemm.cuh"
 
 namespace fuse_b200 {
 
@@ -43,6 +44,7 @@ struct GroupedParams {
   uint32_t* epoch_word;        // device epoch, advanced by the prepare kernel
   int32_t* tile_prefix;        // [experts + 1] tiles before each expert, written by prepare
   uint32_t flags;
+  int32_t tile_m;              // rows of one GEMM tile: 128 (one CTA) or 256 (a CTA pair)
   WaitContext wait;            // wait.epoch is read from epoch_word on the device
 };
 
@@ -62,7 +64,7 @@ __global__ void grouped_prepare_kernel(GroupedParams p) {
       int64_t rows = p.row_offsets[e + 1] - p.row_offsets[e];
       if (rows < 0) rows = 0;
       if (rows > p.capacity) rows = p.capacity;
-      tiles += int32_t((rows + kBlockM - 1) / kBlockM) * p.n_tiles;
+      tiles += int32_t((rows + p.tile_m - 1) / p.tile_m) * p.n_tiles;
     }
     p.tile_prefix[p.experts] = tiles;
   }
@@ -427,6 +429,221 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const Grouped
 
   // Every rank tells its peers that it has finished reading their tokens, and leaves only when
   // all of them have finished reading its own (communication.cuh:237-250).
+  cooperative_groups::this_grid().sync();
+  if (blockIdx.x == 0 && threadIdx.x < 32) {
+    if (lane == 0) ptx::fence_sc_sys();
+    __syncwarp();
+    if (lane < p.world) ptx::st_release_sys(p.peer_done[lane] + p.rank * kReadyFlagStride, w.epoch);
+    __syncwarp();
+    if (lane < p.world && !(p.flags & kFlagSkipPeerWait))
+      flag_wait<true>(p.peer_done[p.rank] + lane * kReadyFlagStride, w.epoch, w, kSitePeerDone, uint32_t(lane));
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// The grouped kernel on CTA pairs (policy.mma_sm_count == 2): clusters of two CTAs work on
+// 256 x 256 tiles of one expert with tcgen05.mma.cta_group::2 -- each CTA holds its own 128 lhs
+// rows and half of the weight tile per K block, six stages; barriers and TMEM as in
+// pair_gemm.cuh.  Each CTA gates its own 128-row panel; a panel past M_e has no rows to wait
+// for (its accumulator rows are never stored).  Communication CTAs come in whole pairs.
+// ------------------------------------------------------------------------------------------
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) grouped_pair_kernel(const GroupedParams p) {
+  using Layout = PairLayoutT<false>;
+  constexpr int kStages = Layout::kStages;
+  constexpr int kBlockN = Layout::kBlockN;
+  constexpr uint32_t kAccumStages = Layout::kAccumStages;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = ptx::smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* smem = smem_raw + (base - raw_addr);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const bool is_comm = int(blockIdx.x) < p.num_comm_ctas;
+  const uint32_t rank = ptx::cluster_ctarank();
+  const bool leader = rank == 0;
+  WaitContext w = p.wait;
+  w.epoch = *p.epoch_word;  // advanced by the prepare kernel earlier on the stream
+
+  if (is_comm) {
+    dispatch_pull_role(p, w, base);
+  } else {
+    const uint32_t bar_base = base + Layout::kBarrierOffset;
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
+    auto tmem_full_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };
+    auto tmem_empty_bar = [&](int s) { return bar_base + 8u * (2 * kStages + kAccumStages + s); };
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + Layout::kTmemSlotOffset);
+    if (threadIdx.x == 0) {
+      for (int s = 0; s < kStages; ++s) {
+        ptx::mbar_init(full_bar(s), 1);
+        ptx::mbar_init(empty_bar(s), 1);
+      }
+      for (int s = 0; s < int(kAccumStages); ++s) {
+        ptx::mbar_init(tmem_full_bar(s), 1);
+        ptx::mbar_init(tmem_empty_bar(s), 2 * kEpilogueThreads);
+      }
+      ptx::fence_mbar_init();
+    }
+    if (warp == 2) {
+      ptx::tmem_alloc_pair(base + Layout::kTmemSlotOffset, Layout::kTmemColumns);
+      ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int32_t pairs = (int32_t(gridDim.x) - p.num_comm_ctas) / 2;
+    const int32_t pair_id = (int32_t(blockIdx.x) - p.num_comm_ctas) / 2;
+    const int32_t tiles = p.tile_prefix[p.experts];  // 256-row tiles
+    const int32_t k_blocks = (p.k + kBlockK - 1) / kBlockK;
+    auto decode = [&](int32_t t, int32_t& expert, int32_t& mp, int32_t& nt) {
+      while (t >= p.tile_prefix[expert + 1]) ++expert;
+      const int32_t local = t - p.tile_prefix[expert];
+      mp = local / p.n_tiles;
+      nt = local - mp * p.n_tiles;
+    };
+    auto rows_of = [&](int32_t expert) {
+      int64_t rows = p.row_offsets[expert + 1] - p.row_offsets[expert];
+      if (rows > p.capacity) rows = p.capacity;
+      return rows < 0 ? int64_t(0) : rows;
+    };
+    bool unwound = false;
+
+    if (warp == 0) {
+      if (lane == 0) {
+        uint32_t stage = 0, phase = 0;
+        int32_t expert = 0;
+        bool ok = true;
+        for (int32_t t = pair_id; ok && t < tiles; t += pairs) {
+          int32_t mp, nt;
+          decode(t, expert, mp, nt);
+          const int32_t mt = mp * 2 + int32_t(rank);  // this CTA's 128-row panel
+          if (int64_t(mt) * kBlockM < rows_of(expert)) {
+            const int64_t flag = (int64_t(expert) * p.cap_tiles + mt) * kReadyFlagStride;
+            ok = flag_wait<false>(p.ready + flag, w.epoch, w, kSitePanelReady, uint32_t(flag / kReadyFlagStride));
+            ptx::fence_proxy_async_global();
+            if (!ok) break;
+          }
+          const CUtensorMap* map_a = p.maps_a + expert;
+          const CUtensorMap* map_b = p.maps_b + expert;
+          for (int32_t kb = 0; kb < k_blocks; ++kb) {
+            ok = mbar_wait(empty_bar(stage), phase ^ 1u, w, kSiteSmemEmpty);
+            if (!ok) break;
+            const uint32_t a_dst = base + stage * Layout::kStageBytes;
+            const uint32_t leader_full = ptx::map_to_cta(full_bar(stage), 0);
+            if (leader) ptx::mbar_expect_tx(full_bar(stage), 2 * Layout::kStageBytes);
+            ptx::tma_load_2d_pair(a_dst, map_a, leader_full, kb * kBlockK, mt * kBlockM);
+            ptx::tma_load_2d_pair(a_dst + Layout::kABytes, map_b, leader_full, kb * kBlockK,
+                                  nt * kBlockN + int32_t(rank) * (kBlockN / 2));
+            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          }
+        }
+        unwound = !ok;
+      }
+    } else if (warp == 1) {
+      if (lane == 0 && leader) {
+        constexpr uint32_t kIdesc = ptx::idesc_bf16_f32(2 * kBlockM, kBlockN, 0, 0);
+        uint32_t stage = 0, phase = 0, accum = 0, accum_phase = 0;
+        bool ok = true;
+        for (int32_t t = pair_id; ok && t < tiles; t += pairs) {
+          ok = mbar_wait(tmem_empty_bar(accum), accum_phase ^ 1u, w, kSiteTmemEmpty);
+          if (!ok) break;
+          ptx::tc_fence_after();
+          const uint32_t d_tmem = tmem_base + accum * kBlockN;
+          for (int32_t kb = 0; kb < k_blocks; ++kb) {
+            ok = mbar_wait(full_bar(stage), phase, w, kSiteSmemFull);
+            if (!ok) break;
+            ptx::tc_fence_after();
+            const uint32_t a_addr = base + stage * Layout::kStageBytes;
+            const uint64_t a_desc = ptx::smem_desc_k_sw128(a_addr);
+            const uint64_t b_desc = ptx::smem_desc_k_sw128(a_addr + Layout::kABytes);
+#pragma unroll
+            for (int k = 0; k < kBlockK / kUmmaK; ++k)
+              ptx::umma_f16_pair(d_tmem, a_desc + uint64_t(2 * k), b_desc + uint64_t(2 * k), kIdesc,
+                                 (kb | k) != 0 ? 1u : 0u);
+            ptx::umma_commit_pair(empty_bar(stage), 3);
+            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          }
+          if (!ok) break;
+          ptx::umma_commit_pair(tmem_full_bar(accum), 3);
+          if (++accum == kAccumStages) { accum = 0; accum_phase ^= 1u; }
+        }
+        if (!ok) {
+          ptx::umma_commit_pair(tmem_full_bar(accum), 3);
+          mbar_wait(tmem_full_bar(accum), accum_phase, w, kSiteDrain, false);
+        }
+        unwound = !ok;
+      }
+    } else if (warp >= 4) {
+      const int quarter = warp & 3;
+      const uint32_t leader_tmem_empty0 = ptx::map_to_cta(tmem_empty_bar(0), 0);
+      const uint32_t leader_tmem_empty1 = ptx::map_to_cta(tmem_empty_bar(1), 0);
+      uint32_t accum = 0, accum_phase = 0;
+      int32_t expert = 0;
+      bool ok = true;
+      for (int32_t t = pair_id; ok && t < tiles; t += pairs) {
+        int32_t mp, nt;
+        decode(t, expert, mp, nt);
+        const int32_t mt = mp * 2 + int32_t(rank);
+        ok = mbar_wait(tmem_full_bar(accum), accum_phase, w, kSiteTmemFull);
+        ok = ptx::named_bar_all(2, kEpilogueThreads, ok);
+        if (!ok) break;
+        ptx::tc_fence_after();
+        const int64_t expert_rows = rows_of(expert);
+        const int32_t row = mt * kBlockM + quarter * 32 + lane;
+        const bool row_ok = row < expert_rows;  // rows past M_e keep the caller's contents
+        uint16_t* d_row = p.output[expert] + int64_t(row) * p.n + nt * kBlockN;
+        const uint32_t taddr = tmem_base + (uint32_t(quarter * 32) << 16) + accum * kBlockN;
+#pragma unroll 1
+        for (int c = 0; c < kBlockN; c += 64) {
+          uint32_t acc0[32], acc1[32];
+          ptx::tmem_ld_32x32b_x32(taddr + c, acc0);
+          ptx::tmem_ld_32x32b_x32(taddr + c + 32, acc1);
+          ptx::tmem_wait_ld();
+          if (c + 64 >= kBlockN) {
+            ptx::tc_fence_before();
+            ptx::mbar_arrive_cluster(accum ? leader_tmem_empty1 : leader_tmem_empty0);
+          }
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              const int32_t col = nt * kBlockN + c + half * 32 + v * 8;
+              if (row_ok && col < p.n) {
+                const uint32_t* a = half == 0 ? &acc0[v * 8] : &acc1[v * 8];
+                uint4 out;
+                __nv_bfloat162 pair = __floats2bfloat162_rn(__uint_as_float(a[0]), __uint_as_float(a[1]));
+                out.x = *reinterpret_cast<const uint32_t*>(&pair);
+                pair = __floats2bfloat162_rn(__uint_as_float(a[2]), __uint_as_float(a[3]));
+                out.y = *reinterpret_cast<const uint32_t*>(&pair);
+                pair = __floats2bfloat162_rn(__uint_as_float(a[4]), __uint_as_float(a[5]));
+                out.z = *reinterpret_cast<const uint32_t*>(&pair);
+                pair = __floats2bfloat162_rn(__uint_as_float(a[6]), __uint_as_float(a[7]));
+                out.w = *reinterpret_cast<const uint32_t*>(&pair);
+                ptx::st_v4(d_row + c + half * 32 + v * 8, out);
+              }
+            }
+          }
+        }
+        if (++accum == kAccumStages) { accum = 0; accum_phase ^= 1u; }
+      }
+      unwound = !ok;
+    }
+    if (unwound) {
+      // error path: copies that were started may still be landing in either CTA's shared memory
+      const uint64_t start = ptx::globaltimer();
+      while (ptx::globaltimer() - start < 200000ull) __nanosleep(1000);
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync();
+    if (warp == 2) {
+      ptx::tc_fence_after();
+      ptx::tmem_dealloc_pair(tmem_base, Layout::kTmemColumns);
+    }
+  }
+
   cooperative_groups::this_grid().sync();
   if (blockIdx.x == 0 && threadIdx.x < 32) {
     if (lane == 0) ptx::fence_sc_sys();

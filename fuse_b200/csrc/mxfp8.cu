@@ -36,16 +36,31 @@ __global__ void quantize_transposed_kernel(const uint16_t* source, int64_t strid
   const int32_t row_groups = rows / 32;
   const int64_t k_atoms = (int64_t(rows) + 127) >> 7;
   const int64_t padded_cols = (int64_t(cols) + 127) & ~int64_t(127);
+  const bool vector_loads = cols % 8 == 0 && stride % 8 == 0 && reinterpret_cast<uintptr_t>(source) % 16 == 0;
   for (int64_t t = blockIdx.x; t < int64_t(col_tiles) * row_groups; t += gridDim.x) {
     const int32_t group = int32_t(t / col_tiles), col0 = int32_t(t % col_tiles) * kTransposeCols;
     __syncthreads();
-    for (int i = threadIdx.x; i < 32 * (kTransposeCols / 2); i += blockDim.x) {
-      const int r = i / (kTransposeCols / 2), c2 = (i % (kTransposeCols / 2)) * 2;
-      uint32_t pair = 0;
-      if (col0 + c2 < cols)
-        pair = *reinterpret_cast<const uint32_t*>(source + int64_t(group * 32 + r) * stride + col0 + c2);
-      tile[r][c2] = uint16_t(pair);
-      tile[r][c2 + 1] = uint16_t(pair >> 16);
+    if (vector_loads) {
+      // 16-byte loads: four per thread in flight
+      for (int i = threadIdx.x; i < 32 * (kTransposeCols / 8); i += blockDim.x) {
+        const int r = i / (kTransposeCols / 8), c8 = (i % (kTransposeCols / 8)) * 8;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (col0 + c8 < cols) v = ptx::ld_cg_v4(source + int64_t(group * 32 + r) * stride + col0 + c8);
+        uint32_t* row = reinterpret_cast<uint32_t*>(&tile[r][c8]);
+        row[0] = v.x;
+        row[1] = v.y;
+        row[2] = v.z;
+        row[3] = v.w;
+      }
+    } else {
+      for (int i = threadIdx.x; i < 32 * (kTransposeCols / 2); i += blockDim.x) {
+        const int r = i / (kTransposeCols / 2), c2 = (i % (kTransposeCols / 2)) * 2;
+        uint32_t pair = 0;
+        if (col0 + c2 < cols)
+          pair = *reinterpret_cast<const uint32_t*>(source + int64_t(group * 32 + r) * stride + col0 + c2);
+        tile[r][c2] = uint16_t(pair);
+        tile[r][c2 + 1] = uint16_t(pair >> 16);
+      }
     }
     __syncthreads();
     const int32_t col = col0 + threadIdx.x;
@@ -98,7 +113,7 @@ cudaError_t quantize_transposed(const fuse_bf16* source, int64_t stride, int row
   DeviceInfo info;
   cudaError_t status = check_device(&info);
   if (status != cudaSuccess) return status;
-  quantize_transposed_kernel<<<info.sm_count * 4, 256, 0, stream>>>(source, stride, rows, cols, data, scales);
+  quantize_transposed_kernel<<<info.sm_count * 8, 256, 0, stream>>>(source, stride, rows, cols, data, scales);
   status = cudaGetLastError();
   if (status == cudaSuccess) host::count_launch();
   return status;

@@ -279,8 +279,8 @@ def main():
                                      expert_row_capacity=cap, rank=rank, world_size=cp, topk=topk)
         total_rows = int(offs[-1])
         flops = 2.0 * total_rows * n * hid
-        for comm, compute in ((args.comm, 148 - args.comm), (20, 128)):
-            gp.policy = N.GroupedGemmPolicy(num_comm_ctas=comm, num_compute_ctas=compute, tile_n=256)
+        for comm, compute, mma in ((args.comm, 148 - args.comm, 1), (args.comm, 148 - args.comm, 2), (20, 128, 2)):
+            gp.policy = N.GroupedGemmPolicy(num_comm_ctas=comm, num_compute_ctas=compute, tile_n=256, mma_sm_count=mma)
             for r in range(cp):
                 gp.peer_input[r] = sym["c5_tokens"].peer_ptrs[r]
                 gp.peer_started[r] = sym["c5_started"].peer_ptrs[r]
@@ -288,7 +288,7 @@ def main():
             rc, plan = api.create_bf16_a2a_grouped_gemm(gp)
             assert rc == 0, rc
             timed(lambda e: api.launch_bf16_grouped_gemm(plan, stream),
-                  f"c5 MoE dispatch+FC1 ({total_rows} rows, comm {comm})", flops)
+                  f"c5 MoE dispatch+FC1 ({total_rows} rows, comm {comm}, mma_sm {mma})", flops)
             barrier()
             api.destroy_bf16_grouped_gemm(plan)
         # pure grouped GEMM denominator: the same rows as one dense GEMM per expert is not

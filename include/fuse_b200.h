@@ -410,7 +410,8 @@ typedef struct fuse_grouped_token_source {
   int32_t rank, token, slot;
 } fuse_grouped_token_source;
 /* grouped_gemm.h:17-53 (GroupedGemmPolicy).  This implementation honours num_comm_ctas,
- * num_compute_ctas and tile_n (128 or 256); mma_sm_count must be 1 and swap_ab false. */
+ * num_compute_ctas and tile_n (128 or 256); mma_sm_count 1, or 2 = CTA pairs on
+ * 256 x 256 tiles (needs tile_n 256 and an even num_comm_ctas); swap_ab must be false. */
 typedef struct fuse_grouped_gemm_policy {
   int32_t num_comm_ctas, num_compute_ctas, swizzle;
   uint8_t along_n;

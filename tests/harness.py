@@ -305,7 +305,7 @@ def oproj_forward_mxfp8(world, rank, batch, seq_local, peer_data, peer_scales, w
 
 
 def moe_dispatch_fc1(world, rank, experts_local, tokens_bits, weights_bits, row_offsets, sources, capacity,
-                     comm=4, compute=128, tile_n=256, launches=1, second_route=None):
+                     comm=4, compute=128, tile_n=256, launches=1, second_route=None, mma_sm_count=1):
     """One rank of the MoE dispatch -> FC1 grouped GEMM.  tokens_bits[r] [T, K] per rank;
     weights_bits [experts_local, N, K]; row_offsets int64 [E+1]; sources int32 [rows, 3].
     Returns (lhs [E, capacity, K] bits, output [E, capacity, N] bits); unused capacity holds 0x7f7f.
@@ -327,7 +327,8 @@ def moe_dispatch_fc1(world, rank, experts_local, tokens_bits, weights_bits, row_
     p = N.Bf16GroupedGemmParams(lhs=lhs_ptrs.data_ptr(), weight_nt=w_ptrs.data_ptr(), output=out_ptrs.data_ptr(),
                                 row_offsets=offs.data_ptr(), source=src.data_ptr(), experts=e, n=n, k=k,
                                 expert_row_capacity=capacity, rank=rank, world_size=world, topk=1)
-    p.policy = N.GroupedGemmPolicy(num_comm_ctas=comm, num_compute_ctas=compute, tile_n=tile_n)
+    p.policy = N.GroupedGemmPolicy(num_comm_ctas=comm, num_compute_ctas=compute, tile_n=tile_n,
+                                   mma_sm_count=mma_sm_count)
     for r in range(world):
         p.peer_input[r] = toks[r].data_ptr()
         p.peer_started[r] = started[r].data_ptr()

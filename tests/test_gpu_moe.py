@@ -77,7 +77,26 @@ def test_moe_dispatch_fc1_matches_oracle(case):
         _check(world, rank, experts_local, toks, weights, offs, src, capacity, lhs, out)
 
 
-def test_moe_boundary_row_counts_empty_experts_and_replay_with_new_routes():
+@pytest.mark.parametrize("case", [c for c in MOE_CASES if c[7] == 256])
+def test_moe_dispatch_fc1_on_cta_pairs_matches_oracle(case):
+    # policy.mma_sm_count = 2: 256 x 256 tiles on CTA pairs, whole pairs of communication CTAs
+    from tests import harness as H
+    world, tokens, experts, topk, k, n, comm, tile_n = case
+    comm += comm % 2
+    experts_local = experts // world
+    chosen = _routes(world, tokens, experts, topk, synthetic.GROUPED_SEED)
+    toks = [synthetic.normal_bf16((tokens, k), synthetic.GROUPED_SEED + 31 * r + 5, 1.0) for r in range(world)]
+    for rank in sorted({0, world - 1}):
+        weights = synthetic.normal_bf16((experts_local, n, k), synthetic.GROUPED_SEED + 1000 + rank, 0.02)
+        offs, src = _rows_for(world, rank, experts_local, tokens, topk, chosen)
+        capacity = max(256, int(-(-int(np.diff(offs).max()) // 256) * 256))
+        lhs, out = H.moe_dispatch_fc1(world, rank, experts_local, toks, weights, offs, src, capacity, comm=comm,
+                                      tile_n=tile_n, mma_sm_count=2)
+        _check(world, rank, experts_local, toks, weights, offs, src, capacity, lhs, out)
+
+
+@pytest.mark.parametrize("mma_sm_count", [1, 2])
+def test_moe_boundary_row_counts_empty_experts_and_replay_with_new_routes(mma_sm_count):
     # Row counts at tile boundaries and empty experts (benchmarks/sm103/grouped_validation.cuh:20-50);
     # then the same plan replayed with different device routes.
     from tests import harness as H
@@ -97,8 +116,10 @@ def test_moe_boundary_row_counts_empty_experts_and_replay_with_new_routes():
 
     first, second = make(counts_a), make(counts_b)
     capacity = 512
-    lhs, out = H.moe_dispatch_fc1(world, 0, e, toks, weights, first[0], first[1], capacity, comm=3, launches=2)
+    comm = 3 if mma_sm_count == 1 else 4
+    lhs, out = H.moe_dispatch_fc1(world, 0, e, toks, weights, first[0], first[1], capacity, comm=comm, launches=2,
+                                  mma_sm_count=mma_sm_count)
     _check(world, 0, e, toks, weights, first[0], first[1], capacity, lhs, out)
-    lhs, out = H.moe_dispatch_fc1(world, 0, e, toks, weights, first[0], first[1], capacity, comm=3,
-                                  second_route=second)
+    lhs, out = H.moe_dispatch_fc1(world, 0, e, toks, weights, first[0], first[1], capacity, comm=comm,
+                                  second_route=second, mma_sm_count=mma_sm_count)
     _check(world, 0, e, toks, weights, second[0], second[1], capacity, lhs, out)

@@ -111,6 +111,15 @@ cudaError_t qkv_backward_data(const fuse_qkv_backward_data_params& p, const fuse
     for (int peer = 0; peer < p.world_size && encoded; ++peer)
       encoded = encode_copy_map(&push.staging[peer], p.peer_dqkv_staging[peer], 2, uint64_t(m), uint64_t(k), 64, 128) ==
                 cudaSuccess;
+    if (encoded && block_n == 256 && comm % 2 == 0 && info.sm_count % 2 == 0 && !vector_epilogue_requested(options) &&
+        launch::pair_tiles_requested()) {
+      // CTA pairs: whole pairs of communication CTAs, 256-row tiles
+      FusedParams pf = f;
+      pf.grad.m_group = 2 * launch::wave_m_group_pairs(pf, info.sm_count);
+      return launch::launch_pair_kernel<kModeHeadGate, GradPushMaps, false, false, true>(
+          maps, maps.a, maps.a, push, pf, p.gemm_tuning.max_swizzle_size ? p.gemm_tuning.max_swizzle_size : 1, info, stream,
+          double(m) * k * 2.0);
+    }
     if (encoded)
       return launch_mode<kModeHeadGate, false, true, false, GradPushMaps>(maps, push, f, block_n, info, stream,
                                                                           !vector_epilogue_requested(options));
@@ -176,6 +185,13 @@ cudaError_t oproj_backward_data(const fuse_oproj_backward_data_params& p,
     tma = encode_peer_store_maps(&stores, p.peer_grad_attention, p.world_size,
                                  uint64_t(p.batch) * uint64_t(f.qkv.global_seq),
                                  int64_t(p.q_heads) / p.world_size * p.head_dim, 0);
+  if (tma && block_n == 256 && info.sm_count % 2 == 0 && launch::pair_tiles_requested()) {
+    Operands pair_maps = maps;
+    if (encode_operand(&pair_maps.a, p.grad_output, m, k, k, false, kBlockM) == cudaSuccess)
+      return launch::launch_pair_kernel<kModeQkvDirect, StoreMaps, false, false, true>(
+          pair_maps, maps.a, maps.a, stores, f, p.gemm_tuning.max_swizzle_size ? p.gemm_tuning.max_swizzle_size : 1, info,
+          stream, 0.0);
+  }
   return launch_mode<kModeQkvDirect, false, true>(maps, stores, f, block_n, info, stream, tma);
 }
 
@@ -199,6 +215,9 @@ cudaError_t weight_gradient(int m, int n, int k, const fuse_bf16* a, const fuse_
   launch::fill_core(&f, m, n, k, block_n, 0, alpha, beta, d, n, FUSE_RASTER_ALONG_M, 8);
   f.wait = host::make_wait(info, 1, 0);
   StoreMaps stores{};
+  if (block_n == 256 && beta == 0.0f && info.sm_count % 2 == 0 && launch::pair_tiles_requested())
+    return launch::launch_pair_kernel<kModePlain, StoreMaps, false, true, true>(maps, maps.a, maps.a, stores, f, 8, info,
+                                                                                stream, 0.0);
   return launch_mode<kModePlain, true, true>(maps, stores, f, block_n, info, stream, beta == 0.0f);
 }
 

@@ -219,7 +219,7 @@ inline bool encode_lhs_pull_maps(LhsPullMaps* maps, const FusedParams& f, uint64
 // Launches pair_gemm_kernel (CTA pairs, 256 x 256 tiles) over `k`, whose tile order is re-planned
 // for 256-row tiles.  `maps.b` must box 128 rows (half a tile); sfa / sfb are only read by the
 // block-scaled variant.
-template <int kMode, class Maps, bool kMx>
+template <int kMode, class Maps, bool kMx, bool kAMn = false, bool kBMn = false>
 cudaError_t launch_pair_kernel(const Operands& maps, const CUtensorMap& sfa, const CUtensorMap& sfb, Maps& stores,
                                FusedParams k, int max_swizzle, const DeviceInfo& info, cudaStream_t stream,
                                double comm_bytes) {
@@ -231,10 +231,10 @@ cudaError_t launch_pair_kernel(const Operands& maps, const CUtensorMap& sfa, con
   k.order.swizzle = select_swizzle(max_swizzle, k.order.m_tiles, k.order.n_tiles);
   if (kMode == kModeQkvDirect) k.order.n_shift = int32_t(int64_t(k.qkv.rank) * k.order.n_tiles / k.qkv.world);
   k.join_tile = k.order.count();
-  if (kMode == kModeLhsPull || kMode == kModeGradPull) plan_join(&k, Layout::kBlockN, info.sm_count, comm_bytes, kMx, 2);
+  if (kMode == kModeLhsPull || kMode == kModeGradPull || kMode == kModeHeadGate) plan_join(&k, Layout::kBlockN, info.sm_count, comm_bytes, kMx, 2);
   const int64_t tiles = k.order.count();
   const int compute_pairs = int(tiles < (info.sm_count - k.num_comm_ctas) / 2 ? tiles : (info.sm_count - k.num_comm_ctas) / 2);
-  return host::launch_kernel(pair_gemm_kernel<kMode, Maps, kMx>, k.num_comm_ctas + 2 * compute_pairs, kThreads,
+  return host::launch_kernel(pair_gemm_kernel<kMode, Maps, kMx, kAMn, kBMn>, k.num_comm_ctas + 2 * compute_pairs, kThreads,
                              Layout::kDynamicBytes, kMode != kModePlain || kMx, stream, maps.a, maps.b, sfa, sfb, stores, k);
 }
 

@@ -66,17 +66,23 @@ using PairLayout = PairLayoutT<false>;
 // (FusedParams::lhs, LhsPullMaps; num_comm_ctas even).
 // kMx: block-scaled E4M3 (tmap_sfa / tmap_sfb: the operands' scale storage as rows of one 512-byte
 // atom, 128 32-bit words); FusedParams::wq_* / clear_* request the weight quantisation prologue.
-template <int kMode, class Maps, bool kMx = false>
+// kAMn / kBMn (BF16 only): the operand is stored with its M (resp. N) axis contiguous and is fed to
+// the tensor core as an MN-major tile -- 64-element groups along MN, each a [64 K rows x 128 bytes]
+// swizzled box; a CTA then holds two groups of A and two groups of its half of B per K block.
+template <int kMode, class Maps, bool kMx = false, bool kAMn = false, bool kBMn = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
                  const __grid_constant__ Maps store_maps, const FusedParams p) {
-  static_assert(kMode == kModePlain || kMode == kModeQkvDirect || kMode == kModeLhsPull || kMode == kModeGradPull,
+  static_assert(kMode == kModePlain || kMode == kModeQkvDirect || kMode == kModeLhsPull || kMode == kModeGradPull ||
+                    kMode == kModeHeadGate,
                 "modes of the pair kernel");
   static_assert(kMode != kModeGradPull || kMx, "the gradient pull feeds the block-scaled GEMM");
+  static_assert(!kMx || (!kAMn && !kBMn), "block-scaled operands are K-major");
   constexpr bool kDirect = kMode == kModeQkvDirect;
-  constexpr bool kGated = kMode == kModeLhsPull || kMode == kModeGradPull;
-  constexpr bool kHeads = kMode == kModeGradPull;  // K groups are Q/K/V heads, one flag line each
+  constexpr bool kGated = kMode == kModeLhsPull || kMode == kModeGradPull || kMode == kModeHeadGate;
+  constexpr bool kHeads = kMode == kModeGradPull || kMode == kModeHeadGate;  // K groups are Q/K/V heads
+  constexpr bool kRemoteWriter = kMode == kModeHeadGate;  // flags released by the sending GPUs
   using Layout = PairLayoutT<kMx>;
   constexpr int kStages = Layout::kStages;
   constexpr int32_t kBlockElems = kMx ? 2 * kBlockK : kBlockK;  // K elements per 128-byte row
@@ -121,7 +127,11 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   if constexpr (kGated) {
     if (is_comm) {
       if (!(p.flags & kFlagComputeOnly)) {
-        if constexpr (kHeads) {
+        if constexpr (kMode == kModeHeadGate) {
+          GradPushPolicy policy(p, store_maps);
+          run_chunk_pipeline(policy, p.wait, base, p.num_comm_ctas);
+          __threadfence_system();
+        } else if constexpr (kHeads) {
           GradPullPolicy policy(p, store_maps);
           run_chunk_pipeline(policy, p.wait, base, p.num_comm_ctas);
         } else {
@@ -216,8 +226,21 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           const uint32_t a_dst = base + stage * Layout::kStageBytes;
           const uint32_t leader_full = ptx::map_to_cta(full_bar(stage), 0);
           if (leader) ptx::mbar_expect_tx(full_bar(stage), 2 * (Layout::kStageBytes + Layout::kSfStageBytes));
-          ptx::tma_load_2d_pair(a_dst, &tmap_a, leader_full, kb * kBlockElems, row0);
-          ptx::tma_load_2d_pair(a_dst + Layout::kABytes, &tmap_b, leader_full, kb * kBlockElems, wrow0);
+          if constexpr (!kAMn) {
+            ptx::tma_load_2d_pair(a_dst, &tmap_a, leader_full, kb * kBlockElems, row0);
+          } else {
+#pragma unroll
+            for (int g = 0; g < kBlockM / 64; ++g)
+              ptx::tma_load_2d_pair(a_dst + g * kMnGroupBytes, &tmap_a, leader_full, row0 + g * 64, kb * kBlockK);
+          }
+          if constexpr (!kBMn) {
+            ptx::tma_load_2d_pair(a_dst + Layout::kABytes, &tmap_b, leader_full, kb * kBlockElems, wrow0);
+          } else {
+#pragma unroll
+            for (int g = 0; g < kBlockN / 2 / 64; ++g)
+              ptx::tma_load_2d_pair(a_dst + Layout::kABytes + g * kMnGroupBytes, &tmap_b, leader_full, wrow0 + g * 64,
+                                    kb * kBlockK);
+          }
           if constexpr (kMx) {
             // scale atoms of this K block: this CTA's A rows, and both 128-row halves of the B tile
             // (rows past the operand read zeros: the tensor map clips)
@@ -237,7 +260,11 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else if (warp == 1) {
     // ------------------------------------------------------------------ UMMA issuer (leader CTA)
     if (lane == 0 && leader) {
-      constexpr uint32_t kIdesc = ptx::idesc_bf16_f32(2 * kBlockM, kBlockN, 0, 0);
+      constexpr uint32_t kIdesc = ptx::idesc_bf16_f32(2 * kBlockM, kBlockN, kAMn ? 1 : 0, kBMn ? 1 : 0);
+      // descriptor step per UMMA (16 K values): 32 bytes inside the swizzle row of a K-major tile,
+      // 16 rows of 128 bytes in an MN-major tile
+      constexpr uint64_t kAStep = kAMn ? (kUmmaK * 128) >> 4 : (kUmmaK * 2) >> 4;
+      constexpr uint64_t kBStep = kBMn ? (kUmmaK * 128) >> 4 : (kUmmaK * 2) >> 4;
       uint32_t stage = 0, phase = 0, accum = 0, accum_phase = 0;
       uint32_t sf_parity = 0;
       (void)sf_parity;
@@ -254,8 +281,9 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           if (!ok) break;
           ptx::tc_fence_after();
           const uint32_t a_addr = base + stage * Layout::kStageBytes;
-          const uint64_t a_desc = ptx::smem_desc_k_sw128(a_addr);
-          const uint64_t b_desc = ptx::smem_desc_k_sw128(a_addr + Layout::kABytes);
+          const uint64_t a_desc = kAMn ? ptx::smem_desc_mn_sw128(a_addr, kMnGroupBytes) : ptx::smem_desc_k_sw128(a_addr);
+          const uint64_t b_desc = kBMn ? ptx::smem_desc_mn_sw128(a_addr + Layout::kABytes, kMnGroupBytes)
+                                       : ptx::smem_desc_k_sw128(a_addr + Layout::kABytes);
           if constexpr (kMx) {
             // scale atoms shared -> TMEM in both CTAs, then four K = 32 UMMAs; UMMA k reads byte k
             // of every 32-bit scale column; two sets of scale columns alternate
@@ -273,7 +301,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           } else {
 #pragma unroll
             for (int k = 0; k < kBlockK / kUmmaK; ++k)
-              ptx::umma_f16_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+              ptx::umma_f16_pair(d_tmem, a_desc + kAStep * k, b_desc + kBStep * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
           }
           ptx::umma_commit_pair(empty_bar(stage), 3);  // frees the stage in both CTAs
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -306,7 +334,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           continue;
         }
         const uint32_t* flags = p.ready + int64_t(mt) * (groups / virt) * kReadyFlagStride;
-        ok = scout_tile<false>(p.wait, flags, groups, virt, kHeads ? 0 : p.lhs.gate_start, gate_word,
+        ok = scout_tile<kRemoteWriter>(p.wait, flags, groups, virt, kHeads ? 0 : p.lhs.gate_start, gate_word,
                                tile_seq * kGateSeqStep, lane, uint32_t(mt * groups));
       }
     }
@@ -434,7 +462,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     ptx::tmem_dealloc_pair(tmem_base, Layout::kTmemColumns);
   }
   }  // do_compute
-  if constexpr (kDirect || kMode == kModeGradPull) {
+  if constexpr (kDirect || kMode == kModeGradPull || kMode == kModeHeadGate) {
     // every rank's transfers are complete before any rank's inputs or outputs may change
     cooperative_groups::this_grid().sync();
     qkv_finalize(p);

@@ -40,9 +40,9 @@ FLOPS_PER_RANK = 2.0 * TOKENS_PER_RANK * HIDDEN * (QKV_N + OPROJ_K)
 QKV_FLOPS = 2.0 * TOKENS_PER_RANK * HIDDEN * QKV_N
 
 # DRAM bytes (read + write) of one launch of the dominant kernel (the fused QKV kernel at this
-# workload, context-parallel size 1, direct route), dram__bytes_read.sum + dram__bytes_write.sum
-# of the ncu capture summarised in profiles/fused_gemm_kernel_forward_c2_ncu.md.
-QKV_DRAM_TRAFFIC_BYTES = 836_608_768
+# workload, context-parallel size 1, direct route, CTA pairs), dram__bytes_read.sum +
+# dram__bytes_write.sum of the ncu capture summarised in profiles/pair_gemm_kernel_forward_c2_ncu.md.
+QKV_DRAM_TRAFFIC_BYTES = 876_308_736
 
 
 _RESULT_FD = None
@@ -437,7 +437,8 @@ def run_gpu_arm(args):
             },
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak, "traffic": QKV_DRAM_TRAFFIC_BYTES,
-                         "kernel": "fused_gemm_kernel<256,4,%s> (QKVProj GEMM -> A2A)" % ("QkvDirect" if args.qkv_route == "direct" else "QkvPush"),
+                         "kernel": ("pair_gemm_kernel<QkvDirect> (QKVProj GEMM -> A2A, CTA pairs)" if args.qkv_route == "direct"
+                                    else "fused_gemm_kernel<256,4,QkvPush> (QKVProj GEMM -> A2A)"),
                          "peak_source": peak_source},
             "e2e": {"value": FLOPS_PER_RANK * world_size / (e2e_ms * 1e-3) / 1e15, "unit": "PFLOPS",
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,

@@ -436,7 +436,8 @@ def run_gpu_arm(args):
                                    "comm_ctas": args.oproj_comm},
             },
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": QKV_DRAM_TRAFFIC_BYTES,
+                         "frac": achieved / peak,
+                         "traffic": QKV_DRAM_TRAFFIC_BYTES if args.qkv_route == "direct" and world_size == 1 else None,
                          "kernel": ("pair_gemm_kernel<QkvDirect> (QKVProj GEMM -> A2A, CTA pairs)" if args.qkv_route == "direct"
                                     else "fused_gemm_kernel<256,4,QkvPush> (QKVProj GEMM -> A2A)"),
                          "peak_source": peak_source},

@@ -347,11 +347,18 @@ int32_t fuse_recommended_gemm_a2a_comm_ctas(const fuse_gemm_problem* problem,
   return 0;  // no calibrated plan yet: the caller passes an explicit budget
 }
 
+// B200 calibration of the lhs pull (one communication CTA moves 30-40 GB/s through its copy
+// pipeline while the GEMM runs; measured at the 8B and 70B projection shapes): enough CTAs to
+// finish the pull in about half of the GEMM's time, an even number so that they form pairs.
 int32_t fuse_recommended_a2a_lhs_gemm_comm_ctas(const fuse_gemm_problem* problem,
                                                 const fuse_ulysses_route* route) {
-  (void)problem;
+  if (problem == nullptr || problem->m <= 0 || problem->n <= 0 || problem->k <= 0) return 0;
   (void)route;
-  return 0;
+  const double pull_bytes = double(problem->m) * double(problem->k) * 2.0;
+  const double gemm_seconds = 2.0 * double(problem->m) * double(problem->n) * double(problem->k) / 1.5e15;
+  int ctas = int(pull_bytes / (35.0e9 * 0.5 * gemm_seconds) + 0.5);
+  ctas += ctas & 1;
+  return ctas < 4 ? 4 : (ctas > 32 ? 32 : ctas);
 }
 
 int fuse_b200_abi_sizeof(int record) {

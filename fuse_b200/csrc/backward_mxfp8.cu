@@ -277,6 +277,16 @@ cudaError_t oproj_data(const fuse_mxfp8_oproj_backward_data_params& mp, const fu
     tma = encode_peer_store_maps(&stores, p.peer_grad_attention, p.world_size,
                                  uint64_t(p.batch) * uint64_t(f.qkv.global_seq),
                                  int64_t(p.q_heads) / p.world_size * p.head_dim, 0);
+  if (tma && block_n == 256 && k % 128 == 0 && info.sm_count % 2 == 0 && launch::pair_tiles_requested()) {
+    Operands pair_maps = maps;
+    CUtensorMap sfa_map, sfb_map;
+    if (encode_operand_u8(&pair_maps.b, wq.data, n, k, k, 128) == cudaSuccess &&
+        launch::encode_scale_atoms(&sfa_map, f.sfa, m, k) == cudaSuccess &&
+        launch::encode_scale_atoms(&sfb_map, f.sfb, n, k) == cudaSuccess)
+      return launch::launch_pair_kernel<kModeQkvDirect, StoreMaps, true>(
+          pair_maps, sfa_map, sfb_map, stores, f, p.gemm_tuning.max_swizzle_size ? p.gemm_tuning.max_swizzle_size : 1, info,
+          stream, 0.0);
+  }
   return launch_mode<kModeQkvDirect, false, false, true>(maps, stores, f, block_n, info, stream, tma);
 }
 

@@ -248,6 +248,15 @@ cudaError_t qkv_forward_mxfp8(const fuse_mxfp8_gemm_a2a_params& mp, const fuse_b
     tma = encode_peer_store_maps(&stores, p.peer_output, r.world_size, uint64_t(r.batch) * uint64_t(r.global_seq),
                                  int64_t(r.q_heads) / r.world_size * r.head_dim,
                                  int64_t(r.kv_heads) / r.world_size * r.head_dim);
+  if (tma && block_n == 256 && g.k % 128 == 0 && info.sm_count % 2 == 0 && launch::pair_tiles_requested()) {
+    Operands pair_maps = maps;
+    CUtensorMap sfa_map, sfb_map;
+    if (encode_operand_u8(&pair_maps.b, w.data, g.n, g.k, g.k, 128) == cudaSuccess &&
+        launch::encode_scale_atoms(&sfa_map, f.sfa, g.m, g.k) == cudaSuccess &&
+        launch::encode_scale_atoms(&sfb_map, f.sfb, g.n, g.k) == cudaSuccess)
+      return launch::launch_pair_kernel<kModeQkvDirect, StoreMaps, true>(pair_maps, sfa_map, sfb_map, stores, f,
+                                                                         g.max_swizzle_size, info, stream, 0.0);
+  }
   return launch_mode<kModeQkvDirect, false, false, true>(maps, stores, f, block_n, info, stream, tma);
 }
 

@@ -73,6 +73,16 @@ def test_ready_sizes():
     assert api.a2a_lhs_gemm_ready_elements(N.GemmProblem(130, 4096, 4096), route) == 2 * 8 * 32
 
 
+def test_auto_budget_of_the_output_projection_pull():
+    route = N.UlyssesRoute(world_size=8)
+    for shape in ((16384, 4096, 4096), (32768, 8192, 8192), (256, 512, 512), (65536, 1024, 16384)):
+        ctas = api.recommended_a2a_lhs_gemm_comm_ctas(N.GemmProblem(*shape), route)
+        assert 4 <= ctas <= 32 and ctas % 2 == 0
+    assert api.recommended_a2a_lhs_gemm_comm_ctas(N.GemmProblem(16384, 4096, 4096), route) in (20, 22)
+    # no calibration for the communication-CTA route of the QKV projection: explicit budgets only
+    assert api.recommended_gemm_a2a_comm_ctas(N.GemmProblem(16384, 6144, 4096), route) == 0
+
+
 def test_mxfp8_traits_and_workspace_overloads():
     for traits in (api.mxfp8_qkv_cutlass_kernel_traits(64), api.mxfp8_qkv_cutlass_kernel_traits(32),
                    api.mxfp8_oproj_cutlass_kernel_traits(32, False), api.mxfp8_oproj_cutlass_kernel_traits(64, True)):

@@ -154,31 +154,34 @@ def main():
     gp = N.Bf16GroupedGemmParams(lhs=lp.data_ptr(), weight_nt=wp.data_ptr(), output=op.data_ptr(),
                                  row_offsets=offs_d.data_ptr(), source=src_d.data_ptr(), experts=experts_local,
                                  n=mn, k=mk, expert_row_capacity=cap, rank=rank, world_size=world, topk=topk)
-    gp.policy = N.GroupedGemmPolicy(num_comm_ctas=6, num_compute_ctas=128, tile_n=256)
     for r in range(world):
         gp.peer_input[r] = msym["moe_tokens"].peer_ptrs[r]
         gp.peer_started[r] = msym["moe_started"].peer_ptrs[r]
         gp.peer_done[r] = msym["moe_done"].peer_ptrs[r]
-    rc, plan = api.create_bf16_a2a_grouped_gemm(gp)
-    assert rc == 0, rc
-    torch.cuda.synchronize()
-    dist.barrier()
-    for _ in range(2):
-        assert api.launch_bf16_grouped_gemm(plan, 0, opts) == 0
-    torch.cuda.synchronize()
-    status = api.read_status()
-    assert status[0] == 0, status[:8]
     want_lhs = np.full((experts_local, cap, mk), 0x7f7f, dtype=np.uint16)
     want_eo = np.full((experts_local, cap, mn), 0x7f7f, dtype=np.uint16)
     assert O.lib().fo_moe_dispatch_fc1(experts_local, O.ptr(offs), O.ptr(src), O.ptr_array(toks_all), O.ptr(ew), mn, mk,
                                        cap, O.ptr(want_lhs), O.ptr(want_eo)) == 0
-    assert np.array_equal(bits(lhs), want_lhs), "dispatched rows"
-    for e in range(experts_local):
-        cnt = int(offs[e + 1] - offs[e])
-        ok, worst, bad = O.within_tolerance(bits(eo)[e, :cnt], want_eo[e, :cnt], 0.002, 0.008)
-        assert ok, ("moe", e, worst, bad)
-    assert api.destroy_bf16_grouped_gemm(plan) == 0
-    dist.barrier()
+    for mma_sm_count in (1, 2):  # one-CTA tiles, then CTA pairs
+        gp.policy = N.GroupedGemmPolicy(num_comm_ctas=6, num_compute_ctas=128, tile_n=256, mma_sm_count=mma_sm_count)
+        lhs.view(torch.int16).fill_(0x7f7f)
+        eo.view(torch.int16).fill_(0x7f7f)
+        rc, plan = api.create_bf16_a2a_grouped_gemm(gp)
+        assert rc == 0, rc
+        torch.cuda.synchronize()
+        dist.barrier()
+        for _ in range(2):
+            assert api.launch_bf16_grouped_gemm(plan, 0, opts) == 0
+        torch.cuda.synchronize()
+        status = api.read_status()
+        assert status[0] == 0, status[:8]
+        assert np.array_equal(bits(lhs), want_lhs), "dispatched rows"
+        for e in range(experts_local):
+            cnt = int(offs[e + 1] - offs[e])
+            ok, worst, bad = O.within_tolerance(bits(eo)[e, :cnt], want_eo[e, :cnt], 0.002, 0.008)
+            assert ok, ("moe", mma_sm_count, e, worst, bad)
+        assert api.destroy_bf16_grouped_gemm(plan) == 0
+        dist.barrier()
 
     # ---- MXFP8 output projection: bytes and scale bytes pulled from every peer ------------------
     to_dev_u8 = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)

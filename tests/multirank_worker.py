@@ -41,14 +41,14 @@ def main():
     lhs = [synthetic.normal_bf16((m, k), synthetic.rank_seed(r) + 1000, 1.0) for r in range(world)]
     wq = synthetic.normal_bf16((n, k), synthetic.BASE_SEED + 11, 0.02)
     attn_all = [synthetic.normal_bf16((rows, ko // world), synthetic.rank_seed(r) + 2000, 1.0) for r in range(world)]
-    wo = synthetic.normal_bf16((384, ko), synthetic.BASE_SEED + 17, 0.02)
+    wo = synthetic.normal_bf16((512, ko), synthetic.BASE_SEED + 17, 0.02)  # 256-wide tiles: CTA pairs
     to_dev = lambda a: torch.from_numpy(a.view(np.int16)).to(dev).view(torch.bfloat16)
     x, wq_d, wo_d = to_dev(lhs[rank]), to_dev(wq), to_dev(wo)
     sym["attn"].view(torch.bfloat16).copy_(to_dev(attn_all[rank]).reshape(-1))
     sym["planar"].view(torch.int16).fill_(-1)
     local = torch.full((m, n), -1, dtype=torch.int16, device=dev).view(torch.bfloat16)
     staging = torch.full((m, ko), -1, dtype=torch.int16, device=dev).view(torch.bfloat16)
-    out = torch.full((m, 384), -1, dtype=torch.int16, device=dev).view(torch.bfloat16)
+    out = torch.full((m, 512), -1, dtype=torch.int16, device=dev).view(torch.bfloat16)
     torch.cuda.synchronize()
     dist.barrier()
 
@@ -79,7 +79,7 @@ def main():
     assert ok, ("planar", worst, bad)
 
     dist.barrier()
-    o_problem = N.GemmProblem(m, 384, ko, max_swizzle_size=8)
+    o_problem = N.GemmProblem(m, 512, ko, max_swizzle_size=8)
     o_route = N.UlyssesRoute(world_size=world, rank=rank, batch=batch, global_seq=s * world, seq_local=s,
                              kind=N.ROUTE_HEAD_TO_SEQUENCE, direction=N.ROUTE_INVERSE)
     o_ready = torch.zeros(api.a2a_lhs_gemm_ready_elements(o_problem, o_route), dtype=torch.int32, device=dev)
@@ -98,7 +98,7 @@ def main():
     dist.barrier()  # peers' inputs stay immutable until every rank is done
 
     # ---- QKV backward: sender push into the peers' staging, flags released on the destination ----
-    hidden = 384
+    hidden = 512
     planes_all = [tuple(synthetic.normal_bf16((rows, heads // world * d), synthetic.rank_seed(r) + 100 * seg + 101, 0.01)
                         for seg, heads in enumerate((q, kv, kv))) for r in range(world)]
     wb = synthetic.normal_bf16((n, hidden), synthetic.BASE_SEED + 23, 0.02)

@@ -966,15 +966,17 @@ __device__ __forceinline__ void run_chunk_pipeline(Policy& policy, const WaitCon
     ptx::st_release_cta_shared(heads + 4u * uint32_t(warp), posted);
   };
 
-  typename Policy::Cursor load_cursor, store_cursor;
+  // The cursor of every chunk in flight is kept from its load to its store (one per stage), so
+  // the unit walk is decoded once per chunk.
+  static_assert(kPullStages == 2, "two cursors in flight");
+  typename Policy::Cursor load_cursor, in_flight0, in_flight1;
   bool more_loads = policy.first(load_cursor, worker, workers);
   if (!more_loads) {
     post(kPublishSentinel);
     return;
   }
-  store_cursor = load_cursor;
   int32_t issued = 0, consumed = 0;
-  bool ok = true, more_stores = true;
+  bool ok = true;
   // Starts the copy of the chunk under the load cursor; false when the policy had to give up
   // (an upstream flag that never came), in which case nothing was started.
   auto start_load = [&]() {
@@ -982,6 +984,8 @@ __device__ __forceinline__ void run_chunk_pipeline(Policy& policy, const WaitCon
                                 bars + 8u * uint32_t(issued % kPullStages), lane) ? 1u : 0u;
     good = __shfl_sync(0xffffffffu, good, 0);
     if (!good) { ok = false; return; }
+    if (issued % kPullStages == 0) in_flight0 = load_cursor;
+    else in_flight1 = load_cursor;
     more_loads = policy.next(load_cursor, workers);
     ++issued;
   };
@@ -989,8 +993,9 @@ __device__ __forceinline__ void run_chunk_pipeline(Policy& policy, const WaitCon
   int64_t lag_unit[kPullLag];
 #pragma unroll
   for (int i = 0; i < kPullLag; ++i) lag_unit[i] = -1;
-  while (ok && more_stores) {
+  while (ok && consumed < issued) {
     const int stage = consumed % kPullStages;
+    const typename Policy::Cursor store_cursor = stage == 0 ? in_flight0 : in_flight1;
     uint32_t landed = 1u;
     if (lane == 0) {
       trace_event(policy.p, 30);  // waiting for the chunk to land
@@ -1028,7 +1033,6 @@ __device__ __forceinline__ void run_chunk_pipeline(Policy& policy, const WaitCon
       for (int i = kPullLag - 1; i > 0; --i) lag_unit[i] = lag_unit[i - 1];
       lag_unit[0] = policy.closes(store_cursor) ? policy.unit(store_cursor) : -1;
     }
-    more_stores = policy.next(store_cursor, workers);
   }
   ptx::bulk_wait<0>();
   __syncwarp();

@@ -234,6 +234,14 @@ cudaError_t oproj_forward(const fuse_a2a_gemm_params& p, const fuse_b200_options
       if (block_n == 256 && num_comm_ctas % 2 == 0 && info.sm_count % 2 == 0 && pair_tiles_requested()) {
         FusedParams pk = k;
         pk.lhs.m_group = 2 * wave_m_group_pairs(pk, info.sm_count);
+        if (launch::embedded_pull_requested()) {
+          Operands pair_maps;
+          if (encode_operand(&pair_maps.a, p.input_staging, p.gemm.m, p.gemm.k, lda, false, kBlockM) == cudaSuccess &&
+              encode_operand(&pair_maps.b, p.rhs_nt, p.gemm.n, p.gemm.k, packed_or(p.gemm.stride_b.row, p.gemm.k), false,
+                             PairLayout::kBlockN / 2) == cudaSuccess)
+            return launch::launch_pair_kernel<kModeLhsPull, LhsPullMaps, false, false, false, true>(
+                pair_maps, pair_maps.a, pair_maps.a, pull, pk, p.gemm.max_swizzle_size, info, stream, 0.0);
+        }
         return launch_pair<kModeLhsPull>(p.input_staging, lda, p.rhs_nt, packed_or(p.gemm.stride_b.row, p.gemm.k), p.gemm,
                                          pull, pk, info, stream, double(p.gemm.m) * p.gemm.k * 2.0);
       }

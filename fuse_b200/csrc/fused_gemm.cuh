@@ -1047,6 +1047,76 @@ __device__ __forceinline__ void run_chunk_pipeline(Policy& policy, const WaitCon
   post(kPublishSentinel);
 }
 
+// The same pipeline run by ONE thread with its own two stages (the copy warp embedded in a compute
+// CTA): chunks are dealt to `workers` such threads, a finished unit is published by the thread
+// itself (fence + flag, kPullLag chunks late except at start-up).  `bars`: two mbarriers of count 1.
+template <class Policy>
+__device__ __forceinline__ void run_chunk_pipeline_thread(Policy& policy, const WaitContext& w, uint32_t ring,
+                                                          uint32_t bars, int32_t worker, int32_t workers) {
+  static_assert(kPullStages == 2, "two cursors in flight");
+  typename Policy::Cursor load_cursor, in_flight0, in_flight1;
+  bool more_loads = policy.first(load_cursor, worker, workers);
+  if (!more_loads) return;
+  int32_t issued = 0, consumed = 0;
+  bool ok = true;
+  auto publish = [&](int64_t unit) {
+    policy.publish_fence();
+    policy.publish_flag(unit);
+  };
+  auto start_load = [&]() {
+    if (!policy.load(load_cursor, ring + uint32_t(issued % kPullStages) * kPullStageBytes,
+                     bars + 8u * uint32_t(issued % kPullStages), 0)) {
+      ok = false;
+      return;
+    }
+    if (issued % kPullStages == 0) in_flight0 = load_cursor;
+    else in_flight1 = load_cursor;
+    more_loads = policy.next(load_cursor, workers);
+    ++issued;
+  };
+  while (ok && issued < kPullStages && more_loads) start_load();
+  int64_t lag_unit[kPullLag];
+#pragma unroll
+  for (int i = 0; i < kPullLag; ++i) lag_unit[i] = -1;
+  while (ok && consumed < issued) {
+    const int stage = consumed % kPullStages;
+    const typename Policy::Cursor store_cursor = stage == 0 ? in_flight0 : in_flight1;
+    if (!mbar_wait(bars + 8u * stage, uint32_t(consumed / kPullStages) & 1u, w, kSiteCommStage)) {
+      ok = false;
+      break;
+    }
+    policy.store(store_cursor, ring + uint32_t(stage) * kPullStageBytes, 0);
+    ptx::bulk_commit();
+    ++consumed;
+    ptx::bulk_wait_read<0>();
+    if (more_loads && issued < consumed + kPullStages) start_load();
+    if (consumed <= kPullEagerChunks) {
+      ptx::bulk_wait<0>();
+#pragma unroll
+      for (int i = kPullLag - 1; i >= 0; --i) {
+        if (lag_unit[i] >= 0) publish(lag_unit[i]);
+        lag_unit[i] = -1;
+      }
+      if (policy.closes(store_cursor)) publish(policy.unit(store_cursor));
+    } else {
+      ptx::bulk_wait<kPullLag>();
+      if (lag_unit[kPullLag - 1] >= 0) publish(lag_unit[kPullLag - 1]);
+#pragma unroll
+      for (int i = kPullLag - 1; i > 0; --i) lag_unit[i] = lag_unit[i - 1];
+      lag_unit[0] = policy.closes(store_cursor) ? policy.unit(store_cursor) : -1;
+    }
+  }
+  ptx::bulk_wait<0>();
+  if (ok) {
+#pragma unroll
+    for (int i = kPullLag - 1; i >= 0; --i)
+      if (lag_unit[i] >= 0) publish(lag_unit[i]);
+  } else {
+    for (int32_t i = consumed; i < issued; ++i)
+      mbar_wait(bars + 8u * uint32_t(i % kPullStages), uint32_t(i / kPullStages) & 1u, w, kSiteDrain, false);
+  }
+}
+
 // Forward lhs pull with tensor copies.  A (M tile, column slice) unit -- 128 rows of one slice of
 // one peer's shard, plus (block-scaled operands) the slice's scale atoms -- is cut into chunks of
 // rows_per_chunk rows x piece_bytes (one stage) and the chunks into sub-units of two, dealt round

@@ -219,11 +219,12 @@ inline bool encode_lhs_pull_maps(LhsPullMaps* maps, const FusedParams& f, uint64
 // Launches pair_gemm_kernel (CTA pairs, 256 x 256 tiles) over `k`, whose tile order is re-planned
 // for 256-row tiles.  `maps.b` must box 128 rows (half a tile); sfa / sfb are only read by the
 // block-scaled variant.
-template <int kMode, class Maps, bool kMx, bool kAMn = false, bool kBMn = false>
+template <int kMode, class Maps, bool kMx, bool kAMn = false, bool kBMn = false, bool kEmbedded = false>
 cudaError_t launch_pair_kernel(const Operands& maps, const CUtensorMap& sfa, const CUtensorMap& sfb, Maps& stores,
                                FusedParams k, int max_swizzle, const DeviceInfo& info, cudaStream_t stream,
                                double comm_bytes) {
-  using Layout = PairLayoutT<kMx>;
+  using Layout = PairLayoutT<kMx, kEmbedded>;
+  if (kEmbedded) k.num_comm_ctas = 0;  // every CTA computes; its copy warp pulls
   cudaError_t status = encode_store_map(&stores.local, k.d, uint64_t(k.m), uint64_t(k.n), k.ldd);
   if (status != cudaSuccess) return status;
   k.order.m_tiles = host::ceil_div(k.m, 2 * kBlockM);
@@ -231,10 +232,10 @@ cudaError_t launch_pair_kernel(const Operands& maps, const CUtensorMap& sfa, con
   k.order.swizzle = select_swizzle(max_swizzle, k.order.m_tiles, k.order.n_tiles);
   if (kMode == kModeQkvDirect) k.order.n_shift = int32_t(int64_t(k.qkv.rank) * k.order.n_tiles / k.qkv.world);
   k.join_tile = k.order.count();
-  if (kMode == kModeLhsPull || kMode == kModeGradPull || kMode == kModeHeadGate) plan_join(&k, Layout::kBlockN, info.sm_count, comm_bytes, kMx, 2);
+  if (!kEmbedded && (kMode == kModeLhsPull || kMode == kModeGradPull || kMode == kModeHeadGate)) plan_join(&k, Layout::kBlockN, info.sm_count, comm_bytes, kMx, 2);
   const int64_t tiles = k.order.count();
   const int compute_pairs = int(tiles < (info.sm_count - k.num_comm_ctas) / 2 ? tiles : (info.sm_count - k.num_comm_ctas) / 2);
-  return host::launch_kernel(pair_gemm_kernel<kMode, Maps, kMx, kAMn, kBMn>, k.num_comm_ctas + 2 * compute_pairs, kThreads,
+  return host::launch_kernel(pair_gemm_kernel<kMode, Maps, kMx, kAMn, kBMn, kEmbedded>, k.num_comm_ctas + 2 * compute_pairs, kThreads,
                              Layout::kDynamicBytes, kMode != kModePlain || kMx, stream, maps.a, maps.b, sfa, sfb, stores, k);
 }
 
@@ -244,6 +245,13 @@ inline cudaError_t encode_scale_atoms(CUtensorMap* map, const void* scales, int6
   const uint64_t atoms = uint64_t((rows + 127) / 128) * uint64_t((k + 127) / 128);
   return host::encode_tensor_map_2d(map, scales, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, atoms, 128, 512, 1, 128,
                                     CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
+// The lhs pull run by one warp of every compute CTA instead of communication CTAs:
+// FUSE_B200_EMBEDDED_PULL=1 (read on every launch).
+inline bool embedded_pull_requested() {
+  const char* text = std::getenv("FUSE_B200_EMBEDDED_PULL");
+  return text != nullptr && std::atoi(text) != 0;
 }
 
 // CTA-pair tiles are used wherever the shape allows; the environment switch FUSE_B200_PAIR=0

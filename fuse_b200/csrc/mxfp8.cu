@@ -382,8 +382,13 @@ cudaError_t oproj_forward_mxfp8(const fuse_mxfp8_a2a_gemm_params& mp, const fuse
         if (encode_operand_u8(&pair_maps.b, w.weights.data, g.n, g.k, g.k, 128) == cudaSuccess &&
             launch::encode_scale_atoms(&sfa_map, f.sfa, g.m, g.k) == cudaSuccess &&
             launch::encode_scale_atoms(&sfb_map, f.sfb, g.n, g.k) == cudaSuccess)
+        {
+          if (launch::embedded_pull_requested())
+            return launch::launch_pair_kernel<kModeLhsPull, LhsPullMaps, true, false, false, true>(
+                pair_maps, sfa_map, sfb_map, pull, pf, g.max_swizzle_size, info, stream, 0.0);
           return launch::launch_pair_kernel<kModeLhsPull, LhsPullMaps, true>(
               pair_maps, sfa_map, sfb_map, pull, pf, g.max_swizzle_size, info, stream, double(g.m) * g.k * (1.0 + 1.0 / 32));
+        }
       }
     }
     if (launch::encode_lhs_pull_maps(&pull, f, uint64_t(r.batch) * uint64_t(r.global_seq)))

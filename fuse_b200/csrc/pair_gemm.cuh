@@ -32,9 +32,11 @@ namespace fuse_b200 {
 // rows); every stage also carries the 512-byte scale atom of this CTA's A rows and the two atoms
 // of ALL 256 B rows (each CTA's tensor core needs the scales of the whole B tile); the
 // accumulator is single-buffered (TMEM also holds the scales) and drained whole by the epilogue.
-template <bool kMx>
+// kEmbedded: one warp of every compute CTA runs the copy pipeline of the lhs pull (no communication
+// CTAs at all); its two 16 KiB stages take the place of the sixth GEMM stage.
+template <bool kMx, bool kEmbedded = false>
 struct PairLayoutT {
-  static constexpr int kStages = 6;
+  static constexpr int kStages = kEmbedded ? 5 : 6;
   static constexpr int kAccumStages = kMx ? 1 : 2;
   static constexpr int kBlockN = 256;                                  // of the pair's tile
   static constexpr uint32_t kABytes = kBlockM * kBlockK * 2;           // this CTA's 128 rows
@@ -45,8 +47,10 @@ struct PairLayoutT {
   static constexpr uint32_t kStagingBuffers = kMx ? 1 : 2;
   static constexpr uint32_t kStagingBlockBytes = kBlockM * 64 * 2;
   static constexpr uint32_t kStagingOffset = kSfOffset + ((kStages * kSfStageBytes + 1023u) & ~1023u);
-  static constexpr uint32_t kBarrierOffset = kStagingOffset + kStagingBuffers * kStagingBlockBytes;
-  static constexpr uint32_t kNumBarriers = 2 * kStages + 2 * kAccumStages;
+  static constexpr uint32_t kCopyRingOffset = kStagingOffset + kStagingBuffers * kStagingBlockBytes;
+  static constexpr uint32_t kCopyRingBytes = kEmbedded ? kPullStages * kPullStageBytes : 0u;
+  static constexpr uint32_t kBarrierOffset = kCopyRingOffset + kCopyRingBytes;
+  static constexpr uint32_t kNumBarriers = 2 * kStages + 2 * kAccumStages + (kEmbedded ? kPullStages : 0);
   static constexpr uint32_t kTmemSlotOffset = kBarrierOffset + kNumBarriers * 8;
   static constexpr uint32_t kComputeBytes = kTmemSlotOffset + 16;
   // communication pairs lay the copy pipeline over the same allocation
@@ -69,7 +73,7 @@ using PairLayout = PairLayoutT<false>;
 // kAMn / kBMn (BF16 only): the operand is stored with its M (resp. N) axis contiguous and is fed to
 // the tensor core as an MN-major tile -- 64-element groups along MN, each a [64 K rows x 128 bytes]
 // swizzled box; a CTA then holds two groups of A and two groups of its half of B per K block.
-template <int kMode, class Maps, bool kMx = false, bool kAMn = false, bool kBMn = false>
+template <int kMode, class Maps, bool kMx = false, bool kAMn = false, bool kBMn = false, bool kEmbedded = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_sfa, const __grid_constant__ CUtensorMap tmap_sfb,
@@ -83,7 +87,8 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   constexpr bool kGated = kMode == kModeLhsPull || kMode == kModeGradPull || kMode == kModeHeadGate;
   constexpr bool kHeads = kMode == kModeGradPull || kMode == kModeHeadGate;  // K groups are Q/K/V heads
   constexpr bool kRemoteWriter = kMode == kModeHeadGate;  // flags released by the sending GPUs
-  using Layout = PairLayoutT<kMx>;
+  static_assert(!kEmbedded || kMode == kModeLhsPull, "the embedded copy warp serves the lhs pull");
+  using Layout = PairLayoutT<kMx, kEmbedded>;
   constexpr int kStages = Layout::kStages;
   constexpr int32_t kBlockElems = kMx ? 2 * kBlockK : kBlockK;  // K elements per 128-byte row
   constexpr int kBlockN = Layout::kBlockN;
@@ -161,6 +166,8 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       ptx::mbar_init(tmem_full_bar(s), 1);                      // commit arrival, in each CTA
       ptx::mbar_init(tmem_empty_bar(s), 2 * kEpilogueThreads);  // both CTAs' epilogues (leader's copy is used)
     }
+    if constexpr (kEmbedded)
+      for (int s = 0; s < kPullStages; ++s) ptx::mbar_init(bar_base + 8u * (2 * kStages + 2 * kAccumStages + s), 1);
     ptx::fence_mbar_init();
     *reinterpret_cast<volatile uint32_t*>(smem + Layout::kTmemSlotOffset + 8) = 0u;  // gate progress
   }
@@ -316,6 +323,17 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         mbar_wait(tmem_full_bar(accum), accum_phase, p.wait, kSiteDrain, false);
       }
       unwound = !ok;
+    }
+  } else if (warp == 2) {
+    // ------------------------------------------------------------------ embedded copy warp
+    if constexpr (kEmbedded) {
+      if (lane == 0) {
+        LhsPullPolicy policy(p, store_maps);
+        run_chunk_pipeline_thread(policy, p.wait, base + Layout::kCopyRingOffset,
+                                  bar_base + 8u * (2 * kStages + 2 * kAccumStages), int32_t(blockIdx.x),
+                                  int32_t(gridDim.x));
+      }
+      __syncwarp();
     }
   } else if (warp == 3) {
     // ------------------------------------------------------------------ gate scout (both CTAs)

@@ -234,7 +234,7 @@ cudaError_t oproj_forward(const fuse_a2a_gemm_params& p, const fuse_b200_options
       if (block_n == 256 && num_comm_ctas % 2 == 0 && info.sm_count % 2 == 0 && pair_tiles_requested()) {
         FusedParams pk = k;
         pk.lhs.m_group = 2 * wave_m_group_pairs(pk, info.sm_count);
-        if (launch::embedded_pull_requested()) {
+        if (launch::embedded_pull_requested(p.route.world_size)) {
           Operands pair_maps;
           if (encode_operand(&pair_maps.a, p.input_staging, p.gemm.m, p.gemm.k, lda, false, kBlockM) == cudaSuccess &&
               encode_operand(&pair_maps.b, p.rhs_nt, p.gemm.n, p.gemm.k, packed_or(p.gemm.stride_b.row, p.gemm.k), false,

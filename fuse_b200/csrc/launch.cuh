@@ -247,11 +247,14 @@ inline cudaError_t encode_scale_atoms(CUtensorMap* map, const void* scales, int6
                                     CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
-// The lhs pull run by one warp of every compute CTA instead of communication CTAs:
-// FUSE_B200_EMBEDDED_PULL=1 (read on every launch).
-inline bool embedded_pull_requested() {
+// The lhs pull of the CTA-pair kernels can be run by one warp of every compute CTA (no SM is given
+// up to communication; `num_comm_ctas` is then only validated).  Measured better on 1 and 2 GPUs,
+// where it is the default; groups of 4 and 8 ranks keep the communication CTAs until the embedded
+// pull has been measured there.  FUSE_B200_EMBEDDED_PULL=0/1 (read on every launch) forces one.
+inline bool embedded_pull_requested(int world) {
   const char* text = std::getenv("FUSE_B200_EMBEDDED_PULL");
-  return text != nullptr && std::atoi(text) != 0;
+  if (text != nullptr) return std::atoi(text) != 0;
+  return world <= 2;
 }
 
 // CTA-pair tiles are used wherever the shape allows; the environment switch FUSE_B200_PAIR=0

@@ -383,7 +383,7 @@ cudaError_t oproj_forward_mxfp8(const fuse_mxfp8_a2a_gemm_params& mp, const fuse
             launch::encode_scale_atoms(&sfa_map, f.sfa, g.m, g.k) == cudaSuccess &&
             launch::encode_scale_atoms(&sfb_map, f.sfb, g.n, g.k) == cudaSuccess)
         {
-          if (launch::embedded_pull_requested())
+          if (launch::embedded_pull_requested(r.world_size))
             return launch::launch_pair_kernel<kModeLhsPull, LhsPullMaps, true, false, false, true>(
                 pair_maps, sfa_map, sfb_map, pull, pf, g.max_swizzle_size, info, stream, 0.0);
           return launch::launch_pair_kernel<kModeLhsPull, LhsPullMaps, true>(

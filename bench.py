@@ -13,7 +13,10 @@ the local repack, i.e. the "pure GEMM + route" point of the scaling curve.
 Prints ONE JSON line.  `value` is the whole-job throughput in PFLOPS (algorithmic
 2*M*N*K FLOPs of both GEMMs, all ranks, over the max-over-ranks device time); `per_gpu` is the
 reference's own way of quoting it (PFLOPS/GPU).  `e2e` runs the same step from pinned HOST
-buffers with the host<->device copies inside the timed region.  `--impl reference` times the
+buffers with the host<->device copies inside the timed region: every step uploads its inputs and
+downloads both results; uploads, kernels and downloads run on three streams ordered by events, so
+a step's downloads overlap the next uploads (one GPU) -- the copies are still all inside the
+timed region, which ends when the last download has finished.  `--impl reference` times the
 CPU restatement of the path (the reference has no CPU implementation of the fused operators,
 only host oracle pieces) on the host cores, on a bounded row sample of the same workload.
 """
@@ -387,29 +390,73 @@ def run_gpu_arm(args):
     planar = sym["qkv_planar"].view(bf16)
     planar_host = torch.empty(planar.shape, dtype=bf16).pin_memory()
     out_host = torch.empty(out.shape, dtype=bf16).pin_memory()
-    flag_host = torch.zeros(N.READY_FLAG_STRIDE, dtype=u32).pin_memory()
+    # one pinned flag line per step: the host runs ahead of the copies that read them
+    flag_host = torch.zeros(e2e_steps + 1, N.READY_FLAG_STRIDE, dtype=u32).pin_memory()
     attn_flag = sym["attn_ready"].view(u32)
-    h2d = x_host.numel() * 2 + attn_host.numel() * 2 + flag_host.numel() * 4
+    h2d = x_host.numel() * 2 + attn_host.numel() * 2 + N.READY_FLAG_STRIDE * 4
     d2h = planar_host.numel() * 2 + out_host.numel() * 2
+
+    # Three streams: uploads, the two fused kernels, downloads.  PCIe is full duplex, so a step's
+    # downloads run beside the next uploads; events order every buffer's reuse (a kernel never
+    # overwrites an output that is still being read back, an upload never overwrites an input that
+    # a kernel still reads).  With peers (N > 1) every step ends with a host barrier, because a
+    # peer may still be pulling this rank's attention output; on one GPU the steps overlap.
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    new_event = lambda: torch.cuda.Event()
+    state = {"planar_read": None, "out_read": None, "qkv_done": None, "oproj_done": None, "step": 0}
 
     def e2e_step():
         epoch[0] += 1
-        x.copy_(x_host, non_blocking=True)
+        with torch.cuda.stream(s_in):
+            if state["qkv_done"] is not None:
+                s_in.wait_event(state["qkv_done"])     # the previous projection has read x
+            x.copy_(x_host, non_blocking=True)
+            x_ready = new_event()
+            x_ready.record(s_in)
+            if state["oproj_done"] is not None:
+                s_in.wait_event(state["oproj_done"])   # the previous output projection has read attn
+            attn.copy_(attn_host, non_blocking=True)
+            line = flag_host[state["step"] % flag_host.shape[0]]
+            state["step"] += 1
+            line.fill_(epoch[0])
+            attn_flag.copy_(line, non_blocking=True)  # upstream epoch: published after the payload
+            attn_ready = new_event()
+            attn_ready.record(s_in)
+        stream.wait_event(x_ready)
+        if state["planar_read"] is not None:
+            stream.wait_event(state["planar_read"])    # the previous Q|K|V has been read back
         launch_qkv()
-        planar_host.copy_(planar, non_blocking=True)
-        attn.copy_(attn_host, non_blocking=True)
-        flag_host.fill_(epoch[0])
-        attn_flag.copy_(flag_host, non_blocking=True)  # upstream epoch: published after the payload
+        state["qkv_done"] = new_event()
+        state["qkv_done"].record(stream)
+        stream.wait_event(attn_ready)
+        if state["out_read"] is not None:
+            stream.wait_event(state["out_read"])
         launch_oproj(upstream=True)
-        out_host.copy_(out, non_blocking=True)
-        # Peers may still be pulling this step's attention output: join before it is overwritten.
-        barrier()
+        state["oproj_done"] = new_event()
+        state["oproj_done"].record(stream)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(state["qkv_done"])
+            planar_host.copy_(planar, non_blocking=True)
+            state["planar_read"] = new_event()
+            state["planar_read"].record(s_out)
+            s_out.wait_event(state["oproj_done"])
+            out_host.copy_(out, non_blocking=True)
+            state["out_read"] = new_event()
+            state["out_read"].record(s_out)
+        if world_size > 1:
+            barrier()
+
+    def e2e_join():
+        torch.cuda.synchronize()
+        if world_size > 1:
+            dist.barrier()
 
     e2e_step()
-    barrier()
+    e2e_join()
     ta = time.perf_counter()
     for _ in range(e2e_steps):
         e2e_step()
+    e2e_join()  # every upload, kernel and download of the timed steps has finished
     tb = time.perf_counter()
     check_status("end-to-end region")
     e2e_ms = torch.tensor([(tb - ta) * 1e3 / e2e_steps], dtype=torch.float64, device=dev)
@@ -485,7 +532,7 @@ def main():
     parser.add_argument("--swizzle", type=int, default=8)
     parser.add_argument("--qkv-route", default="direct", choices=["comm", "direct"],
                         help="QKV routing from communication CTAs or from the GEMM epilogue")
-    parser.add_argument("--e2e-steps", type=int, default=5)
+    parser.add_argument("--e2e-steps", type=int, default=10)
     parser.add_argument("--cpu-rows", type=int, default=1024)
     parser.add_argument("--clock-period-ms", type=float, default=10.0)
     parser.add_argument("--skip-cpu", action="store_true")

@@ -119,6 +119,25 @@ def test_oproj_forward_matches_oracle(case, pull):
         _assert_close(out, want_out, f"output[{rank}]")
 
 
+@pytest.mark.parametrize("pair,embedded", [("0", "0"), ("1", "0"), ("1", "1")])
+def test_oproj_forward_tile_and_pull_variants(monkeypatch, pair, embedded):
+    # one-CTA tiles, CTA pairs with communication CTAs, CTA pairs with the embedded copy warps:
+    # the switches are read on every launch
+    from tests import harness as H
+    monkeypatch.setenv("FUSE_B200_PAIR", pair)
+    monkeypatch.setenv("FUSE_B200_EMBEDDED_PULL", embedded)
+    world, batch, s, heads, d, n, comm = 4, 1, 512, 8, 128, 512, 4
+    k = heads * d
+    peer_in = [synthetic.normal_bf16((batch * s * world, k // world), synthetic.rank_seed(r) + 2000, 1.0)
+               for r in range(world)]
+    w = synthetic.normal_bf16((n, k), synthetic.BASE_SEED + 17, 0.02)
+    for rank in (0, 3):
+        staging, out = H.oproj_forward(world, rank, batch, s, peer_in, w, comm=comm)
+        want_staging, want_out = O.oproj_forward(world, rank, batch, s, peer_in, w)
+        assert np.array_equal(staging, want_staging), f"gathered lhs differs on rank {rank}"
+        _assert_close(out, want_out, f"output[{rank}]")
+
+
 def test_plain_gemm_entry_points_match_fused_outputs():
     import torch
     from tests import harness as H

@@ -481,10 +481,9 @@ def run_gpu_arm(args):
                 "a2a_oproj_gemm": {"ms": oproj_ms,
                                    "pflops_per_gpu": (FLOPS_PER_RANK - QKV_FLOPS) / (oproj_ms * 1e-3) / 1e15,
                                    "comm_ctas": args.oproj_comm,
-                                   # the library's default: one warp of every compute CTA pulls on 1-2 GPUs
-                                   # (no SM given up), communication CTAs on larger groups
-                                   "pull": ("embedded copy warps" if os.environ.get(
-                                       "FUSE_B200_EMBEDDED_PULL", "1" if world_size <= 2 else "0") != "0"
+                                   # the library's default: one warp of every compute CTA pulls (no SM
+                                   # given up); FUSE_B200_EMBEDDED_PULL=0 selects communication CTAs
+                                   "pull": ("embedded copy warps" if os.environ.get("FUSE_B200_EMBEDDED_PULL", "1") != "0"
                                             else "communication CTAs")},
             },
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",

@@ -247,14 +247,14 @@ inline cudaError_t encode_scale_atoms(CUtensorMap* map, const void* scales, int6
                                     CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
-// The lhs pull of the CTA-pair kernels can be run by one warp of every compute CTA (no SM is given
-// up to communication; `num_comm_ctas` is then only validated).  Measured better on 1 and 2 GPUs,
-// where it is the default; groups of 4 and 8 ranks keep the communication CTAs until the embedded
-// pull has been measured there.  FUSE_B200_EMBEDDED_PULL=0/1 (read on every launch) forces one.
+// The lhs pull of the CTA-pair kernels is run by one warp of every compute CTA (no SM is given up
+// to communication; `num_comm_ctas` is then only validated).  Measured better than communication
+// CTAs on 1, 2 and 8 GPUs.  FUSE_B200_EMBEDDED_PULL=0 (read on every launch) brings the
+// communication CTAs back.
 inline bool embedded_pull_requested(int world) {
+  (void)world;
   const char* text = std::getenv("FUSE_B200_EMBEDDED_PULL");
-  if (text != nullptr) return std::atoi(text) != 0;
-  return world <= 2;
+  return text == nullptr || std::atoi(text) != 0;
 }
 
 // CTA-pair tiles are used wherever the shape allows; the environment switch FUSE_B200_PAIR=0

@@ -96,6 +96,24 @@ def test_moe_dispatch_fc1_on_cta_pairs_matches_oracle(case):
 
 
 @pytest.mark.parametrize("mma_sm_count", [1, 2])
+def test_moe_every_boundary_row_count_of_the_reference_list(mma_sm_count):
+    # the reference's boundary list (benchmarks/sm103/grouped_validation.cuh:33), one expert each
+    from tests import harness as H
+    counts = [1, 7, 8, 9, 15, 16, 17, 63, 64, 65, 127, 128, 129, 191, 192, 193, 255, 256, 257, 0]
+    world, tokens, k, n = 2, 400, 256, 256
+    e = len(counts)
+    toks = [synthetic.normal_bf16((tokens, k), 177 + r, 1.0) for r in range(world)]
+    weights = synthetic.normal_bf16((e, n, k), 199, 0.02)
+    rng = np.random.default_rng(15)
+    offs = np.concatenate([[0], np.cumsum(counts)]).astype(np.int64)
+    total = int(offs[-1])
+    src = np.stack([rng.integers(0, world, total), rng.integers(0, tokens, total), rng.integers(0, 2, total)], 1).astype(np.int32)
+    capacity = 512
+    lhs, out = H.moe_dispatch_fc1(world, 1, e, toks, weights, offs, src, capacity, comm=4, mma_sm_count=mma_sm_count)
+    _check(world, 1, e, toks, weights, offs, src, capacity, lhs, out)
+
+
+@pytest.mark.parametrize("mma_sm_count", [1, 2])
 def test_moe_boundary_row_counts_empty_experts_and_replay_with_new_routes(mma_sm_count):
     # Row counts at tile boundaries and empty experts (benchmarks/sm103/grouped_validation.cuh:20-50);
     # then the same plan replayed with different device routes.

@@ -277,7 +277,11 @@ def main():
         gp = N.Bf16GroupedGemmParams(lhs=lp.data_ptr(), weight_nt=wp.data_ptr(), output=op_.data_ptr(),
                                      row_offsets=offs_d.data_ptr(), source=src_d.data_ptr(), experts=e_local, n=n, k=hid,
                                      expert_row_capacity=cap, rank=rank, world_size=cp, topk=topk)
-        total_rows = int(offs[-1])
+        # the timed figure is the max over ranks, i.e. the busiest rank's: count its rows
+        per_rank = np.zeros(cp, np.int64)
+        for r in range(cp):
+            per_rank += np.bincount((chosen[r] // e_local).ravel(), minlength=cp)
+        total_rows = int(per_rank.max())
         flops = 2.0 * total_rows * n * hid
         for comm, compute, mma in ((args.comm, 148 - args.comm, 1), (args.comm, 148 - args.comm, 2), (20, 128, 2)):
             gp.policy = N.GroupedGemmPolicy(num_comm_ctas=comm, num_compute_ctas=compute, tile_n=256, mma_sm_count=mma)
@@ -288,7 +292,7 @@ def main():
             rc, plan = api.create_bf16_a2a_grouped_gemm(gp)
             assert rc == 0, rc
             timed(lambda e: api.launch_bf16_grouped_gemm(plan, stream),
-                  f"c5 MoE dispatch+FC1 ({total_rows} rows, comm {comm}, mma_sm {mma})", flops)
+                  f"c5 MoE dispatch+FC1 ({total_rows} rows on the busiest rank, comm {comm}, mma_sm {mma})", flops)
             barrier()
             api.destroy_bf16_grouped_gemm(plan)
         # pure grouped GEMM denominator: the same rows as one dense GEMM per expert is not

@@ -224,7 +224,9 @@ struct SmemLayout {
   static constexpr uint32_t kStagingBlockBytes = kBlockM * 64 * 2;
   static constexpr uint32_t kBarrierOffset = kStagingOffset + kStagingBuffers * kStagingBlockBytes;
   static constexpr uint32_t kAccumStages = (kMx && kBlockN > 240) ? 1u : 2u;
-  static constexpr uint32_t kNumBarriers = 2 * kStages + 2 * kAccumStages;
+  // + 1: the barrier the UMMA issuer drains on while unwinding (an accumulator-full barrier
+  // only ever completes for a finished tile)
+  static constexpr uint32_t kNumBarriers = 2 * kStages + 2 * kAccumStages + 1;
   static constexpr uint32_t kTmemSlotOffset = kBarrierOffset + kNumBarriers * 8;
   // Two per-tile route tables (column chunk -> destination base pointer, row pitch) used by
   // the direct-push epilogue, double-buffered by tile parity.
@@ -369,6 +371,11 @@ __device__ __forceinline__ void qkv_finalize(const FusedParams& p) {
   if (blockIdx.x != 0 || threadIdx.x >= 32) return;
   const QkvRoute& r = p.qkv;
   const int lane = threadIdx.x;
+  // A launch in which any wait gave up publishes nothing: its transfers may be incomplete, so
+  // the peers must run out their own bounded wait (and record kSitePeerDone) instead of reading
+  // half-written rows behind a fresh epoch.
+  const bool failed = __shfl_sync(0xffffffffu, lane == 0 && aborted(p.wait) ? 1 : 0, 0) != 0;
+  if (failed) return;
   if (lane == 0) ptx::fence_sc_sys();
   __syncwarp();
   if (lane < r.world)
@@ -1706,6 +1713,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
     auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
     auto tmem_full_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };
     auto tmem_empty_bar = [&](int s) { return bar_base + 8u * (2 * kStages + kAccumStages + s); };
+    const uint32_t drain_bar = bar_base + 8u * (2 * kStages + 2 * kAccumStages);
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + Layout::kTmemSlotOffset);
     constexpr uint32_t kTmemColumns = Layout::kTmemColumns;
 
@@ -1720,6 +1728,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         ptx::mbar_init(tmem_full_bar(s), 1);
         ptx::mbar_init(tmem_empty_bar(s), kEpilogueThreads);
       }
+      ptx::mbar_init(drain_bar, 1);
       ptx::fence_mbar_init();
       *reinterpret_cast<volatile uint32_t*>(smem + Layout::kTmemSlotOffset + 8) = 0u;  // gate progress
     }
@@ -1898,9 +1907,10 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           if (++accum == kAccumStages) { accum = 0; accum_phase ^= 1u; }
         }
         if (!ok) {
-          // Unwinding: UMMAs already issued must retire before TMEM is released.
-          ptx::umma_commit(tmem_full_bar(accum));
-          mbar_wait(tmem_full_bar(accum), accum_phase, p.wait, kSiteDrain, false);
+          // Unwinding: UMMAs already issued must retire before TMEM is released.  They retire on
+          // a barrier of their own, so the epilogue never takes a partial tile for a finished one.
+          ptx::umma_commit(drain_bar);
+          mbar_wait(drain_bar, 0u, p.wait, kSiteDrain, false);
         }
       }
     } else if (warp == 3) {

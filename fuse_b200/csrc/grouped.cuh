@@ -269,6 +269,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const Grouped
     auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
     auto tmem_full_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };
     auto tmem_empty_bar = [&](int s) { return bar_base + 8u * (2 * kStages + kAccumStages + s); };
+    const uint32_t drain_bar = bar_base + 8u * (Layout::kNumBarriers - 1);  // unwinding UMMAs retire here
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + Layout::kTmemSlotOffset);
     constexpr uint32_t kTmemColumns = Layout::kTmemColumns;
     if (threadIdx.x == 0) {
@@ -280,6 +281,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const Grouped
         ptx::mbar_init(tmem_full_bar(s), 1);
         ptx::mbar_init(tmem_empty_bar(s), kEpilogueThreads);
       }
+      ptx::mbar_init(drain_bar, 1);
       ptx::fence_mbar_init();
     }
     if (warp == 2) {
@@ -363,8 +365,8 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const Grouped
           if (++accum == kAccumStages) { accum = 0; accum_phase ^= 1u; }
         }
         if (!ok) {
-          ptx::umma_commit(tmem_full_bar(accum));
-          mbar_wait(tmem_full_bar(accum), accum_phase, w, kSiteDrain, false);
+          ptx::umma_commit(drain_bar);
+          mbar_wait(drain_bar, 0u, w, kSiteDrain, false);
         }
       }
     } else if (warp >= 4) {
@@ -471,6 +473,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) grouped
     auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
     auto tmem_full_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };
     auto tmem_empty_bar = [&](int s) { return bar_base + 8u * (2 * kStages + kAccumStages + s); };
+    const uint32_t drain_bar = bar_base + 8u * (Layout::kNumBarriers - 1);  // the leader's; unwinding UMMAs retire here
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + Layout::kTmemSlotOffset);
     if (threadIdx.x == 0) {
       for (int s = 0; s < kStages; ++s) {
@@ -481,6 +484,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) grouped
         ptx::mbar_init(tmem_full_bar(s), 1);
         ptx::mbar_init(tmem_empty_bar(s), 2 * kEpilogueThreads);
       }
+      ptx::mbar_init(drain_bar, 1);
       ptx::fence_mbar_init();
     }
     if (warp == 2) {
@@ -570,8 +574,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) grouped
           if (++accum == kAccumStages) { accum = 0; accum_phase ^= 1u; }
         }
         if (!ok) {
-          ptx::umma_commit_pair(tmem_full_bar(accum), 3);
-          mbar_wait(tmem_full_bar(accum), accum_phase, w, kSiteDrain, false);
+          ptx::umma_commit_pair(drain_bar, 1);
+          mbar_wait(drain_bar, 0u, w, kSiteDrain, false);
         }
         unwound = !ok;
       }

@@ -75,14 +75,12 @@ uint32_t next_launch_id() {
 
 void count_launch(uint64_t kernels) { g_launch_count += kernels; }
 
+// Read on every launch, like the other environment switches.
 uint64_t default_wait_budget_ns() {
-  static const uint64_t budget = [] {
-    const char* text = std::getenv("FUSE_B200_WAIT_MS");
-    double ms = text ? std::atof(text) : 0.0;
-    if (!(ms > 0.0)) ms = 2000.0;
-    return uint64_t(ms * 1.0e6);
-  }();
-  return budget;
+  const char* text = std::getenv("FUSE_B200_WAIT_MS");
+  double ms = text ? std::atof(text) : 0.0;
+  if (!(ms > 0.0)) ms = 2000.0;
+  return uint64_t(ms * 1.0e6);
 }
 
 cudaError_t encode_tensor_map_2d(CUtensorMap* map, const void* base, CUtensorMapDataType dtype,

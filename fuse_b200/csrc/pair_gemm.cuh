@@ -50,7 +50,9 @@ struct PairLayoutT {
   static constexpr uint32_t kCopyRingOffset = kStagingOffset + kStagingBuffers * kStagingBlockBytes;
   static constexpr uint32_t kCopyRingBytes = kEmbedded ? kPullStages * kPullStageBytes : 0u;
   static constexpr uint32_t kBarrierOffset = kCopyRingOffset + kCopyRingBytes;
-  static constexpr uint32_t kNumBarriers = 2 * kStages + 2 * kAccumStages + (kEmbedded ? kPullStages : 0);
+  // + 1: the leader's drain barrier (UMMAs of an unwinding launch retire on it, never on an
+  // accumulator-full barrier)
+  static constexpr uint32_t kNumBarriers = 2 * kStages + 2 * kAccumStages + (kEmbedded ? kPullStages : 0) + 1;
   static constexpr uint32_t kTmemSlotOffset = kBarrierOffset + kNumBarriers * 8;
   static constexpr uint32_t kComputeBytes = kTmemSlotOffset + 16;
   // communication pairs lay the copy pipeline over the same allocation
@@ -106,6 +108,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   auto empty_bar = [&](int s) { return bar_base + 8u * (kStages + s); };
   auto tmem_full_bar = [&](int s) { return bar_base + 8u * (2 * kStages + s); };
   auto tmem_empty_bar = [&](int s) { return bar_base + 8u * (2 * kStages + kAccumStages + s); };
+  const uint32_t drain_bar = bar_base + 8u * (Layout::kNumBarriers - 1);
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(smem + Layout::kTmemSlotOffset);
   const uint32_t gate_word = base + Layout::kTmemSlotOffset + 8u;
 
@@ -168,6 +171,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
     if constexpr (kEmbedded)
       for (int s = 0; s < kPullStages; ++s) ptx::mbar_init(bar_base + 8u * (2 * kStages + 2 * kAccumStages + s), 1);
+    ptx::mbar_init(drain_bar, 1);
     ptx::fence_mbar_init();
     *reinterpret_cast<volatile uint32_t*>(smem + Layout::kTmemSlotOffset + 8) = 0u;  // gate progress
   }
@@ -318,9 +322,10 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (++accum == kAccumStages) { accum = 0; accum_phase ^= 1u; }
       }
       if (!ok) {
-        // Unwinding: UMMAs already issued must retire before TMEM is released.
-        ptx::umma_commit_pair(tmem_full_bar(accum), 3);
-        mbar_wait(tmem_full_bar(accum), accum_phase, p.wait, kSiteDrain, false);
+        // Unwinding: UMMAs already issued must retire before TMEM is released.  They retire on the
+        // leader's own drain barrier, so neither CTA's epilogue takes a partial tile for a finished one.
+        ptx::umma_commit_pair(drain_bar, 1);
+        mbar_wait(drain_bar, 0u, p.wait, kSiteDrain, false);
       }
       unwound = !ok;
     }

@@ -59,7 +59,19 @@ __device__ __forceinline__ bool aborted(const WaitContext& w) {
 
 __device__ __noinline__ inline void report_timeout(const WaitContext w, uint32_t code, uint32_t site,
                                             uint32_t index, uint32_t observed, uint32_t expected) {
-  if (atomicCAS(w.status, 0u, w.launch_id) == 0u) {
+  // The record goes to the first waiter of THIS launch: a record that an earlier launch left
+  // uncleared is overwritten, so that the abort fan-out below still works.
+  uint32_t owner = ptx::ld_relaxed_gpu(w.status);
+  bool claimed = false;
+  while (owner != w.launch_id) {
+    const uint32_t seen = atomicCAS(w.status, owner, w.launch_id);
+    if (seen == owner) {
+      claimed = true;
+      break;
+    }
+    owner = seen;
+  }
+  if (claimed) {
     w.status[1] = code;
     w.status[2] = site;
     w.status[3] = blockIdx.x;

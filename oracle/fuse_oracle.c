@@ -620,6 +620,72 @@ FO_API int fo_moe_dispatch_fc1(int experts_local, const int32_t* row_offsets,
   return 0;
 }
 
+/* ------------------------------------------------------------------------- */
+/* Batch forms of the receiver-view maps (full-size validation samples many   */
+/* elements at once; each entry is exactly the scalar map above).             */
+/* ------------------------------------------------------------------------- */
+
+FO_API void fo_qkv_oracle_source_batch(int world, int destination, uint64_t seq_local,
+                                       uint64_t q_width, uint64_t kv_width, const uint64_t* index,
+                                       int64_t count, int32_t* source_rank,
+                                       uint64_t* source_offset) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < count; ++i)
+    fo_qkv_oracle_source(world, destination, seq_local, q_width, kv_width, index[i],
+                         &source_rank[i], &source_offset[i]);
+}
+
+FO_API void fo_oproj_gather_source_batch(int world, int destination, int seq_local, int64_t width,
+                                         int causal, int cyclic, const uint64_t* index,
+                                         int64_t count, int32_t* source_rank,
+                                         uint64_t* source_offset) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < count; ++i)
+    fo_oproj_gather_source(world, destination, seq_local, width, causal, cyclic, index[i],
+                           &source_rank[i], &source_offset[i]);
+}
+
+FO_API void fo_qkv_backward_source_batch(int world, int rank, int seq_local, int q_heads,
+                                         int kv_heads, int head_dim, int causal,
+                                         const int64_t* row, const int32_t* feature, int64_t count,
+                                         int32_t* owner, int32_t* segment, int64_t* offset) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < count; ++i)
+    fo_qkv_backward_source(world, rank, seq_local, q_heads, kv_heads, head_dim, causal, row[i],
+                           feature[i], &owner[i], &segment[i], &offset[i]);
+}
+
+FO_API void fo_oproj_backward_source_batch(int world, int rank, int batch, int seq_local,
+                                           int64_t width, int causal, const uint64_t* index,
+                                           int64_t count, int32_t* source_rank,
+                                           uint64_t* source_offset) {
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < count; ++i)
+    fo_oproj_backward_source(world, rank, batch, seq_local, width, causal, index[i],
+                             &source_rank[i], &source_offset[i]);
+}
+
+FO_API void fo_global_row_batch(int world, int rank, int seq_local, int causal,
+                                const int64_t* local_row, int64_t count, int64_t* global_row) {
+  for (int64_t i = 0; i < count; ++i)
+    global_row[i] = fo_global_row(world, rank, seq_local, causal, local_row[i]);
+}
+
+FO_API void fo_mxfp8_scale_offset_batch(const int64_t* row, const int64_t* k, int64_t width,
+                                        int64_t count, int64_t* offset) {
+  for (int64_t i = 0; i < count; ++i) offset[i] = fo_mxfp8_scale_offset(row[i], k[i], width);
+}
+
+/* Threads the OpenMP loops of this file use from now on (the benchmark's checker shares the
+ * host cores with the other ranks' processes). */
+FO_API void fo_set_num_threads(int threads) {
+#ifdef _OPENMP
+  if (threads > 0) omp_set_num_threads(threads);
+#else
+  (void)threads;
+#endif
+}
+
 FO_API int fo_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

@@ -27,8 +27,10 @@ P = C.c_void_p
 
 
 def _make(target: str) -> None:
-    subprocess.run(["make", "-C", _HERE, target], check=True, stdout=subprocess.DEVNULL,
-                   stderr=subprocess.PIPE)
+    cmd = ["make", "-C", _HERE, target]
+    if target == "ref":
+        cmd.append("REF_ROOT=" + reference_root())
+    subprocess.run(cmd, check=True, stdout=subprocess.DEVNULL, stderr=subprocess.PIPE)
 
 
 def _sig(lib, name, restype, *argtypes):
@@ -84,8 +86,21 @@ def lib():
     _sig(L, "fo_moe_build_rows", i64, C.c_int, C.c_int, C.c_int, i64, C.c_int, P, P, P)
     _sig(L, "fo_moe_dispatch_fc1", C.c_int, C.c_int, P, P, P, P, i64, i64, i64, P, P)
     _sig(L, "fo_num_threads", C.c_int)
+    _sig(L, "fo_set_num_threads", None, C.c_int)
+    _sig(L, "fo_qkv_oracle_source_batch", None, C.c_int, C.c_int, u64, u64, u64, P, i64, P, P)
+    _sig(L, "fo_oproj_gather_source_batch", None, C.c_int, C.c_int, C.c_int, i64, C.c_int, C.c_int, P, i64, P, P)
+    _sig(L, "fo_qkv_backward_source_batch", None, *([C.c_int] * 7), P, P, i64, P, P, P)
+    _sig(L, "fo_oproj_backward_source_batch", None, C.c_int, C.c_int, C.c_int, C.c_int, i64, C.c_int, P, i64, P, P)
+    _sig(L, "fo_global_row_batch", None, C.c_int, C.c_int, C.c_int, C.c_int, P, i64, P)
+    _sig(L, "fo_mxfp8_scale_offset_batch", None, P, P, i64, i64, P)
     _LIB = L
     return L
+
+
+def reference_root() -> str:
+    """Where the reference project is mounted: $FUSE_REF_ROOT, else a directory named
+    `reference` beside this repository (absent on the GPU box: callers then skip)."""
+    return os.environ.get("FUSE_REF_ROOT") or os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
 
 
 def ref(build: bool = True):
@@ -95,7 +110,7 @@ def ref(build: bool = True):
         return _REF
     path = os.path.join(_HERE, "_ref", "libfuse_ref.so")
     if not os.path.exists(path):
-        if not build or not os.path.isdir(os.environ.get("FUSE_REF_ROOT", "/root/reference")):
+        if not build or not os.path.isdir(reference_root()):
             return None
         try:
             _make("ref")

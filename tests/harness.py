@@ -107,10 +107,15 @@ def oproj_forward(world, rank, batch, seq_local, peer_bits, w_bits, comm=4, caus
 
 
 def qkv_backward(world, batch, seq_local, q_heads, kv_heads, head_dim, planes_bits, w_bits, x_bits, comm=4,
-                 causal=False, alpha=1.0, beta=0.0, dw_init_bits=None, block_n=0, tuning=(1, False), vector=False):
+                 causal=False, alpha=1.0, beta=0.0, dw_init_bits=None, block_n=0, tuning=(1, False), vector=False,
+                 starved_first=False):
     """Runs every rank of the QKV backward (data + weight).  planes_bits[r] = (dQ, dK, dV) of rank r.
     Several ranks on one GPU: every rank's communication CTAs push first (COMM_ONLY), then every
-    rank's GEMM runs (COMPUTE_ONLY).  Returns per rank (staging, dX, dW) bits."""
+    rank's GEMM runs (COMPUTE_ONLY).  Returns per rank (staging, dX, dW) bits.
+    starved_first: before that, rank 0's GEMM is launched alone at epoch 1 with a 30 ms wait
+    budget -- nobody has pushed, so its head gates run out -- and the launch must report the
+    time-out WITHOUT telling any peer that its transfers are complete; the real run then uses
+    epoch 2."""
     m = batch * seq_local
     width = (q_heads + 2 * kv_heads) * head_dim
     hidden = w_bits.shape[1]
@@ -139,6 +144,18 @@ def qkv_backward(world, batch, seq_local, q_heads, kv_heads, head_dim, planes_bi
             p.peer_dqkv_staging[peer] = staging[peer].data_ptr()
             p.peer_ready[peer] = ready[peer].data_ptr()
             p.peer_done_epoch[peer] = done[peer].data_ptr()
+    if starved_first:
+        assert world > 1
+        opts = options(wait_ms=30.0, flags=N.COMPUTE_ONLY | N.SKIP_PEER_WAIT, block_n=block_n)
+        rc = api.launch_qkv_backward_data(params[0], 0, opts)
+        assert rc == 0, f"launch_qkv_backward_data -> cudaError {rc}"
+        torch.cuda.synchronize()
+        status = api.read_status(clear=True)
+        assert status[0] != 0 and status[1] in (1, 2, 3), f"the starved launch did not report: {status[:8]}"
+        for d in done:  # a failed launch publishes no completion epoch
+            assert int(d.abs().sum()) == 0, "a launch that timed out told its peers that it was complete"
+        for p in params:
+            p.epoch = 2
     phases = [0] if world == 1 else [N.COMM_ONLY, N.COMPUTE_ONLY]
     for phase in phases:
         for p in params:

@@ -47,6 +47,25 @@ def test_qkv_backward_matches_oracle(case, vector):
         _close(got[r][2], dw, f"dW[{r}]")
 
 
+def test_timed_out_launch_publishes_no_completion_and_the_next_launch_is_correct():
+    # Head gates that nobody releases (no rank has pushed yet): the GEMM's bounded wait runs out,
+    # the status record says so, and the rank must NOT release its completion epoch to the peers --
+    # they would read half-written rows behind it.  After a clear, the full run is correct.
+    from tests import harness as H
+    world, batch, s, q, kv, d, hidden, comm = 2, 1, 256, 4, 2, 128, 256, 4
+    m, width, rows = batch * s, (q + 2 * kv) * d, batch * s * world
+    planes = [tuple(synthetic.normal_bf16((rows, heads // world * d), synthetic.rank_seed(r) + 100 * seg + 31, 0.01)
+                    for seg, heads in enumerate((q, kv, kv))) for r in range(world)]
+    w = synthetic.normal_bf16((width, hidden), synthetic.BASE_SEED + 11, 0.02)
+    xs = [synthetic.normal_bf16((m, hidden), synthetic.rank_seed(r) + 1000, 1.0) for r in range(world)]
+    got = H.qkv_backward(world, batch, s, q, kv, d, planes, w, xs, comm=comm, starved_first=True)
+    for r in range(world):
+        staging, dx, dw = O.qkv_backward(world, r, batch, s, q, kv, d, planes, w, xs[r])
+        assert np.array_equal(got[r][0], staging), f"routed gradient differs on rank {r}"
+        _close(got[r][1], dx, f"dX[{r}]")
+        _close(got[r][2], dw, f"dW[{r}]")
+
+
 def test_qkv_backward_weight_overwrites_when_beta_is_zero():
     from tests import harness as H
     world, batch, s, q, kv, d, hidden = 1, 1, 200, 2, 2, 64, 136

@@ -137,7 +137,7 @@ def _pure_mxfp8(ctx, m, n, k):
     rc, ws = api.gemm_a2a_mxfp8_workspace_size(prob)
     assert rc == 0
     buf, base = ctx.scratch(ws)
-    pq = N.GemmA2AParams(rhs_nt=w.data_ptr(), local_output=out.data_ptr(), gemm=prob, num_comm_ctas=1, epoch=1)
+    pq = N.GemmA2AParams(rhs_nt=w.data_ptr(), local_output=out.data_ptr(), gemm=prob, num_comm_ctas=0, epoch=1)  # all SMs
     pure = N.Mxfp8GemmA2AParams(projection=pq, workspace=base, workspace_bytes=ws,
                                 activation=N.Mxfp8Activation(data=qd.data_ptr(), scales=qs.data_ptr(),
                                                              data_bytes=qd.numel(), scale_bytes=qs.numel()))

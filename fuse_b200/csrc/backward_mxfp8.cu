@@ -71,7 +71,7 @@ cudaError_t mx_gemm(const Quantised& a, const Quantised& b, fuse_bf16* d, int m,
     // CTA pairs: B boxed by half tiles, scale storage read through tensor maps
     Operands pair_maps = maps;
     CUtensorMap sfa_map, sfb_map;
-    if (encode_operand_u8(&pair_maps.b, b.data, n, k, k, 128) == cudaSuccess &&
+    if (encode_operand_u8(&pair_maps.b, b.data, n, k, k, launch::kPairMxBRows) == cudaSuccess &&
         launch::encode_scale_atoms(&sfa_map, a.scales, m, k) == cudaSuccess &&
         launch::encode_scale_atoms(&sfb_map, b.scales, n, k) == cudaSuccess)
       return launch::launch_pair_kernel<kModePlain, StoreMaps, true>(pair_maps, sfa_map, sfb_map, stores, f,
@@ -201,8 +201,8 @@ cudaError_t qkv_data(const fuse_mxfp8_qkv_backward_data_params& mp, const fuse_b
       Operands pair_maps = maps;
       CUtensorMap sfa_map, sfb_map;
       FusedParams pf = f;
-      pf.grad.m_group = 2 * launch::wave_m_group_pairs(pf, info.sm_count);
-      if (encode_operand_u8(&pair_maps.b, wq.data, n, k, k, 128) == cudaSuccess &&
+      pf.grad.m_group = 2 * launch::wave_m_group_pairs(pf, info.sm_count, launch::kPairMxBlockN);
+      if (encode_operand_u8(&pair_maps.b, wq.data, n, k, k, launch::kPairMxBRows) == cudaSuccess &&
           launch::encode_scale_atoms(&sfa_map, f.sfa, m, k) == cudaSuccess &&
           launch::encode_scale_atoms(&sfb_map, f.sfb, n, k) == cudaSuccess)
         return launch::launch_pair_kernel<kModeGradPull, GradPullMaps, true>(
@@ -280,7 +280,7 @@ cudaError_t oproj_data(const fuse_mxfp8_oproj_backward_data_params& mp, const fu
   if (tma && block_n == 256 && k % 128 == 0 && info.sm_count % 2 == 0 && launch::pair_tiles_requested()) {
     Operands pair_maps = maps;
     CUtensorMap sfa_map, sfb_map;
-    if (encode_operand_u8(&pair_maps.b, wq.data, n, k, k, 128) == cudaSuccess &&
+    if (encode_operand_u8(&pair_maps.b, wq.data, n, k, k, launch::kPairMxBRows) == cudaSuccess &&
         launch::encode_scale_atoms(&sfa_map, f.sfa, m, k) == cudaSuccess &&
         launch::encode_scale_atoms(&sfb_map, f.sfb, n, k) == cudaSuccess)
       return launch::launch_pair_kernel<kModeQkvDirect, StoreMaps, true>(

@@ -1858,6 +1858,16 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         uint32_t stage = 0, phase = 0, accum = 0, accum_phase = 0;
         uint32_t sf_parity = 0;
         (void)sf_parity;
+        // high words of the operand and scale-atom descriptors (constant), low words of stage 0
+        constexpr uint32_t kDescHigh = (1024u >> 4) | (1u << 14) | (2u << 29);
+        constexpr uint32_t kSfDescHigh = (128u >> 4) | (1u << 14);
+        constexpr uint32_t kMnStride = (kMnGroupBytes >> 4) << 16, kKStride = 1u << 16;  // the low word's second field
+        constexpr uint32_t kAStride = kAMn ? kMnStride : kKStride, kBStride = kBMn ? kMnStride : kKStride;
+        const uint32_t a_low0 = (base & 0x3FFFFu) >> 4;
+        const uint32_t sf_low0 = ((base + Layout::kSfOffset) & 0x3FFFFu) >> 4;
+        uint32_t a_low = a_low0, sf_low = sf_low0;
+        (void)kSfDescHigh;
+        (void)sf_low;
         bool ok = true;
         TileWalk walk = walk_template;
         for (int64_t t = walk.first(); ok && t >= 0; t = walk.next()) {
@@ -1868,39 +1878,45 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
           for (int32_t kb = 0; kb < k_blocks; ++kb) {
             ok = mbar_wait(full_bar(stage), phase, p.wait, kSiteSmemFull);
             if (!ok) break;
-            ptx::tc_fence_after();
-            const uint32_t a_addr = base + stage * Layout::kStageBytes;
-            const uint64_t a_desc = kAMn ? ptx::smem_desc_mn_sw128(a_addr, kMnGroupBytes)
-                                         : ptx::smem_desc_k_sw128(a_addr);
-            const uint64_t b_desc = kBMn ? ptx::smem_desc_mn_sw128(a_addr + Layout::kABytes, kMnGroupBytes)
-                                         : ptx::smem_desc_k_sw128(a_addr + Layout::kABytes);
+            // The descriptors of a stage differ from the previous stage's by a constant in their
+            // low word: this thread's instruction stream per K block bounds the kernel, so they
+            // are stepped, not rebuilt.
+            const uint64_t a_desc = (uint64_t(kDescHigh) << 32) | (a_low + kAStride);
+            const uint64_t b_desc = (uint64_t(kDescHigh) << 32) | (a_low + ((Layout::kABytes >> 4) + kBStride));
+            const uint32_t accumulate = kb != 0 ? 1u : 0u;
             if constexpr (kMx) {
               // Copy this K block's scale atoms shared -> TMEM (32 lanes x 16 bytes each, broadcast
               // to the four lane quarters), then four K=32 UMMAs; UMMA k reads byte k of every
               // 32-bit scale column.  tcgen05.cp and tcgen05.mma of one thread execute in order;
               // two sets of scale columns alternate anyway.
               constexpr int kBAtoms = (kBlockN + 127) / 128;
-              const uint32_t sf_smem = base + Layout::kSfOffset + stage * Layout::kSfStageBytes;
+              const uint64_t sf_desc = (uint64_t(kSfDescHigh) << 32) | sf_low;
               const uint32_t sf_tmem = tmem_base + Layout::kTmemSfOffset + (sf_parity ? Layout::kSfColumns : 0u);
               sf_parity ^= 1u;
-              ptx::tmem_cp_32x128b_warpx4(sf_tmem, ptx::smem_desc_scale_atom(sf_smem));
+              ptx::tmem_cp_32x128b_warpx4(sf_tmem, sf_desc);
 #pragma unroll
               for (int j = 0; j < kBAtoms; ++j)
-                ptx::tmem_cp_32x128b_warpx4(sf_tmem + 4u + 4u * j, ptx::smem_desc_scale_atom(sf_smem + 512u * (1 + j)));
+                ptx::tmem_cp_32x128b_warpx4(sf_tmem + 4u + 4u * j, sf_desc + ((512u * (1 + j)) >> 4));
 #pragma unroll
               for (int k = 0; k < 4; ++k)
                 ptx::umma_mxf8(d_tmem, a_desc + 2u * k, b_desc + 2u * k,
                                ptx::idesc_mxf8_e4m3(kBlockM, kBlockN, k, k), sf_tmem, sf_tmem + 4u,
-                               (kb | k) != 0 ? 1u : 0u);
+                               k == 0 ? accumulate : 1u);
+              sf_low += Layout::kSfStageBytes >> 4;
             } else {
+              ptx::umma_f16(d_tmem, a_desc, b_desc, kIdesc, accumulate);
 #pragma unroll
-              for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-                ptx::umma_f16(d_tmem, a_desc + kAStep * k, b_desc + kBStep * k, kIdesc,
-                              (kb | k) != 0 ? 1u : 0u);
-              }
+              for (int k = 1; k < kBlockK / kUmmaK; ++k)
+                ptx::umma_f16_accumulate(d_tmem, a_desc + kAStep * k, b_desc + kBStep * k, kIdesc);
             }
             ptx::umma_commit(empty_bar(stage));  // frees the stage when these UMMAs retire
-            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            a_low += Layout::kStageBytes >> 4;
+            if (++stage == kStages) {
+              stage = 0;
+              phase ^= 1u;
+              a_low = a_low0;
+              sf_low = sf_low0;
+            }
           }
           if (!ok) break;
           ptx::umma_commit(tmem_full_bar(accum));

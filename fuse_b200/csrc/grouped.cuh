@@ -339,6 +339,9 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const Grouped
     } else if (warp == 1) {
       if (lane == 0) {
         constexpr uint32_t kIdesc = ptx::idesc_bf16_f32(kBlockM, kBlockN, 0, 0);
+        constexpr uint32_t kDescHigh = (1024u >> 4) | (1u << 14) | (2u << 29);  // K-major, 128-byte swizzle
+        const uint32_t a_low0 = ((base & 0x3FFFFu) >> 4) | (1u << 16);
+        uint32_t a_low = a_low0;
         uint32_t stage = 0, phase = 0, accum = 0, accum_phase = 0;
         bool ok = true;
         for (int32_t t = compute_id; ok && t < tiles; t += compute_ctas) {
@@ -349,16 +352,16 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const Grouped
           for (int32_t kb = 0; kb < k_blocks; ++kb) {
             ok = mbar_wait(full_bar(stage), phase, w, kSiteSmemFull);
             if (!ok) break;
-            ptx::tc_fence_after();
-            const uint32_t a_addr = base + stage * Layout::kStageBytes;
-            const uint64_t a_desc = ptx::smem_desc_k_sw128(a_addr);
-            const uint64_t b_desc = ptx::smem_desc_k_sw128(a_addr + Layout::kABytes);
+            // descriptors stepped from stage to stage (this thread's instruction stream bounds the kernel)
+            const uint64_t a_desc = (uint64_t(kDescHigh) << 32) | a_low;
+            const uint64_t b_desc = a_desc + (Layout::kABytes >> 4);
+            ptx::umma_f16(d_tmem, a_desc, b_desc, kIdesc, kb != 0 ? 1u : 0u);
 #pragma unroll
-            for (int k = 0; k < kBlockK / kUmmaK; ++k)
-              ptx::umma_f16(d_tmem, a_desc + uint64_t(2 * k), b_desc + uint64_t(2 * k), kIdesc,
-                            (kb | k) != 0 ? 1u : 0u);
+            for (int k = 1; k < kBlockK / kUmmaK; ++k)
+              ptx::umma_f16_accumulate(d_tmem, a_desc + uint64_t(2 * k), b_desc + uint64_t(2 * k), kIdesc);
             ptx::umma_commit(empty_bar(stage));
-            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            a_low += Layout::kStageBytes >> 4;
+            if (++stage == kStages) { stage = 0; phase ^= 1u; a_low = a_low0; }
           }
           if (!ok) break;
           ptx::umma_commit(tmem_full_bar(accum));
@@ -548,6 +551,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) grouped
     } else if (warp == 1) {
       if (lane == 0 && leader) {
         constexpr uint32_t kIdesc = ptx::idesc_bf16_f32(2 * kBlockM, kBlockN, 0, 0);
+        constexpr uint32_t kDescHigh = (1024u >> 4) | (1u << 14) | (2u << 29);  // K-major, 128-byte swizzle
+        const uint32_t a_low0 = ((base & 0x3FFFFu) >> 4) | (1u << 16);
+        uint32_t a_low = a_low0;
         uint32_t stage = 0, phase = 0, accum = 0, accum_phase = 0;
         bool ok = true;
         for (int32_t t = pair_id; ok && t < tiles; t += pairs) {
@@ -558,16 +564,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) grouped
           for (int32_t kb = 0; kb < k_blocks; ++kb) {
             ok = mbar_wait(full_bar(stage), phase, w, kSiteSmemFull);
             if (!ok) break;
-            ptx::tc_fence_after();
-            const uint32_t a_addr = base + stage * Layout::kStageBytes;
-            const uint64_t a_desc = ptx::smem_desc_k_sw128(a_addr);
-            const uint64_t b_desc = ptx::smem_desc_k_sw128(a_addr + Layout::kABytes);
+            // descriptors stepped from stage to stage (this thread's instruction stream bounds the kernel)
+            const uint64_t a_desc = (uint64_t(kDescHigh) << 32) | a_low;
+            const uint64_t b_desc = a_desc + (Layout::kABytes >> 4);
+            ptx::umma_f16_pair(d_tmem, a_desc, b_desc, kIdesc, kb != 0 ? 1u : 0u);
 #pragma unroll
-            for (int k = 0; k < kBlockK / kUmmaK; ++k)
-              ptx::umma_f16_pair(d_tmem, a_desc + uint64_t(2 * k), b_desc + uint64_t(2 * k), kIdesc,
-                                 (kb | k) != 0 ? 1u : 0u);
+            for (int k = 1; k < kBlockK / kUmmaK; ++k)
+              ptx::umma_f16_pair_accumulate(d_tmem, a_desc + uint64_t(2 * k), b_desc + uint64_t(2 * k), kIdesc);
             ptx::umma_commit_pair(empty_bar(stage), 3);
-            if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            a_low += Layout::kStageBytes >> 4;
+            if (++stage == kStages) { stage = 0; phase ^= 1u; a_low = a_low0; }
           }
           if (!ok) break;
           ptx::umma_commit_pair(tmem_full_bar(accum), 3);

@@ -85,11 +85,11 @@ inline int32_t wave_m_group(const FusedParams& p, int sm_count) {
   return group < 1 ? 1 : group;
 }
 
-// The same for CTA pairs (256-row tiles): result in 256-row tiles.
-inline int32_t wave_m_group_pairs(const FusedParams& p, int sm_count) {
+// The same for CTA pairs (256-row tiles, `block_n` columns): result in 256-row tiles.
+inline int32_t wave_m_group_pairs(const FusedParams& p, int sm_count, int block_n = 256) {
   const int32_t compute = (sm_count - p.num_comm_ctas) / 2;
   const int32_t m_tiles = (p.m + 2 * kBlockM - 1) / (2 * kBlockM);
-  const int32_t n_tiles = (p.n + 255) / 256;
+  const int32_t n_tiles = (p.n + block_n - 1) / block_n;
   const int32_t smaller = m_tiles < n_tiles ? m_tiles : n_tiles;
   int32_t swizzle = p.order.swizzle > 0 ? p.order.swizzle : 1;
   while (swizzle > 1 && swizzle > smaller) swizzle /= 2;
@@ -217,8 +217,12 @@ inline bool encode_lhs_pull_maps(LhsPullMaps* maps, const FusedParams& f, uint64
 }
 
 // Launches pair_gemm_kernel (CTA pairs, 256 x 256 tiles) over `k`, whose tile order is re-planned
-// for 256-row tiles.  `maps.b` must box 128 rows (half a tile); sfa / sfb are only read by the
-// block-scaled variant.
+// for those tiles.  `maps.b` must box half a tile's B rows (kPairBRows /
+// kPairMxBRows); sfa / sfb are only read by the block-scaled variant.
+constexpr int kPairBRows = PairLayoutT<false>::kBlockN / 2;
+constexpr int kPairMxBlockN = PairLayoutT<true>::kBlockN;
+constexpr int kPairMxBRows = kPairMxBlockN / 2;
+
 template <int kMode, class Maps, bool kMx, bool kAMn = false, bool kBMn = false, bool kEmbedded = false>
 cudaError_t launch_pair_kernel(const Operands& maps, const CUtensorMap& sfa, const CUtensorMap& sfb, Maps& stores,
                                FusedParams k, int max_swizzle, const DeviceInfo& info, cudaStream_t stream,

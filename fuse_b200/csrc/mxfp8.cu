@@ -152,7 +152,8 @@ cudaError_t qkv_forward_mxfp8(const fuse_mxfp8_gemm_a2a_params& mp, const fuse_b
   const fuse_gemm_problem& g = p.gemm;
   if (!supported_mx_problem(g) || !std::isfinite(p.alpha) || p.epoch == 0 || p.num_comm_ctas < 0)
     return cudaErrorInvalidValue;
-  if (p.num_comm_ctas == 0) return cudaErrorNotSupported;  // no calibrated plan: explicit budgets only
+  // no calibrated plan: explicit budgets only (the GEMM-only launch may name 0: every SM computes)
+  if (p.num_comm_ctas == 0 && phase != MxPhase::kComputeOnly && phase != MxPhase::kPrepareOnly) return cudaErrorNotSupported;
   if (mp.postprocess.q_gamma != nullptr || mp.postprocess.cos != nullptr) return cudaErrorNotSupported;
   const WeightScratch w = weight_scratch(g, mp.workspace);
   if (mp.workspace == nullptr || reinterpret_cast<uintptr_t>(mp.workspace) % 256 != 0 ||
@@ -222,7 +223,7 @@ cudaError_t qkv_forward_mxfp8(const fuse_mxfp8_gemm_a2a_params& mp, const fuse_b
     if (block_n == 256 && g.k % 128 == 0 && reduced.sm_count % 2 == 0 && launch::pair_tiles_requested()) {
       Operands pair_maps = maps;
       CUtensorMap sfa_map, sfb_map;
-      if (encode_operand_u8(&pair_maps.b, w.data, g.n, g.k, g.k, 128) == cudaSuccess &&
+      if (encode_operand_u8(&pair_maps.b, w.data, g.n, g.k, g.k, launch::kPairMxBRows) == cudaSuccess &&
           launch::encode_scale_atoms(&sfa_map, f.sfa, g.m, g.k) == cudaSuccess &&
           launch::encode_scale_atoms(&sfb_map, f.sfb, g.n, g.k) == cudaSuccess)
         return launch::launch_pair_kernel<kModePlain, StoreMaps, true>(pair_maps, sfa_map, sfb_map, stores, f,
@@ -251,7 +252,7 @@ cudaError_t qkv_forward_mxfp8(const fuse_mxfp8_gemm_a2a_params& mp, const fuse_b
   if (tma && block_n == 256 && g.k % 128 == 0 && info.sm_count % 2 == 0 && launch::pair_tiles_requested()) {
     Operands pair_maps = maps;
     CUtensorMap sfa_map, sfb_map;
-    if (encode_operand_u8(&pair_maps.b, w.data, g.n, g.k, g.k, 128) == cudaSuccess &&
+    if (encode_operand_u8(&pair_maps.b, w.data, g.n, g.k, g.k, launch::kPairMxBRows) == cudaSuccess &&
         launch::encode_scale_atoms(&sfa_map, f.sfa, g.m, g.k) == cudaSuccess &&
         launch::encode_scale_atoms(&sfb_map, f.sfb, g.n, g.k) == cudaSuccess)
       return launch::launch_pair_kernel<kModeQkvDirect, StoreMaps, true>(pair_maps, sfa_map, sfb_map, stores, f,
@@ -378,8 +379,8 @@ cudaError_t oproj_forward_mxfp8(const fuse_mxfp8_a2a_gemm_params& mp, const fuse
         Operands pair_maps = maps;
         CUtensorMap sfa_map, sfb_map;
         FusedParams pf = f;
-        pf.lhs.m_group = 2 * launch::wave_m_group_pairs(pf, info.sm_count);
-        if (encode_operand_u8(&pair_maps.b, w.weights.data, g.n, g.k, g.k, 128) == cudaSuccess &&
+        pf.lhs.m_group = 2 * launch::wave_m_group_pairs(pf, info.sm_count, launch::kPairMxBlockN);
+        if (encode_operand_u8(&pair_maps.b, w.weights.data, g.n, g.k, g.k, launch::kPairMxBRows) == cudaSuccess &&
             launch::encode_scale_atoms(&sfa_map, f.sfa, g.m, g.k) == cudaSuccess &&
             launch::encode_scale_atoms(&sfb_map, f.sfb, g.n, g.k) == cudaSuccess)
         {

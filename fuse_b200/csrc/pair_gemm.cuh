@@ -280,6 +280,17 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       uint32_t sf_parity = 0;
       (void)sf_parity;
       (void)kIdesc;
+      // high words of the operand and scale-atom descriptors (constant), low words of stage 0
+      constexpr uint32_t kKMajorHigh = (1024u >> 4) | (1u << 14) | (2u << 29);
+      constexpr uint32_t kADescHigh = kKMajorHigh, kBDescHigh = kKMajorHigh;
+      constexpr uint32_t kSfDescHigh = (128u >> 4) | (1u << 14);
+      constexpr uint32_t kMnStride = (kMnGroupBytes >> 4) << 16, kKStride = 1u << 16;  // the low word's second field
+      constexpr uint32_t kAStride = kAMn ? kMnStride : kKStride, kBStride = kBMn ? kMnStride : kKStride;
+      const uint32_t a_low0 = (base & 0x3FFFFu) >> 4;  // start address field of stage 0's A tile
+      const uint32_t sf_low0 = ((base + Layout::kSfOffset) & 0x3FFFFu) >> 4;
+      uint32_t a_low = a_low0, sf_low = sf_low0;
+      (void)kSfDescHigh;
+      (void)sf_low;
       bool ok = true;
       TileWalk walk = walk_template;
       for (int64_t t = walk.first(); ok && t >= 0; t = walk.next()) {
@@ -290,32 +301,45 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         for (int32_t kb = 0; kb < k_blocks; ++kb) {
           ok = mbar_wait(full_bar(stage), phase, p.wait, kSiteSmemFull);
           if (!ok) break;
-          ptx::tc_fence_after();
-          const uint32_t a_addr = base + stage * Layout::kStageBytes;
-          const uint64_t a_desc = kAMn ? ptx::smem_desc_mn_sw128(a_addr, kMnGroupBytes) : ptx::smem_desc_k_sw128(a_addr);
-          const uint64_t b_desc = kBMn ? ptx::smem_desc_mn_sw128(a_addr + Layout::kABytes, kMnGroupBytes)
-                                       : ptx::smem_desc_k_sw128(a_addr + Layout::kABytes);
+          // (no tcgen05 fence: the operands were written by the copy engine and their arrival is
+          // acquired through the mbarrier; the fence after the accumulator wait above orders this
+          // tile's UMMAs behind the epilogue's TMEM loads)
+          // The descriptors of a stage differ from the previous stage's by a constant in their low
+          // word: this thread's instruction stream per K block is what bounds the kernel, so they
+          // are stepped, not rebuilt.
+          const uint64_t a_desc = (uint64_t(kADescHigh) << 32) | (a_low + kAStride);
+          const uint64_t b_desc = (uint64_t(kBDescHigh) << 32) | (a_low + ((Layout::kABytes >> 4) + kBStride));
+          const uint32_t accumulate = kb != 0 ? 1u : 0u;
           if constexpr (kMx) {
             // scale atoms shared -> TMEM in both CTAs, then four K = 32 UMMAs; UMMA k reads byte k
             // of every 32-bit scale column; two sets of scale columns alternate
-            const uint32_t sf_smem = base + Layout::kSfOffset + stage * Layout::kSfStageBytes;
-            const uint32_t sf_tmem = tmem_base + Layout::kTmemSfOffset + (sf_parity ? Layout::kSfColumns : 0u);
-            sf_parity ^= 1u;
-            ptx::tmem_cp_32x128b_warpx4_pair(sf_tmem, ptx::smem_desc_scale_atom(sf_smem));
-            ptx::tmem_cp_32x128b_warpx4_pair(sf_tmem + 4u, ptx::smem_desc_scale_atom(sf_smem + 512u));
-            ptx::tmem_cp_32x128b_warpx4_pair(sf_tmem + 8u, ptx::smem_desc_scale_atom(sf_smem + 1024u));
+            const uint64_t sf_desc = (uint64_t(kSfDescHigh) << 32) | sf_low;
+            const uint32_t sf_tmem = tmem_base + Layout::kTmemSfOffset + sf_parity;
+            sf_parity ^= Layout::kSfColumns;  // alternates 0 and kSfColumns (12 = 0b1100)
+            ptx::tmem_cp_32x128b_warpx4_pair(sf_tmem, sf_desc);
+            ptx::tmem_cp_32x128b_warpx4_pair(sf_tmem + 4u, sf_desc + (512u >> 4));
+            ptx::tmem_cp_32x128b_warpx4_pair(sf_tmem + 8u, sf_desc + (1024u >> 4));
+            ptx::umma_mxf8_pair(d_tmem, a_desc, b_desc, ptx::idesc_mxf8_e4m3(2 * kBlockM, kBlockN, 0, 0), sf_tmem,
+                                sf_tmem + 4u, accumulate);
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
-              ptx::umma_mxf8_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k,
-                                  ptx::idesc_mxf8_e4m3(2 * kBlockM, kBlockN, k, k), sf_tmem, sf_tmem + 4u,
-                                  (kb | k) != 0 ? 1u : 0u);
+            for (int k = 1; k < 4; ++k)
+              ptx::umma_mxf8_pair_accumulate(d_tmem, a_desc + 2u * k, b_desc + 2u * k,
+                                             ptx::idesc_mxf8_e4m3(2 * kBlockM, kBlockN, k, k), sf_tmem, sf_tmem + 4u);
+            sf_low += Layout::kSfStageBytes >> 4;
           } else {
+            ptx::umma_f16_pair(d_tmem, a_desc, b_desc, kIdesc, accumulate);
 #pragma unroll
-            for (int k = 0; k < kBlockK / kUmmaK; ++k)
-              ptx::umma_f16_pair(d_tmem, a_desc + kAStep * k, b_desc + kBStep * k, kIdesc, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 1; k < kBlockK / kUmmaK; ++k)
+              ptx::umma_f16_pair_accumulate(d_tmem, a_desc + kAStep * k, b_desc + kBStep * k, kIdesc);
           }
           ptx::umma_commit_pair(empty_bar(stage), 3);  // frees the stage in both CTAs
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          a_low += Layout::kStageBytes >> 4;
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+            a_low = a_low0;
+            sf_low = sf_low0;
+          }
         }
         if (!ok) break;
         ptx::umma_commit_pair(tmem_full_bar(accum), 3);

@@ -419,11 +419,24 @@ def run_c4(ctx: Context):
                          lambda: api.launch_qkv_backward_mxfp8_weight(wp, stream), flops, pure=pure_w, cublas=cublas_w)
     del keep_w, pure_w, cublas_w
     torch.cuda.empty_cache()
-    full_row = ctx.row("c4 MXFP8 QKV full backward (data + weight)", full_backward, 2 * flops,
-                       nvlink_bytes=pull_bytes, nvlink_dir="in")
-    summed = data_row["pure"]["ms"] + weight_row["pure"]["ms"]
-    full_row["pure"] = {"ms": summed, "pflops": 2 * flops / summed / 1e12, "what": "sum of the two pure block-scaled GEMMs"}
-    full_row["retention"] = summed / full_row["ms"]
+    # the denominator of the full backward: both pure GEMMs launched back to back in ONE timed sample, so
+    # that it runs under the same power cap as the 9 ms fused sequence (summing two short bursts would not)
+    pure_d, cublas_d, keep_d = _pure_mxfp8(ctx, m, hid, width)
+    pure_w, cublas_w, keep_w = _pure_mxfp8(ctx, width, hid, m)
+
+    def both_pure():
+        rc = pure_d()
+        return rc if rc else pure_w()
+
+    def both_cublas():
+        cublas_d()
+        return cublas_w()
+
+    full_row = ctx.row("c4 MXFP8 QKV full backward (data + weight)", full_backward, 2 * flops, pure=both_pure,
+                       cublas=both_cublas, nvlink_bytes=pull_bytes, nvlink_dir="in")
+    full_row["pure"]["what"] = "this library's two pure block-scaled GEMMs (dX and dW shapes) back to back in one sample"
+    del keep_d, pure_d, cublas_d, keep_w, pure_w, cublas_w
+    torch.cuda.empty_cache()
     # the two HBM-bound quantiser kernels of the weight phase, alone: 2 B read + 1.03 B written per element
     qa = torch.empty((width, m), dtype=U8, device=dev)
     qas = torch.empty(api.mxfp8_scale_bytes(width, m), dtype=U8, device=dev)

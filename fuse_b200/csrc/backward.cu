@@ -116,6 +116,12 @@ cudaError_t qkv_backward_data(const fuse_qkv_backward_data_params& p, const fuse
       // CTA pairs: whole pairs of communication CTAs, 256-row tiles
       FusedParams pf = f;
       pf.grad.m_group = 2 * launch::wave_m_group_pairs(pf, info.sm_count);
+      // no communication CTAs at all: one warp of every compute CTA pushes (FUSE_B200_EMBEDDED_PULL=0:
+      // communication CTAs)
+      if (launch::embedded_pull_requested(p.world_size))
+        return launch::launch_pair_kernel<kModeHeadGate, GradPushMaps, false, false, true, true>(
+            maps, maps.a, maps.a, push, pf, p.gemm_tuning.max_swizzle_size ? p.gemm_tuning.max_swizzle_size : 1, info, stream,
+            0.0);
       return launch::launch_pair_kernel<kModeHeadGate, GradPushMaps, false, false, true>(
           maps, maps.a, maps.a, push, pf, p.gemm_tuning.max_swizzle_size ? p.gemm_tuning.max_swizzle_size : 1, info, stream,
           double(m) * k * 2.0);

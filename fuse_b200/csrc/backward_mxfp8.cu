@@ -205,9 +205,15 @@ cudaError_t qkv_data(const fuse_mxfp8_qkv_backward_data_params& mp, const fuse_b
       if (encode_operand_u8(&pair_maps.b, wq.data, n, k, k, launch::kPairMxBRows) == cudaSuccess &&
           launch::encode_scale_atoms(&sfa_map, f.sfa, m, k) == cudaSuccess &&
           launch::encode_scale_atoms(&sfb_map, f.sfb, n, k) == cudaSuccess)
+      {
+        if (launch::embedded_pull_requested(p.world_size))  // one warp of every compute CTA pulls
+          return launch::launch_pair_kernel<kModeGradPull, GradPullMaps, true, false, false, true>(
+              pair_maps, sfa_map, sfb_map, pull, pf, p.gemm_tuning.max_swizzle_size ? p.gemm_tuning.max_swizzle_size : 1,
+              info, stream, 0.0);
         return launch::launch_pair_kernel<kModeGradPull, GradPullMaps, true>(
             pair_maps, sfa_map, sfb_map, pull, pf, p.gemm_tuning.max_swizzle_size ? p.gemm_tuning.max_swizzle_size : 1, info,
             stream, double(m) * k * (3.0 + 1.0 / 32));
+      }
     }
     if (encoded)
       return launch_mode<kModeGradPull, false, false, true, GradPullMaps>(maps, pull, f, block_n, info, stream,

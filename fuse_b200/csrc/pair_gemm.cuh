@@ -32,8 +32,9 @@ namespace fuse_b200 {
 // rows); every stage also carries the 512-byte scale atom of this CTA's A rows and the two atoms
 // of ALL 256 B rows (each CTA's tensor core needs the scales of the whole B tile); the
 // accumulator is single-buffered (TMEM also holds the scales) and drained whole by the epilogue.
-// kEmbedded: one warp of every compute CTA runs the copy pipeline of the lhs pull (no communication
-// CTAs at all); its two 16 KiB stages take the place of the sixth GEMM stage.
+// kEmbedded: one warp of every compute CTA runs the copy pipeline of the mode -- the lhs pull, the
+// gradient push or the gradient pull -- and there are no communication CTAs at all; its two 16 KiB
+// stages take the place of the sixth GEMM stage.
 template <bool kMx, bool kEmbedded = false>
 struct PairLayoutT {
   static constexpr int kStages = kEmbedded ? 5 : 6;
@@ -89,7 +90,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   constexpr bool kGated = kMode == kModeLhsPull || kMode == kModeGradPull || kMode == kModeHeadGate;
   constexpr bool kHeads = kMode == kModeGradPull || kMode == kModeHeadGate;  // K groups are Q/K/V heads
   constexpr bool kRemoteWriter = kMode == kModeHeadGate;  // flags released by the sending GPUs
-  static_assert(!kEmbedded || kMode == kModeLhsPull, "the embedded copy warp serves the lhs pull");
+  static_assert(!kEmbedded || kGated, "the embedded copy warp serves the pull and push modes");
   using Layout = PairLayoutT<kMx, kEmbedded>;
   constexpr int kStages = Layout::kStages;
   constexpr int32_t kBlockElems = kMx ? 2 * kBlockK : kBlockK;  // K elements per 128-byte row
@@ -152,8 +153,8 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       // memory for the GEMM: the pair's TMEM allocation and barriers involve both CTAs.
       __syncthreads();
       ptx::cluster_sync();
-    } else if (p.flags & kFlagCommOnly) {
-      do_compute = false;
+    } else if ((p.flags & kFlagCommOnly) && !kEmbedded) {
+      do_compute = false;  // (with embedded copy warps every CTA still has its transfers to run)
     }
   }
   if (do_compute) {
@@ -197,9 +198,12 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   const int32_t k_blocks = (p.k + kBlockElems - 1) / kBlockElems;
   bool unwound = false;
 
+  // Role-only launches (several ranks emulated on one GPU): with embedded copy warps every CTA
+  // runs its copy warp unless kFlagComputeOnly and its GEMM roles unless kFlagCommOnly.
+  const bool gemm_roles = !(kEmbedded && (p.flags & kFlagCommOnly));
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
+    if (lane == 0 && gemm_roles) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       TileWalk walk = walk_template;
@@ -270,7 +274,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ UMMA issuer (leader CTA)
-    if (lane == 0 && leader) {
+    if (lane == 0 && leader && gemm_roles) {
       constexpr uint32_t kIdesc = ptx::idesc_bf16_f32(2 * kBlockM, kBlockN, kAMn ? 1 : 0, kBMn ? 1 : 0);
       // descriptor step per UMMA (16 K values): 32 bytes inside the swizzle row of a K-major tile,
       // 16 rows of 128 bytes in an MN-major tile
@@ -356,11 +360,14 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
   } else if (warp == 2) {
     // ------------------------------------------------------------------ embedded copy warp
     if constexpr (kEmbedded) {
-      if (lane == 0) {
-        LhsPullPolicy policy(p, store_maps);
+      if (lane == 0 && !(p.flags & kFlagComputeOnly)) {
+        using Policy = std::conditional_t<kMode == kModeHeadGate, GradPushPolicy,
+                                          std::conditional_t<kMode == kModeGradPull, GradPullPolicy, LhsPullPolicy>>;
+        Policy policy(p, store_maps);
         run_chunk_pipeline_thread(policy, p.wait, base + Layout::kCopyRingOffset,
                                   bar_base + 8u * (2 * kStages + 2 * kAccumStages), int32_t(blockIdx.x),
                                   int32_t(gridDim.x));
+        if constexpr (kMode == kModeHeadGate) __threadfence_system();  // this thread's peer stores are performed
       }
       __syncwarp();
     }
@@ -371,7 +378,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
       const int32_t virt = kHeads ? 1 : p.lhs.virt;
       TileWalk walk = walk_template;
       uint32_t tile_seq = 0;
-      bool ok = true;
+      bool ok = gemm_roles;
       for (int64_t t = walk.first(); ok && t >= 0; t = walk.next(), ++tile_seq) {
         int32_t mp, nt;
         p.order.decode(t, mp, nt);
@@ -395,7 +402,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint32_t accum = 0, accum_phase = 0, staged_blocks = 0;
     bool ok = true;
     TileWalk walk = walk_template;
-    for (int64_t t = walk.first(); ok && t >= 0; t = walk.next()) {
+    for (int64_t t = gemm_roles ? walk.first() : -1; ok && t >= 0; t = walk.next()) {
       int32_t mp, nt;
       p.order.decode(t, mp, nt);
       const int32_t mt = mp * 2 + int32_t(rank);  // this CTA's 128-row tile

@@ -320,6 +320,7 @@ SYMBOLS = {
     "fuse_launch_a2a_gemm_mxfp8_cutlass": (C.c_int, [C.POINTER(Mxfp8A2AGemmParams), _P]),
     "fuse_launch_a2a_gemm_mxfp8_cutlass_ex": (C.c_int, [C.POINTER(Mxfp8A2AGemmParams), C.POINTER(Options), _P]),
     "fuse_create_bf16_a2a_grouped_gemm": (C.c_int, [C.POINTER(Bf16GroupedGemmParams), C.POINTER(C.c_void_p)]),
+    "fuse_create_bf16_grouped_gemm_a2a": (C.c_int, [C.POINTER(Bf16GroupedGemmParams), C.POINTER(C.c_void_p)]),
     "fuse_launch_bf16_grouped_gemm": (C.c_int, [C.c_void_p, _P]),
     "fuse_launch_bf16_grouped_gemm_ex": (C.c_int, [C.c_void_p, C.POINTER(Options), _P]),
     "fuse_destroy_bf16_grouped_gemm": (C.c_int, [C.c_void_p]),

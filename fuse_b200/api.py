@@ -249,6 +249,13 @@ def create_bf16_a2a_grouped_gemm(params: Bf16GroupedGemmParams):
     return rc, plan.value
 
 
+def create_bf16_grouped_gemm_a2a(params: Bf16GroupedGemmParams):
+    """The combine direction (expert FC2 -> rows scattered to the token owners): (cudaError, plan)."""
+    plan = C.c_void_p()
+    rc = N.lib().fuse_create_bf16_grouped_gemm_a2a(C.byref(params), C.byref(plan))
+    return rc, plan.value
+
+
 def launch_bf16_grouped_gemm(plan: int, stream: int = 0, options: Options | None = None) -> int:
     if options is None:
         return N.lib().fuse_launch_bf16_grouped_gemm(plan, stream)

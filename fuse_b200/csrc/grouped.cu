@@ -1,4 +1,4 @@
-// MoE dispatch -> expert FC1 grouped GEMM: plan object and entry points.
+// MoE grouped GEMMs (dispatch -> expert FC1; expert FC2 -> combine): plan object and entry points.
 // Interface: include/fuse/operators/primitives/grouped_gemm.h:10-100 of the reference;
 // plan lifetime and validation follow csrc/operators/sm103/api/grouped.cuh:58-428.
 #include <new>
@@ -12,6 +12,7 @@ struct fuse_bf16_grouped_gemm_plan {
   void* metadata = nullptr;  // one private device allocation: tensor maps, flags, epoch, prefix
   int block_n = 256;
   bool pair = false;  // CTA pairs (policy.mma_sm_count == 2)
+  bool combine = false;  // GEMM -> scatter to the token owners (no communication CTAs)
   int grid = 0;
   int device = -1;
 };
@@ -23,7 +24,9 @@ using namespace launch;
 
 size_t align256(size_t n) { return (n + 255) & ~size_t{255}; }
 
-cudaError_t create_dispatch_plan(const fuse_bf16_grouped_gemm_params& p, fuse_bf16_grouped_gemm_plan** out) {
+// combine: the plan of the FC2 -> scatter direction (peer_output instead of peer_input; every CTA
+// computes, so policy.num_comm_ctas only has to be a valid count)
+cudaError_t create_plan(const fuse_bf16_grouped_gemm_params& p, bool combine, fuse_bf16_grouped_gemm_plan** out) {
   if (out == nullptr) return cudaErrorInvalidValue;
   *out = nullptr;
   if (p.lhs == nullptr || p.weight_nt == nullptr || p.output == nullptr || p.row_offsets == nullptr ||
@@ -32,7 +35,8 @@ cudaError_t create_dispatch_plan(const fuse_bf16_grouped_gemm_params& p, fuse_bf
       p.topk <= 0 || p.policy.num_comm_ctas <= 0 || p.policy.num_compute_ctas <= 0)
     return cudaErrorInvalidValue;
   for (int r = 0; r < p.world_size; ++r)
-    if (!host::aligned16(p.peer_input[r]) || !host::aligned4(p.peer_started[r]) || !host::aligned4(p.peer_done[r]))
+    if (!host::aligned16(combine ? static_cast<const void*>(p.peer_output[r]) : static_cast<const void*>(p.peer_input[r])) ||
+        (combine && p.peer_output[r] == nullptr) || !host::aligned4(p.peer_started[r]) || !host::aligned4(p.peer_done[r]))
       return cudaErrorInvalidValue;
   // geometry outside this implementation's domain
   if (p.n % 8 != 0 || p.k % 8 != 0 || (p.policy.tile_n != 128 && p.policy.tile_n != 256) ||
@@ -58,7 +62,8 @@ cudaError_t create_dispatch_plan(const fuse_bf16_grouped_gemm_params& p, fuse_bf
   // mma_sm_count 2: CTA pairs (256 x 256 tiles); needs the 256-wide tile, whole pairs of
   // communication and compute CTAs, and is otherwise outside this implementation's domain.
   plan->pair = p.policy.mma_sm_count == 2;
-  if (plan->pair && (p.policy.tile_n != 256 || p.policy.num_comm_ctas % 2 != 0 || info.sm_count % 2 != 0)) {
+  plan->combine = combine;
+  if (plan->pair && (p.policy.tile_n != 256 || (!combine && p.policy.num_comm_ctas % 2 != 0) || info.sm_count % 2 != 0)) {
     delete plan;
     return cudaErrorNotSupported;
   }
@@ -103,7 +108,8 @@ cudaError_t create_dispatch_plan(const fuse_bf16_grouped_gemm_params& p, fuse_bf
   g.n_tiles = host::ceil_div(p.n, plan->block_n);
   g.cap_tiles = cap_tiles;
   g.tile_m = plan->pair ? 2 * kBlockM : kBlockM;
-  g.num_comm_ctas = p.policy.num_comm_ctas;
+  g.num_comm_ctas = combine ? 0 : p.policy.num_comm_ctas;
+  g.topk = p.topk;
   g.maps_a = reinterpret_cast<const CUtensorMap*>(base);
   g.maps_b = reinterpret_cast<const CUtensorMap*>(base + maps_bytes);
   g.lhs = reinterpret_cast<uint16_t* const*>(p.lhs);
@@ -115,13 +121,15 @@ cudaError_t create_dispatch_plan(const fuse_bf16_grouped_gemm_params& p, fuse_bf
   g.tile_prefix = reinterpret_cast<int32_t*>(base + 2 * maps_bytes + ready_bytes + 256);
   for (int r = 0; r < p.world_size; ++r) {
     g.peer_input[r] = p.peer_input[r];
+    g.peer_output[r] = reinterpret_cast<uint16_t*>(p.peer_output[r]);
     g.peer_started[r] = p.peer_started[r];
     g.peer_done[r] = p.peer_done[r];
   }
-  const int compute = p.policy.num_compute_ctas < info.sm_count - p.policy.num_comm_ctas
-                          ? p.policy.num_compute_ctas
-                          : info.sm_count - p.policy.num_comm_ctas;
-  plan->grid = p.policy.num_comm_ctas + (plan->pair ? compute / 2 * 2 : compute);
+  const int compute = combine ? info.sm_count
+                              : (p.policy.num_compute_ctas < info.sm_count - p.policy.num_comm_ctas
+                                     ? p.policy.num_compute_ctas
+                                     : info.sm_count - p.policy.num_comm_ctas);
+  plan->grid = g.num_comm_ctas + (plan->pair ? compute / 2 * 2 : compute);
   g.wait.status = info.status;
   if ((status = cudaDeviceSynchronize()) != cudaSuccess) return fail(status);
   *out = plan;
@@ -140,15 +148,22 @@ cudaError_t launch_plan(fuse_bf16_grouped_gemm_plan* plan, const fuse_b200_optio
   if (status != cudaSuccess) return status;
   host::count_launch();
   if (plan->pair)
-    return host::launch_kernel(grouped_pair_kernel, plan->grid, kThreads, PairLayoutT<false>::kDynamicBytes, true, stream,
-                               g);
+    return plan->combine ? host::launch_kernel(grouped_pair_kernel<true>, plan->grid, kThreads,
+                                               PairLayoutT<false>::kDynamicBytes, true, stream, g)
+                         : host::launch_kernel(grouped_pair_kernel<false>, plan->grid, kThreads,
+                                               PairLayoutT<false>::kDynamicBytes, true, stream, g);
   if (plan->block_n == 256) {
     using Layout = SmemLayout<256, 4, false>;
-    return host::launch_kernel(grouped_gemm_kernel<256, 4>, plan->grid, kThreads, Layout::kDynamicBytes, true,
-                               stream, g);
+    return plan->combine ? host::launch_kernel(grouped_gemm_kernel<256, 4, true>, plan->grid, kThreads,
+                                               Layout::kDynamicBytes, true, stream, g)
+                         : host::launch_kernel(grouped_gemm_kernel<256, 4, false>, plan->grid, kThreads,
+                                               Layout::kDynamicBytes, true, stream, g);
   }
   using Layout = SmemLayout<128, 6, false>;
-  return host::launch_kernel(grouped_gemm_kernel<128, 6>, plan->grid, kThreads, Layout::kDynamicBytes, true, stream, g);
+  return plan->combine ? host::launch_kernel(grouped_gemm_kernel<128, 6, true>, plan->grid, kThreads, Layout::kDynamicBytes,
+                                             true, stream, g)
+                       : host::launch_kernel(grouped_gemm_kernel<128, 6, false>, plan->grid, kThreads, Layout::kDynamicBytes,
+                                             true, stream, g);
 }
 
 }  // namespace
@@ -159,7 +174,12 @@ extern "C" {
 int fuse_create_bf16_a2a_grouped_gemm(const fuse_bf16_grouped_gemm_params* params,
                                       fuse_bf16_grouped_gemm_plan** plan) {
   if (params == nullptr) return int(cudaErrorInvalidValue);
-  return int(fuse_b200::create_dispatch_plan(*params, plan));
+  return int(fuse_b200::create_plan(*params, false, plan));
+}
+int fuse_create_bf16_grouped_gemm_a2a(const fuse_bf16_grouped_gemm_params* params,
+                                      fuse_bf16_grouped_gemm_plan** plan) {
+  if (params == nullptr) return int(cudaErrorInvalidValue);
+  return int(fuse_b200::create_plan(*params, true, plan));
 }
 int fuse_launch_bf16_grouped_gemm(fuse_bf16_grouped_gemm_plan* plan, fuse_stream stream) {
   return int(fuse_b200::launch_plan(plan, nullptr, reinterpret_cast<cudaStream_t>(stream)));

@@ -1,4 +1,4 @@
-// MoE dispatch -> expert FC1 grouped GEMM: one persistent kernel.
+// MoE grouped GEMMs: dispatch -> expert FC1, and expert FC2 -> combine; one persistent kernel each.
 //
 // For every local expert e, A_e[M_e, K] is gathered row by row from the ranks that hold the
 // routed tokens (source[row] = {rank, token, slot} -> peer_input[rank][token, :]) into the
@@ -14,8 +14,17 @@
 //       the TMA producer gated on the panel flag, and an epilogue that writes only rows < M_e
 //       (the caller's poison in the unused capacity stays).
 //
-// Replaces csrc/operators/sm103/detail/grouped/{a2a_gemm,persistent_gemm,cutlass_pipeline,
-// communication}.cuh of the reference (dispatch direction).
+// Combine (kCombine): A_e is local and complete at launch; D_e[M_e, N] = A_e W_e^T goes to the
+// expert's output slab AND row by row to the rank that owns the token,
+// peer_output[source.rank][(source.token * topk + source.slot), :].  No communication CTAs: the
+// epilogue of every compute CTA stages each 64-column block in shared memory and its four warps
+// write whole 128-byte row pieces -- eight lanes per row -- to the local slab and over NVLink to
+// the owner, so the scatter of tile i overlaps the UMMAs of tile i+1.  Every rank has entered the
+// invocation before anything is written into it (its started epoch), and the kernel ends with
+// the done handshake: when it returns, every source has finished writing into this rank.
+//
+// Replaces csrc/operators/sm103/detail/grouped/{a2a_gemm,gemm_a2a,persistent_gemm,cutlass_pipeline,
+// communication}.cuh of the reference.
 #pragma once
 
 #include "fused_gemm.cuh"
@@ -38,6 +47,8 @@ struct GroupedParams {
   const int64_t* row_offsets;  // device [experts + 1]
   const GroupedTokenSource* source;
   const uint16_t* peer_input[kMaxWorldSize];
+  uint16_t* peer_output[kMaxWorldSize];  // combine: every rank's [tokens * topk, N] branch outputs
+  int32_t topk;
   uint32_t* peer_started[kMaxWorldSize];
   uint32_t* peer_done[kMaxWorldSize];
   uint32_t* ready;             // [experts * cap_tiles] flag lines: word 0 epoch, word 1 arrivals
@@ -246,9 +257,76 @@ __device__ __forceinline__ void dispatch_pull_role(const GroupedParams& p, const
 }
 
 // ------------------------------------------------------------------------------------------
+// Combine epilogue (csrc/operators/sm103/detail/grouped/gemm_a2a.cuh:15-93 of the reference: one
+// row of the expert's output per routed branch, no weighting or top-k reduction).
+// ------------------------------------------------------------------------------------------
+// Before the first remote write: every destination has entered this invocation (its buffers may
+// be overwritten).  Called by the four epilogue warps together; false when a wait gave up.
+__device__ __forceinline__ bool combine_wait_started(const GroupedParams& p, const WaitContext& w, int warp, int lane) {
+  bool ok = true;
+  if (warp == 4 && lane < p.world && !(p.flags & kFlagSkipPeerWait))
+    ok = flag_wait<true>(p.peer_started[p.rank] + lane * kReadyFlagStride, w.epoch, w, kSitePeerStarted, uint32_t(lane));
+  return ptx::named_bar_all(2, kEpilogueThreads, ok);
+}
+
+// One accumulator tile (this CTA's 128 rows x kBlockN columns at TMEM address `taddr`) -> BF16 ->
+// the expert's output slab and the owners' branch rows.  `release` hands the accumulator back
+// once its last column has been read.
+template <int kBlockN, class Release>
+__device__ __forceinline__ void combine_store_tile(const GroupedParams& p, int32_t expert, int32_t mt, int32_t nt,
+                                                   int64_t expert_rows, uint32_t taddr, uint32_t staging_base,
+                                                   uint32_t& staged_blocks, int warp, int lane, Release release) {
+  const int quarter = warp & 3;
+  const int32_t row_in_tile = quarter * 32 + lane;
+  const int64_t begin = p.row_offsets[expert];
+  // the rows this lane writes in the cooperative phase: 8 lanes per row, 4 rows per warp and step
+  const int32_t piece = lane & 7;
+  uint16_t* local_row[8];
+  uint16_t* remote_row[8];
+#pragma unroll
+  for (int it = 0; it < 8; ++it) {
+    const int32_t r = mt * kBlockM + it * 16 + quarter * 4 + (lane >> 3);
+    local_row[it] = nullptr;
+    remote_row[it] = nullptr;
+    if (r < expert_rows) {  // rows past M_e keep the caller's contents everywhere
+      const GroupedTokenSource src = p.source[begin + r];
+      local_row[it] = p.output[expert] + int64_t(r) * p.n;
+      remote_row[it] = p.peer_output[src.rank] + (int64_t(src.token) * p.topk + src.slot) * p.n;
+    }
+  }
+#pragma unroll 1
+  for (int c = 0; c < kBlockN; c += 64) {
+    const uint32_t staging = staging_base + (staged_blocks & 1u) * uint32_t(kBlockM * 128);
+    ++staged_blocks;
+    uint32_t acc0[32], acc1[32];
+    ptx::tmem_ld_32x32b_x32(taddr + c, acc0);
+    ptx::tmem_ld_32x32b_x32(taddr + c + 32, acc1);
+    ptx::tmem_wait_ld();
+    if (c + 64 >= kBlockN) release();
+    const uint32_t row_addr = staging + uint32_t(row_in_tile) * 128u;
+    stage_accumulators(acc0, row_addr, 0, row_in_tile, 1.0f);
+    stage_accumulators(acc1, row_addr, 4, row_in_tile, 1.0f);
+    // one barrier per block: a buffer is written again two blocks later, behind the barrier that
+    // every thread reaches only after it has read this one
+    ptx::named_bar_sync(1, kEpilogueThreads);
+    const int32_t col = nt * kBlockN + c + piece * 8;
+    if (col < p.n) {
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        if (local_row[it] == nullptr) continue;
+        const int32_t rloc = it * 16 + quarter * 4 + (lane >> 3);
+        const uint4 v = ptx::ld_shared_v4(staging + uint32_t(rloc) * 128u + uint32_t((piece ^ (rloc & 7)) * 16));
+        ptx::st_v4(local_row[it] + col, v);
+        ptx::st_v4(remote_row[it] + col, v);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
 // The grouped kernel.
 // ------------------------------------------------------------------------------------------
-template <int kBlockN, int kStages>
+template <int kBlockN, int kStages, bool kCombine = false>
 __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const GroupedParams p) {
   using Layout = SmemLayout<kBlockN, kStages, false>;
   constexpr uint32_t kAccumStages = Layout::kAccumStages;
@@ -313,11 +391,13 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const Grouped
         for (int32_t t = compute_id; ok && t < tiles; t += compute_ctas) {
           int32_t mt, nt;
           decode(t, expert, mt, nt);
-          // the whole panel (all of K) arrives as one unit
-          const int64_t flag = (int64_t(expert) * p.cap_tiles + mt) * kReadyFlagStride;
-          ok = flag_wait<false>(p.ready + flag, w.epoch, w, kSitePanelReady, uint32_t(flag / kReadyFlagStride));
-          ptx::fence_proxy_async_global();
-          if (!ok) break;
+          if constexpr (!kCombine) {
+            // the whole panel (all of K) arrives as one unit
+            const int64_t flag = (int64_t(expert) * p.cap_tiles + mt) * kReadyFlagStride;
+            ok = flag_wait<false>(p.ready + flag, w.epoch, w, kSitePanelReady, uint32_t(flag / kReadyFlagStride));
+            ptx::fence_proxy_async_global();
+            if (!ok) break;
+          }
           const CUtensorMap* map_a = p.maps_a + expert;
           const CUtensorMap* map_b = p.maps_b + expert;
           for (int32_t kb = 0; kb < k_blocks; ++kb) {
@@ -377,6 +457,9 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const Grouped
       uint32_t accum = 0, accum_phase = 0;
       int32_t expert = 0;
       bool ok = true;
+      uint32_t staged_blocks = 0;
+      (void)staged_blocks;
+      if constexpr (kCombine) ok = combine_wait_started(p, w, warp, lane);
       for (int32_t t = compute_id; ok && t < tiles; t += compute_ctas) {
         int32_t mt, nt;
         decode(t, expert, mt, nt);
@@ -386,6 +469,17 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const Grouped
         ptx::tc_fence_after();
         int64_t expert_rows = p.row_offsets[expert + 1] - p.row_offsets[expert];
         if (expert_rows > p.capacity) expert_rows = p.capacity;
+        if constexpr (kCombine) {
+          const uint32_t bar = tmem_empty_bar(accum);
+          combine_store_tile<kBlockN>(p, expert, mt, nt, expert_rows,
+                                      tmem_base + (uint32_t(quarter * 32) << 16) + accum * kBlockN,
+                                      base + Layout::kStagingOffset, staged_blocks, warp, lane, [&] {
+                                        ptx::tc_fence_before();
+                                        ptx::mbar_arrive(bar);
+                                      });
+          if (++accum == kAccumStages) { accum = 0; accum_phase ^= 1u; }
+          continue;
+        }
         const int32_t row = mt * kBlockM + quarter * 32 + lane;
         const bool row_ok = row < expert_rows;  // rows past M_e keep the caller's contents
         uint16_t* d_row = p.output[expert] + int64_t(row) * p.n + nt * kBlockN;
@@ -424,6 +518,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const Grouped
         if (++accum == kAccumStages) { accum = 0; accum_phase ^= 1u; }
       }
     }
+    if constexpr (kCombine) __threadfence_system();  // this thread's remote rows are performed before the grid joins
     ptx::tc_fence_before();
     __syncthreads();
     if (warp == 2) {
@@ -432,8 +527,9 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const Grouped
     }
   }
 
-  // Every rank tells its peers that it has finished reading their tokens, and leaves only when
-  // all of them have finished reading its own (communication.cuh:237-250).
+  // Every rank tells its peers that it has finished reading their tokens (combine: writing their
+  // branch rows), and leaves only when all of them have finished with its own
+  // (communication.cuh:237-250).
   cooperative_groups::this_grid().sync();
   if (blockIdx.x == 0 && threadIdx.x < 32) {
     if (lane == 0) ptx::fence_sc_sys();
@@ -452,6 +548,7 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const Grouped
 // pair_gemm.cuh.  Each CTA gates its own 128-row panel; a panel past M_e has no rows to wait
 // for (its accumulator rows are never stored).  Communication CTAs come in whole pairs.
 // ------------------------------------------------------------------------------------------
+template <bool kCombine = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) grouped_pair_kernel(const GroupedParams p) {
   using Layout = PairLayoutT<false>;
   constexpr int kStages = Layout::kStages;
@@ -526,7 +623,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) grouped
           int32_t mp, nt;
           decode(t, expert, mp, nt);
           const int32_t mt = mp * 2 + int32_t(rank);  // this CTA's 128-row panel
-          if (int64_t(mt) * kBlockM < rows_of(expert)) {
+          if (!kCombine && int64_t(mt) * kBlockM < rows_of(expert)) {
             const int64_t flag = (int64_t(expert) * p.cap_tiles + mt) * kReadyFlagStride;
             ok = flag_wait<false>(p.ready + flag, w.epoch, w, kSitePanelReady, uint32_t(flag / kReadyFlagStride));
             ptx::fence_proxy_async_global();
@@ -592,6 +689,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) grouped
       uint32_t accum = 0, accum_phase = 0;
       int32_t expert = 0;
       bool ok = true;
+      uint32_t staged_blocks = 0;
+      (void)staged_blocks;
+      if constexpr (kCombine) ok = combine_wait_started(p, w, warp, lane);
       for (int32_t t = pair_id; ok && t < tiles; t += pairs) {
         int32_t mp, nt;
         decode(t, expert, mp, nt);
@@ -601,6 +701,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) grouped
         if (!ok) break;
         ptx::tc_fence_after();
         const int64_t expert_rows = rows_of(expert);
+        if constexpr (kCombine) {
+          const uint32_t bar = accum ? leader_tmem_empty1 : leader_tmem_empty0;
+          combine_store_tile<kBlockN>(p, expert, mt, nt, expert_rows,
+                                      tmem_base + (uint32_t(quarter * 32) << 16) + accum * kBlockN,
+                                      base + Layout::kStagingOffset, staged_blocks, warp, lane, [&] {
+                                        ptx::tc_fence_before();
+                                        ptx::mbar_arrive_cluster(bar);
+                                      });
+          if (++accum == kAccumStages) { accum = 0; accum_phase ^= 1u; }
+          continue;
+        }
         const int32_t row = mt * kBlockM + quarter * 32 + lane;
         const bool row_ok = row < expert_rows;  // rows past M_e keep the caller's contents
         uint16_t* d_row = p.output[expert] + int64_t(row) * p.n + nt * kBlockN;
@@ -645,6 +756,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) grouped
       const uint64_t start = ptx::globaltimer();
       while (ptx::globaltimer() - start < 200000ull) __nanosleep(1000);
     }
+    if constexpr (kCombine) __threadfence_system();  // this thread's remote rows are performed before the grid joins
     ptx::tc_fence_before();
     __syncthreads();
     ptx::cluster_sync();

@@ -180,6 +180,11 @@ __device__ __forceinline__ void st_shared_v4(uint32_t addr, const uint4& v) {
                "r"(v.w)
                : "memory");
 }
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr) : "memory");
+  return v;
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until the issuing thread's bulk groups have finished READING shared memory.
 __device__ __forceinline__ void bulk_wait_read0() {

@@ -447,6 +447,14 @@ typedef struct fuse_bf16_grouped_gemm_params {
 typedef struct fuse_bf16_grouped_gemm_plan fuse_bf16_grouped_gemm_plan;
 FUSE_API int fuse_create_bf16_a2a_grouped_gemm(const fuse_bf16_grouped_gemm_params* params,
                                       fuse_bf16_grouped_gemm_plan** plan);
+/* grouped_gemm.h:97-98 (create_bf16_grouped_gemm_a2a): the combine direction.  lhs[e] is local and
+ * complete at launch; D_e = lhs_e W_e^T is written to output[e] and every routed row r to
+ * peer_output[source.rank][(source.token * topk + source.slot) * n ...] (no weighting, no top-k
+ * reduction: csrc/operators/sm103/detail/grouped/gemm_a2a.cuh:15-93).  Launched and destroyed
+ * through the same two calls as the dispatch plan; every CTA computes (the epilogue scatters), so
+ * policy.num_comm_ctas is only validated. */
+FUSE_API int fuse_create_bf16_grouped_gemm_a2a(const fuse_bf16_grouped_gemm_params* params,
+                                      fuse_bf16_grouped_gemm_plan** plan);
 FUSE_API int fuse_launch_bf16_grouped_gemm(fuse_bf16_grouped_gemm_plan* plan, fuse_stream stream);
 FUSE_API int fuse_launch_bf16_grouped_gemm_ex(fuse_bf16_grouped_gemm_plan* plan, const fuse_b200_options* options,
                                      fuse_stream stream);

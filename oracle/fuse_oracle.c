@@ -620,6 +620,32 @@ FO_API int fo_moe_dispatch_fc1(int experts_local, const int32_t* row_offsets,
   return 0;
 }
 
+/* Per-expert GEMM + scatter (the combine direction): for local expert e, rows r in
+ * [row_offsets[e], row_offsets[e+1]): D_e[r, :] = A_e[r, :] W_e^T goes to the expert's output
+ * slab and to peer_output[source.rank][(source.token * topk + source.slot), :] -- one row per
+ * routed branch, no weighting or top-k reduction
+ * (csrc/operators/sm103/detail/grouped/gemm_a2a.cuh:15-93; receiver check:
+ * benchmarks/sm103/grouped_validation.cuh:143-157). */
+FO_API int fo_moe_fc2_combine(int experts_local, const int32_t* row_offsets, const int32_t* sources,
+                              const uint16_t* lhs, const uint16_t* weights, int64_t n, int64_t k,
+                              int64_t capacity, int topk, uint16_t* output,
+                              uint16_t* const* peer_output) {
+  for (int e = 0; e < experts_local; ++e) {
+    const int64_t begin = row_offsets[e], rows = row_offsets[e + 1] - begin;
+    if (rows == 0) continue;
+    uint16_t* slab = output + (int64_t)e * capacity * n;
+    if (fo_gemm_bf16(0, lhs + (int64_t)e * capacity * k, k, weights + (int64_t)e * n * k, k, slab, n,
+                     rows, n, k, 1.0f, 0.0f))
+      return 1;
+    for (int64_t r = 0; r < rows; ++r) {
+      const int32_t* s = sources + (begin + r) * 3;
+      memcpy(peer_output[s[0]] + ((int64_t)s[1] * topk + s[2]) * n, slab + r * n,
+             sizeof(uint16_t) * (size_t)n);
+    }
+  }
+  return 0;
+}
+
 /* ------------------------------------------------------------------------- */
 /* Batch forms of the receiver-view maps (full-size validation samples many   */
 /* elements at once; each entry is exactly the scalar map above).             */

@@ -85,6 +85,7 @@ def lib():
     _sig(L, "fo_moe_topk", None, P, i64, C.c_int, C.c_int, P)
     _sig(L, "fo_moe_build_rows", i64, C.c_int, C.c_int, C.c_int, i64, C.c_int, P, P, P)
     _sig(L, "fo_moe_dispatch_fc1", C.c_int, C.c_int, P, P, P, P, i64, i64, i64, P, P)
+    _sig(L, "fo_moe_fc2_combine", C.c_int, C.c_int, P, P, P, P, i64, i64, i64, C.c_int, P, P)
     _sig(L, "fo_num_threads", C.c_int)
     _sig(L, "fo_set_num_threads", None, C.c_int)
     _sig(L, "fo_qkv_oracle_source_batch", None, C.c_int, C.c_int, u64, u64, u64, P, i64, P, P)

@@ -371,6 +371,47 @@ def moe_dispatch_fc1(world, rank, experts_local, tokens_bits, weights_bits, row_
     return result
 
 
+def moe_fc2_combine(world, experts_local, lhs_bits, weights_bits, row_offsets, sources, capacity, tokens, topk,
+                    tile_n=256, mma_sm_count=1, launches=1):
+    """Every rank of the expert FC2 -> combine operator, emulated one after the other on one GPU.
+    lhs_bits[r] [E, capacity, K], weights_bits[r] [E, N, K], row_offsets[r] int64 [E+1], sources[r]
+    int32 [rows, 3] per rank r.  Returns (outputs [r] -> [E, capacity, N] bits, received [r] ->
+    [tokens * topk, N] bits); rows nobody routes and unused capacity keep the poison 0x7f7f."""
+    e, n, k = weights_bits[0].shape
+    poison = lambda *shape: torch.full(shape, 0x7f7f, dtype=torch.int16, device=DEV).view(torch.bfloat16)
+    received = [poison(tokens * topk, n) for _ in range(world)]
+    started = [torch.zeros(world * N.READY_FLAG_STRIDE, dtype=torch.int32, device=DEV) for _ in range(world)]
+    done = [torch.zeros(world * N.READY_FLAG_STRIDE, dtype=torch.int32, device=DEV) for _ in range(world)]
+    outputs = []
+    ptrs = lambda t: torch.tensor([t[i].data_ptr() for i in range(e)], dtype=torch.int64, device=DEV)
+    for r in range(world):
+        lhs, w, out = to_device(lhs_bits[r]), to_device(weights_bits[r]), poison(e, capacity, n)
+        lhs_ptrs, w_ptrs, out_ptrs = ptrs(lhs), ptrs(w), ptrs(out)
+        offs = torch.from_numpy(np.ascontiguousarray(row_offsets[r], dtype=np.int64)).to(DEV)
+        src = torch.zeros((max(len(sources[r]), 1), 3), dtype=torch.int32, device=DEV)
+        src[:len(sources[r])] = torch.from_numpy(np.ascontiguousarray(sources[r], dtype=np.int32)).to(DEV)
+        p = N.Bf16GroupedGemmParams(lhs=lhs_ptrs.data_ptr(), weight_nt=w_ptrs.data_ptr(), output=out_ptrs.data_ptr(),
+                                    row_offsets=offs.data_ptr(), source=src.data_ptr(), experts=e, n=n, k=k,
+                                    expert_row_capacity=capacity, rank=r, world_size=world, topk=topk)
+        p.policy = N.GroupedGemmPolicy(num_comm_ctas=4, num_compute_ctas=128, tile_n=tile_n, mma_sm_count=mma_sm_count)
+        for q in range(world):
+            p.peer_output[q] = received[q].data_ptr()
+            p.peer_started[q] = started[q].data_ptr()
+            p.peer_done[q] = done[q].data_ptr()
+        rc, plan = api.create_bf16_grouped_gemm_a2a(p)
+        assert rc == 0, f"create_bf16_grouped_gemm_a2a -> cudaError {rc}"
+        opts = options(flags=N.SKIP_PEER_WAIT if world > 1 else 0)
+        for _ in range(launches):
+            rc = api.launch_bf16_grouped_gemm(plan, 0, opts)
+            assert rc == 0, f"launch_bf16_grouped_gemm -> cudaError {rc}"
+        check_status()
+        outputs.append(to_bits(out))
+        assert api.destroy_bf16_grouped_gemm(plan) == 0
+    for r in range(world):  # every source told every destination (and itself) that its rows are in place
+        assert (done[r][::N.READY_FLAG_STRIDE][:world] == launches).all()
+    return outputs, [to_bits(t) for t in received]
+
+
 def _aligned_scratch(nbytes):
     buf = torch.full((nbytes + 256,), 0x5A, dtype=torch.uint8, device=DEV)
     return buf, (buf.data_ptr() + 255) // 256 * 256

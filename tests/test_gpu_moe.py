@@ -141,3 +141,58 @@ def test_moe_boundary_row_counts_empty_experts_and_replay_with_new_routes(mma_sm
     lhs, out = H.moe_dispatch_fc1(world, 0, e, toks, weights, first[0], first[1], capacity, comm=comm,
                                   second_route=second, mma_sm_count=mma_sm_count)
     _check(world, 0, e, toks, weights, second[0], second[1], capacity, lhs, out)
+
+
+# ---------------------------------------------------------------------------------------------
+# combine: expert FC2 grouped GEMM -> rows scattered to the token owners
+# (world, tokens/rank, experts, topk, K, N, tile_n, mma_sm_count)
+COMBINE_CASES = [
+    (1, 96, 4, 2, 256, 512, 256, 1),
+    (2, 160, 8, 2, 512, 768, 256, 1),
+    (4, 128, 16, 4, 256, 392, 128, 1),      # N neither a tile nor a 64-column multiple
+    (2, 160, 8, 2, 512, 768, 256, 2),       # CTA pairs
+    (4, 200, 8, 3, 320, 1024, 256, 2),
+]
+
+
+@pytest.mark.parametrize("case", COMBINE_CASES)
+def test_moe_fc2_combine_matches_oracle(case):
+    # The reference's checks for this direction (benchmarks/sm103/grouped_validation.cuh:119-157): the
+    # expert's output slab within 0.002 + 0.008|b| with untouched capacity still poisoned, and every
+    # received branch row BIT-EXACT equal to the row its owner's slab holds; rows no expert routes keep
+    # the poison.
+    from tests import harness as H
+    world, tokens, experts, topk, k, n, tile_n, mma = case
+    e_local = experts // world
+    chosen = _routes(world, tokens, experts, topk, seed=23)
+    routes = [_rows_for(world, r, e_local, tokens, topk, chosen) for r in range(world)]
+    capacity = int(-(-max(int(np.diff(o).max()) for o, _ in routes) // 256) * 256)
+    lhs = [synthetic.normal_bf16((e_local, capacity, k), synthetic.GROUPED_SEED + 7 * r, 1.0) for r in range(world)]
+    weights = [synthetic.normal_bf16((e_local, n, k), synthetic.GROUPED_SEED + 500 + r, 0.02) for r in range(world)]
+    outputs, received = H.moe_fc2_combine(world, e_local, lhs, weights, [o for o, _ in routes], [s for _, s in routes],
+                                          capacity, tokens, topk, tile_n=tile_n, mma_sm_count=mma, launches=2)
+    want_received = [np.full((tokens * topk, n), POISON, dtype=np.uint16) for _ in range(world)]
+    table = O.ptr_array(want_received)
+    for r in range(world):
+        offs, src = routes[r]
+        want_out = np.full((e_local, capacity, n), POISON, dtype=np.uint16)
+        assert O.lib().fo_moe_fc2_combine(e_local, O.ptr(offs.astype(np.int32)), O.ptr(np.ascontiguousarray(src, dtype=np.int32)),
+                                          O.ptr(lhs[r]), O.ptr(weights[r]), n, k, capacity, topk, O.ptr(want_out), table) == 0
+        got = outputs[r].reshape(e_local, capacity, n)
+        for ex in range(e_local):
+            rows = int(offs[ex + 1] - offs[ex])
+            ok, worst, bad = O.within_tolerance(got[ex, :rows], want_out[ex, :rows], 0.002, 0.008)
+            assert ok, f"rank {r} expert {ex}: {bad} elements outside 0.002+0.008|b| (max abs err {worst})"
+            assert (got[ex, rows:] == POISON).all(), f"rank {r} expert {ex}: rows past M_e were written"
+            # the scattered rows are the slab's rows, bit for bit
+            for row in range(rows):
+                rank, token, slot = (int(v) for v in src[int(offs[ex]) + row])
+                assert np.array_equal(received[rank].reshape(tokens * topk, n)[token * topk + slot], got[ex, row]), \
+                    f"branch row of rank {rank} token {token} slot {slot} differs from its owner's slab"
+    for r in range(world):
+        got = received[r].reshape(tokens * topk, n)
+        routed = (want_received[r] != POISON).any(axis=1)
+        assert (got[~routed] == POISON).all(), "a branch row nobody routes was written"
+        ok, worst, bad = O.within_tolerance(got[routed], want_received[r][routed], 0.002, 0.008)
+        assert ok, f"received rows of rank {r}: {bad} elements outside tolerance (max abs err {worst})"
+        assert routed.all(), "top-k routing covers every (token, slot)"

@@ -407,6 +407,20 @@ def run_c4(ctx: Context):
         full.data.projection.epoch = epoch[0]
         return api.launch_qkv_backward_mxfp8(full, stream)
 
+    # the two HBM-bound quantiser kernels of the weight phase, alone (measured first, before the long GEMM
+    # sequences heat the part): 2 B read + 1.03 B written per element
+    probe = ctx.gen((m, width), 7, 0.01)
+    qa = torch.empty((width, m), dtype=U8, device=dev)
+    qas = torch.empty(api.mxfp8_scale_bytes(width, m), dtype=U8, device=dev)
+    t_ms = ctx.median_ms(lambda: api.quantize_mxfp8_transposed(probe.data_ptr(), width, m, width, qa.data_ptr(),
+                                                               qas.data_ptr(), stream))
+    r_ms = ctx.median_ms(lambda: api.quantize_mxfp8(probe.data_ptr(), width, m, width, qa.data_ptr(), qas.data_ptr(), stream))
+    quant_bytes = m * width * (2 + 1 + 1 / 32)
+    quantisers = {"name": "c4 K32 quantisers alone (staging [M, 10240])", "bound": "hbm", "bytes_per_launch": quant_bytes,
+                  "transposed": {"ms": t_ms, "gbps": quant_bytes / (t_ms * 1e-3) / 1e9},
+                  "row_wise": {"ms": r_ms, "gbps": quant_bytes / (r_ms * 1e-3) / 1e9}}
+    del qa, qas, probe
+    torch.cuda.empty_cache()
     flops = 2.0 * m * hid * width
     pull_bytes = m * width * (3.0 + 1.0 / 32) * (cp - 1) / cp  # E4M3 + scales + BF16 masters
     pure_d, cublas_d, keep_d = _pure_mxfp8(ctx, m, hid, width)
@@ -437,17 +451,6 @@ def run_c4(ctx: Context):
     full_row["pure"]["what"] = "this library's two pure block-scaled GEMMs (dX and dW shapes) back to back in one sample"
     del keep_d, pure_d, cublas_d, keep_w, pure_w, cublas_w
     torch.cuda.empty_cache()
-    # the two HBM-bound quantiser kernels of the weight phase, alone: 2 B read + 1.03 B written per element
-    qa = torch.empty((width, m), dtype=U8, device=dev)
-    qas = torch.empty(api.mxfp8_scale_bytes(width, m), dtype=U8, device=dev)
-    t_ms = ctx.median_ms(lambda: api.quantize_mxfp8_transposed(staging.data_ptr(), width, m, width, qa.data_ptr(),
-                                                               qas.data_ptr(), stream))
-    r_ms = ctx.median_ms(lambda: api.quantize_mxfp8(staging.data_ptr(), width, m, width, qa.data_ptr(), qas.data_ptr(), stream))
-    quant_bytes = m * width * (2 + 1 + 1 / 32)
-    quantisers = {"name": "c4 K32 quantisers alone (staging [M, 10240])", "bound": "hbm", "bytes_per_launch": quant_bytes,
-                  "transposed": {"ms": t_ms, "gbps": quant_bytes / (t_ms * 1e-3) / 1e9},
-                  "row_wise": {"ms": r_ms, "gbps": quant_bytes / (r_ms * 1e-3) / 1e9}}
-    del qa, qas
     if ctx.validate:
         from tests import fullsize as F
         ctx.barrier()
@@ -553,7 +556,52 @@ def run_c5(ctx: Context):
         ctx.barrier()
     ctx.barrier()
     api.destroy_bf16_grouped_gemm(plan)
-    return [rec]
+    del lhs, eo, w
+    torch.cuda.empty_cache()
+
+    # ---- the way back: expert FC2 (intermediate 2048 -> hidden 7168) whose epilogue scatters every branch
+    # row to the rank that owns the token (same routes; no weighting or top-k reduction in the operator)
+    inter = 2048
+    csym = ctx.world.allocate({"c5_received": tokens * topk * hid * 2, "c5_started2": cp * 128, "c5_done2": cp * 128})
+    received = csym["c5_received"].view(BF16).view(tokens * topk, hid)
+    act = ctx.gen((e_local, cap, inter), ctx.seed + 9, 1.0)
+    w2 = ctx.gen((e_local, hid, inter), 2000 + rank, 0.02)
+    out2 = torch.empty((e_local, cap, hid), dtype=BF16, device=dev)
+    ap_, w2p, o2p = ptrs(act), ptrs(w2), ptrs(out2)
+    cpar = N.Bf16GroupedGemmParams(lhs=ap_.data_ptr(), weight_nt=w2p.data_ptr(), output=o2p.data_ptr(),
+                                   row_offsets=offs_d.data_ptr(), source=src_d.data_ptr(), experts=e_local, n=hid, k=inter,
+                                   expert_row_capacity=cap, rank=rank, world_size=cp, topk=topk)
+    cpar.policy = N.GroupedGemmPolicy(num_comm_ctas=2, num_compute_ctas=146, tile_n=256, mma_sm_count=2)
+    for r in range(cp):
+        cpar.peer_output[r] = csym["c5_received"].peer_ptrs[r]
+        cpar.peer_started[r] = csym["c5_started2"].peer_ptrs[r]
+        cpar.peer_done[r] = csym["c5_done2"].peer_ptrs[r]
+    rc, cplan = api.create_bf16_grouped_gemm_a2a(cpar)
+    assert rc == 0, rc
+    pure2, keep2 = _pure_bf16(ctx, pure_rows, hid, inter)
+    crec = ctx.row(f"c5 MoE FC2+combine (EP{cp}, K 2048 -> N 7168, {busiest} rows on the busiest rank)",
+                   lambda: api.launch_bf16_grouped_gemm(cplan, stream), 2.0 * busiest * hid * inter, pure=pure2,
+                   nvlink_bytes=2.0 * busiest * hid * (cp - 1) / cp, nvlink_dir="out",
+                   extra={"busiest_rank_rows": busiest, "mean_rank_rows": mean_rows,
+                          "policy": {"mma_sm_count": 2, "tile_n": 256, "note": "every CTA computes; the epilogue scatters"}})
+    crec["pflops_per_gpu_mean_rank"] = 2.0 * mean_rows * hid * inter / crec["ms"] / 1e12
+    del keep2, pure2
+    if ctx.validate:
+        from tests import fullsize as F
+        ctx.barrier()
+        F.poison(out2, received)
+        ctx.barrier()
+        assert api.launch_bf16_grouped_gemm(cplan, stream) == 0
+        torch.cuda.synchronize()  # no host barrier: the kernel ends when every owner has written into this rank
+        ctx.check_status("c5 combine validation")
+        check = F.check_moe_fc2_combine(cp, rank, act, w2, out2, received, offs, src[:total], chosen, e_local, topk)
+        crec["validated"] = _merge(ctx, check)
+        crec["validated"]["sample"] = ("1024 branch rows per rank bit-exact against the owner's slab row; FC2 of ~10 rows per "
+                                       "expert vs the oracle; no branch row left unwritten")
+        ctx.barrier()
+    ctx.barrier()
+    api.destroy_bf16_grouped_gemm(cplan)
+    return [rec, crec]
 
 
 RUNNERS = {"bwd": run_bwd, "c3": run_c3, "c4": run_c4, "c5": run_c5}

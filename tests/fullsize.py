@@ -442,3 +442,52 @@ def check_moe_dispatch_fc1(world, tokens, lhs, out, weights, row_offsets, source
     return {"gemm": gemm, "route_bitexact": mismatches == 0, "route_mismatches": mismatches, "route_elements": elements,
             "rows": int(sum(c["elements"] for c in checks) // max(1, weights.shape[1])),
             "unwritten_local": unwritten_rows, "unwritten_routed": 0}
+
+
+def check_moe_fc2_combine(world, rank, lhs, weights, out, received, row_offsets, sources, chosen, experts_local, topk,
+                          sample=1024, per_expert=8, tolerance=(0.002, 0.008)) -> dict:
+    """lhs [E, capacity, K], weights [E, N, K], out [E, capacity, N] of this rank; received =
+    this rank's [tokens * topk, N] branch rows as the owners wrote them; row_offsets / sources =
+    this rank's routes, chosen[r] = rank r's [tokens, topk] expert table (every rank holds all).
+    A seeded sample of (token, slot) branches per rank is compared BIT-EXACT with the row the
+    owner's slab holds (the owners send those rows); FC2 is recomputed by the oracle for a few rows
+    per expert; no branch row may still hold the poison."""
+    experts, n, k = weights.shape
+    tokens = chosen[0].shape[0]
+    rng = np.random.default_rng(4321)
+    picks = np.unique(np.concatenate([[0, tokens * topk - 1], rng.integers(0, tokens * topk, sample)]))
+    picks = np.resize(picks, sample).astype(np.int64)            # the same branches on every rank, fixed count
+    token, slot = picks // topk, picks % topk
+    # as an owner: where each routed branch sits in this rank's slabs
+    row_of = np.full((world, tokens, topk), -1, dtype=np.int64)
+    if len(sources):
+        row_of[sources[:, 0], sources[:, 1], sources[:, 2]] = np.arange(len(sources))
+    offsets = np.asarray(row_offsets, dtype=np.int64)
+    send = torch.zeros((world, sample, n), dtype=out.dtype, device=out.device)
+    for dest in range(world):
+        rows = row_of[dest, token, slot]
+        mine = rows >= 0
+        if mine.any():
+            expert = np.searchsorted(offsets, rows[mine], side="right") - 1
+            local = rows[mine] - offsets[expert]
+            send[dest, index_tensor(np.nonzero(mine)[0], out)] = out[index_tensor(expert, out), index_tensor(local, out)]
+    recv = exchange_rows(send)                                           # [owner, sample, N]
+    owner = (chosen[rank][token, slot] // experts_local).astype(np.int64)
+    expected = recv[index_tensor(owner, out), index_tensor(np.arange(sample), out)]
+    got = received.view(-1, n)[index_tensor(picks, received)]
+    mismatches = int((got.view(torch.int16) != expected.view(torch.int16)).sum())
+    checks = []
+    for e in range(experts):
+        count = int(offsets[e + 1] - offsets[e])
+        if count == 0:
+            continue
+        picked = sorted({0, count - 1} | {int(v) for v in rng.integers(0, count, per_expert)})
+        pt = index_tensor(np.array(picked), lhs)
+        want = O.gemm_bf16(0, bits(lhs[e][pt]), bits(weights[e]), len(picked), n, k)
+        checks.append(compare(bits(out[e][pt]), want, *tolerance))
+    gemm = {"ok": all(c["ok"] for c in checks), "max_abs_err": max((c["max_abs_err"] for c in checks), default=0.0),
+            "bad": sum(c["bad"] for c in checks), "elements": sum(c["elements"] for c in checks),
+            "tolerance": checks[0]["tolerance"] if checks else ""}
+    return {"gemm": gemm, "route_bitexact": mismatches == 0, "route_mismatches": mismatches,
+            "route_elements": int(got.numel()), "rows": int(sample), "unwritten_local": 0,
+            "unwritten_routed": unwritten(received)}

@@ -183,6 +183,62 @@ def main():
         assert api.destroy_bf16_grouped_gemm(plan) == 0
         dist.barrier()
 
+    # ---- MoE combine: expert FC2 whose epilogue scatters branch rows into the owners' buffers ------
+    routes_all = []
+    for r in range(world):
+        o = np.empty(experts_local + 1, dtype=np.int32)
+        tot = O.lib().fo_moe_build_rows(world, r, experts_local, tokens, topk, O.ptr_array(chosen), O.ptr(o), None)
+        sr = np.empty((max(tot, 1), 3), dtype=np.int32)
+        O.lib().fo_moe_build_rows(world, r, experts_local, tokens, topk, O.ptr_array(chosen), O.ptr(o), O.ptr(sr))
+        routes_all.append((o, sr[:tot]))
+    ck, cn = 256, 512
+    act_all = [synthetic.normal_bf16((experts_local, cap, ck), synthetic.GROUPED_SEED + 77 + r, 1.0) for r in range(world)]
+    w2_all = [synthetic.normal_bf16((experts_local, cn, ck), synthetic.GROUPED_SEED + 2000 + r, 0.02) for r in range(world)]
+    want_recv = [np.full((tokens * topk, cn), 0x7f7f, dtype=np.uint16) for _ in range(world)]
+    want_slab = None
+    for r in range(world):  # every rank simulates all ranks: the owners' rows land in its own expectation
+        slab = np.full((experts_local, cap, cn), 0x7f7f, dtype=np.uint16)
+        assert O.lib().fo_moe_fc2_combine(experts_local, O.ptr(routes_all[r][0]), O.ptr(np.ascontiguousarray(routes_all[r][1])),
+                                          O.ptr(act_all[r]), O.ptr(w2_all[r]), cn, ck, cap, topk, O.ptr(slab),
+                                          O.ptr_array(want_recv)) == 0
+        if r == rank:
+            want_slab = slab
+    csym = w.allocate({"comb_recv": tokens * topk * cn * 2, "comb_started": world * N.READY_FLAG_STRIDE * 4,
+                       "comb_done": world * N.READY_FLAG_STRIDE * 4})
+    act_d, w2_d = to_dev(act_all[rank]), to_dev(w2_all[rank])
+    slab_d = torch.full((experts_local, cap, cn), 0x7f7f, dtype=torch.int16, device=dev).view(torch.bfloat16)
+    ap, w2p, sp = ptrs(act_d), ptrs(w2_d), ptrs(slab_d)
+    cp_ = N.Bf16GroupedGemmParams(lhs=ap.data_ptr(), weight_nt=w2p.data_ptr(), output=sp.data_ptr(),
+                                  row_offsets=offs_d.data_ptr(), source=src_d.data_ptr(), experts=experts_local,
+                                  n=cn, k=ck, expert_row_capacity=cap, rank=rank, world_size=world, topk=topk)
+    for r in range(world):
+        cp_.peer_output[r] = csym["comb_recv"].peer_ptrs[r]
+        cp_.peer_started[r] = csym["comb_started"].peer_ptrs[r]
+        cp_.peer_done[r] = csym["comb_done"].peer_ptrs[r]
+    for mma_sm_count in (1, 2):
+        cp_.policy = N.GroupedGemmPolicy(num_comm_ctas=2, num_compute_ctas=128, tile_n=256, mma_sm_count=mma_sm_count)
+        csym["comb_recv"].view(torch.int16).fill_(0x7f7f)
+        slab_d.view(torch.int16).fill_(0x7f7f)
+        rc, cplan = api.create_bf16_grouped_gemm_a2a(cp_)
+        assert rc == 0, rc
+        torch.cuda.synchronize()
+        dist.barrier()
+        assert api.launch_bf16_grouped_gemm(cplan, 0, opts) == 0
+        torch.cuda.synchronize()  # the kernel ends only when every owner has written into this rank
+        status = api.read_status()
+        assert status[0] == 0, status[:8]
+        got_slab = bits(slab_d)
+        for e in range(experts_local):
+            cnt = int(offs[e + 1] - offs[e])
+            ok, worst, bad = O.within_tolerance(got_slab[e, :cnt], want_slab[e, :cnt], 0.002, 0.008)
+            assert ok, ("combine slab", mma_sm_count, e, worst, bad)
+            assert (got_slab[e, cnt:] == 0x7f7f).all()
+        ok, worst, bad = O.within_tolerance(bits(csym["comb_recv"].view(torch.bfloat16)).reshape(tokens * topk, cn),
+                                            want_recv[rank], 0.002, 0.008)
+        assert ok, ("combine received", mma_sm_count, worst, bad)
+        assert api.destroy_bf16_grouped_gemm(cplan) == 0
+        dist.barrier()
+
     # ---- MXFP8 output projection: bytes and scale bytes pulled from every peer ------------------
     to_dev_u8 = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(dev)
     shard = ko // world

@@ -173,6 +173,32 @@ WORKER = textwrap.dedent('''
     check = F.check_moe_dispatch_fc1(world, as_t(toks[rank]), as_t(lhs_m), as_t(eo_m), as_t(ew), offs, src, per_expert=4)
     assert (not check["route_bitexact"]) == (offs[1] > offs[0]), check
 
+    # ---- MoE FC2 + combine: every rank simulates all ranks, then checks its own -----------------
+    routes = []
+    for r in range(world):
+        o = np.empty(e_local + 1, np.int32)
+        tot = O.lib().fo_moe_build_rows(world, r, e_local, t, topk, O.ptr_array(chosen), O.ptr(o), None)
+        sr = np.empty((max(tot, 1), 3), np.int32)
+        O.lib().fo_moe_build_rows(world, r, e_local, t, topk, O.ptr_array(chosen), O.ptr(o), O.ptr(sr))
+        routes.append((o, sr[:tot]))
+    lhs_c = [synthetic.normal_bf16((e_local, cap, mk), 1000 + r, 1.0) for r in range(world)]
+    w_c = [synthetic.normal_bf16((e_local, mn, mk), 1100 + r, 0.02) for r in range(world)]
+    recv_c = [np.full((t * topk, mn), 0xFFFF, np.uint16) for _ in range(world)]
+    outs_c = []
+    for r in range(world):
+        out_r = np.full((e_local, cap, mn), 0xFFFF, np.uint16)
+        assert O.lib().fo_moe_fc2_combine(e_local, O.ptr(routes[r][0]), O.ptr(np.ascontiguousarray(routes[r][1])), O.ptr(lhs_c[r]),
+                                          O.ptr(w_c[r]), mn, mk, cap, topk, O.ptr(out_r), O.ptr_array(recv_c)) == 0
+        outs_c.append(out_r)
+    check = F.check_moe_fc2_combine(world, rank, as_t(lhs_c[rank]), as_t(w_c[rank]), as_t(outs_c[rank]), as_t(recv_c[rank]),
+                                    routes[rank][0], routes[rank][1], chosen, e_local, topk, sample=64, per_expert=4)
+    assert check["gemm"]["ok"] and check["route_bitexact"] and check["unwritten_routed"] == 0, check
+    broken = recv_c[rank].copy()
+    broken[0, 0] ^= 1          # branch (token 0, slot 0) is always in the sample
+    check = F.check_moe_fc2_combine(world, rank, as_t(lhs_c[rank]), as_t(w_c[rank]), as_t(outs_c[rank]), as_t(broken),
+                                    routes[rank][0], routes[rank][1], chosen, e_local, topk, sample=64, per_expert=4)
+    assert not check["route_bitexact"], check
+
     dist.barrier()
     dist.destroy_process_group()
     print("FULLSIZE PASS", rank)

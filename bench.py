@@ -713,14 +713,16 @@ def run_gpu_arm(args):
             "kernels": {
                 "qkv_gemm_a2a": {"ms": qkv_ms, "pflops_per_gpu": QKV_FLOPS / (qkv_ms * 1e-3) / 1e15,
                                  "route": args.qkv_route,
-                                 "comm_ctas": args.qkv_comm if args.qkv_route == "comm" else 0},
+                                 "comm_ctas": ((args.qkv_comm or "auto") if args.qkv_route == "comm"
+                                               else "none: every CTA computes, the epilogue pushes")},
                 "a2a_oproj_gemm": {"ms": oproj_ms,
                                    "pflops_per_gpu": (FLOPS_PER_RANK - QKV_FLOPS) / (oproj_ms * 1e-3) / 1e15,
-                                   "comm_ctas": args.oproj_comm,
-                                   # the library's default: one warp of every compute CTA pulls (no SM
-                                   # given up); FUSE_B200_EMBEDDED_PULL=0 selects communication CTAs
-                                   "pull": ("embedded copy warps" if os.environ.get("FUSE_B200_EMBEDDED_PULL", "1") != "0"
-                                            else "communication CTAs")},
+                                   "comm_ctas": args.oproj_comm or "auto",
+                                   # Auto: the host planner decides (on B200: one warp of every compute CTA
+                                   # pulls, no SM given up); an explicit budget means communication CTAs
+                                   "pull": ("planner's choice" if args.oproj_comm == 0 and "FUSE_B200_EMBEDDED_PULL" not in os.environ
+                                            else ("communication CTAs" if os.environ.get("FUSE_B200_EMBEDDED_PULL", "0") == "0"
+                                                  else "embedded copy warps"))},
             },
             "roofline": {"bound": "tensor", "achieved": achieved, "peak": burst, "unit": "TFLOP/s",
                          "frac": achieved / burst,
@@ -790,8 +792,8 @@ def main():
     parser.add_argument("--steps", type=int, default=50)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="fuse_b200", choices=["fuse_b200", "reference"])
-    parser.add_argument("--qkv-comm", type=int, default=16)
-    parser.add_argument("--oproj-comm", type=int, default=20)
+    parser.add_argument("--qkv-comm", type=int, default=0, help="communication CTAs of the QKV operator (0: Auto)")
+    parser.add_argument("--oproj-comm", type=int, default=0, help="communication CTAs of the OProj operator (0: Auto)")
     parser.add_argument("--swizzle", type=int, default=8)
     parser.add_argument("--qkv-route", default="direct", choices=["comm", "direct"],
                         help="QKV routing from communication CTAs or from the GEMM epilogue")

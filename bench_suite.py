@@ -41,7 +41,7 @@ BF16, U8, I32 = torch.bfloat16, torch.uint8, torch.int32
 
 class Context:
     def __init__(self, rank, world_size, local_rank, world: World, samples=5, warmup=3, validate=True,
-                 validate_rows=256, scale=1.0, comm=16):
+                 validate_rows=256, scale=1.0, comm=0):
         self.rank, self.world_size, self.local_rank, self.world = rank, world_size, local_rank, world
         self.samples, self.warmup, self.validate, self.validate_rows = samples, warmup, validate, validate_rows
         self.scale, self.comm = scale, comm
@@ -523,7 +523,7 @@ def run_c5(ctx: Context):
     for r in range(cp):
         per_rank += np.bincount((chosen[r] // e_local).ravel(), minlength=cp)
     busiest, mean_rows = int(per_rank.max()), float(per_rank.mean())
-    gp.policy = N.GroupedGemmPolicy(num_comm_ctas=20, num_compute_ctas=128, tile_n=256, mma_sm_count=2)
+    gp.policy = N.GroupedGemmPolicy(num_comm_ctas=ctx.comm, num_compute_ctas=148, tile_n=256, mma_sm_count=2)  # 0: Auto
     for r in range(cp):
         gp.peer_input[r] = sym["c5_tokens"].peer_ptrs[r]
         gp.peer_started[r] = sym["c5_started"].peer_ptrs[r]
@@ -536,7 +536,7 @@ def run_c5(ctx: Context):
                   lambda: api.launch_bf16_grouped_gemm(plan, stream), 2.0 * busiest * n * hid, pure=pure,
                   nvlink_bytes=2.0 * busiest * hid * (cp - 1) / cp, nvlink_dir="in",
                   extra={"busiest_rank_rows": busiest, "mean_rank_rows": mean_rows,
-                         "policy": {"num_comm_ctas": 20, "mma_sm_count": 2, "tile_n": 256}})
+                         "policy": {"num_comm_ctas": ctx.comm or "auto", "mma_sm_count": 2, "tile_n": 256}})
     rec["pure"]["what"] = (f"dense-equivalent: one [{pure_rows}, {n}, {hid}] GEMM of this library on all 148 SMs "
                            "(the busiest rank's rows against one expert-sized weight)")
     rec["pflops_per_gpu_mean_rank"] = 2.0 * mean_rows * n * hid / rec["ms"] / 1e12
@@ -627,7 +627,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--scale", type=float, default=1.0, help="scale rows per rank of c3/c4/c5")
     ap.add_argument("--only", default="", help="comma list of bwd,c3,c4,c5")
-    ap.add_argument("--comm", type=int, default=16)
+    ap.add_argument("--comm", type=int, default=0, help="communication CTAs of every operator (0: Auto, the host planner)")
     ap.add_argument("--skip-validate", action="store_true")
     ap.add_argument("--json", action="store_true", help="print the rows as one JSON line as well")
     args = ap.parse_args()

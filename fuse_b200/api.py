@@ -67,6 +67,18 @@ def recommended_a2a_lhs_gemm_comm_ctas(problem: GemmProblem, route: UlyssesRoute
     return N.lib().fuse_recommended_a2a_lhs_gemm_comm_ctas(C.byref(problem), C.byref(route))
 
 
+def plan(kind: int, flops: float, nbytes: float, tiles: int, sm_count: int = 148, group: int = 2,
+         explicit_comm_ctas: int = 0, embedded_allowed: bool = True) -> dict:
+    """The host planner's choice for one launch (fuse_b200_plan): communication CTAs or embedded copy warps."""
+    out = (C.c_double * 5)()
+    rc = N.lib().fuse_b200_plan(kind, flops, nbytes, tiles, sm_count, group, explicit_comm_ctas,
+                                1 if embedded_allowed else 0, C.byref(out))
+    if rc != 0:
+        raise ValueError(f"fuse_b200_plan -> cudaError {rc}")
+    return {"comm_ctas": int(out[0]), "embedded": bool(out[1]), "makespan_us": out[2], "compute_us": out[3],
+            "transfer_us": out[4]}
+
+
 def read_status(clear: bool = True) -> list[int]:
     """The device status record of the current device (word 0 != 0: a device wait gave up)."""
     out = (C.c_uint32 * 16)()

@@ -34,7 +34,7 @@ def sources() -> list[str]:
 
 
 def _newest_header() -> float:
-    stamps = [os.path.getmtime(os.path.join(CSRC, f)) for f in os.listdir(CSRC) if f.endswith(".cuh")]
+    stamps = [os.path.getmtime(os.path.join(CSRC, f)) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h"))]
     stamps += [os.path.getmtime(os.path.join(INCLUDE, f)) for f in os.listdir(INCLUDE)]
     return max(stamps)
 

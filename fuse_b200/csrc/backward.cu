@@ -49,7 +49,11 @@ cudaError_t qkv_backward_data(const fuse_qkv_backward_data_params& p, const fuse
   DeviceInfo info;
   cudaError_t status = check_device(&info);
   if (status != cudaSuccess) return status;
-  const int comm = p.num_comm_ctas ? p.num_comm_ctas : 16;
+  const int m = p.local_tokens, n = p.hidden, k = (p.q_heads + 2 * p.kv_heads) * p.head_dim;
+  // Auto: the planner's choice (embedded copy warps, or a communication budget); explicit: exactly that
+  const planner::Choice plan =
+      launch::plan_transfer(planner::kGradPushBf16, m, n, k, double(m) * k * 2.0, info.sm_count, p.num_comm_ctas < 0 ? 0 : p.num_comm_ctas);
+  const int comm = p.num_comm_ctas ? p.num_comm_ctas : (plan.comm_ctas ? plan.comm_ctas : fuse_recommended_qkv_backward_comm_ctas(&p));
   if (comm <= 0 || comm >= info.sm_count) return cudaErrorInvalidValue;
   if (!host::aligned16(p.grad_q) || !host::aligned16(p.grad_k) || !host::aligned16(p.grad_v) ||
       !host::aligned16(p.weight) || !host::aligned16(p.grad_input))
@@ -59,7 +63,6 @@ cudaError_t qkv_backward_data(const fuse_qkv_backward_data_params& p, const fuse
         !host::aligned4(p.peer_done_epoch[peer]))
       return cudaErrorNotSupported;
 
-  const int m = p.local_tokens, n = p.hidden, k = (p.q_heads + 2 * p.kv_heads) * p.head_dim;
   const int block_n = block_n_of(p.gemm_policy, n, options);
   Operands maps;
   if ((status = encode_operand(&maps.a, p.peer_dqkv_staging[p.rank], m, k, k, false, kBlockM)) != cudaSuccess)
@@ -118,7 +121,7 @@ cudaError_t qkv_backward_data(const fuse_qkv_backward_data_params& p, const fuse
       pf.grad.m_group = 2 * launch::wave_m_group_pairs(pf, info.sm_count);
       // no communication CTAs at all: one warp of every compute CTA pushes (FUSE_B200_EMBEDDED_PULL=0:
       // communication CTAs)
-      if (launch::embedded_pull_requested(p.world_size))
+      if (launch::embedded_copy_selected(p.num_comm_ctas, plan))
         return launch::launch_pair_kernel<kModeHeadGate, GradPushMaps, false, false, true, true>(
             maps, maps.a, maps.a, push, pf, p.gemm_tuning.max_swizzle_size ? p.gemm_tuning.max_swizzle_size : 1, info, stream,
             0.0);
@@ -141,7 +144,9 @@ cudaError_t oproj_backward_data(const fuse_oproj_backward_data_params& p,
   DeviceInfo info;
   cudaError_t status = check_device(&info);
   if (status != cudaSuccess) return status;
-  const int comm = p.num_comm_ctas ? p.num_comm_ctas : 16;
+  // (the default route is the epilogue push, which needs no communication CTA; the budget only
+  // matters when the caller asks for the communication-CTA route)
+  const int comm = p.num_comm_ctas ? p.num_comm_ctas : fuse_recommended_oproj_backward_comm_ctas(&p);
   if (comm <= 0 || comm >= info.sm_count) return cudaErrorInvalidValue;
   if (!host::aligned16(p.grad_output) || !host::aligned16(p.weight) ||
       !host::aligned16(p.local_grad_attention))
@@ -289,7 +294,21 @@ int64_t fuse_oproj_backward_ready_elements(const fuse_oproj_backward_data_params
   return int64_t(host::ceil_div(p->local_tokens, kBlockM)) * host::ceil_div(int(n), 128) *
          FUSE_READY_FLAG_STRIDE;
 }
-int32_t fuse_recommended_qkv_backward_comm_ctas(const fuse_qkv_backward_data_params*) { return 16; }
-int32_t fuse_recommended_oproj_backward_comm_ctas(const fuse_oproj_backward_data_params*) { return 16; }
+// The planner's best communication budget for the operator run with communication CTAs.
+int32_t fuse_recommended_qkv_backward_comm_ctas(const fuse_qkv_backward_data_params* p) {
+  if (p == nullptr || p->local_tokens <= 0 || p->hidden <= 0) return 0;
+  const int64_t k = (int64_t(p->q_heads) + 2 * p->kv_heads) * p->head_dim;
+  return launch::plan_transfer(planner::kGradPushBf16, p->local_tokens, p->hidden, k, double(p->local_tokens) * k * 2.0, 148, 0,
+                               false)
+      .comm_ctas;
+}
+int32_t fuse_recommended_oproj_backward_comm_ctas(const fuse_oproj_backward_data_params* p) {
+  if (p == nullptr || p->local_tokens <= 0 || p->hidden <= 0) return 0;
+  const int64_t n = int64_t(p->q_heads) * p->head_dim;
+  const int64_t tiles = ((int64_t(p->local_tokens) + 127) / 128) * ((n + 255) / 256);
+  return planner::choose(planner::kQkvPushBf16, 2.0 * double(p->local_tokens) * n * p->hidden,
+                         double(p->local_tokens) * n * 2.0, tiles, 148, 1, 0, false)
+      .comm_ctas;
+}
 
 }  // extern "C"

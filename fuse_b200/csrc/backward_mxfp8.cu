@@ -110,7 +110,7 @@ cudaError_t qkv_data(const fuse_mxfp8_qkv_backward_data_params& mp, const fuse_b
                      cudaStream_t stream) {
   const fuse_qkv_backward_data_params& p = mp.projection;
   if (!shape_supported(p) || p.kv_heads <= 0 || p.q_heads % p.kv_heads != 0 || p.kv_heads % p.world_size != 0 ||
-      p.num_comm_ctas <= 0)
+      p.num_comm_ctas < 0)
     return cudaErrorInvalidValue;
   const int seq_local = p.local_tokens / p.batch;
   const int row_block = p.causal_load_balanced ? seq_local / 2 : seq_local;
@@ -120,6 +120,10 @@ cudaError_t qkv_data(const fuse_mxfp8_qkv_backward_data_params& mp, const fuse_b
   cudaError_t status = check_device(&info);
   if (status != cudaSuccess) return status;
   if (p.num_comm_ctas >= info.sm_count) return cudaErrorInvalidValue;
+  // Auto: the planner's choice (embedded copy warps, or a communication budget); explicit: exactly that
+  const planner::Choice plan = launch::plan_transfer(planner::kGradPullMx, m, n, k, double(m) * k * (3.0 + 1.0 / 32),
+                                                     info.sm_count, p.num_comm_ctas);
+  const int num_comm_ctas = p.num_comm_ctas ? p.num_comm_ctas : (plan.comm_ctas ? plan.comm_ctas : 16);
   uint8_t* cursor = static_cast<uint8_t*>(mp.workspace);
   size_t need = 0;
   const Quantised wq = carve(cursor, need, n, k), lhs = carve(cursor, need, m, k);
@@ -143,7 +147,7 @@ cudaError_t qkv_data(const fuse_mxfp8_qkv_backward_data_params& mp, const fuse_b
   if ((status = encode_operand_u8(&maps.a, lhs.data, m, k, k, kBlockM)) != cudaSuccess) return status;
   if ((status = encode_operand_u8(&maps.b, wq.data, n, k, k, block_n)) != cudaSuccess) return status;
   FusedParams f{};
-  launch::fill_core(&f, m, n, k, block_n, p.num_comm_ctas, p.alpha, 0.0f, p.grad_input, n,
+  launch::fill_core(&f, m, n, k, block_n, num_comm_ctas, p.alpha, 0.0f, p.grad_input, n,
                     p.gemm_tuning.along_m ? FUSE_RASTER_ALONG_M : FUSE_RASTER_ALONG_N,
                     p.gemm_tuning.max_swizzle_size ? p.gemm_tuning.max_swizzle_size : 1);
   f.sfa = lhs.scales;
@@ -195,7 +199,7 @@ cudaError_t qkv_data(const fuse_mxfp8_qkv_backward_data_params& mp, const fuse_b
                   encode_copy_map(&pull.masters[peer][s], f.grad.peer_master[peer][s], 2, rows_global, plane_width, 64, 128) ==
                       cudaSuccess;
       }
-    if (encoded && block_n == 256 && p.num_comm_ctas % 2 == 0 && info.sm_count % 2 == 0 &&
+    if (encoded && block_n == 256 && num_comm_ctas % 2 == 0 && info.sm_count % 2 == 0 &&
         !vector_epilogue_requested(options) && launch::pair_tiles_requested()) {
       // CTA pairs: whole pairs of communication CTAs, 256-row tiles
       Operands pair_maps = maps;
@@ -206,7 +210,7 @@ cudaError_t qkv_data(const fuse_mxfp8_qkv_backward_data_params& mp, const fuse_b
           launch::encode_scale_atoms(&sfa_map, f.sfa, m, k) == cudaSuccess &&
           launch::encode_scale_atoms(&sfb_map, f.sfb, n, k) == cudaSuccess)
       {
-        if (launch::embedded_pull_requested(p.world_size))  // one warp of every compute CTA pulls
+        if (launch::embedded_copy_selected(p.num_comm_ctas, plan))  // one warp of every compute CTA pulls
           return launch::launch_pair_kernel<kModeGradPull, GradPullMaps, true, false, false, true>(
               pair_maps, sfa_map, sfb_map, pull, pf, p.gemm_tuning.max_swizzle_size ? p.gemm_tuning.max_swizzle_size : 1,
               info, stream, 0.0);
@@ -227,7 +231,8 @@ cudaError_t qkv_data(const fuse_mxfp8_qkv_backward_data_params& mp, const fuse_b
 cudaError_t oproj_data(const fuse_mxfp8_oproj_backward_data_params& mp, const fuse_b200_options* options,
                        cudaStream_t stream) {
   const fuse_oproj_backward_data_params& p = mp.projection;
-  if (!shape_supported(p) || p.num_comm_ctas <= 0) return cudaErrorInvalidValue;
+  // (the route is the epilogue push: no communication CTA runs, whatever the budget says)
+  if (!shape_supported(p) || p.num_comm_ctas < 0) return cudaErrorInvalidValue;
   const int m = p.local_tokens, n = p.q_heads * p.head_dim, k = p.hidden;
   if (k % 128 != 0) return cudaErrorNotSupported;
   DeviceInfo info;

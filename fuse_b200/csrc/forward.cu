@@ -101,14 +101,22 @@ cudaError_t check_qkv_route(const fuse_gemm_a2a_params& p) {
 
 cudaError_t qkv_forward(const fuse_gemm_a2a_params& p, const fuse_b200_options* options,
                         cudaStream_t stream) {
-  if (!supported_problem(p.gemm) || !std::isfinite(p.alpha) || p.epoch == 0 || p.num_comm_ctas <= 0)
+  // The reference's entry point rejects num_comm_ctas <= 0 (detail/launch.cuh:508-511) and so does the
+  // entry point of the same name here; Auto (0) is accepted through the _ex entry point.
+  if (!supported_problem(p.gemm) || !std::isfinite(p.alpha) || p.epoch == 0 || p.num_comm_ctas < 0 ||
+      (p.num_comm_ctas == 0 && options == nullptr))
     return cudaErrorInvalidValue;
   DeviceInfo info;
   cudaError_t status = check_device(&info);
   if (status != cudaSuccess) return status;
   if (p.num_comm_ctas >= info.sm_count) return cudaErrorInvalidValue;
   if ((status = check_qkv_route(p)) != cudaSuccess) return status;
-  const bool direct = qkv_direct_push(options);
+  // Auto (num_comm_ctas == 0): the epilogue push, which needs no communication CTA at all, unless
+  // the caller asked for the communication-CTA route; that route then gets the planned budget.
+  const bool auto_plan = p.num_comm_ctas == 0;
+  const bool direct = qkv_direct_push(options) ||
+                      (auto_plan && !(options != nullptr && (options->flags & FUSE_B200_QKV_ROUTE_COMM_CTAS)));
+  const int num_comm_ctas = auto_plan ? fuse_recommended_gemm_a2a_comm_ctas(&p.gemm, &p.route) : p.num_comm_ctas;
 
   const int block_n = choose_block_n(p.gemm, options);
   Operands maps;
@@ -117,7 +125,7 @@ cudaError_t qkv_forward(const fuse_gemm_a2a_params& p, const fuse_b200_options* 
   if (status != cudaSuccess) return status;
 
   FusedParams k{};
-  fill_core(&k, p.gemm, block_n, direct ? 0 : p.num_comm_ctas, p.alpha, p.local_output,
+  fill_core(&k, p.gemm, block_n, direct ? 0 : num_comm_ctas, p.alpha, p.local_output,
             FUSE_RASTER_ALONG_M);
   k.ready = p.ready;
   k.flags = options ? options->flags : 0u;
@@ -184,14 +192,16 @@ cudaError_t oproj_forward(const fuse_a2a_gemm_params& p, const fuse_b200_options
                           cudaStream_t stream) {
   if (!supported_problem(p.gemm) || !std::isfinite(p.alpha) || p.epoch == 0 || p.lhs_policy != 0)
     return cudaErrorInvalidValue;
-  int num_comm_ctas = p.num_comm_ctas;
-  if (num_comm_ctas == 0)
-    num_comm_ctas = fuse_recommended_a2a_lhs_gemm_comm_ctas(&p.gemm, &p.route);
-  if (num_comm_ctas < 0) return cudaErrorInvalidValue;
-  if (num_comm_ctas == 0) return cudaErrorNotSupported;
+  if (p.num_comm_ctas < 0) return cudaErrorInvalidValue;
   DeviceInfo info;
   cudaError_t status = check_device(&info);
   if (status != cudaSuccess) return status;
+  // Auto: the planner's choice (embedded copy warps, or a communication budget); explicit: exactly that
+  const planner::Choice plan = plan_transfer(planner::kLhsPullBf16, p.gemm.m, p.gemm.n, p.gemm.k,
+                                             double(p.gemm.m) * p.gemm.k * 2.0, info.sm_count, p.num_comm_ctas);
+  const int num_comm_ctas = p.num_comm_ctas ? p.num_comm_ctas
+                                            : (plan.comm_ctas ? plan.comm_ctas
+                                                              : fuse_recommended_a2a_lhs_gemm_comm_ctas(&p.gemm, &p.route));
   if (num_comm_ctas >= info.sm_count) return cudaErrorInvalidValue;
   if ((status = check_lhs_route(p)) != cudaSuccess) return status;
 
@@ -234,7 +244,7 @@ cudaError_t oproj_forward(const fuse_a2a_gemm_params& p, const fuse_b200_options
       if (block_n == 256 && num_comm_ctas % 2 == 0 && info.sm_count % 2 == 0 && pair_tiles_requested()) {
         FusedParams pk = k;
         pk.lhs.m_group = 2 * wave_m_group_pairs(pk, info.sm_count);
-        if (launch::embedded_pull_requested(p.route.world_size)) {
+        if (launch::embedded_copy_selected(p.num_comm_ctas, plan)) {
           Operands pair_maps;
           if (encode_operand(&pair_maps.a, p.input_staging, p.gemm.m, p.gemm.k, lda, false, kBlockM) == cudaSuccess &&
               encode_operand(&pair_maps.b, p.rhs_nt, p.gemm.n, p.gemm.k, packed_or(p.gemm.stride_b.row, p.gemm.k), false,
@@ -348,25 +358,45 @@ int64_t fuse_a2a_lhs_gemm_ready_elements(const fuse_gemm_problem* problem,
          FUSE_READY_FLAG_STRIDE;
 }
 
+// The communication budgets Auto uses when an operator runs with communication CTAs (the planner's
+// best budget with the embedded copy warps left out; 148 SMs assumed when no device is current).
 int32_t fuse_recommended_gemm_a2a_comm_ctas(const fuse_gemm_problem* problem,
                                             const fuse_ulysses_route* route) {
-  (void)problem;
+  if (problem == nullptr || problem->m <= 0 || problem->n <= 0 || problem->k <= 0) return 0;
   (void)route;
-  return 0;  // no calibrated plan yet: the caller passes an explicit budget
+  const int64_t tiles = ((int64_t(problem->m) + 127) / 128) * ((int64_t(problem->n) + 255) / 256);
+  return fuse_b200::planner::choose(fuse_b200::planner::kQkvPushBf16,
+                                    2.0 * double(problem->m) * double(problem->n) * double(problem->k),
+                                    double(problem->m) * double(problem->n) * 2.0, tiles, 148, 1, 0, false)
+      .comm_ctas;
 }
 
-// B200 calibration of the lhs pull (one communication CTA moves 30-40 GB/s through its copy
-// pipeline while the GEMM runs; measured at the 8B and 70B projection shapes): enough CTAs to
-// finish the pull in about half of the GEMM's time, an even number so that they form pairs.
 int32_t fuse_recommended_a2a_lhs_gemm_comm_ctas(const fuse_gemm_problem* problem,
                                                 const fuse_ulysses_route* route) {
   if (problem == nullptr || problem->m <= 0 || problem->n <= 0 || problem->k <= 0) return 0;
   (void)route;
-  const double pull_bytes = double(problem->m) * double(problem->k) * 2.0;
-  const double gemm_seconds = 2.0 * double(problem->m) * double(problem->n) * double(problem->k) / 1.5e15;
-  int ctas = int(pull_bytes / (35.0e9 * 0.5 * gemm_seconds) + 0.5);
-  ctas += ctas & 1;
-  return ctas < 4 ? 4 : (ctas > 32 ? 32 : ctas);
+  return fuse_b200::launch::plan_transfer(fuse_b200::planner::kLhsPullBf16, problem->m, problem->n, problem->k,
+                                          double(problem->m) * double(problem->k) * 2.0, 148, 0, false)
+      .comm_ctas;
+}
+
+// The planner itself, for callers and tests: kind as in planner.cuh (0 BF16 lhs pull, 1 MXFP8 lhs
+// pull, 2 BF16 gradient push, 3 MXFP8 gradient pull, 4 / 5 QKV push from communication CTAs BF16 /
+// MXFP8, 6 MoE dispatch).  out = {comm_ctas, embedded, makespan_us, compute_us, transfer_us}.
+int fuse_b200_plan(int32_t kind, double flops, double bytes, int64_t tiles, int32_t sm_count, int32_t group,
+                   int32_t explicit_comm_ctas, int32_t embedded_allowed, double out[5]) {
+  if (kind < 0 || kind >= fuse_b200::planner::kKinds || !(flops > 0.0) || !(bytes >= 0.0) || tiles <= 0 ||
+      sm_count <= 0 || (group != 1 && group != 2) || explicit_comm_ctas < 0 || explicit_comm_ctas >= sm_count ||
+      out == nullptr)
+    return int(cudaErrorInvalidValue);
+  const fuse_b200::planner::Choice c = fuse_b200::planner::choose(
+      fuse_b200::planner::Kind(kind), flops, bytes, tiles, sm_count, group, explicit_comm_ctas, embedded_allowed != 0);
+  out[0] = c.comm_ctas;
+  out[1] = c.embedded;
+  out[2] = c.makespan_us;
+  out[3] = c.compute_us;
+  out[4] = c.transfer_us;
+  return 0;
 }
 
 int fuse_b200_abi_sizeof(int record) {

@@ -32,7 +32,7 @@ cudaError_t create_plan(const fuse_bf16_grouped_gemm_params& p, bool combine, fu
   if (p.lhs == nullptr || p.weight_nt == nullptr || p.output == nullptr || p.row_offsets == nullptr ||
       p.source == nullptr || p.experts <= 0 || p.n <= 0 || p.k <= 0 || p.expert_row_capacity <= 0 ||
       p.world_size <= 0 || p.world_size > FUSE_MAX_WORLD_SIZE || p.rank < 0 || p.rank >= p.world_size ||
-      p.topk <= 0 || p.policy.num_comm_ctas <= 0 || p.policy.num_compute_ctas <= 0)
+      p.topk <= 0 || p.policy.num_comm_ctas < 0 || p.policy.num_compute_ctas <= 0)
     return cudaErrorInvalidValue;
   for (int r = 0; r < p.world_size; ++r)
     if (!host::aligned16(combine ? static_cast<const void*>(p.peer_output[r]) : static_cast<const void*>(p.peer_input[r])) ||
@@ -47,6 +47,17 @@ cudaError_t create_plan(const fuse_bf16_grouped_gemm_params& p, bool combine, fu
   cudaError_t status = check_device(&info);
   if (status != cudaSuccess) return status;
   if (p.policy.num_comm_ctas >= info.sm_count) return cudaErrorInvalidValue;
+  // policy.num_comm_ctas == 0: Auto.  Row counts live on the device, so the plan is made for slabs
+  // half full (its budget stays fixed over replays, as a captured launch needs).
+  int dispatch_ctas = p.policy.num_comm_ctas;
+  if (dispatch_ctas == 0 && !combine) {
+    const double rows = 0.5 * double(p.experts) * p.expert_row_capacity;
+    const int group = p.policy.mma_sm_count == 2 ? 2 : 1;
+    const int64_t tiles = int64_t(rows / (128 * group) + 1) * host::ceil_div(p.n, p.policy.tile_n);
+    dispatch_ctas = planner::choose(planner::kDispatchBf16, 2.0 * rows * p.n * p.k, rows * p.k * 2.0, tiles, info.sm_count,
+                                    group, 0, false)
+                        .comm_ctas;
+  }
 
   std::vector<void*> lhs(p.experts), weights(p.experts);
   if ((status = cudaMemcpy(lhs.data(), p.lhs, sizeof(void*) * p.experts, cudaMemcpyDeviceToHost)) != cudaSuccess)
@@ -63,7 +74,7 @@ cudaError_t create_plan(const fuse_bf16_grouped_gemm_params& p, bool combine, fu
   // communication and compute CTAs, and is otherwise outside this implementation's domain.
   plan->pair = p.policy.mma_sm_count == 2;
   plan->combine = combine;
-  if (plan->pair && (p.policy.tile_n != 256 || (!combine && p.policy.num_comm_ctas % 2 != 0) || info.sm_count % 2 != 0)) {
+  if (plan->pair && (p.policy.tile_n != 256 || (!combine && dispatch_ctas % 2 != 0) || info.sm_count % 2 != 0)) {
     delete plan;
     return cudaErrorNotSupported;
   }
@@ -108,7 +119,7 @@ cudaError_t create_plan(const fuse_bf16_grouped_gemm_params& p, bool combine, fu
   g.n_tiles = host::ceil_div(p.n, plan->block_n);
   g.cap_tiles = cap_tiles;
   g.tile_m = plan->pair ? 2 * kBlockM : kBlockM;
-  g.num_comm_ctas = combine ? 0 : p.policy.num_comm_ctas;
+  g.num_comm_ctas = combine ? 0 : dispatch_ctas;
   g.topk = p.topk;
   g.maps_a = reinterpret_cast<const CUtensorMap*>(base);
   g.maps_b = reinterpret_cast<const CUtensorMap*>(base + maps_bytes);
@@ -126,9 +137,9 @@ cudaError_t create_plan(const fuse_bf16_grouped_gemm_params& p, bool combine, fu
     g.peer_done[r] = p.peer_done[r];
   }
   const int compute = combine ? info.sm_count
-                              : (p.policy.num_compute_ctas < info.sm_count - p.policy.num_comm_ctas
+                              : (p.policy.num_compute_ctas < info.sm_count - dispatch_ctas && p.policy.num_comm_ctas != 0
                                      ? p.policy.num_compute_ctas
-                                     : info.sm_count - p.policy.num_comm_ctas);
+                                     : info.sm_count - dispatch_ctas);
   plan->grid = g.num_comm_ctas + (plan->pair ? compute / 2 * 2 : compute);
   g.wait.status = info.status;
   if ((status = cudaDeviceSynchronize()) != cudaSuccess) return fail(status);

@@ -9,6 +9,7 @@
 #include "fused_gemm.cuh"
 #include "pair_gemm.cuh"
 #include "host.cuh"
+#include "planner.cuh"
 
 namespace fuse_b200 {
 namespace launch {
@@ -251,14 +252,21 @@ inline cudaError_t encode_scale_atoms(CUtensorMap* map, const void* scales, int6
                                     CU_TENSOR_MAP_SWIZZLE_NONE);
 }
 
-// The lhs pull of the CTA-pair kernels is run by one warp of every compute CTA (no SM is given up
-// to communication; `num_comm_ctas` is then only validated).  Measured better than communication
-// CTAs on 1, 2 and 8 GPUs.  FUSE_B200_EMBEDDED_PULL=0 (read on every launch) brings the
-// communication CTAs back.
-inline bool embedded_pull_requested(int world) {
-  (void)world;
-  const char* text = std::getenv("FUSE_B200_EMBEDDED_PULL");
-  return text == nullptr || std::atoi(text) != 0;
+// Who moves the data of a pull / push operator on CTA pairs: an explicit `num_comm_ctas` means that
+// many communication CTAs, exactly; Auto (0) follows the planner, which on B200 picks the copy
+// warp embedded in every compute CTA (no SM given up) wherever the geometry allows it.
+// FUSE_B200_EMBEDDED_PULL=1 / 0 (read on every launch) overrides both.
+inline bool embedded_copy_selected(int explicit_comm_ctas, const planner::Choice& plan) {
+  if (const char* text = std::getenv("FUSE_B200_EMBEDDED_PULL")) return std::atoi(text) != 0;
+  return explicit_comm_ctas == 0 && plan.embedded != 0;
+}
+
+// The plan of a transfer-fed GEMM on this device: `tiles` of 256 x 256 (CTA pairs).
+inline planner::Choice plan_transfer(planner::Kind kind, int64_t m, int64_t n, int64_t k, double bytes, int sm_count,
+                                     int explicit_comm_ctas, bool embedded_allowed = true) {
+  const int64_t tiles = ((m + 255) / 256) * ((n + 255) / 256);
+  return planner::choose(kind, 2.0 * double(m) * double(n) * double(k), bytes, tiles, sm_count, 2, explicit_comm_ctas,
+                         embedded_allowed);
 }
 
 // CTA-pair tiles are used wherever the shape allows; the environment switch FUSE_B200_PAIR=0

@@ -237,8 +237,8 @@ cudaError_t qkv_forward_mxfp8(const fuse_mxfp8_gemm_a2a_params& mp, const fuse_b
   const fuse_gemm_problem& g = p.gemm;
   if (!supported_mx_problem(g) || !std::isfinite(p.alpha) || p.epoch == 0 || p.num_comm_ctas < 0)
     return cudaErrorInvalidValue;
-  // no calibrated plan: explicit budgets only (the GEMM-only launch may name 0: every SM computes)
-  if (p.num_comm_ctas == 0 && phase != MxPhase::kComputeOnly && phase != MxPhase::kPrepareOnly) return cudaErrorNotSupported;
+  // num_comm_ctas == 0: Auto -- the epilogue push (no communication CTA), or the planned budget
+  // when the caller asks for the communication-CTA route; the GEMM-only launch then uses every SM
   if (mp.postprocess.q_gamma != nullptr || mp.postprocess.cos != nullptr) return cudaErrorNotSupported;
   const WeightScratch w = weight_scratch(g, mp.workspace);
   if (mp.workspace == nullptr || reinterpret_cast<uintptr_t>(mp.workspace) % 256 != 0 ||
@@ -281,8 +281,14 @@ cudaError_t qkv_forward_mxfp8(const fuse_mxfp8_gemm_a2a_params& mp, const fuse_b
   // Epilogue push by default; communication CTAs when asked for (they need the tile flags).
   const bool direct = routed && !(options && (options->flags & FUSE_B200_QKV_ROUTE_COMM_CTAS) &&
                                   host::aligned4(p.ready));
+  const int planned_comm =
+      p.num_comm_ctas ? p.num_comm_ctas
+                      : planner::choose(planner::kQkvPushMx, 2.0 * double(g.m) * g.n * g.k, double(g.m) * g.n * 2.0,
+                                        int64_t(host::ceil_div(g.m, kBlockM)) * host::ceil_div(g.n, 256), info.sm_count, 1,
+                                        0, false)
+                            .comm_ctas;
   FusedParams f{};
-  launch::fill_core(&f, g.m, g.n, g.k, block_n, (routed && !direct) ? p.num_comm_ctas : 0, p.alpha, 0.0f,
+  launch::fill_core(&f, g.m, g.n, g.k, block_n, (routed && !direct) ? planned_comm : 0, p.alpha, 0.0f,
                     p.local_output, packed_or(g.stride_d.row, g.n),
                     g.raster == FUSE_RASTER_ALONG_N ? FUSE_RASTER_ALONG_N : FUSE_RASTER_ALONG_M,
                     g.max_swizzle_size);
@@ -378,7 +384,6 @@ cudaError_t oproj_forward_mxfp8(const fuse_mxfp8_a2a_gemm_params& mp, const fuse
   if (!supported_mx_problem(g) || !std::isfinite(p.alpha) || p.epoch == 0 || p.num_comm_ctas < 0 ||
       p.lhs_policy != 0)
     return cudaErrorInvalidValue;
-  if (p.num_comm_ctas == 0) return cudaErrorNotSupported;  // no calibrated plan: explicit budgets only
   if (mp.postprocess.residual != nullptr || mp.overlap_postnorm || mp.m_window_tiles != 0 ||
       mp.n_group_tiles != 0)
     return cudaErrorNotSupported;
@@ -390,6 +395,10 @@ cudaError_t oproj_forward_mxfp8(const fuse_mxfp8_a2a_gemm_params& mp, const fuse
   cudaError_t status = check_device(&info);
   if (status != cudaSuccess) return status;
   if (p.num_comm_ctas >= info.sm_count) return cudaErrorInvalidValue;
+  // Auto: the planner's choice (embedded copy warps, or a communication budget); explicit: exactly that
+  const planner::Choice plan = launch::plan_transfer(planner::kLhsPullMx, g.m, g.n, g.k, double(g.m) * g.k * (1.0 + 1.0 / 32),
+                                                     info.sm_count, p.num_comm_ctas);
+  const int num_comm_ctas = p.num_comm_ctas ? p.num_comm_ctas : (plan.comm_ctas ? plan.comm_ctas : 16);
   if (r.world_size <= 0 || r.world_size > FUSE_MAX_WORLD_SIZE || r.rank < 0 || r.rank >= r.world_size ||
       r.batch <= 0 || r.seq_local <= 0 || r.kind != FUSE_ROUTE_HEAD_TO_SEQUENCE ||
       r.direction != FUSE_ROUTE_INVERSE || int64_t(r.seq_local) * r.world_size != r.global_seq ||
@@ -415,7 +424,7 @@ cudaError_t oproj_forward_mxfp8(const fuse_mxfp8_a2a_gemm_params& mp, const fuse
   if ((status = encode_operand_u8(&maps.b, w.weights.data, g.n, g.k, g.k, block_n)) != cudaSuccess) return status;
 
   FusedParams f{};
-  launch::fill_core(&f, g.m, g.n, g.k, block_n, p.num_comm_ctas, p.alpha, 0.0f, p.output,
+  launch::fill_core(&f, g.m, g.n, g.k, block_n, num_comm_ctas, p.alpha, 0.0f, p.output,
                     packed_or(g.stride_d.row, g.n),
                     g.raster == FUSE_RASTER_ALONG_M ? FUSE_RASTER_ALONG_M : FUSE_RASTER_ALONG_N,
                     g.max_swizzle_size);
@@ -458,7 +467,7 @@ cudaError_t oproj_forward_mxfp8(const fuse_mxfp8_a2a_gemm_params& mp, const fuse
   if (!(f.flags & kFlagVectorPull)) {
     LhsPullMaps pull{};
     if (launch::encode_lhs_pull_maps(&pull, f, uint64_t(r.batch) * uint64_t(r.global_seq))) {
-      if (block_n == 256 && g.k % 128 == 0 && p.num_comm_ctas % 2 == 0 && info.sm_count % 2 == 0 &&
+      if (block_n == 256 && g.k % 128 == 0 && num_comm_ctas % 2 == 0 && info.sm_count % 2 == 0 &&
           launch::pair_tiles_requested()) {
         // CTA pairs: whole pairs of communication CTAs, 256-row tiles
         Operands pair_maps = maps;
@@ -469,7 +478,7 @@ cudaError_t oproj_forward_mxfp8(const fuse_mxfp8_a2a_gemm_params& mp, const fuse
             launch::encode_scale_atoms(&sfa_map, f.sfa, g.m, g.k) == cudaSuccess &&
             launch::encode_scale_atoms(&sfb_map, f.sfb, g.n, g.k) == cudaSuccess)
         {
-          if (launch::embedded_pull_requested(r.world_size))
+          if (launch::embedded_copy_selected(p.num_comm_ctas, plan))
             return launch::launch_pair_kernel<kModeLhsPull, LhsPullMaps, true, false, false, true>(
                 pair_maps, sfa_map, sfb_map, pull, pf, g.max_swizzle_size, info, stream, 0.0);
           return launch::launch_pair_kernel<kModeLhsPull, LhsPullMaps, true>(

@@ -178,12 +178,29 @@ FUSE_API void fuse_cutlass_kernel_traits(fuse_kernel_traits* out);
 /* include/fuse/operators/primitives/a2a_gemm.h:88-90. */
 FUSE_API int64_t fuse_a2a_lhs_gemm_ready_elements(const fuse_gemm_problem* problem,
                                          const fuse_ulysses_route* route);
-/* include/fuse/operators/primitives/gemm_a2a.h:76-78 and a2a_gemm.h:92-94: communication-CTA
- * budget chosen by the host plan (0 where no plan exists for the geometry). */
+/* include/fuse/operators/primitives/gemm_a2a.h:76-78 and a2a_gemm.h:92-94: the communication-CTA
+ * budget the host plan chooses when the operator runs with communication CTAs.
+ *
+ * Auto.  Every operator accepts num_comm_ctas == 0 (the reference's "Auto",
+ * csrc/operators/sm103/detail/autotune.cuh:109-203): the host planner scores the candidates from an
+ * offline B200 calibration of compute and copy rates (fuse_b200/csrc/calibration_b200.h, written by
+ * `python -m fuse_b200.calibrate`) and takes the smallest makespan max(compute, transfer).  On B200
+ * that is the epilogue push for the projections that route their OUTPUT (no communication CTA at
+ * all) and, for the operators that move their INPUT, the copy warp embedded in every compute CTA or
+ * a communication budget.  An explicit num_comm_ctas > 0 is used exactly: that many communication
+ * CTAs. */
 FUSE_API int32_t fuse_recommended_gemm_a2a_comm_ctas(const fuse_gemm_problem* problem,
                                             const fuse_ulysses_route* route);
 FUSE_API int32_t fuse_recommended_a2a_lhs_gemm_comm_ctas(const fuse_gemm_problem* problem,
                                                 const fuse_ulysses_route* route);
+
+/* The planner itself (no counterpart in the reference's public interface; its scorer is
+ * csrc/operators/sm103/detail/autotune.cuh).  kind: 0 BF16 lhs pull, 1 MXFP8 lhs pull, 2 BF16
+ * gradient push, 3 MXFP8 gradient pull, 4 / 5 QKV push from communication CTAs (BF16 / MXFP8),
+ * 6 MoE dispatch.  flops / bytes / tiles describe one launch, group = SMs per tile (2: CTA pairs).
+ * out = {comm_ctas, embedded (0/1), makespan_us, compute_us, transfer_us}.  Host only. */
+FUSE_API int fuse_b200_plan(int32_t kind, double flops, double bytes, int64_t tiles, int32_t sm_count, int32_t group,
+                            int32_t explicit_comm_ctas, int32_t embedded_allowed, double out[5]);
 
 /* ---------------------------------------------------------------------------------------------
  * Backward (BF16).  include/fuse/operators/ulysses/{backward_common,qkv_backward,oproj_backward}.h

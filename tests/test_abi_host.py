@@ -50,6 +50,8 @@ def test_parameter_validation_without_a_device():
     assert api.launch_gemm_a2a_cutlass(p) == N.CUDA_ERROR_INVALID_VALUE
     p = N.GemmA2AParams(gemm=good, num_comm_ctas=0, epoch=1)
     assert api.launch_gemm_a2a_cutlass(p) == N.CUDA_ERROR_INVALID_VALUE
+    # ... while the _ex entry point takes 0 as Auto: validation passes, the launch then needs a device
+    assert api.launch_gemm_a2a_cutlass(p, 0, N.Options()) != N.CUDA_ERROR_INVALID_VALUE
     p = N.GemmA2AParams(gemm=good, num_comm_ctas=4, epoch=1, alpha=float("inf"))
     assert api.launch_gemm_a2a_cutlass(p) == N.CUDA_ERROR_INVALID_VALUE
     for bad in (N.GemmProblem(0, 384, 64), N.GemmProblem(256, 384, 60), N.GemmProblem(256, 384, 64, max_swizzle_size=3),
@@ -77,10 +79,46 @@ def test_auto_budget_of_the_output_projection_pull():
     route = N.UlyssesRoute(world_size=8)
     for shape in ((16384, 4096, 4096), (32768, 8192, 8192), (256, 512, 512), (65536, 1024, 16384)):
         ctas = api.recommended_a2a_lhs_gemm_comm_ctas(N.GemmProblem(*shape), route)
-        assert 4 <= ctas <= 32 and ctas % 2 == 0
-    assert api.recommended_a2a_lhs_gemm_comm_ctas(N.GemmProblem(16384, 4096, 4096), route) in (20, 22)
-    # no calibration for the communication-CTA route of the QKV projection: explicit budgets only
-    assert api.recommended_gemm_a2a_comm_ctas(N.GemmProblem(16384, 6144, 4096), route) == 0
+        assert 4 <= ctas <= 48 and ctas % 2 == 0
+    assert 4 <= api.recommended_gemm_a2a_comm_ctas(N.GemmProblem(16384, 6144, 4096), route) <= 48
+
+
+def test_planner_follows_the_scorer_rules_of_the_reference():
+    # csrc/operators/sm103/detail/autotune.cuh:25-75,109-203: minimise max(compute, transfer) over the
+    # measured candidates; an explicit budget is used exactly and never changed; ties go to fewer
+    # communication CTAs; the model is monotone in the bytes to move.
+    c2 = dict(flops=2.0 * 16384 * 4096 * 4096, nbytes=16384 * 4096 * 2.0, tiles=64 * 16)
+    auto = api.plan(0, **c2)
+    assert auto["embedded"] and auto["comm_ctas"] == 0             # B200: no SM given up when the copy warp can be embedded
+    for budget in (8, 20, 32):
+        explicit = api.plan(0, explicit_comm_ctas=budget, **c2)
+        assert explicit["comm_ctas"] == budget and not explicit["embedded"]
+        # Auto is the minimum over the candidates (a communication budget must beat the embedded warps by 3 %)
+        assert explicit["makespan_us"] >= auto["makespan_us"] * 0.97 * (1 - 1e-9)
+    ctas_only = api.plan(0, embedded_allowed=False, **c2)
+    assert not ctas_only["embedded"] and ctas_only["comm_ctas"] in (4, 8, 12, 16, 20, 24, 32, 40, 48)
+    candidates = [api.plan(0, explicit_comm_ctas=b, **c2)["makespan_us"] for b in (4, 8, 12, 16, 20, 24, 32, 40, 48)]
+    assert abs(ctas_only["makespan_us"] - min(candidates)) <= 1e-9 * min(candidates)
+    # the makespan covers the transfer and at least the GEMM on every SM (compute_us is the GEMM on
+    # the compute CTAs alone; communication CTAs that join it afterwards can only shorten that)
+    assert ctas_only["makespan_us"] >= ctas_only["transfer_us"]
+    assert ctas_only["compute_us"] * (148 - ctas_only["comm_ctas"]) / 148 * 0.9 <= ctas_only["makespan_us"] <= ctas_only["compute_us"] * 1.001
+    # more bytes to move never lowers the budget of the communication-CTA plan, nor the makespan
+    last_budget, last_span = 0, 0.0
+    for scale in (0.25, 1.0, 4.0, 16.0):
+        plan = api.plan(0, c2["flops"], c2["nbytes"] * scale, c2["tiles"], embedded_allowed=False)
+        assert plan["comm_ctas"] >= last_budget and plan["makespan_us"] >= last_span * (1 - 1e-9)
+        last_budget, last_span = plan["comm_ctas"], plan["makespan_us"]
+    # budgets of CTA-pair kernels come in pairs; every kind answers; bad requests are rejected
+    for kind in range(7):
+        plan = api.plan(kind, 1.0e12, 5.0e8, 2048, group=2)
+        assert plan["comm_ctas"] % 2 == 0 and plan["comm_ctas"] < 148 and plan["makespan_us"] > 0
+    import pytest
+    for bad in (dict(kind=7), dict(kind=0, explicit_comm_ctas=148), dict(kind=0, tiles=0)):
+        args = dict(kind=0, flops=1e12, nbytes=1e8, tiles=100)
+        args.update(bad)
+        with pytest.raises(ValueError):
+            api.plan(**args)
 
 
 def test_mxfp8_traits_and_workspace_overloads():

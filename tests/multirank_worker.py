@@ -97,6 +97,54 @@ def main():
     assert ok, ("oproj", worst, bad)
     dist.barrier()  # peers' inputs stay immutable until every rank is done
 
+    # ---- the forward pair again at a size where every rank runs several waves of 256 x 256 tiles
+    # (10 x 24 QKV tiles on 74 CTA pairs, K wrap of the pull), checked by row samples: GEMM rows against
+    # the oracle, routed / gathered elements traced through the oracle's maps, bit-exact ------------
+    from tests import fullsize as F
+    F.use_host_threads(world)
+    bs, bq, bkv, bk = 2560, 32, 8, 1024
+    bn, bko = (bq + 2 * bkv) * d, bq * d
+    brows = bs * world
+    bsym = w.allocate({"big_planar": brows * (bn // world) * 2, "big_done": world * N.READY_FLAG_STRIDE * 4,
+                       "big_attn": brows * (bko // world) * 2})
+    gen = lambda shape, seed, scale: to_dev(synthetic.normal_bf16(shape, seed, scale))
+    bx, bwq, bwo = gen((bs, bk), synthetic.rank_seed(rank) + 31, 1.0), gen((bn, bk), 41, 0.02), gen((1024, bko), 43, 0.02)
+    bsym["big_attn"].view(torch.bfloat16).copy_(gen((brows, bko // world), synthetic.rank_seed(rank) + 37, 1.0).reshape(-1))
+    blocal = torch.full((bs, bn), -1, dtype=torch.int16, device=dev).view(torch.bfloat16)
+    bstaging = torch.full((bs, bko), -1, dtype=torch.int16, device=dev).view(torch.bfloat16)
+    bout = torch.full((bs, 1024), -1, dtype=torch.int16, device=dev).view(torch.bfloat16)
+    bsym["big_planar"].view(torch.int16).fill_(-1)
+    bproblem = N.GemmProblem(bs, bn, bk, raster=N.RASTER_ALONG_M, max_swizzle_size=8)
+    broute = N.UlyssesRoute(world_size=world, rank=rank, batch=1, global_seq=brows, seq_local=bs, q_heads=bq, kv_heads=bkv,
+                            head_dim=d, kind=N.ROUTE_QKV_GQA_PACK)
+    bready = torch.zeros(api.qkv_ready_elements(bproblem), dtype=torch.int32, device=dev)
+    bp_ = N.GemmA2AParams(lhs=bx.data_ptr(), rhs_nt=bwq.data_ptr(), local_output=blocal.data_ptr(), ready=bready.data_ptr(),
+                          gemm=bproblem, route=broute, num_comm_ctas=0 if route_mode == "direct" else 8, epoch=1)
+    for r in range(world):
+        bp_.peer_output[r] = bsym["big_planar"].peer_ptrs[r]
+        bp_.peer_route_done_epoch[r] = bsym["big_done"].peer_ptrs[r]
+    torch.cuda.synchronize()
+    dist.barrier()
+    assert api.launch_gemm_a2a_cutlass(bp_, 0, opts) == 0
+    boprob = N.GemmProblem(bs, 1024, bko, raster=N.RASTER_ALONG_N, max_swizzle_size=8)
+    boroute = N.UlyssesRoute(world_size=world, rank=rank, batch=1, global_seq=brows, seq_local=bs,
+                             kind=N.ROUTE_HEAD_TO_SEQUENCE, direction=N.ROUTE_INVERSE)
+    boready = torch.zeros(api.a2a_lhs_gemm_ready_elements(boprob, boroute), dtype=torch.int32, device=dev)
+    bpo = N.A2AGemmParams(input_staging=bstaging.data_ptr(), rhs_nt=bwo.data_ptr(), output=bout.data_ptr(),
+                          ready=boready.data_ptr(), gemm=boprob, route=boroute, num_comm_ctas=0, epoch=1)  # Auto
+    for r in range(world):
+        bpo.peer_input[r] = bsym["big_attn"].peer_ptrs[r]
+    assert api.launch_a2a_gemm_cutlass(bpo, 0, opts) == 0
+    torch.cuda.synchronize()
+    status = api.read_status()
+    assert status[0] == 0, status[:8]
+    picked = F.sample_rows(bs, count=96)
+    qc = F.check_qkv_forward(world, rank, bs, bq, bkv, d, bx, bwq, blocal, bsym["big_planar"].view(torch.bfloat16), picked)
+    oc = F.check_oproj_forward(world, rank, bs, bko, bsym["big_attn"].view(torch.bfloat16), bstaging, bwo, bout, picked)
+    verdict = F.merge(qc, oc)
+    assert verdict["ok"], verdict
+    dist.barrier()
+
     # ---- QKV backward: sender push into the peers' staging, flags released on the destination ----
     hidden = 512
     planes_all = [tuple(synthetic.normal_bf16((rows, heads // world * d), synthetic.rank_seed(r) + 100 * seg + 101, 0.01)

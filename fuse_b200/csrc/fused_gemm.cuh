@@ -1769,7 +1769,9 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
         for (int64_t t = walk.first(); ok && t >= 0; t = walk.next(), ++tile_seq) {
           int32_t mt, nt;
           p.order.decode(t, mt, nt);
-          int32_t gated_upto = -1;  // highest K group already acquired for this tile
+          // K blocks of this tile whose groups the scout has posted complete; the group a block
+          // needs is worked out (a division) only when the walk reaches a block that is not open.
+          int32_t open_blocks = 0;
           for (int32_t ki = 0; ki < k_blocks; ++ki) {
             // K block loaded at step ki: the lhs pull starts at this rank's own shard and wraps.
             int32_t kb = ki;
@@ -1781,12 +1783,12 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
               // K groups whose rows arrive separately: peers' shards (forward pull) or Q/K/V heads
               // (backward).  The gate scout (warp 3) polls the flags, 32 at a time and ahead of
               // this thread, and posts how far this tile's groups are complete.
-              constexpr bool kHeads = kMode != kModeLhsPull;
-              const int32_t group_width = kHeads ? p.grad.head_dim : p.lhs.virt_width;
-              const int32_t groups = kHeads ? p.grad.q_heads + 2 * p.grad.kv_heads : p.lhs.world * p.lhs.virt;
-              int32_t last = (ki * kBlockElems + kBlockElems - 1) / group_width;  // position in K order
-              if (last >= groups) last = groups - 1;
-              if (gated_upto < last) {
+              if (ki >= open_blocks) {
+                constexpr bool kHeads = kMode != kModeLhsPull;
+                const int32_t group_width = kHeads ? p.grad.head_dim : p.lhs.virt_width;
+                const int32_t groups = kHeads ? p.grad.q_heads + 2 * p.grad.kv_heads : p.lhs.world * p.lhs.virt;
+                int32_t last = (ki * kBlockElems + kBlockElems - 1) / group_width;  // position in K order
+                if (last >= groups) last = groups - 1;
                 if (ki == 0) trace_event(p, 10);  // first gate wait of the tile begins
                 uint32_t seen = 0;
                 ok = progress_wait(gate_word, tile_seq * kGateSeqStep + uint32_t(last) + 1u, p.wait, kSiteLhsReady,
@@ -1794,9 +1796,11 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 // One proxy fence covers every group the scout has posted so far.
                 ptx::fence_proxy_async_global();
                 if (ki == 0) trace_event(p, 11);  // first gate passed
-                gated_upto = (seen / kGateSeqStep) > tile_seq ? groups - 1 : int32_t(seen % kGateSeqStep) - 1;
+                if (!ok) break;
+                const int32_t upto = (seen / kGateSeqStep) > tile_seq ? groups - 1 : int32_t(seen % kGateSeqStep) - 1;
+                open_blocks = upto >= groups - 1 ? k_blocks
+                                                 : int32_t((int64_t(upto + 1) * group_width) / kBlockElems);
               }
-              if (!ok) break;
             }
             ok = mbar_wait(empty_bar(stage), phase ^ 1u, p.wait, kSiteSmemEmpty);
             if (!ok) break;
@@ -1837,7 +1841,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             issued_parity = (issued_parity & ~(1u << stage)) | (phase << stage);
             if (++stage == kStages) { stage = 0; phase ^= 1u; }
           }
-          (void)gated_upto;
+          (void)open_blocks;
         }
         (void)tile_seq;
         if (!ok) {

@@ -213,7 +213,11 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         p.order.decode(t, mp, nt);
         const int32_t row0 = mp * 2 * kBlockM + int32_t(rank) * kBlockM;          // this CTA's A rows
         const int32_t wrow0 = nt * kBlockN + int32_t(rank) * (kBlockN / 2);      // this CTA's half of B
-        int32_t gated_upto = -1;
+        // K blocks of this tile whose groups the scout has posted complete.  The group a block needs
+        // is worked out (a division) only when the walk reaches a block that is not open yet: this
+        // thread's time between a stage falling free and its loads going out is what the GEMM
+        // feels, so the common step carries no arithmetic beyond the compare.
+        int32_t open_blocks = 0;
         for (int32_t ki = 0; ki < k_blocks; ++ki) {
           int32_t kb = ki;
           if constexpr (kGated) {
@@ -223,33 +227,36 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               kb += p.lhs.k_block_start;
               if (kb >= k_blocks) kb -= k_blocks;
             }
-            const int32_t groups = kHeads ? p.grad.q_heads + 2 * p.grad.kv_heads : p.lhs.world * p.lhs.virt;
-            const int32_t group_width = kHeads ? p.grad.head_dim : p.lhs.virt_width;
-            int32_t last = (ki * kBlockElems + kBlockElems - 1) / group_width;
-            if (last >= groups) last = groups - 1;
-            if (gated_upto < last) {
+            if (ki >= open_blocks) {
+              const int32_t groups = kHeads ? p.grad.q_heads + 2 * p.grad.kv_heads : p.lhs.world * p.lhs.virt;
+              const int32_t group_width = kHeads ? p.grad.head_dim : p.lhs.virt_width;
+              int32_t last = (ki * kBlockElems + kBlockElems - 1) / group_width;
+              if (last >= groups) last = groups - 1;
               uint32_t seen = 0;
               ok = progress_wait(gate_word, tile_seq * kGateSeqStep + uint32_t(last) + 1u, p.wait, kSiteLhsReady,
                                  uint32_t((mp * 2 + int32_t(rank)) * groups + last), &seen);
               ptx::fence_proxy_async_global();
-              gated_upto = (seen / kGateSeqStep) > tile_seq ? groups - 1 : int32_t(seen % kGateSeqStep) - 1;
+              if (!ok) break;
+              const int32_t upto = (seen / kGateSeqStep) > tile_seq ? groups - 1 : int32_t(seen % kGateSeqStep) - 1;
+              open_blocks = upto >= groups - 1 ? k_blocks
+                                               : int32_t((int64_t(upto + 1) * group_width) / kBlockElems);
             }
-            if (!ok) break;
           }
-          ok = mbar_wait(empty_bar(stage), phase ^ 1u, p.wait, kSiteSmemEmpty);
-          if (!ok) break;
           const uint32_t a_dst = base + stage * Layout::kStageBytes;
           const uint32_t leader_full = ptx::map_to_cta(full_bar(stage), 0);
+          const int32_t k_elem = kb * kBlockElems;
+          ok = mbar_wait(empty_bar(stage), phase ^ 1u, p.wait, kSiteSmemEmpty);
+          if (!ok) break;
           if (leader) ptx::mbar_expect_tx(full_bar(stage), 2 * (Layout::kStageBytes + Layout::kSfStageBytes));
           if constexpr (!kAMn) {
-            ptx::tma_load_2d_pair(a_dst, &tmap_a, leader_full, kb * kBlockElems, row0);
+            ptx::tma_load_2d_pair(a_dst, &tmap_a, leader_full, k_elem, row0);
           } else {
 #pragma unroll
             for (int g = 0; g < kBlockM / 64; ++g)
               ptx::tma_load_2d_pair(a_dst + g * kMnGroupBytes, &tmap_a, leader_full, row0 + g * 64, kb * kBlockK);
           }
           if constexpr (!kBMn) {
-            ptx::tma_load_2d_pair(a_dst + Layout::kABytes, &tmap_b, leader_full, kb * kBlockElems, wrow0);
+            ptx::tma_load_2d_pair(a_dst + Layout::kABytes, &tmap_b, leader_full, k_elem, wrow0);
           } else {
 #pragma unroll
             for (int g = 0; g < kBlockN / 2 / 64; ++g)
@@ -267,7 +274,7 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
           }
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
-        (void)gated_upto;
+        (void)open_blocks;
       }
       (void)tile_seq;
       unwound = !ok;

@@ -45,6 +45,14 @@ cudaError_t device_info(DeviceInfo* info) {
   cudaError_t status = cudaGetDevice(&device);
   if (status != cudaSuccess) return status;
   if (device < 0 || device >= kMaxDevices) return cudaErrorInvalidDevice;
+  // The tensor maps are encoded through the driver API, which needs the device's primary context
+  // current on THIS host thread; a thread that has only ever called cudaSetDevice (a framework's
+  // backward thread, say) does not have it yet.  cudaFree(nullptr) binds it; once per thread and device.
+  thread_local int bound_device = -1;
+  if (bound_device != device) {
+    if ((status = cudaFree(nullptr)) != cudaSuccess) return status;
+    bound_device = device;
+  }
   std::lock_guard<std::mutex> lock(g_mutex);
   DeviceInfo& cached = g_devices[device];
   if (cached.device != device) {

@@ -232,3 +232,30 @@ def test_bounded_wait_reports_instead_of_hanging():
     want_staging, want_out = O.oproj_forward(world, 0, 1, s, [H.to_bits(x) for x in peer_in], H.to_bits(w))
     assert np.array_equal(H.to_bits(staging), want_staging)
     _assert_close(H.to_bits(out), want_out, "output after recovery")
+
+
+def test_launch_from_a_second_host_thread():
+    """A host thread that has never made a CUDA call of its own (a framework's backward thread)
+    launches an operator: the library binds the device's context to the thread itself."""
+    import threading
+    import torch
+    from tests import harness as H
+    m, n, k = 256, 512, 256
+    a = torch.randn((m, k), device=H.DEV).bfloat16()
+    b = torch.randn((n, k), device=H.DEV).bfloat16()
+    d = torch.zeros((m, n), dtype=torch.bfloat16, device=H.DEV)
+    torch.cuda.synchronize()
+    p = N.GemmA2AParams(lhs=a.data_ptr(), rhs_nt=b.data_ptr(), local_output=d.data_ptr(),
+                        gemm=N.GemmProblem(m, n, k, max_swizzle_size=1), num_comm_ctas=1, epoch=1)
+    result = {}
+
+    def run():
+        result["rc"] = api.launch_batched_cutlass_reference(p, 0, 0)
+
+    thread = threading.Thread(target=run)
+    thread.start()
+    thread.join()
+    torch.cuda.synchronize()
+    assert result["rc"] == 0, result
+    want = a.float() @ b.float().t()
+    assert torch.allclose(d.float(), want, atol=0.5, rtol=0.02)

@@ -259,6 +259,15 @@ def dispatch_rates(out):
     api.read_status()
 
 
+# One GPU cannot measure a link.  The lhs pull alone (bench.py: nvlink.copy_only, 32 communication
+# CTAs) moved 492 GB/s on 2 GPUs (half of the bytes remote) and 534 GB/s on 4 (three quarters remote)
+# against 1180 GB/s locally: 10-14 GB/s per CTA over NVLink against 37, i.e. 0.26-0.38; the MoE
+# dispatch on 2 GPUs was transfer-bound with 16 CTAs at 16.6 GB/s per CTA (0.25 for its remote half)
+# and on 8 GPUs ran at >= 14.4 GB/s per CTA with 20 (>= 0.32).  Too few CTAs costs far more than
+# too many (16 against 20 on 2 GPUs: -11 %; 28 against 20: -4 %), so the low side of the range.
+REMOTE_CTA_FACTOR = 0.30
+
+
 def model_comm_us(flops, nbytes, tiles, comm, tflops_per_sm, cta_gbs, startup_us=25.0, sms=SMS, group=2):
     """The planner's makespan of a communication budget (planner.cuh: score_comm), for the fit below."""
     units, comm_units = sms // group, comm // group
@@ -293,6 +302,8 @@ struct Calibration {
   // measured / modelled: the GEMM beside its embedded copy warp against the pure GEMM, and the
   // operator with communication CTAs against the wave model (contention the model leaves out)
   double embedded_compute_factor, comm_model_factor, startup_us;
+  // rate of a communication CTA whose bytes cross NVLink, relative to the local rate above
+  double remote_cta_factor;
 };
 
 constexpr Calibration kCalibrationB200 = {
@@ -304,39 +315,56 @@ constexpr Calibration kCalibrationB200 = {
 '''
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--write", action="store_true")
-    ap.add_argument("--out", default="", help="write b200.json and calibration_b200.h into this directory instead")
-    args = ap.parse_args()
-    torch.cuda.set_device(0)
-    N.lib()
-    raw = {"gpu": torch.cuda.get_device_name(0)}
-    gemm_rates(raw)
-    pull_rates(raw)
-    push_rates(raw)
-    gradpull_rates(raw)
-    dispatch_rates(raw)
+def derive(raw):
+    """The planner's constants from the raw measurements (also from a stored b200.json: --from-json)."""
     cta = lambda kind: statistics.median(v["gbs_per_cta"] for v in raw[kind]["comm_ctas"].values())
-    # start-up: what a transfer takes beyond bytes / rate at the largest budget measured (first flags, pipeline fill)
-    values = [
-        ("bf16_pair_tflops_per_sm", raw["bf16_pair"]["tflops_per_sm"]),
+    c2 = dict(flops=2.0 * 16384 * 4096 * 4096, tiles=64 * 16)
+    pair = raw["bf16_pair"]["tflops_per_sm"]
+    # the planner's own time of the C2 GEMM on all pairs: whole waves of 74 tiles
+    tau = c2["flops"] / c2["tiles"] / (2 * pair * 1e6)
+    waves = -(-c2["tiles"] // (SMS // 2))
+    return [
+        ("bf16_pair_tflops_per_sm", pair),
         ("mx_pair_tflops_per_sm", raw["mx_pair"]["tflops_per_sm"]),
         ("bf16_cta_tflops_per_sm", raw["bf16_cta"]["tflops_per_sm"]),
         ("mx_cta_tflops_per_sm", raw["mx_cta"]["tflops_per_sm"]),
-        ("grouped_pair_tflops_per_sm", raw["bf16_pair"]["tflops_per_sm"] * 0.96),
+        ("grouped_pair_tflops_per_sm", pair * 0.96),
         ("pull_cta_gbs", cta("pull")), ("pull_embedded_gbs", raw["pull"]["embedded"]["gbs_per_cta"]),
         ("push_cta_gbs", cta("push")), ("push_embedded_gbs", raw["push"]["embedded"]["gbs_per_cta"]),
         ("gradpull_cta_gbs", cta("gradpull")), ("gradpull_embedded_gbs", raw["gradpull"]["embedded"]["gbs_per_cta"]),
         ("qkv_push_cta_gbs", cta("pull")),
         ("dispatch_cta_gbs", cta("dispatch")),
-        ("embedded_compute_factor", min(1.0, raw["pull"]["pure_ms"] / raw["pull"]["fused_embedded_ms"])),
+        # both candidates are anchored on what the whole operator measured at the C2 shape: the
+        # planner's time of the embedded variant there IS the measured one, and the communication
+        # budgets carry the median of measured / modelled over the budgets measured
+        ("embedded_compute_factor", min(1.0, waves * tau / (raw["pull"]["fused_embedded_ms"] * 1e3))),
         ("comm_model_factor", statistics.median(
-            ms * 1e3 / model_comm_us(2.0 * 16384 * 4096 * 4096, raw["pull"]["bytes"], 64 * 16, int(comm),
-                                     raw["bf16_pair"]["tflops_per_sm"], cta("pull"))
+            ms * 1e3 / model_comm_us(c2["flops"], raw["pull"]["bytes"], c2["tiles"], int(comm), pair, cta("pull"))
             for comm, ms in raw["pull"]["fused_comm_ms"].items())),
         ("startup_us", 25.0),
+        ("remote_cta_factor", REMOTE_CTA_FACTOR),
     ]
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--write", action="store_true")
+    ap.add_argument("--out", default="", help="write b200.json and calibration_b200.h into this directory instead")
+    ap.add_argument("--from-json", default="", help="derive the constants again from stored measurements (no GPU)")
+    args = ap.parse_args()
+    if args.from_json:
+        with open(args.from_json) as f:
+            raw = json.load(f)
+    else:
+        torch.cuda.set_device(0)
+        N.lib()
+        raw = {"gpu": torch.cuda.get_device_name(0)}
+        gemm_rates(raw)
+        pull_rates(raw)
+        push_rates(raw)
+        gradpull_rates(raw)
+        dispatch_rates(raw)
+    values = derive(raw)
     raw["constants"] = dict(values)
     print(json.dumps(raw, indent=1))
     if args.write or args.out:

@@ -52,7 +52,8 @@ cudaError_t qkv_backward_data(const fuse_qkv_backward_data_params& p, const fuse
   const int m = p.local_tokens, n = p.hidden, k = (p.q_heads + 2 * p.kv_heads) * p.head_dim;
   // Auto: the planner's choice (embedded copy warps, or a communication budget); explicit: exactly that
   const planner::Choice plan =
-      launch::plan_transfer(planner::kGradPushBf16, m, n, k, double(m) * k * 2.0, info.sm_count, p.num_comm_ctas < 0 ? 0 : p.num_comm_ctas);
+      launch::plan_transfer(planner::kGradPushBf16, m, n, k, double(m) * k * 2.0, info.sm_count, p.num_comm_ctas < 0 ? 0 : p.num_comm_ctas,
+                            true, p.world_size);
   const int comm = p.num_comm_ctas ? p.num_comm_ctas : (plan.comm_ctas ? plan.comm_ctas : fuse_recommended_qkv_backward_comm_ctas(&p));
   if (comm <= 0 || comm >= info.sm_count) return cudaErrorInvalidValue;
   if (!host::aligned16(p.grad_q) || !host::aligned16(p.grad_k) || !host::aligned16(p.grad_v) ||

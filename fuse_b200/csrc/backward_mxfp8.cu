@@ -122,7 +122,7 @@ cudaError_t qkv_data(const fuse_mxfp8_qkv_backward_data_params& mp, const fuse_b
   if (p.num_comm_ctas >= info.sm_count) return cudaErrorInvalidValue;
   // Auto: the planner's choice (embedded copy warps, or a communication budget); explicit: exactly that
   const planner::Choice plan = launch::plan_transfer(planner::kGradPullMx, m, n, k, double(m) * k * (3.0 + 1.0 / 32),
-                                                     info.sm_count, p.num_comm_ctas);
+                                                     info.sm_count, p.num_comm_ctas, true, p.world_size);
   const int num_comm_ctas = p.num_comm_ctas ? p.num_comm_ctas : (plan.comm_ctas ? plan.comm_ctas : 16);
   uint8_t* cursor = static_cast<uint8_t*>(mp.workspace);
   size_t need = 0;

@@ -16,25 +16,28 @@ struct Calibration {
   // measured / modelled: the GEMM beside its embedded copy warp against the pure GEMM, and the
   // operator with communication CTAs against the wave model (contention the model leaves out)
   double embedded_compute_factor, comm_model_factor, startup_us;
+  // rate of a communication CTA whose bytes cross NVLink, relative to the local rate above
+  double remote_cta_factor;
 };
 
 constexpr Calibration kCalibrationB200 = {
-    /* bf16_pair_tflops_per_sm    */ 10.75,
-    /* mx_pair_tflops_per_sm      */ 18.48,
-    /* bf16_cta_tflops_per_sm     */ 10.04,
-    /* mx_cta_tflops_per_sm       */ 17.17,
-    /* grouped_pair_tflops_per_sm */ 10.32,
-    /* pull_cta_gbs               */ 40.71,
-    /* pull_embedded_gbs          */ 7.58,
-    /* push_cta_gbs               */ 41.4,
-    /* push_embedded_gbs          */ 5.561,
-    /* gradpull_cta_gbs           */ 41.29,
+    /* bf16_pair_tflops_per_sm    */ 10.87,
+    /* mx_pair_tflops_per_sm      */ 18.66,
+    /* bf16_cta_tflops_per_sm     */ 10.07,
+    /* mx_cta_tflops_per_sm       */ 17.24,
+    /* grouped_pair_tflops_per_sm */ 10.43,
+    /* pull_cta_gbs               */ 36.82,
+    /* pull_embedded_gbs          */ 7.312,
+    /* push_cta_gbs               */ 40.5,
+    /* push_embedded_gbs          */ 5.47,
+    /* gradpull_cta_gbs           */ 42.77,
     /* gradpull_embedded_gbs      */ 10.23,
-    /* qkv_push_cta_gbs           */ 40.71,
-    /* dispatch_cta_gbs           */ 41.27,
-    /* embedded_compute_factor    */ 0.8796,
-    /* comm_model_factor          */ 1.049,
+    /* qkv_push_cta_gbs           */ 36.82,
+    /* dispatch_cta_gbs           */ 41.44,
+    /* embedded_compute_factor    */ 0.9308,
+    /* comm_model_factor          */ 0.9741,
     /* startup_us                 */ 25,
+    /* remote_cta_factor          */ 0.3,
 };
 
 }  // namespace planner

@@ -198,7 +198,8 @@ cudaError_t oproj_forward(const fuse_a2a_gemm_params& p, const fuse_b200_options
   if (status != cudaSuccess) return status;
   // Auto: the planner's choice (embedded copy warps, or a communication budget); explicit: exactly that
   const planner::Choice plan = plan_transfer(planner::kLhsPullBf16, p.gemm.m, p.gemm.n, p.gemm.k,
-                                             double(p.gemm.m) * p.gemm.k * 2.0, info.sm_count, p.num_comm_ctas);
+                                             double(p.gemm.m) * p.gemm.k * 2.0, info.sm_count, p.num_comm_ctas, true,
+                                             p.route.world_size);
   const int num_comm_ctas = p.num_comm_ctas ? p.num_comm_ctas
                                             : (plan.comm_ctas ? plan.comm_ctas
                                                               : fuse_recommended_a2a_lhs_gemm_comm_ctas(&p.gemm, &p.route));

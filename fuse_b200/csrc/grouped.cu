@@ -55,7 +55,7 @@ cudaError_t create_plan(const fuse_bf16_grouped_gemm_params& p, bool combine, fu
     const int group = p.policy.mma_sm_count == 2 ? 2 : 1;
     const int64_t tiles = int64_t(rows / (128 * group) + 1) * host::ceil_div(p.n, p.policy.tile_n);
     dispatch_ctas = planner::choose(planner::kDispatchBf16, 2.0 * rows * p.n * p.k, rows * p.k * 2.0, tiles, info.sm_count,
-                                    group, 0, false)
+                                    group, 0, false, double(p.world_size - 1) / double(p.world_size))
                         .comm_ctas;
   }
 

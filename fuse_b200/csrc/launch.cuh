@@ -263,10 +263,10 @@ inline bool embedded_copy_selected(int explicit_comm_ctas, const planner::Choice
 
 // The plan of a transfer-fed GEMM on this device: `tiles` of 256 x 256 (CTA pairs).
 inline planner::Choice plan_transfer(planner::Kind kind, int64_t m, int64_t n, int64_t k, double bytes, int sm_count,
-                                     int explicit_comm_ctas, bool embedded_allowed = true) {
+                                     int explicit_comm_ctas, bool embedded_allowed = true, int world = 1) {
   const int64_t tiles = ((m + 255) / 256) * ((n + 255) / 256);
   return planner::choose(kind, 2.0 * double(m) * double(n) * double(k), bytes, tiles, sm_count, 2, explicit_comm_ctas,
-                         embedded_allowed);
+                         embedded_allowed, world > 1 ? double(world - 1) / double(world) : 0.0);
 }
 
 // CTA-pair tiles are used wherever the shape allows; the environment switch FUSE_B200_PAIR=0

@@ -397,7 +397,7 @@ cudaError_t oproj_forward_mxfp8(const fuse_mxfp8_a2a_gemm_params& mp, const fuse
   if (p.num_comm_ctas >= info.sm_count) return cudaErrorInvalidValue;
   // Auto: the planner's choice (embedded copy warps, or a communication budget); explicit: exactly that
   const planner::Choice plan = launch::plan_transfer(planner::kLhsPullMx, g.m, g.n, g.k, double(g.m) * g.k * (1.0 + 1.0 / 32),
-                                                     info.sm_count, p.num_comm_ctas);
+                                                     info.sm_count, p.num_comm_ctas, true, p.route.world_size);
   const int num_comm_ctas = p.num_comm_ctas ? p.num_comm_ctas : (plan.comm_ctas ? plan.comm_ctas : 16);
   if (r.world_size <= 0 || r.world_size > FUSE_MAX_WORLD_SIZE || r.rank < 0 || r.rank >= r.world_size ||
       r.batch <= 0 || r.seq_local <= 0 || r.kind != FUSE_ROUTE_HEAD_TO_SEQUENCE ||

@@ -48,25 +48,26 @@ struct Services {
   double embedded_compute;     // GEMM rate factor with the copy ring in place of the sixth stage
   double comm_model;           // measured / modelled time of the operator with communication CTAs
   double startup_us;
+  double remote_cta;           // copy rate of a communication CTA over NVLink / its local rate
 };
 
 inline Services services(Kind kind) {
   const Calibration& c = kCalibrationB200;
   switch (kind) {
-    case kLhsPullBf16: return {c.bf16_pair_tflops_per_sm, c.pull_cta_gbs, c.pull_embedded_gbs, c.embedded_compute_factor, c.comm_model_factor, c.startup_us};
-    case kLhsPullMx: return {c.mx_pair_tflops_per_sm, c.pull_cta_gbs, c.pull_embedded_gbs, c.embedded_compute_factor, c.comm_model_factor, c.startup_us};
-    case kGradPushBf16: return {c.bf16_pair_tflops_per_sm, c.push_cta_gbs, c.push_embedded_gbs, c.embedded_compute_factor, c.comm_model_factor, c.startup_us};
-    case kGradPullMx: return {c.mx_pair_tflops_per_sm, c.gradpull_cta_gbs, c.gradpull_embedded_gbs, c.embedded_compute_factor, c.comm_model_factor, c.startup_us};
-    case kQkvPushBf16: return {c.bf16_cta_tflops_per_sm, c.qkv_push_cta_gbs, 0.0, 1.0, c.comm_model_factor, c.startup_us};
-    case kQkvPushMx: return {c.mx_cta_tflops_per_sm, c.qkv_push_cta_gbs, 0.0, 1.0, c.comm_model_factor, c.startup_us};
-    default: return {c.grouped_pair_tflops_per_sm, c.dispatch_cta_gbs, 0.0, 1.0, c.comm_model_factor, c.startup_us};
+    case kLhsPullBf16: return {c.bf16_pair_tflops_per_sm, c.pull_cta_gbs, c.pull_embedded_gbs, c.embedded_compute_factor, c.comm_model_factor, c.startup_us, c.remote_cta_factor};
+    case kLhsPullMx: return {c.mx_pair_tflops_per_sm, c.pull_cta_gbs, c.pull_embedded_gbs, c.embedded_compute_factor, c.comm_model_factor, c.startup_us, c.remote_cta_factor};
+    case kGradPushBf16: return {c.bf16_pair_tflops_per_sm, c.push_cta_gbs, c.push_embedded_gbs, c.embedded_compute_factor, c.comm_model_factor, c.startup_us, c.remote_cta_factor};
+    case kGradPullMx: return {c.mx_pair_tflops_per_sm, c.gradpull_cta_gbs, c.gradpull_embedded_gbs, c.embedded_compute_factor, c.comm_model_factor, c.startup_us, c.remote_cta_factor};
+    case kQkvPushBf16: return {c.bf16_cta_tflops_per_sm, c.qkv_push_cta_gbs, 0.0, 1.0, c.comm_model_factor, c.startup_us, c.remote_cta_factor};
+    case kQkvPushMx: return {c.mx_cta_tflops_per_sm, c.qkv_push_cta_gbs, 0.0, 1.0, c.comm_model_factor, c.startup_us, c.remote_cta_factor};
+    default: return {c.grouped_pair_tflops_per_sm, c.dispatch_cta_gbs, 0.0, 1.0, c.comm_model_factor, c.startup_us, c.remote_cta_factor};
   }
 }
 
 // Makespan with `comm` communication CTAs (in units of `group` SMs: 2 for CTA pairs) that join the
 // GEMM after their transfers: the same wave model the launch uses to place the join.
 inline Choice score_comm(const Services& s, double flops, double bytes, int64_t tiles, int sm_count, int group,
-                         int comm) {
+                         int comm, double remote_share = 0.0) {
   const int64_t units = sm_count / group, comm_units = comm / group;
   const int64_t compute = tiles < units - comm_units ? tiles : units - comm_units;
   Choice out{comm, 0, 0.0, 0.0, 0.0};
@@ -75,7 +76,9 @@ inline Choice score_comm(const Services& s, double flops, double bytes, int64_t 
     return out;
   }
   const double tau = flops / double(tiles) / (double(group) * s.tflops_per_sm * 1.0e6);  // us per tile and unit
-  const double t_c = s.startup_us + bytes / (double(comm) * s.cta_gbs * 1.0e3);
+  // bytes that cross NVLink move at the (lower) remote rate of a communication CTA
+  const double weighted = bytes * ((1.0 - remote_share) + remote_share / s.remote_cta);
+  const double t_c = s.startup_us + weighted / (double(comm) * s.cta_gbs * 1.0e3);
   const int64_t all = compute + comm_units;
   double best = double((tiles + compute - 1) / compute) * tau;
   best = best > t_c + tau ? best : t_c + tau;  // the last tile cannot start before its rows are there
@@ -103,25 +106,29 @@ inline Choice score_embedded(const Services& s, double flops, double bytes, int6
 
 // explicit_comm > 0: that many communication CTAs, exactly (the plan only reports their score).
 // explicit_comm == 0: Auto.  embedded_allowed: the launch can run embedded copy warps (geometry and
-// kernel family permitting).  step: budgets are multiples of `step` (2 for CTA pairs).
+// kernel family permitting).  remote_share: fraction of the bytes that cross NVLink, (world - 1) /
+// world for the all-to-all routes.
 inline Choice choose(Kind kind, double flops, double bytes, int64_t tiles, int sm_count, int group, int explicit_comm,
-                     bool embedded_allowed) {
+                     bool embedded_allowed, double remote_share = 0.0) {
   const Services s = services(kind);
-  if (explicit_comm > 0) return score_comm(s, flops, bytes, tiles, sm_count, group, explicit_comm);
+  if (explicit_comm > 0) return score_comm(s, flops, bytes, tiles, sm_count, group, explicit_comm, remote_share);
   Choice best{0, 0, 1.0e30, 0.0, 0.0};
   static const int kBudgets[] = {4, 8, 12, 16, 20, 24, 32, 40, 48};
   for (int comm : kBudgets) {
     if (comm % group != 0 || comm >= sm_count) continue;
-    const Choice c = score_comm(s, flops, bytes, tiles, sm_count, group, comm);
+    const Choice c = score_comm(s, flops, bytes, tiles, sm_count, group, comm, remote_share);
     if (c.makespan_us < best.makespan_us * (1.0 - 1.0e-9)) best = c;  // ties: the earlier (smaller) budget
   }
   if (embedded_allowed && s.embedded_gbs > 0.0) {
-    // A communication budget has to be predicted clearly faster (3 %) than the embedded copy warps
-    // to be taken: the calibration copies are local, and over NVLink communication CTAs lose more
-    // than the embedded warps do (on 8 GPUs the embedded pull measured 8 % ahead where one GPU
-    // showed 4 %), so a near tie on one GPU is a win for giving up no SM.
+    // A communication budget has to be predicted clearly faster (10 %) than the embedded copy warps
+    // to be taken.  That is the model's error: it reproduces its own BF16 calibration points to
+    // -9 ... +2 %, and for the block-scaled output projection it put 8 communication CTAs 6.5 % ahead
+    // of the embedded warps where they measured 3.4 % behind.  Wherever both were measured (BF16 and
+    // MXFP8 pulls and pushes, 1 to 8 GPUs) the embedded warps won when the GEMM was the longer side,
+    // and over NVLink communication CTAs lose more than the embedded warps do; a budget is taken
+    // where the transfer is the longer side (narrow GEMMs), which the embedded warps cannot shorten.
     const Choice e = score_embedded(s, flops, bytes, tiles, sm_count, group);
-    if (e.makespan_us * 0.97 <= best.makespan_us) best = e;
+    if (e.makespan_us * 0.90 <= best.makespan_us) best = e;
   }
   return best;
 }

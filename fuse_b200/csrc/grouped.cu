@@ -50,7 +50,15 @@ cudaError_t create_plan(const fuse_bf16_grouped_gemm_params& p, bool combine, fu
   // policy.num_comm_ctas == 0: Auto.  Row counts live on the device, so the plan is made for slabs
   // half full (its budget stays fixed over replays, as a captured launch needs).
   int dispatch_ctas = p.policy.num_comm_ctas;
-  if (dispatch_ctas == 0 && !combine) {
+  // Auto on CTA pairs: no communication CTA at all -- one thread of every compute CTA pulls (its ring
+  // is the epilogue staging the dispatch kernel does not use, so the GEMM keeps all six stages).  A
+  // pull over NVLink is bounded by what ONE SM may have in flight, so 148 SMs pulling a little each
+  // move far more than 20 CTAs pulling flat out.  FUSE_B200_EMBEDDED_PULL=0 keeps communication CTAs.
+  bool embedded = dispatch_ctas == 0 && !combine && p.policy.mma_sm_count == 2 && p.policy.tile_n == 256 &&
+                  info.sm_count % 2 == 0;
+  if (const char* text = std::getenv("FUSE_B200_EMBEDDED_PULL"))
+    if (std::atoi(text) == 0) embedded = false;
+  if (dispatch_ctas == 0 && !combine && !embedded) {
     const double rows = 0.5 * double(p.experts) * p.expert_row_capacity;
     const int group = p.policy.mma_sm_count == 2 ? 2 : 1;
     const int64_t tiles = int64_t(rows / (128 * group) + 1) * host::ceil_div(p.n, p.policy.tile_n);
@@ -120,6 +128,7 @@ cudaError_t create_plan(const fuse_bf16_grouped_gemm_params& p, bool combine, fu
   g.cap_tiles = cap_tiles;
   g.tile_m = plan->pair ? 2 * kBlockM : kBlockM;
   g.num_comm_ctas = combine ? 0 : dispatch_ctas;
+  g.embedded = embedded ? 1 : 0;
   g.topk = p.topk;
   g.maps_a = reinterpret_cast<const CUtensorMap*>(base);
   g.maps_b = reinterpret_cast<const CUtensorMap*>(base + maps_bytes);

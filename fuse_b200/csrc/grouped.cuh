@@ -8,6 +8,10 @@
 //   communication CTAs: the bulk-copy pull pipeline (one row = one chunk) over sub-units of 32
 //       rows of a (expert, 128-row panel), dealt round-robin to the pull warps in panel order;
 //       a panel's flag is published by the arrival that completes it;
+//       on CTA pairs with an Auto budget there are none: one thread of EVERY compute CTA runs the
+//       same pull (a pull over NVLink is bounded by what one SM may have in flight, so 148 SMs
+//       pulling a little each move more than 20 CTAs pulling flat out), its two 16 KiB stages over
+//       the epilogue staging this kernel's register epilogue leaves unused;
 //   compute CTAs: the tcgen05 pipeline of fused_gemm.cuh with a grouped tile decode -- tile ->
 //       (expert, m, n) through the per-launch prefix of tile counts, N fastest so the CTAs of a
 //       wave share a freshly arrived panel -- per-expert tensor maps read from global memory,
@@ -40,6 +44,7 @@ struct GroupedParams {
   int32_t experts, n, k, capacity, lhs_rows;
   int32_t rank, world;
   int32_t n_tiles, cap_tiles, num_comm_ctas;
+  int32_t embedded;            // dispatch on CTA pairs: one thread of every compute CTA pulls, no communication CTAs
   const CUtensorMap* maps_a;   // [experts], lhs slabs   [lhs_rows, K]
   const CUtensorMap* maps_b;   // [experts], weights     [N, K]
   uint16_t* const* lhs;        // device array of per-expert slab pointers
@@ -101,21 +106,22 @@ struct DispatchCursor {
   uint8_t* dst;      // destination of its first row
 };
 
-__device__ __forceinline__ void dispatch_pull_role(const GroupedParams& p, const WaitContext& w,
-                                                   uint32_t smem_base) {
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  if (warp >= kPullWarps) return;
-  const uint32_t ring = smem_base + uint32_t(warp) * kPullStages * kPullStageBytes;
-  const uint32_t bars = smem_base + kPullWarps * kPullStages * kPullStageBytes +
-                        uint32_t(warp) * kPullStages * 8u;
+// One worker of the pull: a whole warp of a communication CTA (kWarp: lane 0 issues, the warp keeps
+// in step) or the single copy thread embedded in a compute CTA.  `ring`: kPullStages stages of
+// kPullStageBytes; `bars`: their mbarriers; sub-units are dealt round-robin to `workers` workers.
+template <bool kWarp>
+__device__ __forceinline__ void dispatch_pull(const GroupedParams& p, const WaitContext& w, uint32_t ring,
+                                              uint32_t bars, int32_t worker, int32_t workers, int lane) {
+  auto broadcast = [&](uint32_t value) { return kWarp ? __shfl_sync(0xffffffffu, value, 0) : value; };
+  auto in_step = [&] {
+    if (kWarp) __syncwarp();
+  };
   if (lane == 0) {
     for (int s = 0; s < kPullStages; ++s) ptx::mbar_init(bars + 8u * s, 1);
     ptx::fence_mbar_init();
   }
-  __syncwarp();
+  in_step();
 
-  const int32_t workers = p.num_comm_ctas * kPullWarps;
-  const int32_t worker = warp * p.num_comm_ctas + int32_t(blockIdx.x);
   const uint32_t row_bytes = uint32_t(p.k) * 2u;
   const int32_t pieces = int32_t((row_bytes + kPullStageBytes - 1) / kPullStageBytes);
   const int32_t subs_per_expert = p.cap_tiles * kPullSubsPerTile;
@@ -155,14 +161,14 @@ __device__ __forceinline__ void dispatch_pull_role(const GroupedParams& p, const
   auto start_load = [&](const DispatchCursor& c, int stage) {  // whole warp
     GroupedTokenSource src{0, 0, 0};
     if (lane == 0) src = p.source[c.first_row + c.row];
-    const int32_t src_rank = __shfl_sync(0xffffffffu, src.rank, 0);
+    const int32_t src_rank = int32_t(broadcast(uint32_t(src.rank)));
     if (src_rank != p.rank && !(p.flags & kFlagSkipPeerWait) && !((started_seen >> src_rank) & 1u)) {
       // the peer's tokens are valid once it has entered this invocation
       uint32_t good = 1u;
       if (lane == 0)
         good = flag_wait<true>(p.peer_started[p.rank] + src_rank * kReadyFlagStride, w.epoch, w,
                                kSitePeerStarted, uint32_t(src_rank)) ? 1u : 0u;
-      good = __shfl_sync(0xffffffffu, good, 0);
+      good = broadcast(good);
       if (!good) { ok = false; return; }
       started_seen |= 1u << src_rank;
     }
@@ -213,7 +219,7 @@ __device__ __forceinline__ void dispatch_pull_role(const GroupedParams& p, const
     uint32_t landed = 1u;
     if (lane == 0)
       landed = mbar_wait(bars + 8u * stage, uint32_t(consumed / kPullStages) & 1u, w, kSiteCommStage) ? 1u : 0u;
-    landed = __shfl_sync(0xffffffffu, landed, 0);
+    landed = broadcast(landed);
     if (!landed) { ok = false; break; }
     if (lane == 0) {
       const uint32_t offset = uint32_t(store_cursor.pieces_done) * kPullStageBytes;
@@ -224,7 +230,7 @@ __device__ __forceinline__ void dispatch_pull_role(const GroupedParams& p, const
     ptx::bulk_commit();
     ++consumed;
     ptx::bulk_wait_read<0>();
-    __syncwarp();
+    in_step();
     if (more_loads && issued < consumed + kPullStages) {
       start_load(load_cursor, issued % kPullStages);
       if (ok) {
@@ -233,7 +239,7 @@ __device__ __forceinline__ void dispatch_pull_role(const GroupedParams& p, const
       }
     }
     ptx::bulk_wait<kPullLag>();
-    __syncwarp();
+    in_step();
     if (lag_flag[kPullLag - 1] >= 0) count(lag_flag[kPullLag - 1], lag_needed[kPullLag - 1]);
 #pragma unroll
     for (int i = kPullLag - 1; i > 0; --i) { lag_flag[i] = lag_flag[i - 1]; lag_needed[i] = lag_needed[i - 1]; }
@@ -243,7 +249,7 @@ __device__ __forceinline__ void dispatch_pull_role(const GroupedParams& p, const
     more_stores = advance(store_cursor);
   }
   ptx::bulk_wait<0>();
-  __syncwarp();
+  in_step();
   if (ok) {
 #pragma unroll
     for (int i = kPullLag - 1; i >= 0; --i)
@@ -254,6 +260,16 @@ __device__ __forceinline__ void dispatch_pull_role(const GroupedParams& p, const
     for (int32_t i = consumed; i < issued; ++i)
       mbar_wait(bars + 8u * uint32_t(i % kPullStages), uint32_t(i / kPullStages) & 1u, w, kSiteDrain, false);
   }
+}
+
+// Communication CTAs: seven pull warps each.
+__device__ __forceinline__ void dispatch_pull_role(const GroupedParams& p, const WaitContext& w,
+                                                   uint32_t smem_base) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (warp >= kPullWarps) return;
+  dispatch_pull<true>(p, w, smem_base + uint32_t(warp) * kPullStages * kPullStageBytes,
+                      smem_base + kPullWarps * kPullStages * kPullStageBytes + uint32_t(warp) * kPullStages * 8u,
+                      warp * p.num_comm_ctas + int32_t(blockIdx.x), p.num_comm_ctas * kPullWarps, lane);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -681,6 +697,17 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) grouped
           mbar_wait(drain_bar, 0u, w, kSiteDrain, false);
         }
         unwound = !ok;
+      }
+    } else if (warp == 2) {
+      // embedded dispatch pull: the ring lies over the epilogue staging (unused by this kernel's
+      // register epilogue), its two mbarriers behind the TMEM slot
+      if constexpr (!kCombine) {
+        static_assert(Layout::kStagingBuffers * Layout::kStagingBlockBytes >= kPullStages * kPullStageBytes, "ring");
+        static_assert(Layout::kTmemSlotOffset + 16 + 8 * kPullStages <= Layout::kBytes, "ring barriers");
+        if (p.embedded && lane == 0)
+          dispatch_pull<false>(p, w, base + Layout::kStagingOffset, base + Layout::kTmemSlotOffset + 16u,
+                               int32_t(blockIdx.x), int32_t(gridDim.x), 0);
+        __syncwarp();
       }
     } else if (warp >= 4) {
       const int quarter = warp & 3;

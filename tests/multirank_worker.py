@@ -210,8 +210,10 @@ def main():
     want_eo = np.full((experts_local, cap, mn), 0x7f7f, dtype=np.uint16)
     assert O.lib().fo_moe_dispatch_fc1(experts_local, O.ptr(offs), O.ptr(src), O.ptr_array(toks_all), O.ptr(ew), mn, mk,
                                        cap, O.ptr(want_lhs), O.ptr(want_eo)) == 0
-    for mma_sm_count in (1, 2):  # one-CTA tiles, then CTA pairs
-        gp.policy = N.GroupedGemmPolicy(num_comm_ctas=6, num_compute_ctas=128, tile_n=256, mma_sm_count=mma_sm_count)
+    # one-CTA tiles, CTA pairs with communication CTAs, CTA pairs with the embedded pull (Auto)
+    for mma_sm_count, dispatch_ctas in ((1, 6), (2, 6), (2, 0)):
+        gp.policy = N.GroupedGemmPolicy(num_comm_ctas=dispatch_ctas, num_compute_ctas=128, tile_n=256,
+                                        mma_sm_count=mma_sm_count)
         lhs.view(torch.int16).fill_(0x7f7f)
         eo.view(torch.int16).fill_(0x7f7f)
         rc, plan = api.create_bf16_a2a_grouped_gemm(gp)

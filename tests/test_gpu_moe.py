@@ -77,12 +77,14 @@ def test_moe_dispatch_fc1_matches_oracle(case):
         _check(world, rank, experts_local, toks, weights, offs, src, capacity, lhs, out)
 
 
+@pytest.mark.parametrize("auto", [False, True])
 @pytest.mark.parametrize("case", [c for c in MOE_CASES if c[7] == 256])
-def test_moe_dispatch_fc1_on_cta_pairs_matches_oracle(case):
-    # policy.mma_sm_count = 2: 256 x 256 tiles on CTA pairs, whole pairs of communication CTAs
+def test_moe_dispatch_fc1_on_cta_pairs_matches_oracle(case, auto):
+    # policy.mma_sm_count = 2: 256 x 256 tiles on CTA pairs, whole pairs of communication CTAs; with
+    # policy.num_comm_ctas = 0 (Auto) no communication CTA at all: one thread of every compute CTA pulls
     from tests import harness as H
     world, tokens, experts, topk, k, n, comm, tile_n = case
-    comm += comm % 2
+    comm = 0 if auto else comm + comm % 2
     experts_local = experts // world
     chosen = _routes(world, tokens, experts, topk, synthetic.GROUPED_SEED)
     toks = [synthetic.normal_bf16((tokens, k), synthetic.GROUPED_SEED + 31 * r + 5, 1.0) for r in range(world)]
@@ -134,7 +136,7 @@ def test_moe_boundary_row_counts_empty_experts_and_replay_with_new_routes(mma_sm
 
     first, second = make(counts_a), make(counts_b)
     capacity = 512
-    comm = 3 if mma_sm_count == 1 else 4
+    comm = 3 if mma_sm_count == 1 else 0  # pairs: Auto, the embedded pull
     lhs, out = H.moe_dispatch_fc1(world, 0, e, toks, weights, first[0], first[1], capacity, comm=comm, launches=2,
                                   mma_sm_count=mma_sm_count)
     _check(world, 0, e, toks, weights, first[0], first[1], capacity, lhs, out)

@@ -635,19 +635,37 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) grouped
         uint32_t stage = 0, phase = 0;
         int32_t expert = 0;
         bool ok = true;
+        // The flag of the NEXT tile's panel is looked at late in this tile's K loop, when the ring is
+        // full and a global round trip costs the GEMM nothing; a panel seen complete then needs no
+        // wait (and no bubble) at the tile boundary.
+        bool panel_seen = false;
         for (int32_t t = pair_id; ok && t < tiles; t += pairs) {
           int32_t mp, nt;
           decode(t, expert, mp, nt);
           const int32_t mt = mp * 2 + int32_t(rank);  // this CTA's 128-row panel
-          if (!kCombine && int64_t(mt) * kBlockM < rows_of(expert)) {
+          if (!kCombine && !panel_seen && int64_t(mt) * kBlockM < rows_of(expert)) {
             const int64_t flag = (int64_t(expert) * p.cap_tiles + mt) * kReadyFlagStride;
             ok = flag_wait<false>(p.ready + flag, w.epoch, w, kSitePanelReady, uint32_t(flag / kReadyFlagStride));
             ptx::fence_proxy_async_global();
             if (!ok) break;
           }
+          panel_seen = false;
           const CUtensorMap* map_a = p.maps_a + expert;
           const CUtensorMap* map_b = p.maps_b + expert;
+          const int32_t look_at = k_blocks > 16 ? k_blocks - 8 : -1;
           for (int32_t kb = 0; kb < k_blocks; ++kb) {
+            if (!kCombine && kb == look_at && t + pairs < tiles) {
+              int32_t next_expert = expert, next_mp, next_nt;
+              decode(t + pairs, next_expert, next_mp, next_nt);
+              const int32_t next_mt = next_mp * 2 + int32_t(rank);
+              if (int64_t(next_mt) * kBlockM >= rows_of(next_expert)) {
+                panel_seen = true;  // no rows in this half: nothing to wait for
+              } else if (ptx::ld_acquire_gpu(p.ready + (int64_t(next_expert) * p.cap_tiles + next_mt) * kReadyFlagStride) >=
+                         w.epoch) {
+                ptx::fence_proxy_async_global();
+                panel_seen = true;
+              }
+            }
             ok = mbar_wait(empty_bar(stage), phase ^ 1u, w, kSiteSmemEmpty);
             if (!ok) break;
             const uint32_t a_dst = base + stage * Layout::kStageBytes;

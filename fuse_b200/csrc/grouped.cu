@@ -54,10 +54,12 @@ cudaError_t create_plan(const fuse_bf16_grouped_gemm_params& p, bool combine, fu
   // is the epilogue staging the dispatch kernel does not use, so the GEMM keeps all six stages).  A
   // pull over NVLink is bounded by what ONE SM may have in flight, so 148 SMs pulling a little each
   // move far more than 20 CTAs pulling flat out.  FUSE_B200_EMBEDDED_PULL=0 keeps communication CTAs.
-  bool embedded = dispatch_ctas == 0 && !combine && p.policy.mma_sm_count == 2 && p.policy.tile_n == 256 &&
-                  info.sm_count % 2 == 0;
-  if (const char* text = std::getenv("FUSE_B200_EMBEDDED_PULL"))
-    if (std::atoi(text) == 0) embedded = false;
+  const bool embedded_possible = !combine && p.policy.mma_sm_count == 2 && p.policy.tile_n == 256 && info.sm_count % 2 == 0;
+  bool embedded = dispatch_ctas == 0 && embedded_possible;
+  if (const char* text = std::getenv("FUSE_B200_EMBEDDED_PULL")) {  // 1 / 0: force / forbid, whatever the budget says
+    embedded = std::atoi(text) != 0 && embedded_possible;
+    if (embedded) dispatch_ctas = 0;
+  }
   if (dispatch_ctas == 0 && !combine && !embedded) {
     const double rows = 0.5 * double(p.experts) * p.expert_row_capacity;
     const int group = p.policy.mma_sm_count == 2 ? 2 : 1;

@@ -20,7 +20,13 @@ tensors, so the symmetric buffers are free again as soon as the copy has run; a 
 the next invocation into them after this rank has taken part in the invocation in between (every
 operator ends with, or is gated by, an epoch handshake between the ranks).  All ranks must call the
 operators in the same order.  Weight gradients are local (no cross-rank reduction: the caller owns
-it, include/fuse/operators/ulysses/oproj_backward.h:202 of the reference)."""
+it, include/fuse/operators/ulysses/oproj_backward.h:202 of the reference); with
+`reduce_weight_grads=True` this caller-side step is done here: a hook on each weight leaf starts the
+all-reduce of its `.grad` over the group, on NCCL's own stream, as soon as autograd has stored it,
+so the reduction of dW_o travels under the attention and QKV backward kernels;
+`finish_weight_grads()` makes the current stream wait for the reductions still in flight (call it
+before the optimizer reads the gradients).  The hook reduces what `.grad` holds, so with gradient
+accumulation switch `reduce_weight_grads` on for the last micro-batch only."""
 from __future__ import annotations
 
 import torch
@@ -39,7 +45,7 @@ def _check(rc: int, what: str) -> None:
 
 class UlyssesProjections:
     def __init__(self, world: World, *, batch: int, seq_local: int, hidden: int, q_heads: int, kv_heads: int,
-                 head_dim: int, max_swizzle_size: int = 8, tag: str = "ulysses"):
+                 head_dim: int, max_swizzle_size: int = 8, tag: str = "ulysses", reduce_weight_grads: bool = False):
         cp = world.world_size
         if q_heads % cp or kv_heads % cp:
             raise ValueError("heads must divide over the ranks")
@@ -89,6 +95,28 @@ class UlyssesProjections:
                                         device=self.device)
         self._epochs = dict(qkv=0, oproj=0, qkv_bwd=0, oproj_bwd=0)
         self._attn_slot = 0
+        self.reduce_weight_grads = reduce_weight_grads and cp > 1
+        self._pending = []
+
+    # ------------------------------------------------------------------ cross-rank weight gradients
+    def _hook(self, weight: torch.Tensor) -> None:
+        """Once per weight leaf: start the all-reduce of its gradient when autograd has stored it."""
+        if not (weight.is_leaf and weight.requires_grad) or getattr(weight, "_fuse_b200_hooked", False):
+            return
+        import torch.distributed as dist
+
+        def start(param):
+            if self.reduce_weight_grads and param.grad is not None:
+                self._pending.append(dist.all_reduce(param.grad, group=self.world.group, async_op=True))
+
+        weight.register_post_accumulate_grad_hook(start)
+        weight._fuse_b200_hooked = True
+
+    def finish_weight_grads(self) -> None:
+        """The current stream waits for every weight-gradient reduction still in flight."""
+        for work in self._pending:
+            work.wait()
+        self._pending.clear()
 
     # ------------------------------------------------------------------ plumbing
     def _stream(self) -> int:
@@ -189,12 +217,16 @@ class UlyssesProjections:
         """x [B*S_local, hidden], w_qkv [(q+2kv)*d, hidden] -> (Q, K, V) of this rank's heads."""
         self._expect(x, (self.m, self.hidden), "x")
         self._expect(w_qkv, (self.width, self.hidden), "w_qkv")
+        if self.cp > 1:
+            self._hook(w_qkv)
         return _QkvProjection.apply(self, x, w_qkv)
 
     def oproj(self, attn: torch.Tensor, w_o: torch.Tensor):
         """attn [B*S_global, q_local*d] (this rank's heads), w_o [hidden, q_heads*d] -> y [B*S_local, hidden]."""
         self._expect(attn, (self.rows_global, self.q_local), "attn")
         self._expect(w_o, (self.hidden, self.attn_width), "w_o")
+        if self.cp > 1:
+            self._hook(w_o)
         return _OutputProjection.apply(self, attn, w_o)
 
     def _expect(self, t: torch.Tensor, shape, name: str) -> None:

@@ -51,6 +51,20 @@ def main():
                                ("dw_o", wo.grad, want["dw_o"])):
             bad, worst = close(got, ref)
             assert bad == 0, (rank, step, name, bad, worst)
+    # the caller-side reduction of the weight gradients, started behind each weight GEMM
+    proj.reduce_weight_grads = True
+    everyone = reference_world(xs, w_qkv, w_o, dys, cp=cp, seq_local=seq, q_heads=q_heads, kv_heads=kv_heads,
+                               head_dim=head_dim)
+    xg, wq, wo = (t.clone().requires_grad_(True) for t in (xs[rank], w_qkv, w_o))
+    q, k, v = proj.qkv(xg, wq)
+    y = proj.oproj(toy_attention(q, k, v, q_heads // cp, kv_heads // cp, head_dim).contiguous(), wo)
+    y.backward(dys[rank])
+    proj.finish_weight_grads()
+    torch.cuda.synchronize()
+    for name, got in (("dw_qkv", wq.grad), ("dw_o", wo.grad)):
+        ref = sum(e[name].float() for e in everyone)
+        bad, worst = close(got, ref, atol=0.03, rtol=0.03)  # BF16 all-reduce of BF16 partial sums
+        assert bad == 0, (rank, "reduced " + name, bad, worst)
     dist.barrier()
     proj.world.close()
     dist.destroy_process_group()

@@ -658,6 +658,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) grouped
               int32_t next_expert = expert, next_mp, next_nt;
               decode(t + pairs, next_expert, next_mp, next_nt);
               const int32_t next_mt = next_mp * 2 + int32_t(rank);
+              if (next_expert != expert) {  // the next tile's operand maps, on their way into the descriptor cache
+                ptx::prefetch_tensormap(p.maps_a + next_expert);
+                ptx::prefetch_tensormap(p.maps_b + next_expert);
+              }
               if (int64_t(next_mt) * kBlockM >= rows_of(next_expert)) {
                 panel_seen = true;  // no rows in this half: nothing to wait for
               } else if (ptx::ld_acquire_gpu(p.ready + (int64_t(next_expert) * p.cap_tiles + next_mt) * kReadyFlagStride) >=

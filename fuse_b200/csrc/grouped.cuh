@@ -548,6 +548,14 @@ __global__ void __launch_bounds__(kThreads, 1) grouped_gemm_kernel(const Grouped
   // (communication.cuh:237-250).
   cooperative_groups::this_grid().sync();
   if (blockIdx.x == 0 && threadIdx.x < 32) {
+    // Combine: "done" tells a peer that its branch rows are complete, so a launch in which a wait
+    // gave up publishes nothing (the peers run out their own bounded wait and record it).  Dispatch:
+    // "done" only says that this rank no longer reads the peer's tokens, true after a failure too.
+    if constexpr (kCombine) {
+      uint32_t failed = lane == 0 && aborted(w) ? 1u : 0u;
+      failed = __shfl_sync(0xffffffffu, failed, 0);
+      if (failed) return;
+    }
     if (lane == 0) ptx::fence_sc_sys();
     __syncwarp();
     if (lane < p.world) ptx::st_release_sys(p.peer_done[lane] + p.rank * kReadyFlagStride, w.epoch);
@@ -817,6 +825,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1) grouped
 
   cooperative_groups::this_grid().sync();
   if (blockIdx.x == 0 && threadIdx.x < 32) {
+    // Combine: "done" tells a peer that its branch rows are complete, so a launch in which a wait
+    // gave up publishes nothing (the peers run out their own bounded wait and record it).  Dispatch:
+    // "done" only says that this rank no longer reads the peer's tokens, true after a failure too.
+    if constexpr (kCombine) {
+      uint32_t failed = lane == 0 && aborted(w) ? 1u : 0u;
+      failed = __shfl_sync(0xffffffffu, failed, 0);
+      if (failed) return;
+    }
     if (lane == 0) ptx::fence_sc_sys();
     __syncwarp();
     if (lane < p.world) ptx::st_release_sys(p.peer_done[lane] + p.rank * kReadyFlagStride, w.epoch);

@@ -322,12 +322,16 @@ def oproj_forward_mxfp8(world, rank, batch, seq_local, peer_data, peer_scales, w
 
 
 def moe_dispatch_fc1(world, rank, experts_local, tokens_bits, weights_bits, row_offsets, sources, capacity,
-                     comm=4, compute=128, tile_n=256, launches=1, second_route=None, mma_sm_count=1):
+                     comm=4, compute=128, tile_n=256, launches=1, second_route=None, mma_sm_count=1,
+                     starved_first=False):
     """One rank of the MoE dispatch -> FC1 grouped GEMM.  tokens_bits[r] [T, K] per rank;
     weights_bits [experts_local, N, K]; row_offsets int64 [E+1]; sources int32 [rows, 3].
     Returns (lhs [E, capacity, K] bits, output [E, capacity, N] bits); unused capacity holds 0x7f7f.
     With `second_route` = (row_offsets, sources) the same plan is launched again with new device
-    routes (no re-creation), and that launch's results are returned."""
+    routes (no re-creation), and that launch's results are returned.
+    starved_first (world > 1): the plan is first launched with a 30 ms wait budget while no peer has
+    entered the invocation -- the pull's wait for the peers' started epoch runs out, the launch must
+    return with a status record -- and is then launched normally."""
     e, n, k = weights_bits.shape
     toks = [to_device(t) for t in tokens_bits]
     w = to_device(weights_bits)
@@ -353,10 +357,25 @@ def moe_dispatch_fc1(world, rank, experts_local, tokens_bits, weights_bits, row_
     rc, plan = api.create_bf16_a2a_grouped_gemm(p)
     assert rc == 0, f"create_bf16_a2a_grouped_gemm -> cudaError {rc}"
     opts = options(flags=N.SKIP_PEER_WAIT if world > 1 else 0)
-    for _ in range(launches):
-        rc = api.launch_bf16_grouped_gemm(plan, 0, opts)
+    if starved_first:
+        assert world > 1
+        rc = api.launch_bf16_grouped_gemm(plan, 0, options(wait_ms=30.0))
         assert rc == 0, f"launch_bf16_grouped_gemm -> cudaError {rc}"
-    check_status()
+        torch.cuda.synchronize()
+        status = api.read_status(clear=True)
+        assert status[0] != 0 and status[1] in (1, 2, 3), f"the starved launch did not report: {status[:8]}"
+        lhs.view(torch.int16).fill_(0x7f7f)
+        out.view(torch.int16).fill_(0x7f7f)
+        launches += 1  # the started epoch below counts every launch
+        for _ in range(launches - 1):
+            rc = api.launch_bf16_grouped_gemm(plan, 0, opts)
+            assert rc == 0, f"launch_bf16_grouped_gemm -> cudaError {rc}"
+        check_status()
+    else:
+        for _ in range(launches):
+            rc = api.launch_bf16_grouped_gemm(plan, 0, opts)
+            assert rc == 0, f"launch_bf16_grouped_gemm -> cudaError {rc}"
+        check_status()
     if second_route is not None:
         lhs.view(torch.int16).fill_(0x7f7f)
         out.view(torch.int16).fill_(0x7f7f)
@@ -372,7 +391,7 @@ def moe_dispatch_fc1(world, rank, experts_local, tokens_bits, weights_bits, row_
 
 
 def moe_fc2_combine(world, experts_local, lhs_bits, weights_bits, row_offsets, sources, capacity, tokens, topk,
-                    tile_n=256, mma_sm_count=1, launches=1):
+                    tile_n=256, mma_sm_count=1, launches=1, starved_first=False):
     """Every rank of the expert FC2 -> combine operator, emulated one after the other on one GPU.
     lhs_bits[r] [E, capacity, K], weights_bits[r] [E, N, K], row_offsets[r] int64 [E+1], sources[r]
     int32 [rows, 3] per rank r.  Returns (outputs [r] -> [E, capacity, N] bits, received [r] ->
@@ -401,6 +420,24 @@ def moe_fc2_combine(world, experts_local, lhs_bits, weights_bits, row_offsets, s
         rc, plan = api.create_bf16_grouped_gemm_a2a(p)
         assert rc == 0, f"create_bf16_grouped_gemm_a2a -> cudaError {rc}"
         opts = options(flags=N.SKIP_PEER_WAIT if world > 1 else 0)
+        if starved_first and r == 0:
+            # no destination has entered the invocation: the wait before the first remote write runs
+            # out, and the failed launch must not tell anyone that its rows are in place
+            assert world > 1
+            rc = api.launch_bf16_grouped_gemm(plan, 0, options(wait_ms=30.0))
+            assert rc == 0, f"launch_bf16_grouped_gemm -> cudaError {rc}"
+            torch.cuda.synchronize()
+            status = api.read_status(clear=True)
+            assert status[0] != 0 and status[1] in (1, 2, 3), f"the starved launch did not report: {status[:8]}"
+            for d_ in done:
+                assert int(d_.abs().sum()) == 0, "a combine launch that timed out published its done epoch"
+            for t in received:
+                assert int((t.view(torch.int16) != 0x7f7f).sum()) == 0, "a starved combine launch wrote remote rows"
+            out.view(torch.int16).fill_(0x7f7f)
+            started[0].zero_()  # the starved launch's own started epoch: the checks below count clean launches
+            api.destroy_bf16_grouped_gemm(plan)
+            rc, plan = api.create_bf16_grouped_gemm_a2a(p)
+            assert rc == 0
         for _ in range(launches):
             rc = api.launch_bf16_grouped_gemm(plan, 0, opts)
             assert rc == 0, f"launch_bf16_grouped_gemm -> cudaError {rc}"

@@ -97,6 +97,23 @@ def test_moe_dispatch_fc1_on_cta_pairs_matches_oracle(case, auto):
         _check(world, rank, experts_local, toks, weights, offs, src, capacity, lhs, out)
 
 
+@pytest.mark.parametrize("comm,mma_sm_count", [(4, 1), (4, 2), (0, 2)])
+def test_moe_dispatch_gives_up_when_a_peer_never_enters_and_runs_clean_afterwards(comm, mma_sm_count):
+    # bounded wait of the pull (communication CTAs, and the copy thread embedded in every compute CTA):
+    # a peer's started epoch that nothing publishes
+    from tests import harness as H
+    world, tokens, experts, topk, k, n = 2, 96, 4, 2, 512, 512
+    experts_local = experts // world
+    chosen = _routes(world, tokens, experts, topk, synthetic.GROUPED_SEED)
+    toks = [synthetic.normal_bf16((tokens, k), synthetic.GROUPED_SEED + 31 * r + 5, 1.0) for r in range(world)]
+    weights = synthetic.normal_bf16((experts_local, n, k), synthetic.GROUPED_SEED + 1000, 0.02)
+    offs, src = _rows_for(world, 0, experts_local, tokens, topk, chosen)
+    capacity = max(256, int(-(-int(np.diff(offs).max()) // 256) * 256))
+    lhs, out = H.moe_dispatch_fc1(world, 0, experts_local, toks, weights, offs, src, capacity, comm=comm,
+                                  mma_sm_count=mma_sm_count, starved_first=True)
+    _check(world, 0, experts_local, toks, weights, offs, src, capacity, lhs, out)
+
+
 @pytest.mark.parametrize("mma_sm_count", [1, 2])
 def test_moe_every_boundary_row_count_of_the_reference_list(mma_sm_count):
     # the reference's boundary list (benchmarks/sm103/grouped_validation.cuh:33), one expert each
@@ -157,14 +174,19 @@ COMBINE_CASES = [
 ]
 
 
+@pytest.mark.parametrize("starved_first", [False, True])
 @pytest.mark.parametrize("case", COMBINE_CASES)
-def test_moe_fc2_combine_matches_oracle(case):
+def test_moe_fc2_combine_matches_oracle(case, starved_first):
     # The reference's checks for this direction (benchmarks/sm103/grouped_validation.cuh:119-157): the
     # expert's output slab within 0.002 + 0.008|b| with untouched capacity still poisoned, and every
     # received branch row BIT-EXACT equal to the row its owner's slab holds; rows no expert routes keep
     # the poison.
+    # starved_first: rank 0 first launches while no destination has entered the invocation; the
+    # bounded wait before its first remote write runs out and the launch publishes no done epoch.
     from tests import harness as H
     world, tokens, experts, topk, k, n, tile_n, mma = case
+    if starved_first and (world == 1 or tile_n != 256):
+        pytest.skip("needs a peer; one case per tile family is enough")
     e_local = experts // world
     chosen = _routes(world, tokens, experts, topk, seed=23)
     routes = [_rows_for(world, r, e_local, tokens, topk, chosen) for r in range(world)]
@@ -172,7 +194,8 @@ def test_moe_fc2_combine_matches_oracle(case):
     lhs = [synthetic.normal_bf16((e_local, capacity, k), synthetic.GROUPED_SEED + 7 * r, 1.0) for r in range(world)]
     weights = [synthetic.normal_bf16((e_local, n, k), synthetic.GROUPED_SEED + 500 + r, 0.02) for r in range(world)]
     outputs, received = H.moe_fc2_combine(world, e_local, lhs, weights, [o for o, _ in routes], [s for _, s in routes],
-                                          capacity, tokens, topk, tile_n=tile_n, mma_sm_count=mma, launches=2)
+                                          capacity, tokens, topk, tile_n=tile_n, mma_sm_count=mma, launches=2,
+                                          starved_first=starved_first)
     want_received = [np.full((tokens * topk, n), POISON, dtype=np.uint16) for _ in range(world)]
     table = O.ptr_array(want_received)
     for r in range(world):

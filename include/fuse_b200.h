@@ -428,7 +428,10 @@ typedef struct fuse_grouped_token_source {
 } fuse_grouped_token_source;
 /* grouped_gemm.h:17-53 (GroupedGemmPolicy).  This implementation honours num_comm_ctas,
  * num_compute_ctas and tile_n (128 or 256); mma_sm_count 1, or 2 = CTA pairs on
- * 256 x 256 tiles (needs tile_n 256 and an even num_comm_ctas); swap_ab must be false. */
+ * 256 x 256 tiles (needs tile_n 256 and an even num_comm_ctas); swap_ab must be false.
+ * num_comm_ctas == 0 is Auto: on CTA pairs the dispatch then has no communication CTA (one thread
+ * of every compute CTA pulls), on one-CTA tiles the host planner picks the budget for slabs half
+ * full and the share of the rows that is remote. */
 typedef struct fuse_grouped_gemm_policy {
   int32_t num_comm_ctas, num_compute_ctas, swizzle;
   uint8_t along_n;

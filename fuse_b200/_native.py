@@ -346,6 +346,8 @@ SYMBOLS = {
     "fuse_recommended_a2a_lhs_gemm_comm_ctas": (C.c_int32, [C.POINTER(GemmProblem), C.POINTER(UlyssesRoute)]),
     "fuse_b200_plan": (C.c_int, [C.c_int32, C.c_double, C.c_double, C.c_int64, C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                  C.POINTER(C.c_double * 5)]),
+    "fuse_b200_plan_remote": (C.c_int, [C.c_int32, C.c_double, C.c_double, C.c_int64, C.c_int32, C.c_int32, C.c_int32,
+                                        C.c_int32, C.c_double, C.POINTER(C.c_double * 5)]),
     "fuse_b200_generate_bf16": (C.c_int, [_P, C.c_uint64, C.c_uint64, C.c_float, C.c_int, _P]),
     "fuse_b200_tile_order_decode": (C.c_int, [C.c_int32] * 4 + [C.c_int64, C.POINTER(C.c_int32), C.POINTER(C.c_int32)]),
     "fuse_b200_select_swizzle": (C.c_int32, [C.c_int32] * 3),

@@ -68,11 +68,12 @@ def recommended_a2a_lhs_gemm_comm_ctas(problem: GemmProblem, route: UlyssesRoute
 
 
 def plan(kind: int, flops: float, nbytes: float, tiles: int, sm_count: int = 148, group: int = 2,
-         explicit_comm_ctas: int = 0, embedded_allowed: bool = True) -> dict:
-    """The host planner's choice for one launch (fuse_b200_plan): communication CTAs or embedded copy warps."""
+         explicit_comm_ctas: int = 0, embedded_allowed: bool = True, remote_share: float = 0.0) -> dict:
+    """The host planner's choice for one launch (fuse_b200_plan_remote): communication CTAs or embedded
+    copy warps.  remote_share: fraction of the bytes that crosses NVLink, (world - 1) / world."""
     out = (C.c_double * 5)()
-    rc = N.lib().fuse_b200_plan(kind, flops, nbytes, tiles, sm_count, group, explicit_comm_ctas,
-                                1 if embedded_allowed else 0, C.byref(out))
+    rc = N.lib().fuse_b200_plan_remote(kind, flops, nbytes, tiles, sm_count, group, explicit_comm_ctas,
+                                       1 if embedded_allowed else 0, remote_share, C.byref(out))
     if rc != 0:
         raise ValueError(f"fuse_b200_plan -> cudaError {rc}")
     return {"comm_ctas": int(out[0]), "embedded": bool(out[1]), "makespan_us": out[2], "compute_us": out[3],

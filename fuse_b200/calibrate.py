@@ -266,6 +266,12 @@ def dispatch_rates(out):
 # and on 8 GPUs ran at >= 14.4 GB/s per CTA with 20 (>= 0.32).  Too few CTAs costs far more than
 # too many (16 against 20 on 2 GPUs: -11 %; 28 against 20: -4 %), so the low side of the range.
 REMOTE_CTA_FACTOR = 0.30
+# The gradient PUSH (BF16 QKV backward data, C2 shape) is the one transfer whose embedded variant loses
+# over NVLink: 0.570 ms on one GPU, 0.598-0.606 on 2 (16 communication CTAs: 0.612-0.617), 0.638-0.645
+# on 4 (12 CTAs 0.630, 16 CTAs 0.611-0.614, 20 CTAs 0.619, 24 CTAs 0.673).  Communication CTAs are
+# flat in the remote share, the embedded push grows with it; the crossover lies between 1/2 and 3/4.
+PUSH_EMBEDDED_MAX_REMOTE_SHARE = 0.6
+PUSH_REMOTE_MIN_CTAS = 16
 
 
 def model_comm_us(flops, nbytes, tiles, comm, tflops_per_sm, cta_gbs, startup_us=25.0, sms=SMS, group=2):
@@ -304,6 +310,9 @@ struct Calibration {
   double embedded_compute_factor, comm_model_factor, startup_us;
   // rate of a communication CTA whose bytes cross NVLink, relative to the local rate above
   double remote_cta_factor;
+  // gradient push: the embedded copy warps are used up to this share of remote bytes, beyond it
+  // communication CTAs, at least this many (measured on 2 and 4 GPUs)
+  double push_embedded_max_remote_share, push_remote_min_ctas;
 };
 
 constexpr Calibration kCalibrationB200 = {
@@ -343,6 +352,8 @@ def derive(raw):
             for comm, ms in raw["pull"]["fused_comm_ms"].items())),
         ("startup_us", 25.0),
         ("remote_cta_factor", REMOTE_CTA_FACTOR),
+        ("push_embedded_max_remote_share", PUSH_EMBEDDED_MAX_REMOTE_SHARE),
+        ("push_remote_min_ctas", float(PUSH_REMOTE_MIN_CTAS)),
     ]
 
 
@@ -373,7 +384,7 @@ def main():
         os.makedirs(json_dir, exist_ok=True)
         with open(os.path.join(json_dir, "b200.json"), "w") as f:
             json.dump(raw, f, indent=1)
-        body = "\n".join(f"    /* {name:26s} */ {value:.4g}," for name, value in values)
+        body = "\n".join(f"    /* {name:30s} */ {value:.4g}," for name, value in values)
         with open(os.path.join(header_dir, "calibration_b200.h"), "w") as f:
             f.write(HEADER % body)
 

@@ -386,12 +386,19 @@ int32_t fuse_recommended_a2a_lhs_gemm_comm_ctas(const fuse_gemm_problem* problem
 // MXFP8, 6 MoE dispatch).  out = {comm_ctas, embedded, makespan_us, compute_us, transfer_us}.
 int fuse_b200_plan(int32_t kind, double flops, double bytes, int64_t tiles, int32_t sm_count, int32_t group,
                    int32_t explicit_comm_ctas, int32_t embedded_allowed, double out[5]) {
+  return fuse_b200_plan_remote(kind, flops, bytes, tiles, sm_count, group, explicit_comm_ctas, embedded_allowed, 0.0, out);
+}
+
+int fuse_b200_plan_remote(int32_t kind, double flops, double bytes, int64_t tiles, int32_t sm_count, int32_t group,
+                          int32_t explicit_comm_ctas, int32_t embedded_allowed, double remote_share, double out[5]) {
+  if (!(remote_share >= 0.0 && remote_share < 1.0)) return int(cudaErrorInvalidValue);
   if (kind < 0 || kind >= fuse_b200::planner::kKinds || !(flops > 0.0) || !(bytes >= 0.0) || tiles <= 0 ||
       sm_count <= 0 || (group != 1 && group != 2) || explicit_comm_ctas < 0 || explicit_comm_ctas >= sm_count ||
       out == nullptr)
     return int(cudaErrorInvalidValue);
   const fuse_b200::planner::Choice c = fuse_b200::planner::choose(
-      fuse_b200::planner::Kind(kind), flops, bytes, tiles, sm_count, group, explicit_comm_ctas, embedded_allowed != 0);
+      fuse_b200::planner::Kind(kind), flops, bytes, tiles, sm_count, group, explicit_comm_ctas, embedded_allowed != 0,
+      remote_share);
   out[0] = c.comm_ctas;
   out[1] = c.embedded;
   out[2] = c.makespan_us;

@@ -56,7 +56,7 @@ inline Services services(Kind kind) {
   switch (kind) {
     case kLhsPullBf16: return {c.bf16_pair_tflops_per_sm, c.pull_cta_gbs, c.pull_embedded_gbs, c.embedded_compute_factor, c.comm_model_factor, c.startup_us, c.remote_cta_factor};
     case kLhsPullMx: return {c.mx_pair_tflops_per_sm, c.pull_cta_gbs, c.pull_embedded_gbs, c.embedded_compute_factor, c.comm_model_factor, c.startup_us, c.remote_cta_factor};
-    case kGradPushBf16: return {c.bf16_pair_tflops_per_sm, c.push_cta_gbs, c.push_embedded_gbs, c.embedded_compute_factor, c.comm_model_factor, c.startup_us, c.remote_cta_factor};
+    case kGradPushBf16: return {c.bf16_pair_tflops_per_sm, c.push_cta_gbs, c.push_embedded_gbs, c.embedded_compute_factor, c.comm_model_factor, c.startup_us, 1.0};
     case kGradPullMx: return {c.mx_pair_tflops_per_sm, c.gradpull_cta_gbs, c.gradpull_embedded_gbs, c.embedded_compute_factor, c.comm_model_factor, c.startup_us, c.remote_cta_factor};
     case kQkvPushBf16: return {c.bf16_cta_tflops_per_sm, c.qkv_push_cta_gbs, 0.0, 1.0, c.comm_model_factor, c.startup_us, c.remote_cta_factor};
     case kQkvPushMx: return {c.mx_cta_tflops_per_sm, c.qkv_push_cta_gbs, 0.0, 1.0, c.comm_model_factor, c.startup_us, c.remote_cta_factor};
@@ -76,7 +76,8 @@ inline Choice score_comm(const Services& s, double flops, double bytes, int64_t 
     return out;
   }
   const double tau = flops / double(tiles) / (double(group) * s.tflops_per_sm * 1.0e6);  // us per tile and unit
-  // bytes that cross NVLink move at the (lower) remote rate of a communication CTA
+  // bytes that cross NVLink move at the (lower) remote rate of a communication CTA (pulls: loads
+  // wait for the round trip; pushes are posted stores and measured flat in the remote share)
   const double weighted = bytes * ((1.0 - remote_share) + remote_share / s.remote_cta);
   const double t_c = s.startup_us + weighted / (double(comm) * s.cta_gbs * 1.0e3);
   const int64_t all = compute + comm_units;
@@ -128,6 +129,16 @@ inline Choice choose(Kind kind, double flops, double bytes, int64_t tiles, int s
     // and over NVLink communication CTAs lose more than the embedded warps do; a budget is taken
     // where the transfer is the longer side (narrow GEMMs), which the embedded warps cannot shorten.
     const Choice e = score_embedded(s, flops, bytes, tiles, sm_count, group);
+    // The gradient push is the one transfer whose embedded variant loses over NVLink (measured: ahead
+    // of 16 communication CTAs by 2 % on 2 GPUs, behind by 4.5 % on 4): beyond the calibrated share
+    // of remote bytes it runs on communication CTAs, at least the calibrated number of them.
+    const Calibration& c = kCalibrationB200;
+    if (kind == kGradPushBf16 && remote_share > c.push_embedded_max_remote_share) {
+      const int floor_ctas = int(c.push_remote_min_ctas);
+      if (best.comm_ctas < floor_ctas && floor_ctas % group == 0 && floor_ctas < sm_count)
+        best = score_comm(s, flops, bytes, tiles, sm_count, group, floor_ctas, remote_share);
+      return best;
+    }
     if (e.makespan_us * 0.90 <= best.makespan_us) best = e;
   }
   return best;

@@ -201,6 +201,11 @@ FUSE_API int32_t fuse_recommended_a2a_lhs_gemm_comm_ctas(const fuse_gemm_problem
  * out = {comm_ctas, embedded (0/1), makespan_us, compute_us, transfer_us}.  Host only. */
 FUSE_API int fuse_b200_plan(int32_t kind, double flops, double bytes, int64_t tiles, int32_t sm_count, int32_t group,
                             int32_t explicit_comm_ctas, int32_t embedded_allowed, double out[5]);
+/* The same with the share of the bytes that crosses NVLink, (world - 1) / world for the all-to-all
+ * routes (fuse_b200_plan plans for local copies, share 0). */
+FUSE_API int fuse_b200_plan_remote(int32_t kind, double flops, double bytes, int64_t tiles, int32_t sm_count,
+                                   int32_t group, int32_t explicit_comm_ctas, int32_t embedded_allowed,
+                                   double remote_share, double out[5]);
 
 /* ---------------------------------------------------------------------------------------------
  * Backward (BF16).  include/fuse/operators/ulysses/{backward_common,qkv_backward,oproj_backward}.h

@@ -93,8 +93,8 @@ def test_planner_follows_the_scorer_rules_of_the_reference():
     for budget in (8, 20, 32):
         explicit = api.plan(0, explicit_comm_ctas=budget, **c2)
         assert explicit["comm_ctas"] == budget and not explicit["embedded"]
-        # Auto is the minimum over the candidates (a communication budget must beat the embedded warps by 3 %)
-        assert explicit["makespan_us"] >= auto["makespan_us"] * 0.97 * (1 - 1e-9)
+        # Auto is the minimum over the candidates (a communication budget must beat the embedded warps by 10 %)
+        assert explicit["makespan_us"] >= auto["makespan_us"] * 0.90 * (1 - 1e-9)
     ctas_only = api.plan(0, embedded_allowed=False, **c2)
     assert not ctas_only["embedded"] and ctas_only["comm_ctas"] in (4, 8, 12, 16, 20, 24, 32, 40, 48)
     candidates = [api.plan(0, explicit_comm_ctas=b, **c2)["makespan_us"] for b in (4, 8, 12, 16, 20, 24, 32, 40, 48)]
@@ -109,6 +109,17 @@ def test_planner_follows_the_scorer_rules_of_the_reference():
         plan = api.plan(0, c2["flops"], c2["nbytes"] * scale, c2["tiles"], embedded_allowed=False)
         assert plan["comm_ctas"] >= last_budget and plan["makespan_us"] >= last_span * (1 - 1e-9)
         last_budget, last_span = plan["comm_ctas"], plan["makespan_us"]
+    # over NVLink (share of remote bytes = (world - 1) / world): pulls stay on the embedded copy warps, the
+    # gradient push moves to communication CTAs (at least 16) beyond the calibrated share, and the
+    # MoE dispatch on one-CTA tiles gets a larger budget the more of its rows are remote
+    bwd = dict(flops=2.0 * 16384 * 4096 * 6144, nbytes=16384 * 6144 * 2.0, tiles=64 * 16)
+    assert api.plan(0, remote_share=7 / 8, **c2)["embedded"]
+    assert api.plan(2, remote_share=0.5, **bwd)["embedded"]
+    far = api.plan(2, remote_share=0.75, **bwd)
+    assert not far["embedded"] and far["comm_ctas"] >= 16
+    c5 = dict(flops=2.0 * 65536 * 4096 * 7168, nbytes=65536 * 7168 * 2.0, tiles=512 * 16, group=1, embedded_allowed=False)
+    budgets = [api.plan(6, remote_share=share, **c5)["comm_ctas"] for share in (0.0, 0.5, 0.75, 0.875)]
+    assert budgets == sorted(budgets) and budgets[-1] > budgets[0]
     # budgets of CTA-pair kernels come in pairs; every kind answers; bad requests are rejected
     for kind in range(7):
         plan = api.plan(kind, 1.0e12, 5.0e8, 2048, group=2)

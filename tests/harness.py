@@ -323,7 +323,7 @@ def oproj_forward_mxfp8(world, rank, batch, seq_local, peer_data, peer_scales, w
 
 def moe_dispatch_fc1(world, rank, experts_local, tokens_bits, weights_bits, row_offsets, sources, capacity,
                      comm=4, compute=128, tile_n=256, launches=1, second_route=None, mma_sm_count=1,
-                     starved_first=False):
+                     starved_first=False, graph=False):
     """One rank of the MoE dispatch -> FC1 grouped GEMM.  tokens_bits[r] [T, K] per rank;
     weights_bits [experts_local, N, K]; row_offsets int64 [E+1]; sources int32 [rows, 3].
     Returns (lhs [E, capacity, K] bits, output [E, capacity, N] bits); unused capacity holds 0x7f7f.
@@ -331,7 +331,10 @@ def moe_dispatch_fc1(world, rank, experts_local, tokens_bits, weights_bits, row_
     routes (no re-creation), and that launch's results are returned.
     starved_first (world > 1): the plan is first launched with a 30 ms wait budget while no peer has
     entered the invocation -- the pull's wait for the peers' started epoch runs out, the launch must
-    return with a status record -- and is then launched normally."""
+    return with a status record -- and is then launched normally.
+    graph: after one eager launch the launch is captured into a CUDA graph once, and every launch
+    counted by `launches` and the one with `second_route` is a replay of that graph (the row counts
+    and routes are read on the device, so a replay follows new routes)."""
     e, n, k = weights_bits.shape
     toks = [to_device(t) for t in tokens_bits]
     w = to_device(weights_bits)
@@ -357,6 +360,20 @@ def moe_dispatch_fc1(world, rank, experts_local, tokens_bits, weights_bits, row_
     rc, plan = api.create_bf16_a2a_grouped_gemm(p)
     assert rc == 0, f"create_bf16_a2a_grouped_gemm -> cudaError {rc}"
     opts = options(flags=N.SKIP_PEER_WAIT if world > 1 else 0)
+    launch = lambda: api.launch_bf16_grouped_gemm(plan, 0, opts)
+    if graph:
+        assert launch() == 0
+        torch.cuda.synchronize()
+        captured = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(captured):
+            rc = api.launch_bf16_grouped_gemm(plan, torch.cuda.current_stream().cuda_stream, opts)
+            assert rc == 0, f"launch_bf16_grouped_gemm under stream capture -> cudaError {rc}"
+        lhs.view(torch.int16).fill_(0x7f7f)
+        out.view(torch.int16).fill_(0x7f7f)
+
+        def launch():
+            captured.replay()
+            return 0
     if starved_first:
         assert world > 1
         rc = api.launch_bf16_grouped_gemm(plan, 0, options(wait_ms=30.0))
@@ -368,12 +385,12 @@ def moe_dispatch_fc1(world, rank, experts_local, tokens_bits, weights_bits, row_
         out.view(torch.int16).fill_(0x7f7f)
         launches += 1  # the started epoch below counts every launch
         for _ in range(launches - 1):
-            rc = api.launch_bf16_grouped_gemm(plan, 0, opts)
+            rc = launch()
             assert rc == 0, f"launch_bf16_grouped_gemm -> cudaError {rc}"
         check_status()
     else:
         for _ in range(launches):
-            rc = api.launch_bf16_grouped_gemm(plan, 0, opts)
+            rc = launch()
             assert rc == 0, f"launch_bf16_grouped_gemm -> cudaError {rc}"
         check_status()
     if second_route is not None:
@@ -381,11 +398,11 @@ def moe_dispatch_fc1(world, rank, experts_local, tokens_bits, weights_bits, row_
         out.view(torch.int16).fill_(0x7f7f)
         offs.copy_(torch.from_numpy(np.ascontiguousarray(second_route[0], dtype=np.int64)))
         src[:len(second_route[1])] = torch.from_numpy(np.ascontiguousarray(second_route[1], dtype=np.int32)).to(DEV)
-        rc = api.launch_bf16_grouped_gemm(plan, 0, opts)
+        rc = launch()
         assert rc == 0
         check_status()
     result = to_bits(lhs), to_bits(out)
-    assert int(started[0][rank * N.READY_FLAG_STRIDE]) == launches + (1 if second_route else 0)
+    assert int(started[0][rank * N.READY_FLAG_STRIDE]) == launches + (1 if second_route else 0) + (1 if graph else 0)
     assert api.destroy_bf16_grouped_gemm(plan) == 0
     return result
 

@@ -132,10 +132,12 @@ def test_moe_every_boundary_row_count_of_the_reference_list(mma_sm_count):
     _check(world, 1, e, toks, weights, offs, src, capacity, lhs, out)
 
 
+@pytest.mark.parametrize("graph", [False, True])
 @pytest.mark.parametrize("mma_sm_count", [1, 2])
-def test_moe_boundary_row_counts_empty_experts_and_replay_with_new_routes(mma_sm_count):
+def test_moe_boundary_row_counts_empty_experts_and_replay_with_new_routes(mma_sm_count, graph):
     # Row counts at tile boundaries and empty experts (benchmarks/sm103/grouped_validation.cuh:20-50);
-    # then the same plan replayed with different device routes.
+    # then the same plan replayed with different device routes -- eagerly, and as replays of ONE
+    # captured CUDA graph (the launch allocates nothing and reads row counts and routes on the device).
     from tests import harness as H
     world, tokens, k, n = 2, 600, 256, 512
     counts_a = [1, 0, 127, 128, 129, 257, 0, 63]
@@ -155,10 +157,10 @@ def test_moe_boundary_row_counts_empty_experts_and_replay_with_new_routes(mma_sm
     capacity = 512
     comm = 3 if mma_sm_count == 1 else 0  # pairs: Auto, the embedded pull
     lhs, out = H.moe_dispatch_fc1(world, 0, e, toks, weights, first[0], first[1], capacity, comm=comm, launches=2,
-                                  mma_sm_count=mma_sm_count)
+                                  mma_sm_count=mma_sm_count, graph=graph)
     _check(world, 0, e, toks, weights, first[0], first[1], capacity, lhs, out)
     lhs, out = H.moe_dispatch_fc1(world, 0, e, toks, weights, first[0], first[1], capacity, comm=comm,
-                                  second_route=second, mma_sm_count=mma_sm_count)
+                                  second_route=second, mma_sm_count=mma_sm_count, graph=graph)
     _check(world, 0, e, toks, weights, second[0], second[1], capacity, lhs, out)
 
 

@@ -384,9 +384,15 @@ cudaError_t oproj_forward_mxfp8(const fuse_mxfp8_a2a_gemm_params& mp, const fuse
   if (!supported_mx_problem(g) || !std::isfinite(p.alpha) || p.epoch == 0 || p.num_comm_ctas < 0 ||
       p.lhs_policy != 0)
     return cudaErrorInvalidValue;
-  if (mp.postprocess.residual != nullptr || mp.overlap_postnorm || mp.m_window_tiles != 0 ||
-      mp.n_group_tiles != 0)
-    return cudaErrorNotSupported;
+  if (mp.postprocess.residual != nullptr || mp.overlap_postnorm) return cudaErrorNotSupported;
+  // m_window_tiles / n_group_tiles shape the reference scheduler's tile windows
+  // (csrc/operators/sm103/detail/persistent_gemm.cuh:55-59: both powers of two when either is set).
+  // They do not change results; this library walks its own order, so valid values are accepted as
+  // hints and an invalid pair is refused as the reference refuses it.
+  if (mp.m_window_tiles != 0 || mp.n_group_tiles != 0) {
+    auto power_of_two = [](int32_t v) { return v > 0 && (v & (v - 1)) == 0; };
+    if (!power_of_two(mp.m_window_tiles) || !power_of_two(mp.n_group_tiles)) return cudaErrorNotSupported;
+  }
   const LhsScratch w = lhs_scratch(g, mp.workspace);
   if (mp.workspace == nullptr || reinterpret_cast<uintptr_t>(mp.workspace) % 256 != 0 ||
       mp.workspace_bytes < w.bytes)

@@ -287,7 +287,7 @@ def qkv_forward_mxfp8(world, batch, seq_local, q_heads, kv_heads, head_dim, act_
 
 
 def oproj_forward_mxfp8(world, rank, batch, seq_local, peer_data, peer_scales, w_bits, comm=4, causal=False,
-                        cyclic=False, alpha=1.0, block_n=0):
+                        cyclic=False, alpha=1.0, block_n=0, window=(0, 0), expect_rc=0):
     """One rank of the MXFP8 output-projection operator.  peer_data[p] uint8 [B*S_global, K/world],
     peer_scales[p] its native scale bytes.  Returns (staged bytes [M,K], staged scales, output bits)."""
     n, k = w_bits.shape
@@ -306,11 +306,15 @@ def oproj_forward_mxfp8(world, rank, batch, seq_local, peer_data, peer_scales, w
                            causal_load_balanced=int(causal), cyclic_peer_order=int(cyclic))
     proj = N.A2AGemmParams(rhs_nt=w.data_ptr(), output=out.data_ptr(), gemm=problem, route=route,
                            num_comm_ctas=comm, epoch=1, alpha=alpha)
-    mp = N.Mxfp8A2AGemmParams(projection=proj, workspace=base, workspace_bytes=ws_bytes)
+    mp = N.Mxfp8A2AGemmParams(projection=proj, workspace=base, workspace_bytes=ws_bytes,
+                              m_window_tiles=window[0], n_group_tiles=window[1])
     for q in range(world):
         mp.activation[q] = N.Mxfp8Activation(data=datas[q].data_ptr(), scales=scales[q].data_ptr(),
                                              data_bytes=datas[q].numel(), scale_bytes=scales[q].numel())
     rc = api.launch_a2a_gemm_mxfp8_cutlass(mp, 0, options(block_n=block_n))
+    if expect_rc != 0:
+        assert rc == expect_rc, f"launch_a2a_gemm_mxfp8_cutlass -> cudaError {rc}, expected {expect_rc}"
+        return None
     assert rc == 0, f"launch_a2a_gemm_mxfp8_cutlass -> cudaError {rc}"
     check_status()
     view = api.a2a_gemm_mxfp8_staging_view(mp)

@@ -110,6 +110,17 @@ def test_prepared_and_in_kernel_weight_paths_agree():
     assert np.array_equal(full[0], prep[0]) and np.array_equal(peers_full[0], peers_prep[0])
 
 
+def test_oproj_forward_mxfp8_refuses_scheduler_windows_the_reference_refuses():
+    # csrc/operators/sm103/detail/persistent_gemm.cuh:55-59: both window sizes powers of two when either is set
+    from tests import harness as H
+    world, batch, s, heads, d, n = 1, 1, 256, 4, 128, 512
+    src = synthetic.normal_bf16((batch * s, heads * d), 5, 1.0)
+    data, scales = O.mxfp8_quantize(src)
+    w = synthetic.normal_bf16((n, heads * d), 6, 0.02)
+    for window in ((3, 4), (64, 0), (0, 4), (-2, 2)):
+        H.oproj_forward_mxfp8(world, 0, batch, s, [data], [scales], w, comm=2, window=window, expect_rc=801)
+
+
 # (world, batch, seq_local, heads, head_dim, n, comm, causal, cyclic)
 MX_OPROJ_CASES = [
     (1, 1, 256, 4, 128, 512, 2, False, False),
@@ -133,9 +144,10 @@ def test_oproj_forward_mxfp8_matches_oracle(case):
     w = synthetic.normal_bf16((n, k), synthetic.BASE_SEED + 17, 0.02)
     want_wq, want_wsf = O.mxfp8_quantize(w)
     for rank in sorted({0, world - 1}):
+        # (the scheduler windows of the reference's published rows, H64 / P4, are accepted as hints)
         staged, staged_scales, out = H.oproj_forward_mxfp8(world, rank, batch, s, [q[0] for q in quant],
                                                            [q[1] for q in quant], w, comm=comm, causal=causal,
-                                                           cyclic=cyclic)
+                                                           cyclic=cyclic, window=(64, 4) if rank else (0, 0))
         # byte + scale-byte transport oracle (benchmarks/sm103/fused_mxfp8.cuh:25-47)
         m = batch * s
         want_data = np.empty((m, k), dtype=np.uint8)

@@ -342,6 +342,73 @@ def run_c3(ctx: Context):
 
 
 # ---------------------------------------------------------------------------------------------------
+# MXFP8 QKV forward at the Llama-3-8B shape (the a6 operator; not a BASELINE config, measured for completeness)
+# ---------------------------------------------------------------------------------------------------
+
+def run_a6(ctx: Context):
+    cp, rank, dev, stream = ctx.world_size, ctx.rank, ctx.dev, ctx.stream
+    m, hid, q, kv, d = 16384, 4096, 32, 8, 128
+    n, rows = (q + 2 * kv) * d, m * cp
+    sym = ctx.world.allocate({"a6_planar": rows * (n // cp) * 2, "a6_done": cp * 128})
+    x = ctx.gen((m, hid), ctx.seed + 1000, 1.0)
+    xq = torch.empty((m, hid), dtype=U8, device=dev)
+    xs = torch.zeros(api.mxfp8_scale_bytes(m, hid), dtype=U8, device=dev)
+    assert api.quantize_mxfp8(x.data_ptr(), hid, m, hid, xq.data_ptr(), xs.data_ptr(), stream) == 0
+    torch.cuda.synchronize()
+    del x
+    w = ctx.gen((n, hid), 11, 0.02)
+    local = torch.empty((m, n), dtype=BF16, device=dev)
+    prob = N.GemmProblem(m, n, hid, raster=N.RASTER_ALONG_M, max_swizzle_size=8)
+    rc, ws = api.gemm_a2a_mxfp8_workspace_size(prob)
+    assert rc == 0
+    buf, base = ctx.scratch(ws)
+    route = N.UlyssesRoute(world_size=cp, rank=rank, batch=1, global_seq=rows, seq_local=m, q_heads=q, kv_heads=kv,
+                           head_dim=d, kind=N.ROUTE_QKV_GQA_PACK)
+    ready = torch.zeros(api.qkv_ready_elements(prob), dtype=torch.int32, device=dev)
+    proj = N.GemmA2AParams(rhs_nt=w.data_ptr(), local_output=local.data_ptr(), ready=ready.data_ptr(), gemm=prob,
+                           route=route, num_comm_ctas=ctx.comm, epoch=0)
+    for r in range(cp):
+        proj.peer_output[r] = sym["a6_planar"].peer_ptrs[r]
+        proj.peer_route_done_epoch[r] = sym["a6_done"].peer_ptrs[r]
+    mp = N.Mxfp8GemmA2AParams(projection=proj, workspace=base, workspace_bytes=ws,
+                              activation=N.Mxfp8Activation(data=xq.data_ptr(), scales=xs.data_ptr(),
+                                                           data_bytes=xq.numel(), scale_bytes=xs.numel()))
+    opts = N.Options()
+    opts.flags = 0 if ctx.comm else N.QKV_ROUTE_DIRECT
+    epoch = [0]
+
+    def mx_qkv():
+        epoch[0] += 1
+        mp.projection.epoch = epoch[0]
+        return api.launch_gemm_a2a_mxfp8_cutlass(mp, stream, opts)
+
+    pure, cublas, keep = _pure_mxfp8(ctx, m, n, hid)
+    rec = ctx.row(f"a6 MXFP8 QKVProj->A2A (M {m}, N {n}, K {hid}, W quantised in-kernel)", mx_qkv, 2.0 * m * n * hid,
+                  pure=pure, cublas=cublas, nvlink_bytes=2.0 * m * n * (cp - 1) / cp, nvlink_dir="out")
+    del keep, pure, cublas
+    if ctx.validate:
+        from tests import fullsize as F
+        ctx.barrier()
+        F.poison(local, sym["a6_planar"].view(BF16))
+        buf.fill_(0xA5)
+        ctx.barrier()
+        assert mx_qkv() == 0
+        torch.cuda.synchronize()
+        ctx.check_status("a6 validation")
+        ctx.barrier()
+        w0 = base - buf.data_ptr()
+        wq = buf[w0:w0 + n * hid].view(n, hid)
+        sf0 = w0 + (n * hid + 255) // 256 * 256
+        wsf = buf[sf0:sf0 + api.mxfp8_scale_bytes(n, hid)]
+        picked = F.sample_rows(m, count=ctx.validate_rows)
+        check = F.check_qkv_forward_mxfp8(cp, rank, m, q, kv, d, xq, xs, w, wq, wsf, local, sym["a6_planar"].view(BF16),
+                                          picked)
+        rec["validated"] = _merge(ctx, check)
+        ctx.barrier()
+    return [rec]
+
+
+# ---------------------------------------------------------------------------------------------------
 # C4: Qwen3-32B MXFP8 QKV full backward
 # ---------------------------------------------------------------------------------------------------
 
@@ -604,7 +671,7 @@ def run_c5(ctx: Context):
     return [rec, crec]
 
 
-RUNNERS = {"bwd": run_bwd, "c3": run_c3, "c4": run_c4, "c5": run_c5}
+RUNNERS = {"bwd": run_bwd, "a6": run_a6, "c3": run_c3, "c4": run_c4, "c5": run_c5}
 
 
 def run(ctx: Context, only=None):
@@ -626,7 +693,7 @@ def main():
     ap.add_argument("--samples", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--scale", type=float, default=1.0, help="scale rows per rank of c3/c4/c5")
-    ap.add_argument("--only", default="", help="comma list of bwd,c3,c4,c5")
+    ap.add_argument("--only", default="", help="comma list of bwd,a6,c3,c4,c5")
     ap.add_argument("--comm", type=int, default=0, help="communication CTAs of every operator (0: Auto, the host planner)")
     ap.add_argument("--skip-validate", action="store_true")
     ap.add_argument("--json", action="store_true", help="print the rows as one JSON line as well")

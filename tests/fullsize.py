@@ -116,12 +116,14 @@ def _row_positions(m: int, rows: np.ndarray) -> np.ndarray:
 # ---------------------------------------------------------------------------------------------
 
 def check_qkv_forward(world, rank, seq_local, q_heads, kv_heads, head_dim, x, w, local, planar, rows,
-                      alpha=1.0, tolerance=(0.01, 0.01)) -> dict:
-    """x [M,K], w [N,K], local [M,N], planar = this rank's flat Q|K|V buffer (batch 1)."""
-    m, n, k = seq_local, (q_heads + 2 * kv_heads) * head_dim, x.shape[1]
-    rt = index_tensor(rows, x)
+                      alpha=1.0, tolerance=(0.01, 0.01), expected_local=None) -> dict:
+    """x [M,K], w [N,K], local [M,N], planar = this rank's flat Q|K|V buffer (batch 1).
+    expected_local: the oracle's rows of `local` when the caller computed them (block-scaled operands)."""
+    m, n = seq_local, (q_heads + 2 * kv_heads) * head_dim
+    rt = index_tensor(rows, local)
     mine = local[rt].contiguous()
-    want = O.gemm_bf16(0, bits(x[rt]), bits(w), len(rows), n, k, alpha=alpha)
+    want = expected_local if expected_local is not None else \
+        O.gemm_bf16(0, bits(x[rt]), bits(w), len(rows), n, x.shape[1], alpha=alpha)
     gemm = compare(bits(mine), want, *tolerance)
     gathered = bits(all_gather_rows(mine))                                # [world, R, N]
     # every element the sampled source rows contribute to THIS rank's planar buffer
@@ -146,6 +148,24 @@ def check_qkv_forward(world, rank, seq_local, q_heads, kv_heads, head_dim, x, w,
     return {"gemm": gemm, "route_bitexact": mismatches == 0, "route_mismatches": mismatches,
             "route_elements": int(len(index)), "rows": int(len(rows)),
             "unwritten_local": unwritten(local), "unwritten_routed": unwritten(planar)}
+
+
+def check_qkv_forward_mxfp8(world, rank, seq_local, q_heads, kv_heads, head_dim, data, scales, w, wq, wq_scales, local,
+                            planar, rows, alpha=1.0, tolerance=(0.01, 0.01)) -> dict:
+    """data [M, K] E4M3 + native `scales` (the pre-quantised activation); w [N, K] BF16 master, wq /
+    wq_scales its in-kernel quantisation; local [M, N]; planar = this rank's flat Q|K|V buffer."""
+    k = data.shape[1]
+    rt = index_tensor(rows, data)
+    want_wq, want_ws = O.mxfp8_quantize(bits(w))
+    weight_mismatches = _bytes_equal(wq, want_wq) + _bytes_equal(wq_scales, want_ws)
+    got_s = scale_rows(scales, rows, k).cpu().numpy()
+    want = O.gemm_mxfp8(np.ascontiguousarray(data[rt].cpu().numpy()), compact_scales(got_s, k), want_wq, want_ws, alpha=alpha)
+    route = check_qkv_forward(world, rank, seq_local, q_heads, kv_heads, head_dim, None, None, local, planar, rows,
+                              expected_local=want, tolerance=tolerance)
+    route["route_mismatches"] += weight_mismatches
+    route["route_bitexact"] = route["route_mismatches"] == 0
+    route["route_elements"] += int(want_wq.size + want_ws.size)
+    return route
 
 
 def check_oproj_forward(world, rank, seq_local, k, attn, staging, w, out, rows, causal=False, cyclic=False,

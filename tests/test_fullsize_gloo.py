@@ -110,6 +110,26 @@ WORKER = textwrap.dedent('''
                                         u8_t(bad_s), as_t(wmx), u8_t(wq), u8_t(ws), as_t(out_mx), rows_mx)
     assert not check["route_bitexact"], check
 
+    # ---- MXFP8 QKV forward ----------------------------------------------------------------------
+    qf, kvf, df, kf = 2 * world, world, 128, 256
+    nf = (qf + 2 * kvf) * df
+    acts = [O.mxfp8_quantize(synthetic.normal_bf16((sm, kf), 800 + r, 1.0)) for r in range(world)]
+    wf = synthetic.normal_bf16((nf, kf), 29, 0.02)
+    wfq, wfs = O.mxfp8_quantize(wf)
+    locals_f = [O.gemm_mxfp8(a[0], a[1], wfq, wfs) for a in acts]
+    planar_f = [np.full(sm * world * nf // world, 0xFFFF, dtype=np.uint16) for _ in range(world)]
+    table_f = O.ptr_array(planar_f)
+    for r in range(world):
+        O.lib().fo_qkv_forward_route(world, r, 1, sm, qf, kvf, df, O.ptr(locals_f[r]), nf, table_f)
+    check = F.check_qkv_forward_mxfp8(world, rank, sm, qf, kvf, df, u8_t(acts[rank][0]), u8_t(acts[rank][1]), as_t(wf),
+                                      u8_t(wfq), u8_t(wfs), as_t(locals_f[rank]), as_t(planar_f[rank]), rows_mx)
+    assert check["gemm"]["ok"] and check["route_bitexact"] and check["unwritten_routed"] == 0, check
+    bad_w = wfq.copy()
+    bad_w[3, 5] ^= 1                       # one byte of the in-kernel weight quantisation
+    check = F.check_qkv_forward_mxfp8(world, rank, sm, qf, kvf, df, u8_t(acts[rank][0]), u8_t(acts[rank][1]), as_t(wf),
+                                      u8_t(bad_w), u8_t(wfs), as_t(locals_f[rank]), as_t(planar_f[rank]), rows_mx)
+    assert not check["route_bitexact"], check
+
     # ---- MXFP8 QKV backward data --------------------------------------------------------------
     import ctypes as C
     qm, kvm, dm, hm = 2 * world, world, 128, 64

@@ -409,6 +409,82 @@ def run_a6(ctx: Context):
 
 
 # ---------------------------------------------------------------------------------------------------
+# MXFP8 output-projection backward at the Llama-3-70B shape (the other half of a10; not a BASELINE config)
+# ---------------------------------------------------------------------------------------------------
+
+def run_a10(ctx: Context):
+    cp, rank, dev, stream = ctx.world_size, ctx.rank, ctx.dev, ctx.stream
+    m = max(256, int(32768 * ctx.scale) // 256 * 256)
+    hid, q, d = 8192, 64, 128
+    a, rows = q * d, m * cp
+    sym = ctx.world.allocate({"a10_routed": rows * (a // cp) * 2, "a10_done": cp * 128})
+    dy = ctx.gen((m, hid), ctx.seed + 301, 0.01)
+    dyq = torch.empty((m, hid), dtype=U8, device=dev)
+    dys = torch.zeros(api.mxfp8_scale_bytes(m, hid), dtype=U8, device=dev)
+    assert api.quantize_mxfp8(dy.data_ptr(), hid, m, hid, dyq.data_ptr(), dys.data_ptr(), stream) == 0
+    wo = ctx.gen((hid, a), 17, 0.02)
+    saved = ctx.gen((m, a), ctx.seed + 302, 1.0)
+    da = torch.empty((m, a), dtype=BF16, device=dev)
+    dwo = torch.empty((hid, a), dtype=BF16, device=dev)
+    routed = sym["a10_routed"].view(BF16)
+    proj = N.OprojBackwardDataParams(weight=wo.data_ptr(), local_grad_attention=da.data_ptr(), local_tokens=m, hidden=hid,
+                                     batch=1, q_heads=q, head_dim=d, world_size=cp, rank=rank,
+                                     num_comm_ctas=ctx.comm or 16, epoch=0)
+    proj.gemm_tuning.max_swizzle_size = 1
+    for r in range(cp):
+        proj.peer_grad_attention[r] = sym["a10_routed"].peer_ptrs[r]
+        proj.peer_done_epoch[r] = sym["a10_done"].peer_ptrs[r]
+    rc, ws = api.oproj_backward_mxfp8_data_workspace_size(proj)
+    assert rc == 0
+    buf, base = ctx.scratch(ws)
+    mp = N.Mxfp8OprojBackwardDataParams(projection=proj, grad_output=N.Mxfp8Activation(
+        data=dyq.data_ptr(), scales=dys.data_ptr(), data_bytes=dyq.numel(), scale_bytes=dys.numel()),
+        workspace=base, workspace_bytes=ws)
+    wproj = N.OprojBackwardWeightParams(grad_output=dy.data_ptr(), saved_attention=saved.data_ptr(),
+                                        grad_weight=dwo.data_ptr(), local_tokens=m, hidden=hid, q_heads=q, head_dim=d)
+    rc, ws2 = api.oproj_backward_mxfp8_weight_workspace_size(wproj)
+    assert rc == 0
+    buf2, base2 = ctx.scratch(ws2)
+    wp = N.Mxfp8OprojBackwardWeightParams(projection=wproj, workspace=base2, workspace_bytes=ws2)
+    epoch = [0]
+
+    def data():
+        epoch[0] += 1
+        mp.projection.epoch = epoch[0]
+        return api.launch_oproj_backward_mxfp8_data(mp, stream)
+
+    def weight():
+        return api.launch_oproj_backward_mxfp8_weight(wp, stream)
+
+    flops = 2.0 * m * hid * a
+    pure, cublas, keep = _pure_mxfp8(ctx, m, a, hid)
+    data_row = ctx.row(f"a10 MXFP8 OProj backward data (M {m}: dA -> A2A, incl. Wo^T quantisation)", data, flops, pure=pure,
+                       cublas=cublas, nvlink_bytes=2.0 * m * a * (cp - 1) / cp, nvlink_dir="out")
+    del keep, pure, cublas
+    pure, cublas, keep = _pure_mxfp8(ctx, hid, a, m)
+    weight_row = ctx.row("a10 MXFP8 OProj backward weight (two transposed quantisations + dWo)", weight, flops, pure=pure,
+                         cublas=cublas)
+    del keep, pure, cublas
+    if ctx.validate:
+        from tests import fullsize as F
+        ctx.barrier()
+        F.poison(da, dwo, routed)
+        ctx.barrier()
+        assert data() == 0 and weight() == 0
+        torch.cuda.synchronize()
+        ctx.check_status("a10 validation")
+        ctx.barrier()
+        picked = F.sample_rows(m, count=ctx.validate_rows)
+        check_d = F.check_oproj_backward_data_mxfp8(cp, rank, m, a, dyq, dys, wo, da, routed.view(rows, a // cp), picked)
+        check_w = F.check_weight_gradient_mxfp8(dy, saved, dwo, F.sample_rows(hid, count=64, edge=8),
+                                                F.sample_rows(a, count=512, edge=16))
+        data_row["validated"] = _merge(ctx, check_d)
+        weight_row["validated"] = _merge(ctx, check_w)
+        ctx.barrier()
+    return [data_row, weight_row]
+
+
+# ---------------------------------------------------------------------------------------------------
 # C4: Qwen3-32B MXFP8 QKV full backward
 # ---------------------------------------------------------------------------------------------------
 
@@ -671,7 +747,7 @@ def run_c5(ctx: Context):
     return [rec, crec]
 
 
-RUNNERS = {"bwd": run_bwd, "a6": run_a6, "c3": run_c3, "c4": run_c4, "c5": run_c5}
+RUNNERS = {"bwd": run_bwd, "a6": run_a6, "c3": run_c3, "a10": run_a10, "c4": run_c4, "c5": run_c5}
 
 
 def run(ctx: Context, only=None):
@@ -693,7 +769,7 @@ def main():
     ap.add_argument("--samples", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--scale", type=float, default=1.0, help="scale rows per rank of c3/c4/c5")
-    ap.add_argument("--only", default="", help="comma list of bwd,a6,c3,c4,c5")
+    ap.add_argument("--only", default="", help="comma list of bwd,a6,c3,a10,c4,c5")
     ap.add_argument("--comm", type=int, default=0, help="communication CTAs of every operator (0: Auto, the host planner)")
     ap.add_argument("--skip-validate", action="store_true")
     ap.add_argument("--json", action="store_true", help="print the rows as one JSON line as well")

@@ -290,12 +290,14 @@ def check_weight_gradient(a_km, b_kn, dw, picked, alpha=1.0, tolerance=(0.02, 0.
 
 
 def check_oproj_backward_data(world, rank, seq_local, a_width, dy, wo, da, routed, rows, causal=False, alpha=1.0,
-                              tolerance=(0.02, 0.02)) -> dict:
-    """dy [M, H]; wo [H, A]; da [M, A]; routed = this rank's head shard [B*S_global, A/world] of every rank's dA."""
-    hidden, shard = dy.shape[1], a_width // world
+                              tolerance=(0.02, 0.02), expected_local=None) -> dict:
+    """dy [M, H]; wo [H, A]; da [M, A]; routed = this rank's head shard [B*S_global, A/world] of every rank's dA.
+    expected_local: the oracle's rows of `da` when the caller computed them (block-scaled operands)."""
+    shard = a_width // world
     rt = index_tensor(rows, da)
     mine = da[rt].contiguous()
-    want = O.gemm_bf16(1, bits(dy[rt]), bits(wo), len(rows), a_width, hidden, alpha=alpha)
+    want = expected_local if expected_local is not None else \
+        O.gemm_bf16(1, bits(dy[rt]), bits(wo), len(rows), a_width, dy.shape[1], alpha=alpha)
     gemm = compare(bits(mine), want, *tolerance)
     gathered = bits(all_gather_rows(mine))                                # [world, R, A]
     g = np.concatenate([global_rows(world, source, seq_local, causal, rows) for source in range(world)])
@@ -411,6 +413,19 @@ def check_qkv_backward_data_mxfp8(world, rank, seq_local, q_heads, kv_heads, mas
             "route_mismatches": mismatches + weight_mismatches,
             "route_elements": int(want_master.size + got.size + got_s.size + want_wq.size + want_ws.size),
             "rows": int(len(rows)), "unwritten_local": unwritten(dx), "unwritten_routed": unwritten(staging)}
+
+
+def check_oproj_backward_data_mxfp8(world, rank, seq_local, a_width, dy_q, dy_s, wo, da, routed, rows, causal=False,
+                                    alpha=1.0, tolerance=(0.01, 0.01)) -> dict:
+    """dy_q [M, H] E4M3 + native dy_s (the upstream-quantised output gradient); wo [H, A] BF16 master,
+    re-quantised along H inside the operator; da [M, A]; routed as in check_oproj_backward_data."""
+    hidden = dy_q.shape[1]
+    rt = index_tensor(rows, dy_q)
+    w_q, w_s = O.mxfp8_quantize_transposed(bits(wo))                      # [A, H] along H
+    got_s = scale_rows(dy_s, rows, hidden).cpu().numpy()
+    want = O.gemm_mxfp8(np.ascontiguousarray(dy_q[rt].cpu().numpy()), compact_scales(got_s, hidden), w_q, w_s, alpha=alpha)
+    return check_oproj_backward_data(world, rank, seq_local, a_width, None, None, da, routed, rows, causal=causal,
+                                     tolerance=tolerance, expected_local=want)
 
 
 def check_weight_gradient_mxfp8(a_km, b_kn, dw, picked, columns, alpha=1.0, tolerance=(0.01, 0.01)) -> dict:

@@ -130,6 +130,27 @@ WORKER = textwrap.dedent('''
                                       u8_t(bad_w), u8_t(wfs), as_t(locals_f[rank]), as_t(planar_f[rank]), rows_mx)
     assert not check["route_bitexact"], check
 
+    # ---- MXFP8 output-projection backward data ----------------------------------------------------
+    hb, qb = 128, 2 * world
+    ab = qb * 128
+    dys_b = [synthetic.normal_bf16((sm, hb), 900 + r, 0.01) for r in range(world)]
+    dyq_b = [O.mxfp8_quantize(x) for x in dys_b]
+    wob = synthetic.normal_bf16((hb, ab), 31, 0.02)
+    wobq, wobs = O.mxfp8_quantize_transposed(wob)
+    da_b = [O.gemm_mxfp8(dq[0], dq[1], wobq, wobs) for dq in dyq_b]
+    shard_b = ab // world
+    routed_b = np.empty((sm * world, shard_b), np.uint16)          # this rank's head shard of every rank's dA
+    for src in range(world):
+        routed_b[src * sm:(src + 1) * sm] = da_b[src][:, rank * shard_b:(rank + 1) * shard_b]
+    check = F.check_oproj_backward_data_mxfp8(world, rank, sm, ab, u8_t(dyq_b[rank][0]), u8_t(dyq_b[rank][1]), as_t(wob),
+                                              as_t(da_b[rank]), as_t(routed_b), rows_mx)
+    assert check["gemm"]["ok"] and check["route_bitexact"], check
+    bad_r = routed_b.copy()
+    bad_r[int(rows_mx[1]), 3] ^= 1
+    check = F.check_oproj_backward_data_mxfp8(world, rank, sm, ab, u8_t(dyq_b[rank][0]), u8_t(dyq_b[rank][1]), as_t(wob),
+                                              as_t(da_b[rank]), as_t(bad_r), rows_mx)
+    assert not check["route_bitexact"], check
+
     # ---- MXFP8 QKV backward data --------------------------------------------------------------
     import ctypes as C
     qm, kvm, dm, hm = 2 * world, world, 128, 64

@@ -83,8 +83,9 @@ cudaError_t check_qkv_route(const fuse_gemm_a2a_params& p) {
       (p.completion_epoch != nullptr && !r.defer_v_a2a) || r.q_heads % r.kv_heads != 0 ||
       r.q_heads % r.world_size != 0 || r.kv_heads % r.world_size != 0 || r.head_dim % 8 != 0)
     return cudaErrorNotSupported;
-  // Offline-interleaved weights and the deferred-V variant are not built yet.
-  if (r.qkv_peer_interleaved || r.defer_v_a2a) return cudaErrorNotSupported;
+  // Offline-interleaved weights are not built.
+  if (r.qkv_peer_interleaved) return cudaErrorNotSupported;
+  if (p.completion_epoch != nullptr && !host::aligned4(p.completion_epoch)) return cudaErrorInvalidValue;
   if (int64_t(r.seq_local) * r.world_size != r.global_seq ||
       int64_t(r.batch) * r.seq_local != p.gemm.m ||
       int64_t(r.batch) * r.global_seq > INT32_MAX ||
@@ -140,6 +141,8 @@ cudaError_t qkv_forward(const fuse_gemm_a2a_params& p, const fuse_b200_options* 
   k.qkv.q_heads = p.route.q_heads;
   k.qkv.kv_heads = p.route.kv_heads;
   k.qkv.head_dim = p.route.head_dim;
+  k.qkv.defer_v = p.route.defer_v_a2a ? 1 : 0;
+  k.qkv.completion_epoch = p.route.defer_v_a2a ? p.completion_epoch : nullptr;
   for (int peer = 0; peer < p.route.world_size; ++peer) {
     k.qkv.peer_output[peer] = p.peer_output[peer];
     k.qkv.peer_done[peer] = p.peer_route_done_epoch[peer];
@@ -151,10 +154,11 @@ cudaError_t qkv_forward(const fuse_gemm_a2a_params& p, const fuse_b200_options* 
   const fuse_ulysses_route& r = p.route;
   bool tma = !vector_epilogue_requested(options) && r.head_dim % 64 == 0 && r.seq_local % kBlockM == 0;
   if (tma) {
-    tma = encode_peer_store_maps(&stores, p.peer_output, r.world_size,
-                                 uint64_t(r.batch) * uint64_t(r.global_seq),
-                                 int64_t(r.q_heads) / r.world_size * r.head_dim,
-                                 int64_t(r.kv_heads) / r.world_size * r.head_dim);
+    // (defer_v: one map per destination over its [rows, q_local + kv_local] tensor)
+    const int64_t q_local = int64_t(r.q_heads) / r.world_size * r.head_dim;
+    const int64_t kv_local = int64_t(r.kv_heads) / r.world_size * r.head_dim;
+    tma = encode_peer_store_maps(&stores, p.peer_output, r.world_size, uint64_t(r.batch) * uint64_t(r.global_seq),
+                                 r.defer_v_a2a ? q_local + kv_local : q_local, r.defer_v_a2a ? 0 : kv_local);
   }
   if (tma && block_n == 256 && pair_tiles_requested())
     return launch_pair<kModeQkvDirect>(p.lhs, packed_or(p.gemm.stride_a.row, p.gemm.k), p.rhs_nt,

@@ -104,8 +104,13 @@ struct QkvRoute {
   int32_t world, rank, batch, seq_local, global_seq;
   int32_t q_heads, kv_heads, head_dim;
   int32_t causal;  // head-only (output-projection backward) routes may use the causal row map
+  // defer_v (UlyssesRoute::defer_v_a2a, csrc/operators/sm103/detail/gemm_a2a.cuh:199-215,521-533):
+  // V stays in the local output; Q and K of a destination's heads share ONE row-major tensor
+  // [B*S_global, q_local + kv_local] there (Q columns, then K columns).
+  int32_t defer_v;
   uint16_t* peer_output[kMaxWorldSize];
   uint32_t* peer_done[kMaxWorldSize];
+  uint32_t* completion_epoch;  // local word: the epoch, once this rank's whole local output (V included) is written
 };
 
 struct LhsRoute {
@@ -287,6 +292,12 @@ __device__ __forceinline__ void qkv_chunk_destination(const QkvRoute& r, int32_t
   const int32_t local_width = segment == 0 ? q_local : kv_local;
   const int32_t owner = within / local_width;
   const int32_t local_col = within - owner * local_width;
+  if (r.defer_v) {
+    if (segment == 2) return;  // V is not routed: base stays null and the chunk is skipped
+    base = r.peer_output[owner] + (segment == 1 ? q_local : 0) + local_col;
+    stride = q_local + kv_local;
+    return;
+  }
   const int64_t segment_base =
       segment == 0 ? 0 : rows_total * q_local + (segment == 2 ? rows_total * kv_local : 0);
   base = r.peer_output[owner] + segment_base + local_col;
@@ -381,6 +392,8 @@ __device__ __forceinline__ void qkv_finalize(const FusedParams& p) {
   if (lane < r.world)
     ptx::st_release_sys(r.peer_done[lane] + r.rank * kReadyFlagStride, p.wait.epoch);
   __syncwarp();
+  // (the grid has joined: the whole local output, the deferred V included, is written)
+  if (lane == 0 && r.completion_epoch != nullptr) ptx::st_release_sys(r.completion_epoch, p.wait.epoch);
   if (lane < r.world && !(p.flags & kFlagSkipPeerWait))
     flag_wait<true>(r.peer_done[r.rank] + lane * kReadyFlagStride, p.wait.epoch, p.wait,
                     kSitePeerDone, uint32_t(lane));
@@ -1463,8 +1476,8 @@ __device__ __forceinline__ void store_accumulators(const uint32_t (&acc)[32], ui
       out.w = *reinterpret_cast<const uint32_t*>(&pair);
       ptx::st_v4(dst + v * 8, out);
       if constexpr (kPushToPeer) {
-        uint16_t* base = peer.col_base[peer.chunk0 + v];
-        ptx::st_v4(base + peer.dest_row * peer.col_stride[peer.chunk0 + v], out);
+        uint16_t* base = peer.col_base[peer.chunk0 + v];  // null: a chunk that is not routed (deferred V)
+        if (base != nullptr) ptx::st_v4(base + peer.dest_row * peer.col_stride[peer.chunk0 + v], out);
       }
     }
   }
@@ -2016,9 +2029,14 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 const int32_t within = col - (segment == 0 ? 0 : q_width + (segment == 2 ? kv_width : 0));
                 const int32_t local_width = (segment == 0 ? q_width : kv_width) / r.world;
                 const int32_t owner = within / local_width;  // segment > 0 only when kv_heads > 0
-                ptx::tma_store_2d(&store_maps.peer[owner][segment], staging, within - owner * local_width,
-                                  int32_t(global_row(r.world, r.rank, r.seq_local, r.global_seq,
-                                                     r.causal != 0, mt * kBlockM)));
+                // defer_v: one [rows, q_local + kv_local] tensor per destination (map 0), V not routed
+                const int32_t map = r.defer_v ? 0 : segment;
+                const int32_t dest_col =
+                    within - owner * local_width + (r.defer_v && segment == 1 ? q_width / r.world : 0);
+                if (!(r.defer_v && segment == 2))
+                  ptx::tma_store_2d(&store_maps.peer[owner][map], staging, dest_col,
+                                    int32_t(global_row(r.world, r.rank, r.seq_local, r.global_seq,
+                                                       r.causal != 0, mt * kBlockM)));
               }
             }
             ptx::bulk_commit();

@@ -194,6 +194,26 @@ FO_API int fo_qkv_forward_destination(int world, int rank, int batch, int seq_lo
   return 1;
 }
 
+/* The same with UlyssesRoute::defer_v_a2a: V is not routed (returns 2), and Q and K of the
+ * destination's heads share one row-major tensor [B*S_global, q_local + kv_local] there, Q
+ * columns first.  csrc/operators/sm103/detail/gemm_a2a.cuh:199-215 (one descriptor of width
+ * q_local + kv_local, offset 0), :408 (V tasks skipped), :505-533 (destination feature = local
+ * feature: Q at head*d, K at q_local + head*d). */
+FO_API int fo_qkv_forward_destination_defer_v(int world, int rank, int batch, int seq_local, int q_heads,
+                                              int kv_heads, int head_dim, int64_t source_row,
+                                              int global_feature, int32_t* dest_rank,
+                                              int64_t* dest_offset) {
+  int32_t address[5];
+  if (!fo_map_qkv_gqa_feature(world, q_heads, kv_heads, head_dim, global_feature, address))
+    return 0;
+  (void)batch;
+  const int64_t q_local = q_heads / world * head_dim, kv_local = kv_heads / world * head_dim;
+  if (address[2] == 2) return 2;
+  *dest_rank = address[0];
+  *dest_offset = fo_global_row(world, rank, seq_local, 0, source_row) * (q_local + kv_local) + address[1];
+  return 1;
+}
+
 /* Forward QKV route, receiver view: element `index` of destination rank's
  * planar Q|K|V buffer -> (source rank, element offset in that rank's [M,N] GEMM
  * output).  benchmarks/sm103/fused_validation.cuh:104-138 (batch == 1). */
@@ -505,6 +525,23 @@ FO_API void fo_qkv_forward_route(int world, int rank, int batch, int seq_local, 
       fo_qkv_forward_destination(world, rank, batch, seq_local, q_heads, kv_heads, head_dim, row,
                                  feature, &dest, &offset);
       peer_output[dest][offset] = local_output[row * ldd + feature];
+    }
+}
+
+/* The deferred-V variant: Q and K only, into every destination's [rows, q_local + kv_local] tensor. */
+FO_API void fo_qkv_forward_route_defer_v(int world, int rank, int batch, int seq_local, int q_heads,
+                                         int kv_heads, int head_dim, const uint16_t* local_output,
+                                         int64_t ldd, uint16_t* const* peer_output) {
+  const int64_t m = (int64_t)batch * seq_local;
+  const int n = (q_heads + 2 * kv_heads) * head_dim;
+#pragma omp parallel for schedule(static)
+  for (int64_t row = 0; row < m; ++row)
+    for (int feature = 0; feature < n; ++feature) {
+      int32_t dest;
+      int64_t offset;
+      if (fo_qkv_forward_destination_defer_v(world, rank, batch, seq_local, q_heads, kv_heads, head_dim, row,
+                                             feature, &dest, &offset) == 1)
+        peer_output[dest][offset] = local_output[row * ldd + feature];
     }
 }
 

@@ -44,8 +44,10 @@ def check_status():
 
 def qkv_forward(world, batch, seq_local, q_heads, kv_heads, head_dim, lhs_bits, w_bits, comm=4,
                 alpha=1.0, raster=N.RASTER_HEURISTIC, swizzle=4, block_n=0, epochs=1, route="comm",
-                vector_epilogue=False):
-    """Runs every rank of the QKV operator (route: "comm" CTAs or "direct" epilogue push).  Returns (local_outputs, peer_outputs) as bits."""
+                vector_epilogue=False, defer_v=False):
+    """Runs every rank of the QKV operator (route: "comm" CTAs or "direct" epilogue push).  Returns (local_outputs, peer_outputs) as bits.
+    defer_v: UlyssesRoute.defer_v_a2a (V stays local, Q | K share one tensor per destination) with a
+    completion_epoch word per rank, which must hold the last epoch afterwards."""
     m = batch * seq_local
     n = (q_heads + 2 * kv_heads) * head_dim
     k = w_bits.shape[1]
@@ -57,6 +59,7 @@ def qkv_forward(world, batch, seq_local, q_heads, kv_heads, head_dim, lhs_bits, 
     peer = [poisoned(rows * n // world) for _ in range(world)]
     done = [torch.zeros(world * N.READY_FLAG_STRIDE, dtype=torch.int32, device=DEV) for _ in range(world)]
     ready = [torch.zeros(api.qkv_ready_elements(problem), dtype=torch.int32, device=DEV) for _ in range(world)]
+    completion = [torch.zeros(N.READY_FLAG_STRIDE, dtype=torch.int32, device=DEV) for _ in range(world)]
     route_flag = N.QKV_ROUTE_DIRECT if route == "direct" else N.QKV_ROUTE_COMM_CTAS
     opts = options(flags=(N.SKIP_PEER_WAIT if world > 1 else 0) | route_flag |
                    (N.VECTOR_EPILOGUE if vector_epilogue else 0), block_n=block_n)
@@ -64,10 +67,11 @@ def qkv_forward(world, batch, seq_local, q_heads, kv_heads, head_dim, lhs_bits, 
         for r in range(world):
             route = N.UlyssesRoute(world_size=world, rank=r, batch=batch, global_seq=seq_local * world,
                                    seq_local=seq_local, q_heads=q_heads, kv_heads=kv_heads,
-                                   head_dim=head_dim, kind=N.ROUTE_QKV_GQA_PACK)
+                                   head_dim=head_dim, kind=N.ROUTE_QKV_GQA_PACK, defer_v_a2a=int(defer_v))
             p = N.GemmA2AParams(lhs=xs[r].data_ptr(), rhs_nt=w.data_ptr(), local_output=local[r].data_ptr(),
                                 ready=ready[r].data_ptr(), gemm=problem, route=route, num_comm_ctas=comm,
-                                epoch=epoch, alpha=alpha)
+                                epoch=epoch, alpha=alpha,
+                                completion_epoch=completion[r].data_ptr() if defer_v else None)
             for peer_rank in range(world):
                 p.peer_output[peer_rank] = peer[peer_rank].data_ptr()
                 p.peer_route_done_epoch[peer_rank] = done[peer_rank].data_ptr()
@@ -76,6 +80,8 @@ def qkv_forward(world, batch, seq_local, q_heads, kv_heads, head_dim, lhs_bits, 
     check_status()
     for d in done:  # every source told every destination
         assert (d[::N.READY_FLAG_STRIDE][:world] == epochs).all()
+    for c in completion:  # the local completion word: the last epoch with the deferred V, untouched otherwise
+        assert int(c[0]) == (epochs if defer_v else 0)
     return [to_bits(t) for t in local], [to_bits(t) for t in peer]
 
 

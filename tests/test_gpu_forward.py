@@ -61,6 +61,33 @@ def test_qkv_forward_matches_oracle(case, route):
         _assert_close(peers[dest], want_peers[dest], f"peer_output[{dest}]")
 
 
+@pytest.mark.parametrize("route,vector,block_n", [("direct", False, 0), ("direct", False, 128), ("direct", True, 0),
+                                                  ("comm", False, 0)])
+@pytest.mark.parametrize("case", [(1, 1, 256, 4, 2, 128, 256), (2, 1, 384, 8, 4, 128, 512), (4, 2, 128, 16, 4, 64, 320),
+                                  (2, 1, 200, 8, 8, 40, 192)])
+def test_qkv_forward_with_the_all_to_all_of_v_deferred(case, route, vector, block_n):
+    # UlyssesRoute::defer_v_a2a (csrc/operators/sm103/detail/gemm_a2a.cuh:199-215,408,505-533): V stays in
+    # the local output, Q and K of a destination's heads land in ONE [B*S_global, q_local + kv_local]
+    # tensor there, and completion_epoch is published once the local output is complete.
+    from tests import harness as H
+    world, batch, s, q, kv, d, k = case
+    m, n = batch * s, (q + 2 * kv) * d
+    lhs, w = _inputs(world, m, k, n)
+    local, peers = H.qkv_forward(world, batch, s, q, kv, d, lhs, w, comm=4, route=route, vector_epilogue=vector,
+                                 block_n=block_n, defer_v=True, epochs=2)
+    want_local, _ = O.qkv_forward(world, batch, s, q, kv, d, lhs, w, defer_v=True)
+    for r in range(world):
+        _assert_close(local[r], want_local[r], f"local_output[{r}]")
+    # the GPU's own local outputs re-routed by the oracle; what nobody routes (the V share of the
+    # buffer) keeps the caller's poison
+    expected = [np.full(peers[0].size, 0xFFFF, dtype=np.uint16) for _ in range(world)]
+    table = O.ptr_array(expected)
+    for r in range(world):
+        O.lib().fo_qkv_forward_route_defer_v(world, r, batch, s, q, kv, d, O.ptr(np.ascontiguousarray(local[r])), n, table)
+    for dest in range(world):
+        assert np.array_equal(peers[dest], expected[dest]), f"routed bytes differ at destination {dest}"
+
+
 def test_qkv_forward_two_payloads_and_epochs():
     # Stale data cannot pass: a second payload through the same buffers and flags with the next
     # epoch (benchmarks/sm103/fused_bf16.cu: two generations, poisoned outputs).

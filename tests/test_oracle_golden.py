@@ -283,3 +283,24 @@ def test_oracle_against_reference_headers_directly():
     for x in xs:
         assert L.fo_f32_to_e4m3(float(x)) == R.ref_f32_to_e4m3(float(x))
         assert L.fo_f32_to_bf16(float(x)) == R.ref_f32_to_bf16(float(x))
+
+
+def test_qkv_route_with_v_deferred_keeps_q_and_k_per_row_and_v_local():
+    # UlyssesRoute::defer_v_a2a (csrc/operators/sm103/detail/gemm_a2a.cuh:199-215,408,505-533): one
+    # [B*S_global, q_local + kv_local] tensor per destination, Q columns then K columns; V is not routed
+    from fuse_b200 import synthetic
+    world, s, q, kv, d, k = 4, 8, 8, 4, 8, 16
+    lhs = [synthetic.normal_bf16((s, k), 40 + r, 1.0) for r in range(world)]
+    w = synthetic.normal_bf16(((q + 2 * kv) * d, k), 9, 0.02)
+    local, peers = O.qkv_forward(world, 1, s, q, kv, d, lhs, w, defer_v=True)
+    plain_local, plain_peers = O.qkv_forward(world, 1, s, q, kv, d, lhs, w)
+    ql, kvl = q // world * d, kv // world * d
+    rows = s * world
+    for dest in range(world):
+        got = peers[dest][:rows * (ql + kvl)].reshape(rows, ql + kvl)
+        assert (peers[dest][rows * (ql + kvl):] == 0xFFFF).all()          # the V share is never written
+        planar_q = plain_peers[dest][:rows * ql].reshape(rows, ql)
+        planar_k = plain_peers[dest][rows * ql:rows * (ql + kvl)].reshape(rows, kvl)
+        assert np.array_equal(got[:, :ql], planar_q) and np.array_equal(got[:, ql:], planar_k)
+    for r in range(world):
+        assert np.array_equal(local[r], plain_local[r])                    # V stays where the GEMM wrote it

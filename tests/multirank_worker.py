@@ -78,6 +78,32 @@ def main():
     ok, worst, bad = O.within_tolerance(bits(sym["planar"].view(torch.bfloat16)), want_peers[rank])
     assert ok, ("planar", worst, bad)
 
+    # ---- the same operator with the all-to-all of V deferred (UlyssesRoute.defer_v_a2a): Q | K per row in
+    # ONE tensor per destination, V only in the local output, completion_epoch published locally
+    dist.barrier()  # every rank has read its planar buffer before the next launch writes into it
+    sym["planar"].view(torch.int16).fill_(-1)
+    torch.cuda.synchronize()
+    dist.barrier()
+    completion = torch.zeros(N.READY_FLAG_STRIDE, dtype=torch.int32, device=dev)
+    p.route.defer_v_a2a = 1
+    p.completion_epoch = completion.data_ptr()
+    p.epoch = 3
+    assert api.launch_gemm_a2a_cutlass(p, 0, opts) == 0
+    torch.cuda.synchronize()
+    status = api.read_status()
+    assert status[0] == 0, status[:8]
+    assert int(completion[0]) == 3
+    want_local, want_peers = O.qkv_forward(world, batch, s, q, kv, d, lhs, wq, defer_v=True)
+    ok, worst, bad = O.within_tolerance(bits(local), want_local[rank])
+    assert ok, ("local with V deferred", worst, bad)
+    got = bits(sym["planar"].view(torch.bfloat16))
+    routed = want_peers[rank] != 0xFFFF   # (a routed BF16 value is never the all-ones NaN pattern)
+    assert (got[~routed] == 0xFFFF).all(), "an element outside Q | K was written with V deferred"
+    ok, worst, bad = O.within_tolerance(got[routed], want_peers[rank][routed])
+    assert ok, ("Q | K with V deferred", worst, bad)
+    p.route.defer_v_a2a = 0
+    p.completion_epoch = None
+
     dist.barrier()
     o_problem = N.GemmProblem(m, 512, ko, max_swizzle_size=8)
     o_route = N.UlyssesRoute(world_size=world, rank=rank, batch=batch, global_seq=s * world, seq_local=s,

@@ -83,8 +83,9 @@ cudaError_t check_qkv_route(const fuse_gemm_a2a_params& p) {
       (p.completion_epoch != nullptr && !r.defer_v_a2a) || r.q_heads % r.kv_heads != 0 ||
       r.q_heads % r.world_size != 0 || r.kv_heads % r.world_size != 0 || r.head_dim % 8 != 0)
     return cudaErrorNotSupported;
-  // Offline-interleaved weights are not built.
-  if (r.qkv_peer_interleaved) return cudaErrorNotSupported;
+  // Offline-interleaved weights: refused with the N raster, as the reference refuses it
+  // (csrc/operators/sm103/detail/gemm_a2a.cuh:258-259).
+  if (r.qkv_peer_interleaved && p.gemm.raster == FUSE_RASTER_ALONG_N) return cudaErrorNotSupported;
   if (p.completion_epoch != nullptr && !host::aligned4(p.completion_epoch)) return cudaErrorInvalidValue;
   if (int64_t(r.seq_local) * r.world_size != r.global_seq ||
       int64_t(r.batch) * r.seq_local != p.gemm.m ||
@@ -142,6 +143,7 @@ cudaError_t qkv_forward(const fuse_gemm_a2a_params& p, const fuse_b200_options* 
   k.qkv.kv_heads = p.route.kv_heads;
   k.qkv.head_dim = p.route.head_dim;
   k.qkv.defer_v = p.route.defer_v_a2a ? 1 : 0;
+  k.qkv.interleaved = p.route.qkv_peer_interleaved ? 1 : 0;
   k.qkv.completion_epoch = p.route.defer_v_a2a ? p.completion_epoch : nullptr;
   for (int peer = 0; peer < p.route.world_size; ++peer) {
     k.qkv.peer_output[peer] = p.peer_output[peer];

@@ -108,6 +108,10 @@ struct QkvRoute {
   // V stays in the local output; Q and K of a destination's heads share ONE row-major tensor
   // [B*S_global, q_local + kv_local] there (Q columns, then K columns).
   int32_t defer_v;
+  // interleaved (UlyssesRoute::qkv_peer_interleaved, csrc/operators/sm103/detail/gemm_a2a.cuh:404-415):
+  // the projection weight was prepacked offline so that inside Q and inside K physical head p belongs
+  // to owner p % world as its local head p / world; V and the routed layout are unchanged.
+  int32_t interleaved;
   uint16_t* peer_output[kMaxWorldSize];
   uint32_t* peer_done[kMaxWorldSize];
   uint32_t* completion_epoch;  // local word: the epoch, once this rank's whole local output (V included) is written
@@ -279,6 +283,20 @@ __device__ __forceinline__ int64_t global_row(int32_t world, int32_t rank, int32
   return int64_t(batch) * global_seq + int64_t(rank) * seq_local + seq;
 }
 
+// Owner rank and column inside the owner's segment of position `within` of segment `segment`
+// (0 Q, 1 K, 2 V; `local_width` = the segment's width per rank).
+__device__ __forceinline__ void qkv_owner_column(const QkvRoute& r, int32_t segment, int32_t within,
+                                                 int32_t local_width, int32_t& owner, int32_t& local_col) {
+  if (r.interleaved && segment < 2) {
+    const int32_t head = within / r.head_dim;
+    owner = head % r.world;
+    local_col = head / r.world * r.head_dim + (within - head * r.head_dim);
+  } else {
+    owner = within / local_width;
+    local_col = within - owner * local_width;
+  }
+}
+
 // Destination of one 8-column chunk of the packed QKV feature axis: base pointer of row 0 in
 // the owning rank's planar Q | K | V tensor and that tensor's row pitch
 // (include/fuse/layout/ulysses.h:77-107; csrc/operators/sm103/detail/gemm_a2a.cuh:190-215).
@@ -290,8 +308,8 @@ __device__ __forceinline__ void qkv_chunk_destination(const QkvRoute& r, int32_t
   const int32_t segment = feature < q_width ? 0 : (feature < q_width + kv_width ? 1 : 2);
   const int32_t within = feature - (segment == 0 ? 0 : q_width + (segment == 2 ? kv_width : 0));
   const int32_t local_width = segment == 0 ? q_local : kv_local;
-  const int32_t owner = within / local_width;
-  const int32_t local_col = within - owner * local_width;
+  int32_t owner, local_col;
+  qkv_owner_column(r, segment, within, local_width, owner, local_col);
   if (r.defer_v) {
     if (segment == 2) return;  // V is not routed: base stays null and the chunk is skipped
     base = r.peer_output[owner] + (segment == 1 ? q_local : 0) + local_col;
@@ -2028,11 +2046,11 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
                 const int32_t segment = col < q_width ? 0 : (col < q_width + kv_width ? 1 : 2);
                 const int32_t within = col - (segment == 0 ? 0 : q_width + (segment == 2 ? kv_width : 0));
                 const int32_t local_width = (segment == 0 ? q_width : kv_width) / r.world;
-                const int32_t owner = within / local_width;  // segment > 0 only when kv_heads > 0
+                int32_t owner, local_col;  // segment > 0 only when kv_heads > 0
+                qkv_owner_column(r, segment, within, local_width, owner, local_col);
                 // defer_v: one [rows, q_local + kv_local] tensor per destination (map 0), V not routed
                 const int32_t map = r.defer_v ? 0 : segment;
-                const int32_t dest_col =
-                    within - owner * local_width + (r.defer_v && segment == 1 ? q_width / r.world : 0);
+                const int32_t dest_col = local_col + (r.defer_v && segment == 1 ? q_width / r.world : 0);
                 if (!(r.defer_v && segment == 2))
                   ptx::tma_store_2d(&store_maps.peer[owner][map], staging, dest_col,
                                     int32_t(global_row(r.world, r.rank, r.seq_local, r.global_seq,

@@ -430,10 +430,11 @@ pair_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const int32_t segment = col < q_width ? 0 : (col < q_width + kv_width ? 1 : 2);
             const int32_t within = col - (segment == 0 ? 0 : q_width + (segment == 2 ? kv_width : 0));
             const int32_t local_width = (segment == 0 ? q_width : kv_width) / r.world;
-            const int32_t owner = within / local_width;
+            int32_t owner, local_col;
+            qkv_owner_column(r, segment, within, local_width, owner, local_col);
             // defer_v: one [rows, q_local + kv_local] tensor per destination (map 0), V not routed
             const int32_t map = r.defer_v ? 0 : segment;
-            const int32_t dest_col = within - owner * local_width + (r.defer_v && segment == 1 ? q_width / r.world : 0);
+            const int32_t dest_col = local_col + (r.defer_v && segment == 1 ? q_width / r.world : 0);
             if (!(r.defer_v && segment == 2))
               ptx::tma_store_2d(&store_maps.peer[owner][map], staging, dest_col,
                                 int32_t(global_row(r.world, r.rank, r.seq_local, r.global_seq, r.causal != 0,

@@ -214,6 +214,60 @@ FO_API int fo_qkv_forward_destination_defer_v(int world, int rank, int batch, in
   return 1;
 }
 
+/* The route with its two variants as flags: defer_v (above) and interleaved
+ * (UlyssesRoute::qkv_peer_interleaved, csrc/operators/sm103/detail/gemm_a2a.cuh:404-415: inside Q and
+ * inside K, physical head p of the prepacked projection belongs to owner p % world as its local head
+ * p / world; V and the routed layout are unchanged).  Returns 1 (routed), 2 (not routed) or 0. */
+FO_API int fo_qkv_forward_destination_variant(int world, int rank, int batch, int seq_local, int q_heads,
+                                              int kv_heads, int head_dim, int defer_v, int interleaved,
+                                              int64_t source_row, int global_feature, int32_t* dest_rank,
+                                              int64_t* dest_offset) {
+  int32_t address[5];
+  if (!fo_map_qkv_gqa_feature(world, q_heads, kv_heads, head_dim, global_feature, address))
+    return 0;
+  const int64_t rows = (int64_t)batch * seq_local * world;
+  const int64_t q_local = q_heads / world * head_dim, kv_local = kv_heads / world * head_dim;
+  const int segment = address[2];
+  int owner = address[0];
+  int64_t column = address[1] - (segment == 0 ? 0 : q_local + (segment == 2 ? kv_local : 0));
+  if (interleaved && segment < 2) {
+    const int q_width = q_heads * head_dim, kv_width = kv_heads * head_dim;
+    const int within = global_feature - (segment == 0 ? 0 : q_width);
+    (void)kv_width;
+    const int head = within / head_dim;
+    owner = head % world;
+    column = (int64_t)(head / world) * head_dim + within % head_dim;
+  }
+  if (defer_v && segment == 2) return 2;
+  const int64_t row = fo_global_row(world, rank, seq_local, 0, source_row);
+  *dest_rank = owner;
+  if (defer_v) {
+    *dest_offset = row * (q_local + kv_local) + (segment == 1 ? q_local : 0) + column;
+  } else {
+    const int64_t width = segment == 0 ? q_local : kv_local;
+    const int64_t base = segment == 0 ? 0 : rows * q_local + (segment == 2 ? rows * kv_local : 0);
+    *dest_offset = base + row * width + column;
+  }
+  return 1;
+}
+
+FO_API void fo_qkv_forward_route_variant(int world, int rank, int batch, int seq_local, int q_heads,
+                                         int kv_heads, int head_dim, int defer_v, int interleaved,
+                                         const uint16_t* local_output, int64_t ldd,
+                                         uint16_t* const* peer_output) {
+  const int64_t m = (int64_t)batch * seq_local;
+  const int n = (q_heads + 2 * kv_heads) * head_dim;
+#pragma omp parallel for schedule(static)
+  for (int64_t row = 0; row < m; ++row)
+    for (int feature = 0; feature < n; ++feature) {
+      int32_t dest;
+      int64_t offset;
+      if (fo_qkv_forward_destination_variant(world, rank, batch, seq_local, q_heads, kv_heads, head_dim, defer_v,
+                                             interleaved, row, feature, &dest, &offset) == 1)
+        peer_output[dest][offset] = local_output[row * ldd + feature];
+    }
+}
+
 /* Forward QKV route, receiver view: element `index` of destination rank's
  * planar Q|K|V buffer -> (source rank, element offset in that rank's [M,N] GEMM
  * output).  benchmarks/sm103/fused_validation.cuh:104-138 (batch == 1). */

@@ -80,6 +80,7 @@ def lib():
     _sig(L, "fo_gemm_mxfp8_nt", C.c_int, P, P, P, P, P, i64, i64, i64, i64, f32)
     _sig(L, "fo_qkv_forward_route", None, *([C.c_int] * 7), P, i64, P)
     _sig(L, "fo_qkv_forward_route_defer_v", None, *([C.c_int] * 7), P, i64, P)
+    _sig(L, "fo_qkv_forward_route_variant", None, *([C.c_int] * 9), P, i64, P)
     _sig(L, "fo_qkv_forward_destination_defer_v", C.c_int, *([C.c_int] * 7), i64, C.c_int, P, P)
     _sig(L, "fo_oproj_forward_gather", None, C.c_int, C.c_int, C.c_int, C.c_int, i64, C.c_int,
          C.c_int, P, P)
@@ -170,13 +171,16 @@ def gemm_bf16(mode: int, a: np.ndarray, b: np.ndarray, m: int, n: int, k: int, a
     return out
 
 
-def qkv_forward(world, batch, seq_local, q_heads, kv_heads, head_dim, lhs, rhs_nt, alpha=1.0, defer_v=False):
+def qkv_forward(world, batch, seq_local, q_heads, kv_heads, head_dim, lhs, rhs_nt, alpha=1.0, defer_v=False,
+                interleaved=False):
     """Simulate every rank of the fused QKV projection + sequence->head all-to-all.
 
     lhs: list of [M, K] uint16 (BF16 bits) per rank; rhs_nt: [N, K].  Returns
     (local_outputs, peer_outputs): per rank [M, N] and the planar Q|K|V buffer (flat uint16).
     defer_v: V stays local; the destination buffer is [B*S_global, q_local + kv_local] (Q | K per
-    row), still sized like the planar buffer, elements nobody routes keep 0xFFFF."""
+    row), still sized like the planar buffer, elements nobody routes keep 0xFFFF.
+    interleaved: rhs_nt is the offline-prepacked weight (inside Q and K physical head p = local_head *
+    world + owner); the routed layout is the standard one."""
     L = lib()
     m = batch * seq_local
     n = (q_heads + 2 * kv_heads) * head_dim
@@ -185,9 +189,14 @@ def qkv_forward(world, batch, seq_local, q_heads, kv_heads, head_dim, lhs, rhs_n
     local = [gemm_bf16(0, lhs[r], rhs_nt, m, n, k, alpha) for r in range(world)]
     peers = [np.full(rows * n // world, 0xFFFF, dtype=np.uint16) for _ in range(world)]
     table = ptr_array(peers)
-    route = L.fo_qkv_forward_route_defer_v if defer_v else L.fo_qkv_forward_route
     for r in range(world):
-        route(world, r, batch, seq_local, q_heads, kv_heads, head_dim, ptr(local[r]), n, table)
+        if interleaved:
+            L.fo_qkv_forward_route_variant(world, r, batch, seq_local, q_heads, kv_heads, head_dim, int(defer_v), 1,
+                                           ptr(local[r]), n, table)
+        elif defer_v:
+            L.fo_qkv_forward_route_defer_v(world, r, batch, seq_local, q_heads, kv_heads, head_dim, ptr(local[r]), n, table)
+        else:
+            L.fo_qkv_forward_route(world, r, batch, seq_local, q_heads, kv_heads, head_dim, ptr(local[r]), n, table)
     return local, peers
 
 

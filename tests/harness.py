@@ -44,7 +44,7 @@ def check_status():
 
 def qkv_forward(world, batch, seq_local, q_heads, kv_heads, head_dim, lhs_bits, w_bits, comm=4,
                 alpha=1.0, raster=N.RASTER_HEURISTIC, swizzle=4, block_n=0, epochs=1, route="comm",
-                vector_epilogue=False, defer_v=False):
+                vector_epilogue=False, defer_v=False, interleaved=False):
     """Runs every rank of the QKV operator (route: "comm" CTAs or "direct" epilogue push).  Returns (local_outputs, peer_outputs) as bits.
     defer_v: UlyssesRoute.defer_v_a2a (V stays local, Q | K share one tensor per destination) with a
     completion_epoch word per rank, which must hold the last epoch afterwards."""
@@ -67,7 +67,8 @@ def qkv_forward(world, batch, seq_local, q_heads, kv_heads, head_dim, lhs_bits, 
         for r in range(world):
             route = N.UlyssesRoute(world_size=world, rank=r, batch=batch, global_seq=seq_local * world,
                                    seq_local=seq_local, q_heads=q_heads, kv_heads=kv_heads,
-                                   head_dim=head_dim, kind=N.ROUTE_QKV_GQA_PACK, defer_v_a2a=int(defer_v))
+                                   head_dim=head_dim, kind=N.ROUTE_QKV_GQA_PACK, defer_v_a2a=int(defer_v),
+                                   qkv_peer_interleaved=int(interleaved))
             p = N.GemmA2AParams(lhs=xs[r].data_ptr(), rhs_nt=w.data_ptr(), local_output=local[r].data_ptr(),
                                 ready=ready[r].data_ptr(), gemm=problem, route=route, num_comm_ctas=comm,
                                 epoch=epoch, alpha=alpha,

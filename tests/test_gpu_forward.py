@@ -88,6 +88,52 @@ def test_qkv_forward_with_the_all_to_all_of_v_deferred(case, route, vector, bloc
         assert np.array_equal(peers[dest], expected[dest]), f"routed bytes differ at destination {dest}"
 
 
+@pytest.mark.parametrize("defer_v", [False, True])
+@pytest.mark.parametrize("route,vector,block_n", [("direct", False, 0), ("direct", False, 128), ("direct", True, 0),
+                                                  ("comm", False, 0)])
+@pytest.mark.parametrize("case", [(2, 1, 384, 8, 4, 128, 512), (4, 2, 128, 16, 4, 64, 320), (2, 1, 200, 8, 8, 40, 192)])
+def test_qkv_forward_with_offline_interleaved_weights(case, route, vector, block_n, defer_v):
+    # UlyssesRoute::qkv_peer_interleaved (include/fuse/layout/ulysses.h:35-39,
+    # csrc/operators/sm103/detail/gemm_a2a.cuh:404-415): with the weight prepacked so that physical head p
+    # of Q and of K belongs to owner p % world, the routed Q | K | V is what the standard weight gives.
+    from tests import harness as H
+    from tests.test_oracle_golden import _prepack_interleaved
+    world, batch, s, q, kv, d, k = case
+    m, n = batch * s, (q + 2 * kv) * d
+    lhs, w = _inputs(world, m, k, n)
+    local, peers = H.qkv_forward(world, batch, s, q, kv, d, lhs, _prepack_interleaved(w, world, q, kv, d), comm=4,
+                                 route=route, vector_epilogue=vector, block_n=block_n, defer_v=defer_v, interleaved=True,
+                                 raster=N.RASTER_ALONG_M)
+    _, want_peers = O.qkv_forward(world, batch, s, q, kv, d, lhs, w, defer_v=defer_v)   # standard weight, standard route
+    expected = [np.full(peers[0].size, 0xFFFF, dtype=np.uint16) for _ in range(world)]
+    table = O.ptr_array(expected)
+    for r in range(world):
+        O.lib().fo_qkv_forward_route_variant(world, r, batch, s, q, kv, d, int(defer_v), 1,
+                                             O.ptr(np.ascontiguousarray(local[r])), n, table)
+    for dest in range(world):
+        assert np.array_equal(peers[dest], expected[dest]), f"routed bytes differ at destination {dest}"
+        routed = want_peers[dest] != 0xFFFF
+        assert (peers[dest][~routed] == 0xFFFF).all()
+        _assert_close(peers[dest][routed], want_peers[dest][routed], f"peer_output[{dest}]")
+
+
+def test_qkv_forward_interleaved_weights_are_refused_with_the_n_raster():
+    # csrc/operators/sm103/detail/gemm_a2a.cuh:258-259
+    import torch
+    from tests import harness as H
+    x = torch.zeros((256, 128), dtype=torch.bfloat16, device=H.DEV)
+    w = torch.zeros((1024, 128), dtype=torch.bfloat16, device=H.DEV)
+    out = torch.zeros((256, 1024), dtype=torch.bfloat16, device=H.DEV)
+    flags = torch.zeros(4096, dtype=torch.int32, device=H.DEV)
+    route = N.UlyssesRoute(world_size=1, rank=0, batch=1, global_seq=256, seq_local=256, q_heads=4, kv_heads=2,
+                           head_dim=128, kind=N.ROUTE_QKV_GQA_PACK, qkv_peer_interleaved=1)
+    p = N.GemmA2AParams(lhs=x.data_ptr(), rhs_nt=w.data_ptr(), local_output=out.data_ptr(), ready=flags.data_ptr(),
+                        gemm=N.GemmProblem(256, 1024, 128, raster=N.RASTER_ALONG_N), route=route, num_comm_ctas=2, epoch=1)
+    p.peer_output[0] = out.data_ptr()
+    p.peer_route_done_epoch[0] = flags.data_ptr()
+    assert api.launch_gemm_a2a_cutlass(p, 0) == 801
+
+
 def test_qkv_forward_two_payloads_and_epochs():
     # Stale data cannot pass: a second payload through the same buffers and flags with the next
     # epoch (benchmarks/sm103/fused_bf16.cu: two generations, poisoned outputs).

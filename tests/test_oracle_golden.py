@@ -304,3 +304,33 @@ def test_qkv_route_with_v_deferred_keeps_q_and_k_per_row_and_v_local():
         assert np.array_equal(got[:, :ql], planar_q) and np.array_equal(got[:, ql:], planar_k)
     for r in range(world):
         assert np.array_equal(local[r], plain_local[r])                    # V stays where the GEMM wrote it
+
+
+def _prepack_interleaved(w, world, q, kv, d):
+    """The offline prepack UlyssesRoute::qkv_peer_interleaved expects: inside Q and inside K, physical
+    head p = local_head * world + owner holds logical head owner * local_heads + local_head."""
+    out = w.copy()
+    for base, heads in ((0, q), (q * d, kv)):
+        local_heads = heads // world
+        for p in range(heads):
+            owner, local_head = p % world, p // world
+            logical = owner * local_heads + local_head
+            out[base + p * d:base + (p + 1) * d] = w[base + logical * d:base + (logical + 1) * d]
+    return out
+
+
+def test_qkv_route_with_interleaved_weights_leaves_the_routed_layout_unchanged():
+    # include/fuse/layout/ulysses.h:35-39: "The final routed Q/K/V layout is unchanged."
+    from fuse_b200 import synthetic
+    world, s, q, kv, d, k = 4, 8, 8, 4, 8, 16
+    lhs = [synthetic.normal_bf16((s, k), 60 + r, 1.0) for r in range(world)]
+    w = synthetic.normal_bf16(((q + 2 * kv) * d, k), 11, 0.02)
+    _, plain = O.qkv_forward(world, 1, s, q, kv, d, lhs, w)
+    _, packed = O.qkv_forward(world, 1, s, q, kv, d, lhs, _prepack_interleaved(w, world, q, kv, d), interleaved=True)
+    for dest in range(world):
+        assert np.array_equal(plain[dest], packed[dest])
+    _, plain_d = O.qkv_forward(world, 1, s, q, kv, d, lhs, w, defer_v=True)
+    _, packed_d = O.qkv_forward(world, 1, s, q, kv, d, lhs, _prepack_interleaved(w, world, q, kv, d), defer_v=True,
+                                interleaved=True)
+    for dest in range(world):
+        assert np.array_equal(plain_d[dest], packed_d[dest])

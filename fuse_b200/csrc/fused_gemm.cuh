@@ -2060,11 +2060,29 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
             ptx::bulk_commit();
           };
           if constexpr (kAccumStages == 1) {
-            // Single accumulator: drain it whole into packed BF16 registers and hand TMEM back
-            // before any staging, so the next tile's UMMAs overlap the stores.
-            uint32_t packed[kBlockN / 2];
+            // Single accumulator: the first 64 columns go straight to the staging block (its store is
+            // in flight while the rest is read), the other 192 into packed BF16 registers; TMEM is
+            // handed back before those are staged, so the next tile's UMMAs overlap the stores.
+            {
+              const uint32_t staging =
+                  base + Layout::kStagingOffset + (staged_blocks % Layout::kStagingBuffers) * Layout::kStagingBlockBytes;
+              ++staged_blocks;
+              if (epi_tid == 0) ptx::bulk_wait_read<Layout::kStagingBuffers - 1>();
+              ptx::named_bar_sync(1, kEpilogueThreads);
+              uint32_t acc0[32], acc1[32];
+              ptx::tmem_ld_32x32b_x32(taddr, acc0);
+              ptx::tmem_ld_32x32b_x32(taddr + 32, acc1);
+              ptx::tmem_wait_ld();
+              const uint32_t row_addr = staging + uint32_t(row_in_tile) * 128u;
+              stage_accumulators(acc0, row_addr, 0, row_in_tile, p.alpha);
+              stage_accumulators(acc1, row_addr, 4, row_in_tile, p.alpha);
+              ptx::fence_proxy_async_shared();
+              ptx::named_bar_sync(1, kEpilogueThreads);
+              if (epi_tid == 0) issue_stores(0, staging);
+            }
+            uint32_t packed[(kBlockN - 64) / 2];
 #pragma unroll
-            for (int c = 0; c < kBlockN; c += 64) {
+            for (int c = 64; c < kBlockN; c += 64) {
               uint32_t acc0[32], acc1[32];
               ptx::tmem_ld_32x32b_x32(taddr + c, acc0);
               ptx::tmem_ld_32x32b_x32(taddr + c + 32, acc1);
@@ -2073,16 +2091,16 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
               for (int e = 0; e < 16; ++e) {
                 __nv_bfloat162 pair = __floats2bfloat162_rn(p.alpha * __uint_as_float(acc0[2 * e]),
                                                             p.alpha * __uint_as_float(acc0[2 * e + 1]));
-                packed[c / 2 + e] = *reinterpret_cast<const uint32_t*>(&pair);
+                packed[(c - 64) / 2 + e] = *reinterpret_cast<const uint32_t*>(&pair);
                 pair = __floats2bfloat162_rn(p.alpha * __uint_as_float(acc1[2 * e]),
                                              p.alpha * __uint_as_float(acc1[2 * e + 1]));
-                packed[c / 2 + 16 + e] = *reinterpret_cast<const uint32_t*>(&pair);
+                packed[(c - 64) / 2 + 16 + e] = *reinterpret_cast<const uint32_t*>(&pair);
               }
             }
             ptx::tc_fence_before();
             ptx::mbar_arrive(tmem_empty_bar(accum));
 #pragma unroll
-            for (int c = 0; c < kBlockN; c += 64) {
+            for (int c = 64; c < kBlockN; c += 64) {
               const uint32_t staging =
                   base + Layout::kStagingOffset + (staged_blocks % Layout::kStagingBuffers) * Layout::kStagingBlockBytes;
               ++staged_blocks;
@@ -2091,8 +2109,8 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a,
               const uint32_t row_addr = staging + uint32_t(row_in_tile) * 128u;
 #pragma unroll
               for (int v = 0; v < 8; ++v) {
-                const uint4 out = make_uint4(packed[c / 2 + v * 4], packed[c / 2 + v * 4 + 1],
-                                             packed[c / 2 + v * 4 + 2], packed[c / 2 + v * 4 + 3]);
+                const uint4 out = make_uint4(packed[(c - 64) / 2 + v * 4], packed[(c - 64) / 2 + v * 4 + 1],
+                                             packed[(c - 64) / 2 + v * 4 + 2], packed[(c - 64) / 2 + v * 4 + 3]);
                 ptx::st_shared_v4(row_addr + uint32_t((v ^ (row_in_tile & 7)) * 16), out);
               }
               ptx::fence_proxy_async_shared();

@@ -192,3 +192,20 @@ def test_philox_known_answers_and_value_map():
     assert np.array_equal(vals[:2000], expect)
     z = synthetic.bf16_bits_to_f32(synthetic.normal_bf16((1 << 16,), 5, 0.02))
     assert abs(z.mean()) < 5e-4 and abs(z.std() - 0.02) < 5e-4
+
+
+def test_header_compiles_as_plain_c():
+    # the boundary is a C ABI: the header must be usable from C (cgo, ctypes generators, other FFIs)
+    import shutil
+    import subprocess
+    import tempfile
+    gcc = shutil.which("gcc")
+    if gcc is None:
+        pytest.skip("no C compiler")
+    with tempfile.TemporaryDirectory() as tmp:
+        source = os.path.join(tmp, "abi.c")
+        with open(source, "w") as f:
+            f.write('#include "fuse_b200.h"\nint main(void) { fuse_gemm_problem p; (void)p; return (int)sizeof(fuse_ulysses_route) == 0; }\n')
+        result = subprocess.run([gcc, "-std=c11", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", "-I",
+                                 os.path.join(ROOT, "include"), source], capture_output=True, text=True)
+        assert result.returncode == 0, result.stderr

@@ -199,6 +199,8 @@ def test_header_compiles_as_plain_c():
     import shutil
     import subprocess
     import tempfile
+
+    import pytest
     gcc = shutil.which("gcc")
     if gcc is None:
         pytest.skip("no C compiler")

@@ -1,4 +1,4 @@
-"""The reference-side binding of INTEGRATION.md, complete (tests/binding/sm100_entry.cpp), compiled
+"""The complete reference-side binding (tests/binding/sm100_entry.cpp), compiled
 against the reference's OWN headers: every public function of the hot path is DEFINED there with
 the reference's declaration in scope, so a signature or record that drifted fails to compile."""
 import os
